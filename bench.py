@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-LLM hot path on B200.
+
+Headline workload (N = 1): the Q4_0 dequant-GEMV of LLaMA-7B's FFN-up shape, weight
+11008 x 4096 in GGUF Q4_0 blocks, fp32 activation vector (M = 1), fp32 output. One "step" is one
+sweep over R distinct weight copies (R x 25.4 MB > the 126 MB L2), one GEMV launch per copy,
+so every launch streams its weight from HBM. metric = achieved HBM GB/s computed from the
+ALGORITHMIC bytes of a launch (packed weight + x + y).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+With N > 1 (under torchrun) every rank runs the same sweep on its own GPU ("replicas only":
+a standalone GEMV has nothing to exchange) and rank 0 prints the aggregate.
+`--impl reference` times C-ML's own CPU path (dequantize, then its fp32 linear) on the host.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+N_ROWS, K_COLS = 11008, 4096
+COPIES = 24                       # 24 x 25.36 MB = 609 MB of distinct weights per sweep (> L2)
+EXTRA_M = (8, 32)
+
+
+def alg_bytes(M, rows=N_ROWS, cols=K_COLS):
+    """Algorithmic bytes of one Q4_0 GEMV launch: packed weight (18 B per 32 weights) + x + y."""
+    return rows * cols // 32 * 18 + M * cols * 4 + M * rows * 4
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_reference_leg(budget_s=12.0):
+    """C-ML's own CPU path on one 11008 x 4096 Q4_0 weight, M = 1: gguf_dequantize to fp32
+    followed by its fp32 linear (what its loader + forward do), timed on the host cores."""
+    ob = entry.load_oracle_binding()
+    synth = entry.load_synth()
+    ref = ob.load_ref()
+    rng = np.random.default_rng(1234)
+    blocks = synth.q4_0_blocks(rng, N_ROWS, K_COLS)
+    x = rng.standard_normal((1, K_COLS)).astype(np.float32)
+    W = np.empty(N_ROWS * K_COLS, np.float32)
+    y = np.empty((1, N_ROWS), np.float32)
+    if ref is not None:
+        kind = "reference"
+        deq = lambda: ref.ref_gguf_dequantize(2, ob.p(blocks), ob.p(W), W.size)
+        lin = lambda: ref.ref_linear(ob.p(x), ob.p(W), 1, N_ROWS, K_COLS, ob.p(y))
+    else:
+        kind = "port"
+        orc = ob.load_orc()
+        deq = lambda: orc.orc_gguf_dequantize(2, ob.p(blocks), ob.p(W), W.size)
+        lin = lambda: orc.orc_linear_nt(ob.p(x), ob.p(W), 1, N_ROWS, K_COLS, ob.p(y))
+    deq(); lin()
+    t_deq, t_lin, reps = 0.0, 0.0, 0
+    t_end = time.perf_counter() + budget_s
+    while reps < 3 or (time.perf_counter() < t_end and reps < 200):
+        t0 = time.perf_counter(); deq(); t1 = time.perf_counter(); lin(); t2 = time.perf_counter()
+        t_deq += t1 - t0; t_lin += t2 - t1; reps += 1
+    per_call = (t_deq + t_lin) / reps
+    return {"value": alg_bytes(1) / per_call / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+            "sample": f"{reps} x (gguf_dequantize Q4_0 11008x4096 + fp32 linear M=1); "
+                      f"dequant {1e3 * t_deq / reps:.2f} ms + linear {1e3 * t_lin / reps:.2f} ms per call; "
+                      f"linear alone = {alg_bytes(1) / (t_lin / reps) / 1e9:.3f} GB/s of packed-weight bytes",
+            "host_cores_available": os.cpu_count(), "ms_per_call": 1e3 * per_call}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    steps_t = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        base = cpu_reference_leg(budget_s=0.0)       # one bounded sample (3 calls) per step
+        if i >= args.warmup:
+            steps_t.append(time.perf_counter() - t0)
+    v = base["value"]
+    line = {"impl": "reference", "metric": "q4_0_dequant_gemv_hbm_gbs", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * float(np.mean(steps_t)),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "Q4_0 dequant-GEMV 11008x4096, M=1 (C-ML CPU path: gguf_dequantize + fp32 linear)"},
+            "cpu_baseline": base, "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--copies", type=int, default=COPIES)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    pkg, synth = entry.load_package(), entry.load_synth()
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    rng = np.random.default_rng(1234 + rank)
+    copies = args.copies
+    stream = torch.cuda.Stream(device=dev)
+    sp = stream.cuda_stream
+    weights, keep = [], []
+    for c in range(copies):
+        blocks = synth.q4_0_blocks(rng, N_ROWS, K_COLS)
+        qs, sc = pkg.repack_gguf(pkg.Q4_0, blocks, N_ROWS, K_COLS)
+        d_qs, d_sc = torch.from_numpy(qs).to(dev), torch.from_numpy(sc).to(dev)
+        keep.append((d_qs, d_sc))
+        weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_qs.data_ptr(), d_sc.data_ptr()))
+    x_host = {M: torch.from_numpy(rng.standard_normal((M, K_COLS)).astype(np.float32)).pin_memory() for M in (1,) + EXTRA_M}
+    x_dev = {M: x_host[M].to(dev) for M in x_host}
+    y_dev = {M: torch.empty((M, N_ROWS), dtype=torch.float32, device=dev) for M in x_host}
+    y_host = {M: torch.empty((M, N_ROWS), dtype=torch.float32).pin_memory() for M in x_host}
+    gemv = pkg.lib.cmlb200_gemv
+    launches = 0
+
+    def sweep(M):
+        nonlocal launches
+        xp, yp = x_dev[M].data_ptr(), y_dev[M].data_ptr()
+        for W in weights:
+            pkg.check(gemv(W, xp, yp, M, sp), "cmlb200_gemv")
+        launches += len(weights) * (1 if M <= 4 else (M + 3) // 4)
+
+    def timed(M, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                sweep(M)
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                sweep(M)
+            e1.record(stream)
+            e1.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def e2e_timed(M, steps, warmup):
+        """The call a C-ML user makes: host activations in, host result out, every launch.
+        The weight stays resident (it is loaded once, as cml_llama_load_gguf does)."""
+        xb = M * K_COLS * 4
+        yb = M * N_ROWS * 4
+        def one(W):
+            pkg.check(pkg.lib.cmlb200_memcpy_h2d(x_dev[M].data_ptr(), x_host[M].data_ptr(), xb, sp))
+            pkg.check(gemv(W, x_dev[M].data_ptr(), y_dev[M].data_ptr(), M, sp))
+            pkg.check(pkg.lib.cmlb200_memcpy_d2h(y_host[M].data_ptr(), y_dev[M].data_ptr(), yb, sp))
+            pkg.check(pkg.lib.cmlb200_stream_sync(sp))
+        for _ in range(warmup):
+            for W in weights:
+                one(W)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            for W in weights:
+                one(W)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        return dt, xb * copies, yb * copies
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches = 0
+    ms = timed(1, args.steps, args.warmup)
+    timed_launches = args.steps * copies
+    clocks = sampler.stop() if rank == 0 else None
+
+    per_launch_s = ms * 1e-3 / timed_launches
+    gbs_one = alg_bytes(1) / per_launch_s / 1e9
+    value = gbs_one * world
+    extra = {}
+    for M in EXTRA_M:
+        msM = timed(M, max(2, args.steps // 4), 3)
+        extra[f"M{M}_gbs"] = alg_bytes(M) / (msM * 1e-3 / (max(2, args.steps // 4) * copies)) / 1e9 * world
+    e2e_dt, h2d, d2h = e2e_timed(1, max(2, args.steps // 4), 3)
+    e2e_gbs = alg_bytes(1) * copies * max(2, args.steps // 4) / e2e_dt / 1e9 * world
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        cpu = None if (args.no_cpu_baseline or world > 1) else cpu_reference_leg()
+        line = {
+            "metric": "q4_0_dequant_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "Q4_0 dequant-GEMV 11008x4096 (LLaMA-7B FFN-up), M=1, fp32 activations",
+                       "launches_per_step": copies, "distinct_weight_copies": copies,
+                       "l2_policy": f"inputs larger than L2: {copies} x 25.4 MB of distinct weights per step",
+                       "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "pct_of_8TBps": 100.0 * gbs_one / 8000.0},
+            "extra": extra,
+            "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
+                         "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
+                         "traffic": None, "algorithmic_bytes_per_launch": alg_bytes(1), "us_per_launch": per_launch_s * 1e6},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "host fp32 activations -> H2D -> GEMV -> D2H host result, synchronised per call; weights resident"},
+            "gpu_launches": timed_launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,522 @@
+// Prefill dequant-GEMM on the 5th-generation tensor cores (sm_100a):
+//   Y[M,N] (bf16) = X[M,K] (bf16) . dequant(W[N,K])^T, fp32 accumulation in tensor memory.
+//
+// Replaces C-ML's "dequantize the whole weight to an fp32 temporary, then a scalar
+// triple loop" (src/nn/qlora.c:264-317) and its dequantize-at-load + fp32 matmul
+// (src/core/gguf.c:271-295, src/ops/ir/execution.c:989-1052).
+//
+// One CTA owns a tile of 128 weight rows (the MMA "M" side, operand A) by MT <= 256
+// activation rows (the MMA "N" side, operand B) and walks K in slabs of 64:
+//   warp 0      one lane issues TMA tensor loads of the bf16 activation slab (128B swizzle)
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x MT x 16, kind::f16)
+//   warps 2..9  stream the packed weights with cp.async into a private ring, expand them to
+//               bf16 (one fp32 multiply, one rounding) and store them in the canonical
+//               K-major 128B-swizzled layout the MMA reads; afterwards they are the epilogue:
+//               tcgen05.ld the fp32 accumulators, round to bf16 and write Y.
+// No cluster multicast is used. Every wait on an mbarrier is bounded; on expiry the CTA
+// raises a status flag (readable with cmlb200_gemm_status) and drains instead of hanging.
+#include <cuda.h>
+#include "common.cuh"
+
+namespace {
+
+constexpr int BN = 128;             // weight rows per CTA (MMA M)
+constexpr int BK = 64;              // K slab: 64 bf16 = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int DQ_WARPS = 8;
+constexpr int DQ_THREADS = DQ_WARPS * 32;
+constexpr int THREADS = 64 + DQ_THREADS;
+constexpr int A_BYTES = BN * BK * 2;            // 16 KB
+constexpr int B_BYTES_MAX = 256 * BK * 2;       // 32 KB
+// cp.async prefetch depth of the packed weights; 32-byte slots (Q8_0) get a shorter ring so
+// that every format fits the same 227 KB shared-memory budget
+template <int TYPE> struct Ring { static constexpr int depth = (TYPE == CMLB200_Q8_0) ? 2 : 4;
+                                  static constexpr int slot = (TYPE == CMLB200_Q8_0) ? 32 : 16; };
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ int g_gemm_status = 0;   // 0 = ok; otherwise a code identifying the wait that expired
+
+struct SmemLayout {
+    // offsets from the 1024-byte aligned base
+    static constexpr int a_off = 0;                                   // STAGES * A_BYTES
+    static constexpr int b_off = STAGES * A_BYTES;                    // STAGES * B_BYTES_MAX
+    static constexpr int raw_off = b_off + STAGES * B_BYTES_MAX;      // depth * DQ_THREADS * slot = 16 KB
+    static constexpr int sc_off = raw_off + 16384;                    // depth * DQ_THREADS * 4 <= 4 KB
+    static constexpr int lut_off = sc_off + 4096;                     // 256 * 8
+    static constexpr int bar_off = lut_off + 256 * 8;                 // barriers + tmem slot + abort flag
+    static constexpr int total = bar_off + 256;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and raises the abort flag) when the limit is hit or when
+// another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if (it > 64) {
+            if (*abort_flag) return false;
+            __nanosleep(128);
+        }
+    }
+    *abort_flag = code;
+    atomicCAS(&g_gemm_status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+    // K-major, 128-byte swizzle: 8-row groups 1024 B apart (SBO), LBO unused (=1), version 1
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Expand the 32 weights this thread owns (row n, K offset k0 + 32*h) into four 16-byte
+// chunks of bf16, in element order. `raw` points at this thread's slot of the packed ring.
+template <int TYPE>
+__device__ __forceinline__ void expand32(const uint8_t* raw, float scale, const float2* lut, uint4 (&out)[4]) {
+    if (TYPE == CMLB200_Q8_0) {
+        const uint4 v0 = *reinterpret_cast<const uint4*>(raw);
+        const uint4 v1 = *reinterpret_cast<const uint4*>(raw + 16);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                const uint32_t word = w[2 * c + (p >> 1)];
+                const int sh = (p & 1) * 16;
+                const float a = (float)(int)(int8_t)((word >> sh) & 0xFF) * scale;
+                const float b = (float)(int)(int8_t)((word >> (sh + 8)) & 0xFF) * scale;
+                o[p] = pack_bf16(a, b);
+            }
+            out[c] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(raw);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (TYPE == CMLB200_NF4) {
+            // word i = bytes 4i..4i+3 = elements 8i..8i+7; lut[byte] = (high-nibble value, low-nibble value)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const float2 t = lut[(w[c] >> (8 * p)) & 0xFF];
+                    o[p] = pack_bf16(t.x * scale, t.y * scale);
+                }
+                out[c] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        } else {
+            // Q4_0: byte j -> element j (low nibble) and j+16 (high nibble); lut[byte] = (low-8, high-8)
+            float lo[16], hi[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const float2 t = lut[(w[j >> 2] >> (8 * (j & 3))) & 0xFF];
+                lo[j] = t.x * scale;
+                hi[j] = t.y * scale;
+            }
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                out[c] = make_uint4(pack_bf16(lo[8 * c], lo[8 * c + 1]), pack_bf16(lo[8 * c + 2], lo[8 * c + 3]),
+                                    pack_bf16(lo[8 * c + 4], lo[8 * c + 5]), pack_bf16(lo[8 * c + 6], lo[8 * c + 7]));
+                out[c + 2] = make_uint4(pack_bf16(hi[8 * c], hi[8 * c + 1]), pack_bf16(hi[8 * c + 2], hi[8 * c + 3]),
+                                        pack_bf16(hi[8 * c + 4], hi[8 * c + 5]), pack_bf16(hi[8 * c + 6], hi[8 * c + 7]));
+            }
+        }
+    }
+}
+
+// grid = (ceil(N/128), ceil(M/MT), splits). With splits > 1 each z-slice covers a K range and
+// writes fp32 partial sums [split][M][N] to `partial`; a second kernel reduces them.
+template <int TYPE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ qs,
+            const void* __restrict__ scales, __nv_bfloat16* __restrict__ y, float* __restrict__ partial,
+            int M, int N, int K, int MT, int nf4_block, int kb_per_split) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + SmemLayout::bar_off;
+    // barrier slots (8 B each): full_a[S], full_b[S], empty[S], accum
+    auto full_a = [&](int s) { return bars + 8 * s; };
+    auto full_b = [&](int s) { return bars + 8 * (STAGES + s); };
+    auto empty = [&](int s) { return bars + 8 * (2 * STAGES + s); };
+    const uint32_t accum_bar = bars + 8 * (3 * STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SmemLayout::bar_off + 8 * (3 * STAGES + 1));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::bar_off + 8 * (3 * STAGES + 1) + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * MT;
+    const int total_kb = K / BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(total_kb, kb_begin + kb_per_split);
+    const int nkb = kb_end - kb_begin;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < MT) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_a(s), DQ_WARPS);
+            mbar_init(full_b(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp >= 2) {
+        // byte -> (first, second) value table for the 4-bit formats
+        float2* lut = reinterpret_cast<float2*>(smem + SmemLayout::lut_off);
+        const int b = threadIdx.x - 64;
+        if (TYPE == CMLB200_NF4) lut[b] = make_float2(kNF4[b >> 4], kNF4[b & 15]);
+        else lut[b] = make_float2((float)((b & 15) - 8), (float)((b >> 4) - 8));
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activation slabs (operand B) ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(empty(s), ph ^ 1, abort_flag, 1)) break;
+                mbar_expect_tx(full_b(s), (uint32_t)MT * BK * 2);
+                tma_load_2d(sbase + SmemLayout::b_off + s * B_BYTES_MAX, &xmap, (kb_begin + i) * BK, m0, full_b(s));
+                issued = i + 1;
+            }
+            // never leave a bulk copy in flight behind an exiting CTA
+            for (int i = max(0, issued - STAGES); i < issued; i++)
+                mbar_wait(full_b(i % STAGES), (i / STAGES) & 1, abort_flag, 2);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                ok = mbar_wait(full_a(s), ph, abort_flag, 3) && mbar_wait(full_b(s), ph, abort_flag, 4);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = make_desc_sw128(sbase + SmemLayout::a_off + s * A_BYTES);
+                const uint64_t bdesc = make_desc_sw128(sbase + SmemLayout::b_off + s * B_BYTES_MAX);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; kk++)   // advance 32 bytes inside the swizzle row per K=16 step
+                    umma_f16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (i | kk) ? 1u : 0u);
+                umma_commit(empty(s));
+            }
+            umma_commit(accum_bar);   // arrives once every MMA issued so far has retired
+        }
+    } else {
+        // ---------------- weight expansion (operand A), then epilogue ----------------
+        const int t = threadIdx.x - 64;
+        const int r = t >> 1, h = t & 1;
+        const int n = min(n0 + r, N - 1);     // rows past N repeat the last row; never stored
+        constexpr int RAW = Ring<TYPE>::slot;
+        constexpr int RING = Ring<TYPE>::depth;
+        static_assert(RING * DQ_THREADS * RAW <= 16384, "packed-weight ring overflows its shared-memory region");
+        const uint8_t* wrow = qs + (size_t)n * ((size_t)K * RAW / 32);
+        uint8_t* raw_ring = smem + SmemLayout::raw_off;
+        uint32_t* sc_ring = reinterpret_cast<uint32_t*>(smem + SmemLayout::sc_off);
+        const float2* lut = reinterpret_cast<const float2*>(smem + SmemLayout::lut_off);
+
+        auto prefetch = [&](int i) {
+            if (i < nkb) {
+                const int slot = i % RING;
+                const size_t kblk = (size_t)(kb_begin + i) * 2 + h;   // 32-element block index in the row
+                const uint32_t dst = smem_u32(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW);
+                cp_async16(dst, wrow + kblk * RAW);
+                if (RAW == 32) cp_async16(dst + 16, wrow + kblk * RAW + 16);
+                const uint32_t sdst = smem_u32(sc_ring + slot * DQ_THREADS + t);
+                if (TYPE == CMLB200_NF4) {
+                    const size_t e = (size_t)n * K + kblk * 32;
+                    cp_async4(sdst, reinterpret_cast<const float*>(scales) + e / (size_t)nf4_block);
+                } else {
+                    // two fp16 scales of this K slab share one aligned 32-bit word
+                    const size_t sidx = (size_t)n * (K / 32) + (size_t)(kb_begin + i) * 2;
+                    cp_async4(sdst, reinterpret_cast<const uint16_t*>(scales) + sidx);
+                }
+            }
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int i = 0; i < RING - 1; i++) prefetch(i);
+
+        bool ok = true;
+        for (int i = 0; i < nkb; i++) {
+            prefetch(i + RING - 1);
+            cp_async_wait<RING - 1>();
+            const int slot = i % RING;
+            float scale;
+            const uint32_t sw = sc_ring[slot * DQ_THREADS + t];
+            if (TYPE == CMLB200_NF4) scale = __uint_as_float(sw);
+            else scale = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
+            uint4 out[4];
+            expand32<TYPE>(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW, scale, lut, out);
+
+            const int s = i % STAGES;
+            const uint32_t ph = (i / STAGES) & 1;
+            // one lane polls; the verdict is made warp-uniform so that no lane can be left
+            // behind at the __syncwarp below
+            int okl = ok ? 1 : 0;
+            if (ok && lane == 0) okl = mbar_wait(empty(s), ph ^ 1, abort_flag, 5) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+            if (ok) {
+                uint8_t* arow = smem + SmemLayout::a_off + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4*>(arow + (((4 * h + c) ^ (r & 7)) << 4)) = out[c];
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
+            }
+        }
+        cp_async_wait<0>();
+
+        // ---- epilogue: D[n][m] (lane = weight row, column = activation row) -> Y[m][n]
+        {
+            int okl = ok ? 1 : 0;
+            if (ok && lane == 0) okl = mbar_wait(accum_bar, 0, abort_flag, 6) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int q = warp & 3;                 // the TMEM lane quadrant this warp may read
+            const int half = (warp - 2) >> 2;       // two warps share a quadrant and split the columns
+            const int nrow = n0 + q * 32 + lane;
+            for (int c0 = half * 32; c0 < MT; c0 += 64) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (nrow < N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int m = m0 + c0 + j;
+                        if (m < M && c0 + j < MT) {
+                            if (partial) partial[((size_t)blockIdx.z * M + m) * N + nrow] = __uint_as_float(v[j]);
+                            else y[(size_t)m * N + nrow] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, size_t mn, int splits) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += stride) {
+        float s = 0.f;
+        for (int z = 0; z < splits; z++) s += partial[(size_t)z * mn + i];
+        y[i] = __float2bfloat16_rn(s);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encoder(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CMLB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        CMLB_REQUIRE(p && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    *out = fn;
+    return CMLB200_OK;
+}
+
+// Scratch for split-K partial sums, grown on demand, one per device in use.
+struct Workspace { float* ptr; size_t bytes; };
+Workspace g_ws[16] = {};
+
+template <int TYPE>
+int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, float* ws, int splits_forced, cudaStream_t st) {
+    const int N = W->rows, K = W->cols;
+    int MT = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+    EncodeTiledFn enc;
+    int rc = get_encoder(&enc);
+    if (rc) return rc;
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)MT};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (x must be 16-byte aligned, K*2 a multiple of 16)", (int)cr);
+
+    const int gx = (N + BN - 1) / BN, gy = (M + MT - 1) / MT;
+    const int total_kb = K / BK;
+    int splits = 1;
+    if (splits_forced > 0) splits = splits_forced;
+    else {
+        // few tiles: split K so that every SM gets a CTA, but keep at least 8 slabs per CTA
+        const int sms = cmlb_num_sms();
+        while (gx * gy * splits * 2 <= sms && total_kb / (splits * 2) >= 8) splits *= 2;
+    }
+    if (splits > total_kb) splits = total_kb;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    float* partial = nullptr;
+    if (splits > 1) {
+        const size_t need = (size_t)splits * M * N * sizeof(float);
+        if (ws) partial = ws;
+        else {
+            int dev = 0;
+            CMLB_CUDA(cudaGetDevice(&dev));
+            CMLB_REQUIRE(dev < 16, "device index %d out of range", dev);
+            if (g_ws[dev].bytes < need) {
+                if (g_ws[dev].ptr) CMLB_CUDA(cudaFree(g_ws[dev].ptr));
+                g_ws[dev].ptr = nullptr;
+                g_ws[dev].bytes = 0;
+                CMLB_CUDA(cudaMalloc((void**)&g_ws[dev].ptr, need));
+                g_ws[dev].bytes = need;
+            }
+            partial = g_ws[dev].ptr;
+        }
+    }
+    auto kern = gemm_kernel<TYPE>;
+    const int smem = SmemLayout::total + 1024;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, (const uint8_t*)W->qs, W->scales, (__nv_bfloat16*)y, partial,
+                                                    M, N, K, MT, W->block, kb_per_split);
+    CMLB_LAUNCH_CHECK();
+    if (splits > 1) {
+        const size_t mn = (size_t)M * N;
+        int grid = (int)((mn + 255) / 256);
+        if (grid > cmlb_num_sms() * 8) grid = cmlb_num_sms() * 8;
+        splitk_reduce_kernel<<<grid, 256, 0, st>>>(partial, (__nv_bfloat16*)y, mn, splits);
+        CMLB_LAUNCH_CHECK();
+    }
+    return CMLB200_OK;
+}
+
+int gemm_entry(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, float* ws, int splits, void* stream) {
+    CMLB_REQUIRE(W && W->qs && W->scales && x && y, "cmlb200_gemm_bf16: NULL argument");
+    CMLB_REQUIRE(M >= 1, "cmlb200_gemm_bf16: M=%d must be positive", M);
+    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % BK == 0, "cmlb200_gemm_bf16: cols=%d must be a positive multiple of 64", W->cols);
+    CMLB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)W->scales & 3) == 0,
+                 "cmlb200_gemm_bf16: x and the weight planes must be 16-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    switch (W->type) {
+        case CMLB200_Q8_0: return launch_gemm<CMLB200_Q8_0>(W, x, y, M, ws, splits, st);
+        case CMLB200_Q4_0: return launch_gemm<CMLB200_Q4_0>(W, x, y, M, ws, splits, st);
+        case CMLB200_NF4:
+            CMLB_REQUIRE(W->block >= 32 && W->block % 32 == 0 && W->cols % W->block == 0,
+                         "cmlb200_gemm_bf16: NF4 block size %d must be a multiple of 32 that divides cols", W->block);
+            return launch_gemm<CMLB200_NF4>(W, x, y, M, ws, splits, st);
+        default: CMLB_REQUIRE(false, "cmlb200_gemm_bf16: unsupported weight type %d", W->type);
+    }
+    return CMLB200_EINVAL;
+}
+
+}  // namespace
+
+extern "C" int cmlb200_gemm_bf16(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M, void* stream) {
+    return gemm_entry(W, d_x_bf16, d_y_bf16, M, nullptr, 0, stream);
+}
+
+extern "C" int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
+                                        int splits, void* stream) {
+    CMLB_REQUIRE(splits >= 1, "cmlb200_gemm_bf16_splitk: splits must be >= 1");
+    return gemm_entry(W, d_x_bf16, d_y_bf16, M, nullptr, splits, stream);
+}
+
+extern "C" int cmlb200_gemm_status(int* status, int reset) {
+    CMLB_REQUIRE(status, "cmlb200_gemm_status: NULL argument");
+    CMLB_CUDA(cudaDeviceSynchronize());
+    CMLB_CUDA(cudaMemcpyFromSymbol(status, g_gemm_status, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        CMLB_CUDA(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+    }
+    return CMLB200_OK;
+}

@@ -1,0 +1,260 @@
+// Dequant-fused GEMV / skinny GEMM for decode (M <= 32), fp32 activations,
+// fp32 accumulation: y[M,N] = x[M,K] . dequant(W[N,K])^T.
+//
+// Replaces "dequantize the whole weight to fp32, then run an fp32 matmul"
+// (C-ML src/nn/qlora.c:264-317; src/core/gguf.c:271-295 followed by
+// src/ops/ir/execution.c:989-1052 / 3090-3134). The weight is streamed once
+// from HBM in its packed form with 128-bit loads; each lane expands its 16
+// bytes in registers, multiplies with activations staged in shared memory,
+// and rows are reduced with warp shuffles.
+#include "common.cuh"
+
+namespace {
+
+enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kSegMaxFloats = 12288;  // activation floats staged per K segment (48 KB)
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    // weights are read exactly once: bypass L1 allocation
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Dot product of the 16 packed bytes in `v` with the matching activations.
+// ELEMS = activations covered by 16 bytes: 16 (Q8_0) or 32 (Q4_0, NF4).
+template <int TYPE>
+__device__ __forceinline__ float dot16(const uint4& v, const float* __restrict__ xs) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.f;
+    if (TYPE == CMLB200_Q8_0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + 4 * i);
+            s = fmaf((float)(int)(int8_t)(w[i] & 0xFF), xv.x, s);
+            s = fmaf((float)(int)(int8_t)((w[i] >> 8) & 0xFF), xv.y, s);
+            s = fmaf((float)(int)(int8_t)((w[i] >> 16) & 0xFF), xv.z, s);
+            s = fmaf((float)((int)w[i] >> 24), xv.w, s);
+        }
+    } else if (TYPE == CMLB200_Q4_0) {
+        // byte j: low nibble -> element j, high nibble -> element j + 16
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 xl = *reinterpret_cast<const float4*>(xs + 4 * i);
+            const float4 xh = *reinterpret_cast<const float4*>(xs + 16 + 4 * i);
+            const uint32_t u = w[i];
+            s = fmaf((float)((int)(u & 15) - 8), xl.x, s);
+            s = fmaf((float)((int)((u >> 4) & 15) - 8), xh.x, s);
+            s = fmaf((float)((int)((u >> 8) & 15) - 8), xl.y, s);
+            s = fmaf((float)((int)((u >> 12) & 15) - 8), xh.y, s);
+            s = fmaf((float)((int)((u >> 16) & 15) - 8), xl.z, s);
+            s = fmaf((float)((int)((u >> 20) & 15) - 8), xh.z, s);
+            s = fmaf((float)((int)((u >> 24) & 15) - 8), xl.w, s);
+            s = fmaf((float)((int)(u >> 28) - 8), xh.w, s);
+        }
+    } else {
+        // NF4: byte i -> element 2i (high nibble), 2i+1 (low nibble)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 xa = *reinterpret_cast<const float4*>(xs + 8 * i);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + 8 * i + 4);
+            const uint32_t u = w[i];
+            s = fmaf(kNF4[(u >> 4) & 15], xa.x, s);
+            s = fmaf(kNF4[u & 15], xa.y, s);
+            s = fmaf(kNF4[(u >> 12) & 15], xa.z, s);
+            s = fmaf(kNF4[(u >> 8) & 15], xa.w, s);
+            s = fmaf(kNF4[(u >> 20) & 15], xb.x, s);
+            s = fmaf(kNF4[(u >> 16) & 15], xb.y, s);
+            s = fmaf(kNF4[u >> 28], xb.z, s);
+            s = fmaf(kNF4[(u >> 24) & 15], xb.w, s);
+        }
+    }
+    return s;
+}
+
+template <int TYPE>
+__device__ __forceinline__ float load_scale(const void* scales, size_t row, int K, int chunk, int nf4_block) {
+    if (TYPE == CMLB200_Q8_0)
+        return cml_half_to_float(reinterpret_cast<const uint16_t*>(scales)[row * (size_t)(K / 32) + (chunk >> 1)]);
+    if (TYPE == CMLB200_Q4_0)
+        return cml_half_to_float(reinterpret_cast<const uint16_t*>(scales)[row * (size_t)(K / 32) + chunk]);
+    return reinterpret_cast<const float*>(scales)[(row * (size_t)K + (size_t)chunk * 32) / (size_t)nf4_block];
+}
+
+// One warp owns R consecutive rows (2R when SWIGLU pairs gate and up); its 32
+// lanes split K in 16-byte chunks. MT activation rows are handled per pass.
+template <int TYPE, int MT, int R, int EPI>
+__global__ void __launch_bounds__(kThreads)
+gemv_kernel(const uint8_t* __restrict__ qs, const void* __restrict__ scales,
+            const uint8_t* __restrict__ qs2, const void* __restrict__ scales2,
+            const float* __restrict__ x, float* __restrict__ y, int N, int K, int m0, int nf4_block, int kseg) {
+    extern __shared__ __align__(16) float xs[];   // [MT][kseg]
+    constexpr int ELEMS = (TYPE == CMLB200_Q8_0) ? 16 : 32;
+    constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t row_bytes = (size_t)K * 16 / ELEMS;
+    const int ngroups = (N + R - 1) / R;
+
+    for (int g0 = blockIdx.x * kWarps; g0 < ngroups; g0 += gridDim.x * kWarps) {
+        const int g = g0 + warp;
+        float acc[NW][R][MT];
+#pragma unroll
+        for (int a = 0; a < NW; a++)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < MT; m++) acc[a][r][m] = 0.f;
+
+        for (int k0 = 0; k0 < K; k0 += kseg) {
+            const int klen = min(kseg, K - k0);
+            __syncthreads();
+            for (int m = 0; m < MT; m++)
+                for (int i = threadIdx.x * 4; i < klen; i += kThreads * 4)
+                    *reinterpret_cast<float4*>(xs + m * kseg + i) =
+                        *reinterpret_cast<const float4*>(x + (size_t)(m0 + m) * K + k0 + i);
+            __syncthreads();
+            if (g < ngroups) {
+                const int c0 = k0 / ELEMS, nchunks = klen / ELEMS;
+                for (int c = lane; c < nchunks; c += 32) {
+                    uint4 wv[NW][R];
+                    float sc[NW][R];
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const int row = min(g * R + r, N - 1);
+                        wv[0][r] = ld_stream(qs + row * row_bytes + (size_t)(c0 + c) * 16);
+                        sc[0][r] = load_scale<TYPE>(scales, row, K, c0 + c, nf4_block);
+                        if (NW == 2) {
+                            wv[1][r] = ld_stream(qs2 + row * row_bytes + (size_t)(c0 + c) * 16);
+                            sc[1][r] = load_scale<TYPE>(scales2, row, K, c0 + c, nf4_block);
+                        }
+                    }
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float* xp = xs + m * kseg + c * ELEMS;
+#pragma unroll
+                        for (int a = 0; a < NW; a++)
+#pragma unroll
+                            for (int r = 0; r < R; r++)
+                                acc[a][r][m] = fmaf(sc[a][r], dot16<TYPE>(wv[a][r], xp), acc[a][r][m]);
+                    }
+                }
+            }
+        }
+        if (g < ngroups) {
+#pragma unroll
+            for (int a = 0; a < NW; a++)
+#pragma unroll
+                for (int r = 0; r < R; r++)
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        float v = acc[a][r][m];
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                        acc[a][r][m] = v;
+                    }
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int row = g * R + r;
+                    if (row < N) {
+#pragma unroll
+                        for (int m = 0; m < MT; m++) {
+                            float* out = y + (size_t)(m0 + m) * N + row;
+                            if (EPI == EPI_STORE) *out = acc[0][r][m];
+                            else if (EPI == EPI_ACCUM) *out += acc[0][r][m];
+                            else {
+                                const float gte = acc[0][r][m];
+                                *out = (gte / (1.0f + expf(-gte))) * acc[1][r][m];   // silu(g) * u
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int TYPE, int MT, int EPI>
+int launch_gemv(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, float* y, int m0, cudaStream_t st) {
+    constexpr int R = (EPI == EPI_SWIGLU) ? 1 : 2;
+    const int N = W->rows, K = W->cols;
+    int kseg = K;
+    if ((size_t)kseg * MT > (size_t)kSegMaxFloats) kseg = (kSegMaxFloats / MT) / 64 * 64;
+    const size_t smem = (size_t)kseg * MT * sizeof(float);
+    auto kern = gemv_kernel<TYPE, MT, R, EPI>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSegMaxFloats * 4));
+        attr_done = true;
+    }
+    const int ngroups = (N + R - 1) / R;
+    int grid = (ngroups + kWarps - 1) / kWarps;
+    const int cap = cmlb_num_sms() * 4;
+    if (grid > cap) grid = cap;
+    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)W->qs, W->scales, W2 ? (const uint8_t*)W2->qs : nullptr,
+                                        W2 ? W2->scales : nullptr, x, y, N, K, m0, W->block, kseg);
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+template <int TYPE, int EPI>
+int gemv_type(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, float* y, int M, cudaStream_t st) {
+    int m0 = 0, rc = 0;
+    while (m0 < M && rc == 0) {
+        const int left = M - m0;
+        if (left >= 4) { rc = launch_gemv<TYPE, 4, EPI>(W, W2, x, y, m0, st); m0 += 4; }
+        else if (left >= 2) { rc = launch_gemv<TYPE, 2, EPI>(W, W2, x, y, m0, st); m0 += 2; }
+        else { rc = launch_gemv<TYPE, 1, EPI>(W, W2, x, y, m0, st); m0 += 1; }
+    }
+    return rc;
+}
+
+int check_qmat(const cmlb200_qmat* W, const char* who) {
+    CMLB_REQUIRE(W && W->qs && W->scales, "%s: NULL weight", who);
+    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "%s: weight shape %dx%d (cols must be a multiple of 32)", who, W->rows, W->cols);
+    CMLB_REQUIRE(W->type == CMLB200_Q4_0 || W->type == CMLB200_Q8_0 || W->type == CMLB200_NF4, "%s: unsupported weight type %d", who, W->type);
+    if (W->type == CMLB200_NF4)
+        CMLB_REQUIRE(W->block >= 32 && W->block % 32 == 0 && W->cols % W->block == 0,
+                     "%s: NF4 block size %d must be a multiple of 32 that divides cols=%d", who, W->block, W->cols);
+    CMLB_REQUIRE(((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)W->scales & 3) == 0, "%s: weight planes must be 16-byte aligned", who);
+    return CMLB200_OK;
+}
+
+template <int EPI>
+int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, float* y, int M, void* stream,
+                  const char* who) {
+    int rc = check_qmat(W, who);
+    if (rc) return rc;
+    if (EPI == EPI_SWIGLU) {
+        rc = check_qmat(W2, who);
+        if (rc) return rc;
+        CMLB_REQUIRE(W2->type == W->type && W2->rows == W->rows && W2->cols == W->cols && W2->block == W->block,
+                     "%s: gate and up weights must have the same type and shape", who);
+    }
+    CMLB_REQUIRE(x && y, "%s: NULL activation pointer", who);
+    CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
+    CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
+    cudaStream_t st = as_stream(stream);
+    switch (W->type) {
+        case CMLB200_Q8_0: return gemv_type<CMLB200_Q8_0, EPI>(W, W2, x, y, M, st);
+        case CMLB200_Q4_0: return gemv_type<CMLB200_Q4_0, EPI>(W, W2, x, y, M, st);
+        default: return gemv_type<CMLB200_NF4, EPI>(W, W2, x, y, M, st);
+    }
+}
+
+}  // namespace
+
+extern "C" int cmlb200_gemv(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream) {
+    return gemv_dispatch<EPI_STORE>(W, nullptr, d_x, d_y, M, stream, "cmlb200_gemv");
+}
+extern "C" int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream) {
+    return gemv_dispatch<EPI_ACCUM>(W, nullptr, d_x, d_y, M, stream, "cmlb200_gemv_accum");
+}
+extern "C" int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const float* d_x, float* d_y,
+                                   int M, void* stream) {
+    return gemv_dispatch<EPI_SWIGLU>(Wg, Wu, d_x, d_y, M, stream, "cmlb200_gemv_swiglu");
+}

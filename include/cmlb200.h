@@ -1,0 +1,130 @@
+/*
+ * cmlb200.h -- the C-ABI boundary between C11 host code and the sm_100a CUDA
+ * kernels of the quantized-LLM path (plain pointers and sizes only).
+ *
+ * Every entry point replaces a piece of C-ML's CPU path; the C-ML location it
+ * stands in for is cited as file:line relative to the C-ML source tree.
+ * All functions return 0 on success and a negative CMLB200_E* code otherwise;
+ * cmlb200_last_error() gives a human-readable reason for the calling thread.
+ * Pointers named d_* are device pointers, h_* are host pointers. `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).
+ * There is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef CMLB200_H
+#define CMLB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CMLB200_OK 0
+#define CMLB200_EINVAL (-1)   /* NULL pointer, bad shape, unsupported type (C-ML returns -1/NULL here too) */
+#define CMLB200_ECUDA (-2)    /* a CUDA runtime call failed */
+#define CMLB200_ENOMEM (-3)
+#define CMLB200_ETIMEOUT (-4) /* a bounded device-side wait expired */
+#define CMLB200_ENCCL (-5)
+
+/* Weight formats. The first two use the GGUF tensor-type ids
+ * (include/core/gguf.h:29-41); NF4 has no GGUF id in C-ML. */
+#define CMLB200_Q4_0 2
+#define CMLB200_Q8_0 7
+#define CMLB200_NF4 100
+
+/* A quantized [rows, cols] weight (rows = out features N, cols = in features
+ * K; y = x . W^T as in src/nn/qlora.c:309-317) in the repacked device layout:
+ *   qs     Q8_0: rows*cols int8, row-major.
+ *          Q4_0: rows*cols/2 bytes, row-major; the 16 bytes of GGUF block b of
+ *                a row sit at byte 16*b of that row, unchanged (byte j = element
+ *                j in the low nibble, j+16 in the high nibble).
+ *          NF4 : rows*cols/2 bytes exactly as cml_quantize_nf4 packs them
+ *                (element 2i = high nibble of byte i, src/core/quantization.c:303-305).
+ *   scales Q8_0/Q4_0: rows*(cols/32) fp16, row-major (the `d` of each block).
+ *          NF4 : rows*cols/block fp32 absmax values.
+ * Both planes must be 16-byte aligned; cols must be a multiple of 32 (and of
+ * `block` for NF4) so that every row starts on a 16-byte boundary. */
+typedef struct cmlb200_qmat {
+    int type;
+    int rows;
+    int cols;
+    int block;      /* 32 for Q4_0/Q8_0, the NF4 block size otherwise */
+    void* qs;       /* device */
+    void* scales;   /* device */
+} cmlb200_qmat;
+
+const char* cmlb200_last_error(void);
+
+/* ---- device plumbing (no counterpart in C-ML, which runs this path on the host) */
+int cmlb200_device_count(int* count);
+int cmlb200_set_device(int device);
+int cmlb200_malloc(void** d_ptr, size_t bytes);
+int cmlb200_free(void* d_ptr);
+int cmlb200_host_alloc_pinned(void** h_ptr, size_t bytes);
+int cmlb200_host_free_pinned(void* h_ptr);
+int cmlb200_memcpy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
+int cmlb200_memcpy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
+int cmlb200_memcpy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);
+int cmlb200_memset(void* d_dst, int value, size_t bytes, void* stream);
+int cmlb200_stream_create(void** stream);
+int cmlb200_stream_destroy(void* stream);
+int cmlb200_stream_sync(void* stream);
+int cmlb200_device_sync(void);
+
+/* ---- one-time repack (host side; replaces nothing in C-ML -- its loader
+ * expands blocks to fp32 instead, src/core/gguf.c:271-295). Sizes in bytes of
+ * the two planes for a [rows, cols] matrix of `type`. */
+size_t cmlb200_qs_bytes(int type, int rows, int cols, int block);
+size_t cmlb200_scale_bytes(int type, int rows, int cols, int block);
+/* GGUF blocks (BlockQ4_0 / BlockQ8_0 array in file order,
+ * include/core/gguf_quant.h:14-31) -> the two planes; and back. The quantized
+ * content is unchanged, so unrepack(repack(b)) == b byte for byte. */
+int cmlb200_repack_gguf(int type, const void* h_blocks, int rows, int cols, void* h_qs, void* h_scales);
+int cmlb200_unrepack_gguf(int type, const void* h_qs, const void* h_scales, int rows, int cols, void* h_blocks);
+
+/* ---- dequantisation to fp32, bit-exact with C-ML ------------------------- */
+/* gguf_dequantize(type, src, dst, numel) (src/core/gguf_quant.c:351-391) on
+ * raw GGUF blocks resident on the device. Same argument checks: NULL, numel==0,
+ * unknown type or numel % 32 != 0 -> CMLB200_EINVAL. */
+int cmlb200_gguf_dequantize(int type, const void* d_blocks, float* d_dst, size_t numel, void* stream);
+/* The same values from the repacked planes (checks the repack on device). */
+int cmlb200_dequant_qmat(const cmlb200_qmat* W, float* d_dst, void* stream);
+/* cml_dequantize_nf4 (src/core/quantization.c:314-370):
+ * out[e] = CML_NF4_TABLE[idx(e)] * scales[min(e/block, num_scales-1)]. */
+int cmlb200_dequantize_nf4(const uint8_t* d_packed, const float* d_scales, int num_scales, int block,
+                           size_t numel, float* d_out, void* stream);
+
+/* ---- dequant-fused matmul -------------------------------------------------- */
+/* Decode / skinny path, M <= 32: y[M, rows] = x[M, cols] . dequant(W)^T with
+ * fp32 activations, fp32 accumulation and fp32 output. Replaces "dequantize,
+ * then fp32 matmul": cml_nf4_tensor_dequantize + the triple loop of
+ * src/nn/qlora.c:264-317, and gguf_read_tensor's dequantize-at-load followed by
+ * UOP_MATMUL / UOP_LINEAR (src/core/gguf.c:271-295, src/ops/ir/execution.c:989-1052,
+ * 3090-3134). */
+int cmlb200_gemv(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
+/* The same product with the SwiGLU of src/nn/llama.c:126-155 fused in:
+ * y[M, rows] = silu(x . Wg^T) * (x . Wu^T); Wg and Wu have identical shapes. */
+int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const float* d_x, float* d_y,
+                        int M, void* stream);
+/* y += x . W^T (residual add fused; src/nn/llama.c:523-530 and :538-543). */
+int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
+
+/* Prefill path, M >= 1 (any M; built for M >= 64): bf16 activations, weights
+ * dequantised to bf16 tiles in shared memory, tcgen05 MMAs accumulating fp32
+ * in tensor memory, bf16 output. Same reference lines as cmlb200_gemv.
+ * cols must be a multiple of 64. */
+int cmlb200_gemm_bf16(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
+                      void* stream);
+/* Same, with the number of K splits chosen by the caller (1 = none). With more than one
+ * split the partial sums pass through an fp32 scratch buffer owned by the library. */
+int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
+                             int splits, void* stream);
+/* Synchronises the device and reports whether a bounded wait inside the tensor-core kernel
+ * expired since the last reset (0 = none). C-ML has no counterpart: its path cannot stall. */
+int cmlb200_gemm_status(int* status, int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CMLB200_H */

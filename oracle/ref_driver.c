@@ -1,0 +1,273 @@
+/*
+ * ref_driver.c -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * Flat-pointer wrappers around the *compiled C-ML reference* so the tests and
+ * the benchmark's CPU-baseline leg can call C-ML's own functions via ctypes
+ * without re-declaring its structs in Python. This file is compiled against
+ * the reference's headers and linked with oracle/_ref/libcml_ref.so (see
+ * oracle/Makefile); it contains no C-ML source.
+ */
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "cml.h"
+#include "core/gguf_quant.h"
+#include "core/quantization.h"
+#include "distributed/tensor_parallel.h"
+#include "nn/llama.h"
+#include "nn/llm_ops.h"
+#include "nn/qlora.h"
+#include "ops/uops.h"
+#include "tensor/tensor.h"
+
+static TensorConfig f32cfg(void) {
+    TensorConfig c = {.dtype = DTYPE_FLOAT32, .device = DEVICE_CPU, .has_dtype = true, .has_device = true};
+    return c;
+}
+
+static Tensor* t_from(const float* data, int ndim, const int* shape) {
+    int sh[4];
+    for (int i = 0; i < ndim; i++) sh[i] = shape[i];
+    TensorConfig c = f32cfg();
+    return tensor_from_data(data, sh, ndim, &c);
+}
+
+int ref_init(void) { return cml_init(); }
+
+/* gguf_dequantize (src/core/gguf_quant.c:351) */
+int ref_gguf_dequantize(int type, const void* src, float* dst, size_t numel) {
+    return gguf_dequantize((GGUFTensorType)type, src, dst, numel);
+}
+int ref_gguf_type_is_quantized(int type) { return gguf_type_is_quantized((GGUFTensorType)type) ? 1 : 0; }
+int ref_gguf_quant_block_size(int type) { return gguf_quant_block_size((GGUFTensorType)type); }
+size_t ref_gguf_quant_type_size(int type) { return gguf_quant_type_size((GGUFTensorType)type); }
+
+const float* ref_nf4_table(void) { return CML_NF4_TABLE; }
+
+/* cml_quantize_nf4 (src/core/quantization.c:213). Returns num_scales or -1. */
+int ref_nf4_quantize(const float* x, size_t numel, int block, uint8_t* packed, float* scales) {
+    int sh[1] = {(int)numel};
+    Tensor* t = t_from(x, 1, sh);
+    if (!t) return -1;
+    float* sc = NULL;
+    int ns = 0;
+    Tensor* p = cml_quantize_nf4(t, block, &sc, &ns);
+    tensor_free(t);
+    if (!p) return -1;
+    memcpy(packed, tensor_data_ptr(p), (numel + 1) / 2);
+    memcpy(scales, sc, (size_t)ns * sizeof(float));
+    free(sc);
+    tensor_free(p);
+    return ns;
+}
+
+/* cml_dequantize_nf4 (src/core/quantization.c:314) */
+int ref_nf4_dequantize(const uint8_t* packed, const float* scales, int num_scales, int block,
+                       size_t numel, float* out) {
+    int sh[1] = {(int)((numel + 1) / 2)};
+    TensorConfig c = {.dtype = DTYPE_UINT8, .device = DEVICE_CPU, .has_dtype = true, .has_device = true};
+    Tensor* p = tensor_from_data(packed, sh, 1, &c);
+    if (!p) return -1;
+    Tensor* o = cml_dequantize_nf4(p, scales, num_scales, block, numel);
+    tensor_free(p);
+    if (!o) return -1;
+    memcpy(out, tensor_data_ptr(o), numel * sizeof(float));
+    tensor_free(o);
+    return 0;
+}
+
+/* uop_linear(x[M,K], W[N,K], NULL) (src/ops/uops.c:663 -> src/ops/ir/execution.c:3090) */
+int ref_linear(const float* x, const float* W, int M, int N, int K, float* y) {
+    int xs[2] = {M, K}, ws[2] = {N, K};
+    Tensor* tx = t_from(x, 2, xs);
+    Tensor* tw = t_from(W, 2, ws);
+    if (!tx || !tw) return -1;
+    Tensor* ty = uop_linear(tx, tw, NULL);
+    if (!ty) return -1;
+    float* d = (float*)tensor_data_ptr(ty);
+    if (!d) return -1;
+    memcpy(y, d, (size_t)M * N * sizeof(float));
+    tensor_free(ty);
+    tensor_free(tx);
+    tensor_free(tw);
+    return 0;
+}
+
+/* cml_qlora_linear_forward (src/nn/qlora.c:240) on a weight that this wrapper
+ * quantizes through cml_qlora_linear_create (:134). If packed_in is non-NULL
+ * its bytes and scales replace the freshly quantized ones, so callers can
+ * feed arbitrary NF4 indices. lora_B may be NULL (stays zero). */
+int ref_qlora_forward(const float* x, int M, int in_f, int out_f, const float* W_fp32,
+                      const uint8_t* packed_in, const float* scales_in, int block, int rank,
+                      float alpha, const float* lora_A, const float* lora_B, float* y) {
+    int ws[2] = {out_f, in_f}, xs[2] = {M, in_f};
+    float* zeros = NULL;
+    if (!W_fp32) {
+        zeros = (float*)calloc((size_t)out_f * in_f, sizeof(float));
+        W_fp32 = zeros;
+    }
+    Tensor* tw = t_from(W_fp32, 2, ws);
+    free(zeros);
+    if (!tw) return -1;
+    CMLQLoRALinear* q = cml_qlora_linear_create(tw, rank, alpha, block);
+    tensor_free(tw);
+    if (!q) return -1;
+    if (packed_in && scales_in) {
+        memcpy(tensor_data_ptr(q->base_weight_nf4->packed_data), packed_in, ((size_t)out_f * in_f + 1) / 2);
+        memcpy(q->base_weight_nf4->scales, scales_in, (size_t)q->base_weight_nf4->num_scales * sizeof(float));
+    }
+    if (lora_A) memcpy(tensor_data_ptr(q->lora_A), lora_A, (size_t)rank * in_f * sizeof(float));
+    if (lora_B) memcpy(tensor_data_ptr(q->lora_B), lora_B, (size_t)out_f * rank * sizeof(float));
+    Tensor* tx = t_from(x, 2, xs);
+    Tensor* ty = tx ? cml_qlora_linear_forward(q, tx) : NULL;
+    int rc = -1;
+    if (ty) {
+        memcpy(y, tensor_data_ptr(ty), (size_t)M * out_f * sizeof(float));
+        tensor_free(ty);
+        rc = 0;
+    }
+    if (tx) tensor_free(tx);
+    cml_qlora_linear_free(q);
+    return rc;
+}
+
+/* A reference LLaMA built from flat fp32 arrays in the reference's own
+ * orientation (projections [in,out]); the fill pattern follows what the
+ * reference's tests do with the public struct fields. */
+typedef struct {
+    int vocab, hidden, inter, layers, heads, kv_heads, max_seq;
+    float rope_theta, eps;
+} RefLlamaCfg;
+
+void* ref_llama_create(const RefLlamaCfg* c, const float* embed, const float* final_norm,
+                       const float* lm_head, const float* const* wq, const float* const* wk,
+                       const float* const* wv, const float* const* wo, const float* const* wg,
+                       const float* const* wu, const float* const* wd, const float* const* n1,
+                       const float* const* n2) {
+    CMLLLaMAConfig cfg = {.vocab_size = c->vocab, .hidden_size = c->hidden, .intermediate_size = c->inter,
+                          .num_layers = c->layers, .num_heads = c->heads, .num_kv_heads = c->kv_heads,
+                          .max_seq_len = c->max_seq, .rope_theta = c->rope_theta, .rms_norm_eps = c->eps,
+                          .tensor_parallel_size = 1, .tensor_parallel_rank = 0};
+    CMLLLaMAModel* m = cml_llama_create(&cfg);
+    if (!m) return NULL;
+    int hd = c->hidden / c->heads, qw = c->heads * hd, kvw = c->kv_heads * hd;
+    int es[2] = {c->vocab, c->hidden}, ns[1] = {c->hidden}, ls[2] = {c->hidden, c->vocab};
+    int qs[2] = {c->hidden, qw}, ks[2] = {c->hidden, kvw}, os[2] = {qw, c->hidden};
+    int gs[2] = {c->hidden, c->inter}, ds[2] = {c->inter, c->hidden};
+    m->embed_tokens = t_from(embed, 2, es);
+    m->norm = final_norm ? t_from(final_norm, 1, ns) : NULL;
+    m->lm_head = t_from(lm_head, 2, ls);
+    for (int l = 0; l < c->layers; l++) {
+        CMLLLaMALayer* L = m->layers[l];
+        L->q_proj = t_from(wq[l], 2, qs);
+        L->k_proj = t_from(wk[l], 2, ks);
+        L->v_proj = t_from(wv[l], 2, ks);
+        L->o_proj = t_from(wo[l], 2, os);
+        L->gate_proj = t_from(wg[l], 2, gs);
+        L->up_proj = t_from(wu[l], 2, gs);
+        L->down_proj = t_from(wd[l], 2, ds);
+        L->input_layernorm = t_from(n1[l], 1, ns);
+        L->post_attn_layernorm = t_from(n2[l], 1, ns);
+    }
+    m->weights_loaded = true;
+    return m;
+}
+
+/* cml_llama_forward (src/nn/llama.c:550); logits [seq, vocab] copied out. */
+int ref_llama_forward(void* model, const int* tokens, int seq, float* logits) {
+    CMLLLaMAModel* m = (CMLLLaMAModel*)model;
+    Tensor* t = cml_llama_forward(m, tokens, seq);
+    if (!t) return -1;
+    float* d = (float*)tensor_data_ptr(t);
+    if (!d) return -1;
+    memcpy(logits, d, (size_t)seq * m->config.vocab_size * sizeof(float));
+    return 0; /* the logits tensor is left to the IR context, as the reference's own callers do mid-sequence */
+}
+
+void ref_llama_reset(void* model) { cml_llama_reset((CMLLLaMAModel*)model); }
+int ref_llama_cur_len(void* model) { return ((CMLLLaMAModel*)model)->current_seq_len; }
+void ref_llama_free(void* model) { cml_llama_free((CMLLLaMAModel*)model); }
+
+int ref_sample_greedy(const float* logits, int rows, int vocab) {
+    int sh[2] = {rows, vocab};
+    Tensor* t = t_from(logits, 2, sh);
+    CMLGenerationConfig g = cml_generation_default_config();
+    g.do_sample = false;
+    int id = cml_llama_sample_token(t, &g);
+    tensor_free(t);
+    return id;
+}
+
+/* cml_rope_forward on a 2-D tensor (src/nn/llm_ops.c:702), in place. */
+int ref_rope_2d(float* x, int seq, int width, int head_dim, int start_pos, float base) {
+    int sh[2] = {seq, width};
+    Tensor* t = t_from(x, 2, sh);
+    CMLRoPEConfig rc = {.dim = head_dim, .max_seq_len = 1 << 20, .base = base};
+    if (!t || !cml_rope_forward(t, start_pos, &rc)) return -1;
+    memcpy(x, tensor_data_ptr(t), (size_t)seq * width * sizeof(float));
+    tensor_free(t);
+    return 0;
+}
+
+/* cml_gqa_forward (src/nn/llm_ops.c:194), batch 1, causal, no external mask. */
+int ref_gqa(const float* q, const float* k, const float* v, int seq, int kv_len, int heads,
+            int kv_heads, int hd, float* out) {
+    int qs[3] = {1, seq, heads * hd}, ks[3] = {1, kv_len, kv_heads * hd};
+    Tensor* tq = t_from(q, 3, qs);
+    Tensor* tk = t_from(k, 3, ks);
+    Tensor* tv = t_from(v, 3, ks);
+    CMLGQAConfig g = {.num_heads = heads, .num_kv_heads = kv_heads, .head_dim = hd, .scale = 0.f,
+                      .causal = true, .window_size = 0};
+    Tensor* o = (tq && tk && tv) ? cml_gqa_forward(tq, tk, tv, &g, NULL) : NULL;
+    int rc = -1;
+    if (o) {
+        memcpy(out, tensor_data_ptr(o), (size_t)seq * heads * hd * sizeof(float));
+        tensor_free(o);
+        rc = 0;
+    }
+    if (tq) tensor_free(tq);
+    if (tk) tensor_free(tk);
+    if (tv) tensor_free(tv);
+    return rc;
+}
+
+/* cml_tp_shard_weight / column / row forward / all-reduce
+ * (src/distributed/tensor_parallel.c). Runs all tp ranks in-process, as the
+ * reference's own test does, and returns the reduced [M, N] result of a
+ * column-parallel W1[N1,K] followed by row-parallel W2[N,N1]. */
+int ref_tp_column_then_row(const float* x, int M, int K, const float* W1, int N1, const float* W2,
+                           int N, int tp, float* y) {
+    int xs[2] = {M, K}, w1s[2] = {N1, K}, w2s[2] = {N, N1};
+    Tensor* tx = t_from(x, 2, xs);
+    Tensor* t1 = t_from(W1, 2, w1s);
+    Tensor* t2 = t_from(W2, 2, w2s);
+    Tensor** parts = (Tensor**)calloc((size_t)tp, sizeof(Tensor*));
+    int rc = -1;
+    if (!tx || !t1 || !t2 || !parts) return -1;
+    for (int r = 0; r < tp; r++) {
+        CMLColumnParallelLinear* cp = cml_column_parallel_create(t1, NULL, tp, r);
+        CMLRowParallelLinear* rp = cml_row_parallel_create(t2, NULL, tp, r);
+        if (!cp || !rp) goto done;
+        Tensor* mid = cml_column_parallel_forward(cp, tx);
+        if (!mid) goto done;
+        parts[r] = cml_row_parallel_forward(rp, mid);
+        tensor_free(mid);
+        cml_column_parallel_free(cp);
+        cml_row_parallel_free(rp);
+        if (!parts[r]) goto done;
+    }
+    Tensor* sum = cml_tp_all_reduce_sum(parts, tp);
+    if (sum) {
+        memcpy(y, tensor_data_ptr(sum), (size_t)M * N * sizeof(float));
+        tensor_free(sum);
+        rc = 0;
+    }
+done:
+    for (int r = 0; r < tp; r++) if (parts[r]) tensor_free(parts[r]);
+    free(parts);
+    tensor_free(tx);
+    tensor_free(t1);
+    tensor_free(t2);
+    return rc;
+}

@@ -1,0 +1,137 @@
+"""Regenerates tests/golden/golden.npz by running the COMPILED C-ML REFERENCE
+(oracle/_ref/, built by oracle/Makefile from the C-ML source tree) on small seeded inputs.
+Run it only where the C-ML source tree is available:  python tests/golden/make_golden.py
+The stored vectors pin the oracle (and through it the CUDA path) on machines that do not
+have the reference, e.g. the GPU box."""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+
+def main():
+    ob = entry.load_oracle_binding()
+    ob.build_ref()
+    ref = ob.load_ref()
+    assert ref is not None, "oracle/_ref/ is not built (needs the C-ML source tree)"
+    synth = entry.load_synth()
+    p = ob.p
+    rng = np.random.default_rng(20240601)
+    out = {}
+
+    # --- block dequantisation: random blocks plus every special fp16 scale class
+    for name, qtype, bb in (("q8_0", 7, 34), ("q4_0", 2, 18)):
+        rows, cols = 8, 256
+        blocks = (synth.q8_0_blocks if qtype == 7 else synth.q4_0_blocks)(rng, rows, cols).reshape(-1, bb)
+        special = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x7BFF, 0x7C00, 0xFC00, 0x3C00, 0xBC00,
+                            0x0200, 0x8001, 0x1400, 0x2E66, 0x211F, 0x7E00], np.uint16)
+        blocks[:16, :2] = special.view(np.uint8).reshape(16, 2)
+        blocks = np.ascontiguousarray(blocks.reshape(-1))
+        deq = np.empty(rows * cols, np.float32)
+        assert ref.ref_gguf_dequantize(qtype, p(blocks), p(deq), rows * cols) == 0
+        out[f"{name}_blocks"] = blocks
+        out[f"{name}_dequant_bits"] = deq.view(np.uint32)
+        x = rng.standard_normal((3, cols)).astype(np.float32)
+        y = np.empty((3, rows), np.float32)
+        Wf = deq.reshape(rows, cols).copy()
+        Wf[~np.isfinite(Wf)] = 0.0
+        assert ref.ref_linear(p(x), p(Wf), 3, rows, cols, p(y)) == 0
+        out[f"{name}_x"] = x
+        out[f"{name}_linear_y"] = y
+
+    # --- NF4 quantise / dequantise / QLoRA forward
+    n_out, n_in, block, rank = 12, 128, 64, 4
+    W = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    W[0, :64] = 0.0                      # an all-zero block exercises the 1e-10 absmax floor
+    packed = np.zeros(n_out * n_in // 2, np.uint8)
+    scales = np.zeros(n_out * n_in // block, np.float32)
+    assert ref.ref_nf4_quantize(p(W), W.size, block, p(packed), p(scales)) == len(scales)
+    deq = np.empty(W.size, np.float32)
+    assert ref.ref_nf4_dequantize(p(packed), p(scales), len(scales), block, W.size, p(deq)) == 0
+    x = rng.standard_normal((5, n_in)).astype(np.float32)
+    A = (rng.standard_normal((rank, n_in)) * 0.1).astype(np.float32)
+    B = (rng.standard_normal((n_out, rank)) * 0.1).astype(np.float32)
+    y0 = np.empty((5, n_out), np.float32)
+    y1 = np.empty((5, n_out), np.float32)
+    assert ref.ref_qlora_forward(p(x), 5, n_in, n_out, p(W), None, None, block, rank, 8.0, p(A), None, p(y0)) == 0
+    assert ref.ref_qlora_forward(p(x), 5, n_in, n_out, p(W), None, None, block, rank, 8.0, p(A), p(B), p(y1)) == 0
+    out.update(nf4_W=W, nf4_packed=packed, nf4_scales=scales, nf4_dequant_bits=deq.view(np.uint32), nf4_x=x,
+               nf4_A=A, nf4_B=B, nf4_y_noB=y0, nf4_y_withB=y1,
+               nf4_table_bits=np.array(ref.ref_nf4_table().contents, np.float32).view(np.uint32))
+    # odd length: padding nibble and the clamped last block
+    odd = (rng.standard_normal(131) * 0.3).astype(np.float32)
+    op = np.zeros(66, np.uint8)
+    osc = np.zeros(3, np.float32)
+    assert ref.ref_nf4_quantize(p(odd), 131, 64, p(op), p(osc)) == 3
+    od = np.empty(131, np.float32)
+    assert ref.ref_nf4_dequantize(p(op), p(osc), 3, 64, 131, p(od)) == 0
+    out.update(nf4_odd_x=odd, nf4_odd_packed=op, nf4_odd_scales=osc, nf4_odd_dequant_bits=od.view(np.uint32))
+
+    # --- RoPE (2-D input, as llama.c passes it) and GQA
+    seq, heads, kvh, hd = 5, 4, 2, 16
+    q = rng.standard_normal((seq, heads * hd)).astype(np.float32)
+    qr = q.copy()
+    assert ref.ref_rope_2d(p(qr), seq, heads * hd, hd, 3, 10000.0) == 0
+    k = rng.standard_normal((seq + 3, kvh * hd)).astype(np.float32)
+    v = rng.standard_normal((seq + 3, kvh * hd)).astype(np.float32)
+    att = np.empty((seq, heads * hd), np.float32)
+    assert ref.ref_gqa(p(q), p(k), p(v), seq, seq + 3, heads, kvh, hd, p(att)) == 0
+    out.update(rope_in=q, rope_out=qr, gqa_k=k, gqa_v=v, gqa_out=att)
+
+    # --- tiny LLaMA: prefill 6 tokens, then 3 single-token steps (reference orientation [in,out])
+    cfg = dict(vocab=48, hidden=32, inter=64, layers=2, heads=4, kv_heads=2, max_seq=16)
+    hdm = cfg["hidden"] // cfg["heads"]
+    qw, kvw = cfg["heads"] * hdm, cfg["kv_heads"] * hdm
+    w = lambda *s: (rng.standard_normal(s) * 0.08).astype(np.float32)
+    Wt = dict(embed=w(cfg["vocab"], cfg["hidden"]), final_norm=(1 + 0.1 * rng.standard_normal(cfg["hidden"])).astype(np.float32),
+              lm_head=w(cfg["hidden"], cfg["vocab"]))
+    per = {k2: [] for k2 in ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "n1", "n2")}
+    for _ in range(cfg["layers"]):
+        per["wq"].append(w(cfg["hidden"], qw)); per["wk"].append(w(cfg["hidden"], kvw)); per["wv"].append(w(cfg["hidden"], kvw))
+        per["wo"].append(w(qw, cfg["hidden"])); per["wg"].append(w(cfg["hidden"], cfg["inter"]))
+        per["wu"].append(w(cfg["hidden"], cfg["inter"])); per["wd"].append(w(cfg["inter"], cfg["hidden"]))
+        per["n1"].append((1 + 0.1 * rng.standard_normal(cfg["hidden"])).astype(np.float32))
+        per["n2"].append((1 + 0.1 * rng.standard_normal(cfg["hidden"])).astype(np.float32))
+    rc = ob.RefLlamaCfg(cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv_heads"],
+                        cfg["max_seq"], 10000.0, 1e-5)
+    import ctypes as C
+    model = ref.ref_llama_create(C.byref(rc), p(Wt["embed"]), p(Wt["final_norm"]), p(Wt["lm_head"]),
+                                 *[ob.ptr_array(per[k2]) for k2 in ("wq", "wk", "wv", "wo", "wg", "wu", "wd", "n1", "n2")])
+    assert model
+    tokens = rng.integers(0, cfg["vocab"], 9).astype(np.int32)
+    logits = [np.empty((6, cfg["vocab"]), np.float32)]
+    assert ref.ref_llama_forward(model, p(tokens[:6]), 6, p(logits[0])) == 0
+    for i in range(3):
+        lg = np.empty((1, cfg["vocab"]), np.float32)
+        assert ref.ref_llama_forward(model, p(tokens[6 + i:7 + i]), 1, p(lg)) == 0
+        logits.append(lg)
+    out["llama_cfg"] = np.array([cfg[k2] for k2 in ("vocab", "hidden", "inter", "layers", "heads", "kv_heads", "max_seq")], np.int32)
+    out["llama_tokens"] = tokens
+    out["llama_logits"] = np.concatenate(logits, 0)
+    out["llama_greedy_last"] = np.array([ref.ref_sample_greedy(p(logits[0]), 6, cfg["vocab"])], np.int32)
+    for k2, v2 in Wt.items():
+        out[f"llama_{k2}"] = v2
+    for k2, v2 in per.items():
+        out[f"llama_{k2}"] = np.stack(v2)
+
+    # --- tensor parallel: column-parallel then row-parallel then all-reduce, tp = 1, 2, 4
+    M, K, N1, N = 3, 32, 64, 16
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    W1 = w(N1, K)
+    W2 = w(N, N1)
+    out.update(tp_x=x, tp_W1=W1, tp_W2=W2)
+    for tp in (1, 2, 4):
+        y = np.empty((M, N), np.float32)
+        assert ref.ref_tp_column_then_row(p(x), M, K, p(W1), N1, p(W2), N, tp, p(y)) == 0
+        out[f"tp_y_{tp}"] = y
+
+    np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
+    print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,68 @@
+"""GPU parity of the tcgen05 prefill dequant-GEMM (bf16 activations/outputs, fp32 accumulate
+in tensor memory). Tolerance 1e-2 relative to max|y| (bf16 tensor-core prefill), as the path
+is specified; the oracle is fed the fp32 values of the bf16-rounded activations."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err_inf
+from gpu_util import gemm_status, make_weight, stream_ptr, to_dev
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _gemm(pkg, synth, W, x, N, dev, splits=0):
+    M = x.shape[0]
+    xb, _ = synth.bf16_round(x)
+    d_x = to_dev(xb.reshape(x.shape), dev)
+    d_y = torch.zeros((M, N), dtype=torch.uint16, device=dev)
+    if splits:
+        pkg.check(pkg.lib.cmlb200_gemm_bf16_splitk(W.q, d_x.data_ptr(), d_y.data_ptr(), M, splits, stream_ptr()), "gemm")
+    else:
+        pkg.check(pkg.lib.cmlb200_gemm_bf16(W.q, d_x.data_ptr(), d_y.data_ptr(), M, stream_ptr()), "gemm")
+    assert gemm_status(pkg) == 0, "a bounded wait inside the tensor-core kernel expired"
+    return synth.bf16_to_f32(d_y.cpu().numpy())
+
+
+@pytest.mark.parametrize("kind", ["nf4", "q4_0", "q8_0"])
+@pytest.mark.parametrize("M", [1, 16, 64, 100, 300])
+def test_gemm_matches_oracle(pkg, synth, ob, orc, torch_dev, kind, M):
+    rng = np.random.default_rng(200 + M)
+    N, K = 200, 512                                    # ragged N (tile is 128 rows)
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    _, xr = synth.bf16_round(x)
+    got = _gemm(pkg, synth, W, x, N, torch_dev)
+    want = ob.linear_nt(orc, xr.reshape(x.shape), Wf)
+    assert rel_err_inf(got, want) <= TOL
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4])
+def test_gemm_split_k_agrees(pkg, synth, ob, orc, torch_dev, splits):
+    rng = np.random.default_rng(300)
+    N, K, M = 256, 2048, 64
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "nf4", N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    _, xr = synth.bf16_round(x)
+    got = _gemm(pkg, synth, W, x, N, torch_dev, splits=splits)
+    assert rel_err_inf(got, ob.linear_nt(orc, xr.reshape(x.shape), Wf)) <= TOL
+
+
+@pytest.mark.parametrize("M", [64, 512, 2048])
+def test_gemm_nf4_config_shape_sampled(pkg, synth, ob, orc, torch_dev, M):
+    """NF4 4096 x 4096, block 64 at the benchmark's M values; the oracle checks sampled rows and
+    columns (its full triple loop would take minutes)."""
+    rng = np.random.default_rng(400 + M)
+    N = K = 4096
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "nf4", N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    _, xr = synth.bf16_round(x)
+    got = _gemm(pkg, synth, W, x, N, torch_dev)
+    ms = rng.choice(M, 16, replace=False)
+    ns = rng.choice(N, 256, replace=False)
+    want = ob.linear_nt(orc, xr.reshape(x.shape)[ms], Wf[ns])
+    assert np.abs(got[np.ix_(ms, ns)] - want).max() / np.abs(want).max() <= TOL
+    # whole-output check against an fp64 matmul of the same dequantised weights
+    full = xr.reshape(x.shape).astype(np.float64) @ Wf.T.astype(np.float64)
+    assert rel_err_inf(got, full) <= TOL

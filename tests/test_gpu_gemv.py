@@ -1,0 +1,106 @@
+"""GPU parity of the decode dequant-GEMV (fp32 activations, fp32 accumulate) against the
+oracle: max relative error <= 2e-3 (the tolerance the path is specified with), measured
+element-wise with a floor of 1e-3 * max|y|."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err, rel_err_inf
+from gpu_util import make_weight, stream_ptr, to_dev
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _run(pkg, fn, W, x, N, dev, y0=None, W2=None):
+    M = x.shape[0]
+    d_x = to_dev(x, dev)
+    d_y = torch.zeros((M, N), dtype=torch.float32, device=dev) if y0 is None else to_dev(y0, dev)
+    if W2 is None:
+        pkg.check(fn(W.q, d_x.data_ptr(), d_y.data_ptr(), M, stream_ptr()), "gemv")
+    else:
+        pkg.check(fn(W.q, W2.q, d_x.data_ptr(), d_y.data_ptr(), M, stream_ptr()), "gemv_swiglu")
+    torch.cuda.synchronize()
+    return d_y.cpu().numpy()
+
+
+@pytest.mark.parametrize("kind", ["q8_0", "q4_0", "nf4"])
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 32])
+def test_gemv_matches_oracle(pkg, synth, ob, orc, torch_dev, kind, M):
+    rng = np.random.default_rng(100 + M)
+    N, K = 515, 1024                                  # ragged N: not a multiple of the row group
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    got = _run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev)
+    want = ob.linear_nt(orc, x, Wf)
+    assert rel_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("kind,N,K", [("q8_0", 4096, 4096), ("q4_0", 11008, 4096), ("q4_0", 4096, 11008), ("nf4", 4096, 4096)])
+def test_gemv_config_shapes_sampled_rows(pkg, synth, ob, orc, torch_dev, kind, N, K):
+    """Full benchmark shapes; the oracle checks 96 sampled output rows (it is a scalar loop)."""
+    rng = np.random.default_rng(7)
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    got = _run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev)
+    rows = rng.choice(N, 96, replace=False)
+    want = ob.linear_nt(orc, x, Wf[rows])
+    scale = np.abs(x @ Wf.T).max()
+    assert np.abs(got[:, rows] - want).max() / scale <= 1e-5
+    assert rel_err(got[:, rows], want) <= TOL
+
+
+def test_gemv_linearity_at_full_size(pkg, synth, ob, orc, torch_dev):
+    """Size-independent property at the full Q4_0 config: W.(a*x1 + x2) = a*W.x1 + W.x2."""
+    rng = np.random.default_rng(8)
+    N, K = 11008, 4096
+    W, _ = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    x1 = rng.standard_normal((1, K)).astype(np.float32)
+    x2 = rng.standard_normal((1, K)).astype(np.float32)
+    y1 = _run(pkg, pkg.lib.cmlb200_gemv, W, x1, N, torch_dev)
+    y2 = _run(pkg, pkg.lib.cmlb200_gemv, W, x2, N, torch_dev)
+    y3 = _run(pkg, pkg.lib.cmlb200_gemv, W, (np.float32(0.5) * x1 + x2), N, torch_dev)
+    assert rel_err_inf(y3, 0.5 * y1 + y2) <= 1e-5
+    # batching is row-independent: M=8 output rows equal eight M=1 calls
+    X = rng.standard_normal((8, K)).astype(np.float32)
+    Y = _run(pkg, pkg.lib.cmlb200_gemv, W, X, N, torch_dev)
+    for m in (0, 3, 7):
+        assert rel_err_inf(Y[m:m + 1], _run(pkg, pkg.lib.cmlb200_gemv, W, X[m:m + 1], N, torch_dev)) <= 1e-5
+
+
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+def test_gemv_accumulate_and_swiglu_epilogues(pkg, synth, ob, orc, torch_dev, kind):
+    rng = np.random.default_rng(9)
+    N, K, M = 300, 512, 2
+    Wg, Wgf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    Wu, Wuf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    y0 = rng.standard_normal((M, N)).astype(np.float32)
+    acc = _run(pkg, pkg.lib.cmlb200_gemv_accum, Wg, x, N, torch_dev, y0=y0)
+    assert rel_err(acc, y0 + ob.linear_nt(orc, x, Wgf)) <= TOL
+    g, u = ob.linear_nt(orc, x, Wgf), ob.linear_nt(orc, x, Wuf)
+    want = (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u
+    got = _run(pkg, pkg.lib.cmlb200_gemv_swiglu, Wg, x, N, torch_dev, W2=Wu)
+    assert rel_err(got, want) <= TOL
+
+
+def test_gemv_long_k_segments(pkg, synth, ob, orc, torch_dev):
+    """K larger than one shared-memory activation segment (the 70B down-projection has K = 28672)."""
+    rng = np.random.default_rng(10)
+    N, K = 64, 28672
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    for M in (1, 4):
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev), ob.linear_nt(orc, x, Wf)) <= TOL
+
+
+def test_gemv_matches_stored_reference_output(pkg, golden, torch_dev):
+    """The stored uop_linear output of the compiled reference on dequantised Q4_0 / Q8_0 weights."""
+    from gpu_util import DevQMat
+    for name, qtype in (("q8_0", 7), ("q4_0", 2)):
+        blocks = golden[f"{name}_blocks"].reshape(-1, 34 if qtype == 7 else 18).copy()
+        finite = np.isfinite(golden[f"{name}_dequant_bits"].view(np.float32).reshape(-1, 32)).all(1)
+        blocks[~finite, :2] = 0                       # the generator zeroed non-finite weights
+        W = DevQMat.from_gguf(pkg, torch_dev, qtype, np.ascontiguousarray(blocks.reshape(-1)), 8, 256)
+        got = _run(pkg, pkg.lib.cmlb200_gemv, W, golden[f"{name}_x"], 8, torch_dev)
+        assert rel_err_inf(got, golden[f"{name}_linear_y"]) <= 1e-5
