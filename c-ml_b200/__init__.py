@@ -20,7 +20,7 @@ lib = C.CDLL(str(LIB_PATH))
 class QMat(C.Structure):
     """cmlb200_qmat (include/cmlb200.h)."""
     _fields_ = [("type", C.c_int), ("rows", C.c_int), ("cols", C.c_int), ("block", C.c_int),
-                ("qs", C.c_void_p), ("scales", C.c_void_p)]
+                ("qs", C.c_void_p), ("scales", C.c_void_p), ("flags", C.c_int)]
 
 
 def _sig(name, restype, *argtypes):
@@ -49,6 +49,7 @@ _sig("cmlb200_device_sync", ci)
 _sig("cmlb200_qs_bytes", sz, ci, ci, ci, ci)
 _sig("cmlb200_scale_bytes", sz, ci, ci, ci, ci)
 _sig("cmlb200_repack_gguf", ci, ci, vp, ci, ci, vp, vp)
+_sig("cmlb200_scales_have_subnormals", ci, vp, sz)
 _sig("cmlb200_unrepack_gguf", ci, ci, vp, vp, ci, ci, vp)
 _sig("cmlb200_gguf_dequantize", ci, ci, vp, vp, sz, vp)
 _sig("cmlb200_dequant_qmat", ci, C.POINTER(QMat), vp, vp)

@@ -9,9 +9,16 @@
 // and rows are reduced with warp shuffles.
 #include "common.cuh"
 
+// gemv_dp4a.cu: the integer-dot kernels for Q4_0 / Q8_0 at small M
+int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint32_t* xq, float* y,
+                       int M, int epi, cudaStream_t st);
+size_t cmlb200_xq_bytes_(int M, int K);
+int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
+
 namespace {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+constexpr int kDp4aMaxM = 4;     // beyond this the per-row integer work outweighs the fp32 path
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
@@ -239,6 +246,7 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
+    if (W->type != CMLB200_NF4 && M <= kDp4aMaxM) return cmlb200_gemv_dp4a_(W, W2, x, nullptr, y, M, EPI, st);
     switch (W->type) {
         case CMLB200_Q8_0: return gemv_type<CMLB200_Q8_0, EPI>(W, W2, x, y, M, st);
         case CMLB200_Q4_0: return gemv_type<CMLB200_Q4_0, EPI>(W, W2, x, y, M, st);

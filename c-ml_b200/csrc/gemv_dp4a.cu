@@ -1,0 +1,355 @@
+// Decode GEMV for Q4_0 / Q8_0 at M <= 4, built to stay under the instruction-issue budget
+// that HBM speed leaves per weight (about 3 lane-operations per 4-bit weight on B200).
+//
+// A straight fp32 path needs ~4 operations per weight just to turn a nibble into a float and
+// multiply it. Here the activation vector is re-expressed once per launch as block-fixed-point:
+// for every 32-element block of x (the same blocks the weights are quantized in)
+//     x_k  ~=  s_b * X_k,   X_k a signed 21-bit integer,  s_b = max|x_block| / (2^20 - 1),
+// and X_k is split into three signed 7-bit digits X_k = d0*2^14 + d1*2^7 + d2 held as int8x4
+// words. The block dot product  sum_k q_k * X_k  then is three exact integer dot products on
+// dp4a (4 multiply-adds per lane-operation), recombined in int32 (Q4_0) or fp32 (Q8_0), and
+// scaled by d_b * s_b in fp32; blocks are accumulated in fp32. The only approximation is the
+// rounding of x to 21 bits relative to its block maximum (error <= 2^-21 * max|x_block| per
+// element, i.e. of the order of the fp32 rounding the reference's own sequential sum commits),
+// far inside the 2e-3 tolerance of this path. The Q4_0 "-8" offset is applied exactly as
+// -8 * sum_k X_k with the block sum precomputed.
+//
+// Replaces, like gemv.cu, C-ML's dequantize-then-fp32-matmul (src/core/gguf.c:271-295 +
+// src/ops/ir/execution.c:989-1052, 3090-3134).
+//
+// Work split: each warp owns a contiguous group of R weight rows; its lanes split K by
+// 32-element blocks (one 128-bit weight load per lane, row and step) and U steps are requested
+// together, so U*R 128-bit loads are in flight per lane. x digits live in shared memory and
+// are read once per R rows. Launched with programmatic dependent launch: weight rows are prefetched
+// before griddepcontrol.wait, activations are only read after it.
+#include "common.cuh"
+
+namespace {
+
+enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int XW = 28;            // words per block of x digits: 3 planes x 8 words + scale + block sum + 2 pad
+constexpr int XFULL = (1 << 20) - 1;
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint16_t ldg_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+// x[M][K] (fp32) -> xq[M][K/32][XW] (global scratch). One launch serves every GEMV that
+// consumes the same activations (q/k/v projections, gate/up).
+__global__ void __launch_bounds__(256) x_digits_kernel(const float* __restrict__ x, int M, int K, uint32_t* __restrict__ xq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int nblk = K / 32;
+    const int sub = threadIdx.x & 7;                  // 8 lanes share a block, 4 elements each
+    const int item = (blockIdx.x * 256 + threadIdx.x) >> 3;
+    if (item < nblk * M) {                            // whole groups of 8 lanes enter or skip together
+        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)item * 32 + sub * 4);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffu << (threadIdx.x & 24), amax, o));
+        const float inv = amax > 0.f ? (float)XFULL / amax : 0.f;
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
+        int xsum = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int X = __float2int_rn(e[i] * inv);
+            X = max(-XFULL, min(XFULL, X));
+            xsum += X;
+            const int d2 = ((X + 64) & 127) - 64;
+            const int X1 = (X - d2) >> 7;
+            const int d1 = ((X1 + 64) & 127) - 64;
+            const int d0 = (X1 - d1) >> 7;
+            w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+            w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+            w2 |= (uint32_t)(d2 & 0xFF) << (8 * i);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) xsum += __shfl_xor_sync(0xffu << (threadIdx.x & 24), xsum, o);
+        uint32_t* dst = xq + (size_t)item * XW;
+        dst[sub] = w0;
+        dst[8 + sub] = w1;
+        dst[16 + sub] = w2;
+        if (sub == 0) {
+            dst[24] = __float_as_uint(amax / (float)XFULL);
+            dst[25] = (uint32_t)xsum;
+        }
+    }
+}
+
+// Integer part of one block dot product, returned as a float: sum_k q_k * X_k (with the
+// Q4_0 offset applied).
+template <int TYPE>
+__device__ __forceinline__ float block_dot(const uint4& q0, const uint4& q1, const uint32_t* __restrict__ xb) {
+    // the three digit planes, 8 words each
+    const uint4 a0 = *reinterpret_cast<const uint4*>(xb), a1 = *reinterpret_cast<const uint4*>(xb + 4);
+    const uint4 b0 = *reinterpret_cast<const uint4*>(xb + 8), b1 = *reinterpret_cast<const uint4*>(xb + 12);
+    const uint4 c0 = *reinterpret_cast<const uint4*>(xb + 16), c1 = *reinterpret_cast<const uint4*>(xb + 20);
+    const int A[8] = {(int)a0.x, (int)a0.y, (int)a0.z, (int)a0.w, (int)a1.x, (int)a1.y, (int)a1.z, (int)a1.w};
+    const int B[8] = {(int)b0.x, (int)b0.y, (int)b0.z, (int)b0.w, (int)b1.x, (int)b1.y, (int)b1.z, (int)b1.w};
+    const int Cc[8] = {(int)c0.x, (int)c0.y, (int)c0.z, (int)c0.w, (int)c1.x, (int)c1.y, (int)c1.z, (int)c1.w};
+    int s0 = 0, s1 = 0, s2 = 0;
+    if (TYPE == CMLB200_Q4_0) {
+        const uint32_t w[4] = {q0.x, q0.y, q0.z, q0.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int lo = (int)(w[i] & 0x0F0F0F0Fu);          // elements 4i..4i+3
+            const int hi = (int)((w[i] >> 4) & 0x0F0F0F0Fu);   // elements 16+4i..16+4i+3
+            s0 = __dp4a(lo, A[i], s0); s0 = __dp4a(hi, A[4 + i], s0);
+            s1 = __dp4a(lo, B[i], s1); s1 = __dp4a(hi, B[4 + i], s1);
+            s2 = __dp4a(lo, Cc[i], s2); s2 = __dp4a(hi, Cc[4 + i], s2);
+        }
+        const int total = s0 * 16384 + s1 * 128 + s2 - 8 * (int)xb[25];   // |total| < 2^30
+        return (float)total;
+    } else {
+        const int w[8] = {(int)q0.x, (int)q0.y, (int)q0.z, (int)q0.w, (int)q1.x, (int)q1.y, (int)q1.z, (int)q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            s0 = __dp4a(w[i], A[i], s0);
+            s1 = __dp4a(w[i], B[i], s1);
+            s2 = __dp4a(w[i], Cc[i], s2);
+        }
+        return fmaf((float)s0, 16384.0f, (float)(s1 * 128 + s2));
+    }
+}
+
+// U block-steps of R rows are loaded together (U*R 128-bit loads in flight per lane); for
+// K = 4096 and Q4_0 that is the warp's entire share of its rows, requested in one burst.
+template <int TYPE, int MT, int R, int U, int EPI, bool QUIRK>
+__global__ void __launch_bounds__(THREADS)
+gemv_dp4a_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
+                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
+                 const uint32_t* __restrict__ xq, float* __restrict__ y, int N, int K, int m0, int rows_per_warp) {
+    extern __shared__ __align__(16) uint32_t xd[];     // [MT][K/32][XW]
+    constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int QB = (TYPE == CMLB200_Q8_0) ? 32 : 16;   // quant bytes per block
+    constexpr int QV = QB / 16;                            // 128-bit loads per block
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nblk = K / 32;
+    const size_t row_bytes = (size_t)nblk * QB;
+
+    // contiguous row range of this warp
+    const long long gw = (long long)blockIdx.x * WARPS + warp;
+    const int row_begin = (int)min((long long)N, gw * rows_per_warp);
+    const int row_end = min(N, row_begin + rows_per_warp);
+
+    uint4 q[NW][U][R][QV];
+    uint16_t dh[NW][U][R];
+    auto load_step = [&](int r0, int b0) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + 32 * u;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int row = r0 + r;
+                if (b < nblk && row < row_end) {
+                    const uint8_t* p = qs + (size_t)row * row_bytes + (size_t)b * QB;
+#pragma unroll
+                    for (int v = 0; v < QV; v++) q[0][u][r][v] = ldg_stream(p + 16 * v);
+                    dh[0][u][r] = ldg_u16(scales + (size_t)row * nblk + b);
+                    if (NW == 2) {
+                        const uint8_t* p2 = qs2 + (size_t)row * row_bytes + (size_t)b * QB;
+#pragma unroll
+                        for (int v = 0; v < QV; v++) q[1][u][r][v] = ldg_stream(p2 + 16 * v);
+                        dh[1][u][r] = ldg_u16(scales2 + (size_t)row * nblk + b);
+                    }
+                } else {
+#pragma unroll
+                    for (int a = 0; a < NW; a++) {
+#pragma unroll
+                        for (int v = 0; v < QV; v++) q[a][u][r][v] = make_uint4(0, 0, 0, 0);
+                        dh[a][u][r] = 0;        // scale 0 -> contributes nothing
+                    }
+                }
+            }
+        }
+    };
+
+    // Weights do not depend on the preceding kernel: request the first burst before the
+    // dependency wait; activations are only touched after it.
+    if (row_begin < row_end) load_step(row_begin, lane);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    {   // activation digits of rows m0..m0+MT-1: one contiguous run of the scratch
+        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)m0 * nblk * XW);
+        uint4* dst = reinterpret_cast<uint4*>(xd);
+        for (int i = threadIdx.x; i < MT * nblk * (XW / 4); i += THREADS) dst[i] = src[i];
+    }
+    __syncthreads();
+
+    for (int r0 = row_begin; r0 < row_end; r0 += R) {
+        float acc[NW][R][MT];
+#pragma unroll
+        for (int a = 0; a < NW; a++)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < MT; m++) acc[a][r][m] = 0.f;
+
+        for (int b0 = lane; b0 < nblk; b0 += 32 * U) {
+            if (r0 != row_begin || b0 != lane) load_step(r0, b0);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int b = min(b0 + 32 * u, nblk - 1);       // out-of-range steps carry scale 0
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    const uint32_t* xb = xd + ((size_t)m * nblk + b) * XW;
+                    const float xs = __uint_as_float(xb[24]);
+#pragma unroll
+                    for (int a = 0; a < NW; a++)
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            const float t = block_dot<TYPE>(q[a][u][r][0], q[a][u][r][QV - 1], xb);
+                            const float d = QUIRK ? cml_half_to_float(dh[a][u][r]) : __half2float(__ushort_as_half(dh[a][u][r]));
+                            acc[a][r][m] = fmaf(t, d * xs, acc[a][r][m]);
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < NW; a++)
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    float v = acc[a][r][m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    acc[a][r][m] = v;
+                }
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int row = r0 + r;
+                if (row < row_end) {
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        float* out = y + (size_t)(m0 + m) * N + row;
+                        if (EPI == EPI_STORE) *out = acc[0][r][m];
+                        else if (EPI == EPI_ACCUM) *out += acc[0][r][m];
+                        else {
+                            const float g = acc[0][r][m];
+                            *out = (g / (1.0f + expf(-g))) * acc[1][r][m];
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Scratch for the activation digits of the plain entry points: one fixed 1 MiB buffer per
+// device, allocated on first use and never moved (so captured CUDA graphs stay valid).
+constexpr size_t kScratchBytes = 1u << 20;
+uint32_t* g_scratch[16] = {};
+
+int library_scratch(uint32_t** out) {
+    int dev = 0;
+    CMLB_CUDA(cudaGetDevice(&dev));
+    CMLB_REQUIRE(dev >= 0 && dev < 16, "device index %d out of range", dev);
+    if (!g_scratch[dev]) CMLB_CUDA(cudaMalloc((void**)&g_scratch[dev], kScratchBytes));
+    *out = g_scratch[dev];
+    return CMLB200_OK;
+}
+
+template <typename Kern, typename... Args>
+int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CMLB_CUDA(cudaLaunchKernelEx(&cfg, kern, args...));
+    return CMLB200_OK;
+}
+
+template <int TYPE, int MT, int EPI, bool QUIRK>
+int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, float* y, int m0, cudaStream_t st) {
+    constexpr int R = (EPI == EPI_SWIGLU) ? 2 : 4;
+    constexpr int U = (TYPE == CMLB200_Q8_0) ? 1 : 2;
+    const int N = W->rows, K = W->cols;
+    const size_t smem = (size_t)(K / 32) * MT * XW * sizeof(uint32_t);
+    CMLB_REQUIRE(smem <= 200 * 1024, "cmlb200_gemv: K=%d too large for the shared-memory activation digits", K);
+    auto kern = gemv_dp4a_kernel<TYPE, MT, R, U, EPI, QUIRK>;
+    static size_t attr_smem = 0;
+    if (smem > 48 * 1024 && smem > attr_smem) {
+        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_smem = smem;
+    }
+    // One group of R rows per warp while that keeps the grid within ~8 CTAs per SM; beyond
+    // that, more rows per warp (a multiple of R).
+    int rows_per_warp = R;
+    const long long slots = (long long)cmlb_num_sms() * 8 * WARPS;
+    while ((long long)(N + rows_per_warp - 1) / rows_per_warp > slots) rows_per_warp += R;
+    const int nwarps = (N + rows_per_warp - 1) / rows_per_warp;
+    const int grid = (nwarps + WARPS - 1) / WARPS;
+    return launch_pdl(kern, dim3(grid), dim3(THREADS), smem, st, (const uint8_t*)W->qs, (const uint16_t*)W->scales,
+                      W2 ? (const uint8_t*)W2->qs : (const uint8_t*)nullptr,
+                      W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xq, y, N, K, m0, rows_per_warp);
+}
+
+template <int TYPE, int EPI, bool QUIRK>
+int run_type(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, float* y, int M, cudaStream_t st) {
+    int m0 = 0, rc = 0;
+    while (m0 < M && rc == 0) {
+        if (M - m0 >= 2) { rc = launch<TYPE, 2, EPI, QUIRK>(W, W2, xq, y, m0, st); m0 += 2; }
+        else { rc = launch<TYPE, 1, EPI, QUIRK>(W, W2, xq, y, m0, st); m0 += 1; }
+    }
+    return rc;
+}
+
+template <int TYPE, bool QUIRK>
+int run_epi(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, float* y, int M, int epi, cudaStream_t st) {
+    switch (epi) {
+        case EPI_STORE: return run_type<TYPE, EPI_STORE, QUIRK>(W, W2, xq, y, M, st);
+        case EPI_ACCUM: return run_type<TYPE, EPI_ACCUM, QUIRK>(W, W2, xq, y, M, st);
+        default: return run_type<TYPE, EPI_SWIGLU, QUIRK>(W, W2, xq, y, M, st);
+    }
+}
+
+}  // namespace
+
+size_t cmlb200_xq_bytes_(int M, int K) { return (size_t)M * (K / 32) * XW * sizeof(uint32_t); }
+
+// Activation digits for M rows of K floats into caller-provided scratch.
+int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st) {
+    const int items = M * (K / 32);
+    return launch_pdl(x_digits_kernel, dim3((items * 8 + 255) / 256), dim3(256), 0, st, x, M, K, xq);
+}
+
+// Internal entry used by gemv.cu's dispatcher (arguments already validated there).
+// epi: 0 store, 1 accumulate, 2 swiglu (W2 = up projection). xq = digits from
+// cmlb200_x_digits_, or NULL to compute them from x into the library's own scratch.
+int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint32_t* xq, float* y,
+                       int M, int epi, cudaStream_t st) {
+    if (!xq) {
+        uint32_t* ws = nullptr;
+        int rc = library_scratch(&ws);
+        if (rc) return rc;
+        CMLB_REQUIRE(cmlb200_xq_bytes_(M, W->cols) <= kScratchBytes, "cmlb200_gemv: M*K too large for the built-in activation scratch");
+        rc = cmlb200_x_digits_(x, M, W->cols, ws, st);
+        if (rc) return rc;
+        xq = ws;
+    }
+    const bool quirk = (W->flags & CMLB200_QMAT_SUBNORMAL_SCALES) || (W2 && (W2->flags & CMLB200_QMAT_SUBNORMAL_SCALES));
+    const bool q8 = W->type == CMLB200_Q8_0;
+    if (quirk) return q8 ? run_epi<CMLB200_Q8_0, true>(W, W2, xq, y, M, epi, st) : run_epi<CMLB200_Q4_0, true>(W, W2, xq, y, M, epi, st);
+    return q8 ? run_epi<CMLB200_Q8_0, false>(W, W2, xq, y, M, epi, st) : run_epi<CMLB200_Q4_0, false>(W, W2, xq, y, M, epi, st);
+}

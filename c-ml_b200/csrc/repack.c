@@ -71,3 +71,13 @@ int cmlb200_unrepack_gguf(int type, const void* h_qs, const void* h_scales, int 
     }
     return CMLB200_OK;
 }
+
+int cmlb200_scales_have_subnormals(const void* h_scales_f16, size_t count) {
+    const unsigned char* p = (const unsigned char*)h_scales_f16;
+    if (!p) return 0;
+    for (size_t i = 0; i < count; i++) {
+        const unsigned h = (unsigned)p[2 * i] | ((unsigned)p[2 * i + 1] << 8);
+        if ((h & 0x7C00u) == 0 && (h & 0x03FFu) != 0) return 1;
+    }
+    return 0;
+}

@@ -52,7 +52,15 @@ typedef struct cmlb200_qmat {
     int block;      /* 32 for Q4_0/Q8_0, the NF4 block size otherwise */
     void* qs;       /* device */
     void* scales;   /* device */
+    int flags;      /* CMLB200_QMAT_* bits */
 } cmlb200_qmat;
+
+/* Set when some fp16 block scale is subnormal. C-ML's fp16_to_fp32 widens a subnormal half to
+ * half its IEEE value (src/core/gguf_quant.c:35-36); matmul kernels reproduce that only when
+ * this flag is set, so the common case pays nothing for it. cmlb200_scales_have_subnormals()
+ * computes the flag from a host scale plane (or an array of GGUF blocks' scales). */
+#define CMLB200_QMAT_SUBNORMAL_SCALES 1
+int cmlb200_scales_have_subnormals(const void* h_scales_f16, size_t count);
 
 const char* cmlb200_last_error(void);
 

@@ -95,6 +95,9 @@ def load_ref():
         _sig(lib, "ref_nf4_quantize", ci, vp, sz, ci, vp, vp)
         _sig(lib, "ref_nf4_dequantize", ci, vp, vp, ci, ci, sz, vp)
         _sig(lib, "ref_linear", ci, vp, vp, ci, ci, ci, vp)
+        _sig(lib, "ref_weight_create", vp, vp, ci, ci)
+        _sig(lib, "ref_weight_free", None, vp)
+        _sig(lib, "ref_linear_resident", ci, vp, vp, ci, vp)
         _sig(lib, "ref_qlora_forward", ci, vp, ci, ci, ci, vp, vp, vp, ci, ci, cf, vp, vp, vp)
         _sig(lib, "ref_llama_create", vp, C.POINTER(RefLlamaCfg), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp)
         _sig(lib, "ref_llama_forward", ci, vp, vp, ci, vp)

@@ -7,9 +7,11 @@
  * the reference's headers and linked with oracle/_ref/libcml_ref.so (see
  * oracle/Makefile); it contains no C-ML source.
  */
+#include <fcntl.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 #include "cml.h"
 #include "core/gguf_quant.h"
@@ -31,6 +33,21 @@ static Tensor* t_from(const float* data, int ndim, const int* shape) {
     for (int i = 0; i < ndim; i++) sh[i] = shape[i];
     TensorConfig c = f32cfg();
     return tensor_from_data(data, sh, ndim, &c);
+}
+
+/* The reference prints "No BLAS library found" to stderr on every matmul when no BLAS
+ * shared object is installed (src/backend/blas.c:250, retried from src/ops/ir/execution.c:220).
+ * The wrappers that reach a matmul silence fd 2 for the duration of the call. */
+static int g_saved_err = -1;
+static void quiet_begin(void) {
+    fflush(stderr);
+    g_saved_err = dup(2);
+    int nul = open("/dev/null", O_WRONLY);
+    if (nul >= 0) { dup2(nul, 2); close(nul); }
+}
+static void quiet_end(void) {
+    fflush(stderr);
+    if (g_saved_err >= 0) { dup2(g_saved_err, 2); close(g_saved_err); g_saved_err = -1; }
 }
 
 int ref_init(void) { return cml_init(); }
@@ -83,14 +100,38 @@ int ref_linear(const float* x, const float* W, int M, int N, int K, float* y) {
     Tensor* tx = t_from(x, 2, xs);
     Tensor* tw = t_from(W, 2, ws);
     if (!tx || !tw) return -1;
+    quiet_begin();
     Tensor* ty = uop_linear(tx, tw, NULL);
-    if (!ty) return -1;
-    float* d = (float*)tensor_data_ptr(ty);
+    float* d = ty ? (float*)tensor_data_ptr(ty) : NULL;
+    quiet_end();
     if (!d) return -1;
     memcpy(y, d, (size_t)M * N * sizeof(float));
     tensor_free(ty);
     tensor_free(tx);
     tensor_free(tw);
+    return 0;
+}
+
+/* The same call on a weight tensor that stays resident between calls, as the reference's
+ * own forward pass has it (weights are Tensor objects created once at load). */
+void* ref_weight_create(const float* W, int N, int K) {
+    int ws[2] = {N, K};
+    return t_from(W, 2, ws);
+}
+void ref_weight_free(void* w) { if (w) tensor_free((Tensor*)w); }
+int ref_linear_resident(const float* x, void* w, int M, float* y) {
+    Tensor* tw = (Tensor*)w;
+    int xs[2] = {M, tw->shape[1]};
+    Tensor* tx = t_from(x, 2, xs);
+    if (!tx) return -1;
+    quiet_begin();
+    Tensor* ty = uop_linear(tx, tw, NULL);
+    float* d = ty ? (float*)tensor_data_ptr(ty) : NULL;
+    quiet_end();
+    if (!d) return -1;
+    memcpy(y, d, (size_t)M * tw->shape[0] * sizeof(float));
+    tensor_free(ty);
+    tensor_free(tx);
     return 0;
 }
 
@@ -177,9 +218,10 @@ void* ref_llama_create(const RefLlamaCfg* c, const float* embed, const float* fi
 /* cml_llama_forward (src/nn/llama.c:550); logits [seq, vocab] copied out. */
 int ref_llama_forward(void* model, const int* tokens, int seq, float* logits) {
     CMLLLaMAModel* m = (CMLLLaMAModel*)model;
+    quiet_begin();
     Tensor* t = cml_llama_forward(m, tokens, seq);
-    if (!t) return -1;
-    float* d = (float*)tensor_data_ptr(t);
+    float* d = t ? (float*)tensor_data_ptr(t) : NULL;
+    quiet_end();
     if (!d) return -1;
     memcpy(logits, d, (size_t)seq * m->config.vocab_size * sizeof(float));
     return 0; /* the logits tensor is left to the IR context, as the reference's own callers do mid-sequence */

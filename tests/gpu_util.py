@@ -20,7 +20,11 @@ class DevQMat:
     def __init__(self, pkg, dev, qtype, rows, cols, qs, scales, block=32):
         self.qs = to_dev(qs, dev)
         self.scales = to_dev(scales, dev)
-        self.q = pkg.QMat(qtype, rows, cols, block, self.qs.data_ptr(), self.scales.data_ptr())
+        flags = 0
+        if qtype != pkg.NF4:
+            sc = np.ascontiguousarray(scales)
+            flags = pkg.lib.cmlb200_scales_have_subnormals(pkg.np_ptr(sc), sc.size // 2)
+        self.q = pkg.QMat(qtype, rows, cols, block, self.qs.data_ptr(), self.scales.data_ptr(), flags)
 
     @classmethod
     def from_gguf(cls, pkg, dev, qtype, blocks, rows, cols):

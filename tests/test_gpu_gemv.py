@@ -104,3 +104,22 @@ def test_gemv_matches_stored_reference_output(pkg, golden, torch_dev):
         W = DevQMat.from_gguf(pkg, torch_dev, qtype, np.ascontiguousarray(blocks.reshape(-1)), 8, 256)
         got = _run(pkg, pkg.lib.cmlb200_gemv, W, golden[f"{name}_x"], 8, torch_dev)
         assert rel_err_inf(got, golden[f"{name}_linear_y"]) <= 1e-5
+
+
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+def test_gemv_with_subnormal_scales_follows_reference_quirk(pkg, synth, ob, orc, torch_dev, kind):
+    """Blocks whose fp16 scale is subnormal widen to half the IEEE value in C-ML; the matmul
+    kernels follow when the weight carries CMLB200_QMAT_SUBNORMAL_SCALES."""
+    from gpu_util import DevQMat
+    rng = np.random.default_rng(21)
+    N, K = 64, 256
+    qtype, bb = (7, 34) if kind == "q8_0" else (2, 18)
+    blocks = (synth.q8_0_blocks if kind == "q8_0" else synth.q4_0_blocks)(rng, N, K).reshape(-1, bb)
+    blocks[:, :2] = rng.integers(1, 0x0400, len(blocks), dtype=np.uint16).view(np.uint8).reshape(-1, 2)  # all subnormal
+    blocks = np.ascontiguousarray(blocks.reshape(-1))
+    W = DevQMat.from_gguf(pkg, torch_dev, qtype, blocks, N, K)
+    assert W.q.flags == 1
+    Wf = ob.dequant_blocks(orc, qtype, blocks, N * K).reshape(N, K)
+    for M in (1, 2, 8):
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev), ob.linear_nt(orc, x, Wf)) <= TOL
