@@ -167,6 +167,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--copies", type=int, default=COPIES)
+    ap.add_argument("--path", default="tiles", choices=["tiles", "planes"],
+                    help="tiles: tcgen05 integer tensor-core GEMV over tile-major weights; planes: CUDA-core GEMV")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
     args = ap.parse_args()
@@ -194,15 +196,23 @@ def main():
     weights, keep = [], []
     for c in range(copies):
         blocks = synth.q4_0_blocks(rng, N_ROWS, K_COLS)
-        qs, sc = pkg.repack_gguf(pkg.Q4_0, blocks, N_ROWS, K_COLS)
-        d_qs, d_sc = torch.from_numpy(qs).to(dev), torch.from_numpy(sc).to(dev)
-        keep.append((d_qs, d_sc))
-        weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_qs.data_ptr(), d_sc.data_ptr()))
+        if args.path == "tiles":
+            d_t = torch.from_numpy(pkg.repack_tiles(pkg.Q4_0, blocks, N_ROWS, K_COLS)).to(dev)
+            keep.append(d_t)
+            weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_t.data_ptr(), None, 0))
+        else:
+            qs, sc = pkg.repack_gguf(pkg.Q4_0, blocks, N_ROWS, K_COLS)
+            d_qs, d_sc = torch.from_numpy(qs).to(dev), torch.from_numpy(sc).to(dev)
+            keep.append((d_qs, d_sc))
+            weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_qs.data_ptr(), d_sc.data_ptr(), 0))
     x_host = {M: torch.from_numpy(rng.standard_normal((M, K_COLS)).astype(np.float32)).pin_memory() for M in (1,) + EXTRA_M}
     x_dev = {M: x_host[M].to(dev) for M in x_host}
     y_dev = {M: torch.empty((M, N_ROWS), dtype=torch.float32, device=dev) for M in x_host}
     y_host = {M: torch.empty((M, N_ROWS), dtype=torch.float32).pin_memory() for M in x_host}
-    gemv = pkg.lib.cmlb200_gemv
+    if args.path == "tiles":
+        gemv = lambda W, xp, yp, M, sp: pkg.lib.cmlb200_gemv_tiles(W, xp, yp, M, 0, sp)
+    else:
+        gemv = pkg.lib.cmlb200_gemv
     def sweep(M, sweeps=SWEEPS_PER_STEP):
         xp, yp = x_dev[M].data_ptr(), y_dev[M].data_ptr()
         for _ in range(sweeps):

@@ -57,6 +57,11 @@ _sig("cmlb200_dequantize_nf4", ci, vp, vp, ci, ci, sz, vp, vp)
 _sig("cmlb200_gemv", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_accum", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_swiglu", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, ci, vp)
+_sig("cmlb200_tiles_bytes", sz, ci, ci, ci)
+_sig("cmlb200_repack_tiles", ci, ci, vp, ci, ci, vp)
+_sig("cmlb200_unrepack_tiles", ci, ci, vp, ci, ci, vp)
+_sig("cmlb200_gemv_tiles", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
+_sig("cmlb200_gemv_tiles_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_gemm_bf16", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemm_bf16_splitk", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemm_status", ci, C.POINTER(ci), ci)
@@ -84,3 +89,11 @@ def repack_gguf(qtype: int, blocks, rows: int, cols: int):
     sc = np.empty(lib.cmlb200_scale_bytes(qtype, rows, cols, 32), np.uint8)
     check(lib.cmlb200_repack_gguf(qtype, np_ptr(blocks), rows, cols, np_ptr(qs), np_ptr(sc)), "repack")
     return qs, sc
+
+
+def repack_tiles(qtype: int, blocks, rows: int, cols: int):
+    """Host repack of GGUF blocks into the tile-major buffer of the tensor-core decode path."""
+    import numpy as np
+    out = np.empty(lib.cmlb200_tiles_bytes(qtype, rows, cols), np.uint8)
+    check(lib.cmlb200_repack_tiles(qtype, np_ptr(blocks), rows, cols, np_ptr(out)), "repack_tiles")
+    return out

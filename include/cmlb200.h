@@ -118,6 +118,24 @@ int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const fl
 /* y += x . W^T (residual add fused; src/nn/llama.c:523-530 and :538-543). */
 int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
 
+/* ---- tile-major weights for the tensor-core decode path ----------------------------------
+ * The same GGUF blocks regrouped as "units": for row tile t (128 rows, the last one zero
+ * padded) and block column b one contiguous unit holds the 128 rows' quants of block b
+ * followed by their 128 fp16 scales (Q4_0: 128x16 B + 256 B = 2304 B; Q8_0: 128x16 B for
+ * elements 0..15, 128x16 B for elements 16..31, + 256 B = 4352 B); units are ordered [t][b].
+ * Content is unchanged: cmlb200_unrepack_tiles restores the file bytes exactly. */
+size_t cmlb200_tiles_bytes(int type, int rows, int cols);
+int cmlb200_repack_tiles(int type, const void* h_blocks, int rows, int cols, void* h_tiles);
+int cmlb200_unrepack_tiles(int type, const void* h_tiles, int rows, int cols, void* h_blocks);
+/* y[M, rows] = x . dequant(W)^T (accumulate == 0) or y += ... (accumulate != 0) for M <= 32 on
+ * the integer tensor cores; W->qs points at the tile-major buffer, W->scales is ignored,
+ * cols must be a multiple of 128. Same C-ML lines replaced as cmlb200_gemv. The activation
+ * digits pass through a scratch buffer owned by the library (one per device): calls on
+ * different streams of one device must not overlap. */
+int cmlb200_gemv_tiles(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, int accumulate, void* stream);
+/* Like cmlb200_gemm_status, for the kernel behind cmlb200_gemv_tiles. */
+int cmlb200_gemv_tiles_status(int* status, int reset);
+
 /* Prefill path, M >= 1 (any M; built for M >= 64): bf16 activations, weights
  * dequantised to bf16 tiles in shared memory, tcgen05 MMAs accumulating fp32
  * in tensor memory, bf16 output. Same reference lines as cmlb200_gemv.

@@ -75,3 +75,18 @@ def test_compute_entry_points_validate_before_launching(pkg):
     W = pkg.QMat(pkg.Q4_0, 8, 96, 32, fake, fake)            # tensor-core path wants cols % 64 == 0
     assert lib.cmlb200_gemm_bf16(W, fake, fake, 64, None) == -1
     assert lib.cmlb200_gemm_bf16(pkg.QMat(pkg.Q4_0, 8, 128, 32, fake, fake), fake, fake, 0, None) == -1
+
+
+@pytest.mark.parametrize("qtype", [7, 2])
+def test_tile_major_repack_is_a_bijection(pkg, synth, qtype):
+    rng = np.random.default_rng(6)
+    rows, cols = 200, 256                     # two row tiles, the second partial
+    blocks = (synth.q8_0_blocks if qtype == 7 else synth.q4_0_blocks)(rng, rows, cols)
+    tiles = pkg.repack_tiles(qtype, blocks, rows, cols)
+    unit = 4352 if qtype == 7 else 2304
+    assert tiles.size == unit * 2 * (cols // 32)
+    back = np.zeros_like(blocks)
+    pkg.check(pkg.lib.cmlb200_unrepack_tiles(qtype, pkg.np_ptr(tiles), rows, cols, pkg.np_ptr(back)))
+    assert np.array_equal(back, blocks)
+    assert pkg.lib.cmlb200_repack_tiles(qtype, pkg.np_ptr(blocks), rows, 48, pkg.np_ptr(tiles)) == -1
+    assert pkg.lib.cmlb200_tiles_bytes(100, rows, cols) == 0
