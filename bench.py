@@ -167,8 +167,6 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--copies", type=int, default=COPIES)
-    ap.add_argument("--path", default="tiles", choices=["tiles", "planes"],
-                    help="tiles: tcgen05 integer tensor-core GEMV over tile-major weights; planes: CUDA-core GEMV")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
     args = ap.parse_args()
@@ -196,23 +194,17 @@ def main():
     weights, keep = [], []
     for c in range(copies):
         blocks = synth.q4_0_blocks(rng, N_ROWS, K_COLS)
-        if args.path == "tiles":
-            d_t = torch.from_numpy(pkg.repack_tiles(pkg.Q4_0, blocks, N_ROWS, K_COLS)).to(dev)
-            keep.append(d_t)
-            weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_t.data_ptr(), None, 0))
-        else:
-            qs, sc = pkg.repack_gguf(pkg.Q4_0, blocks, N_ROWS, K_COLS)
-            d_qs, d_sc = torch.from_numpy(qs).to(dev), torch.from_numpy(sc).to(dev)
-            keep.append((d_qs, d_sc))
-            weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_qs.data_ptr(), d_sc.data_ptr(), 0))
+        qs, sc = pkg.repack_gguf(pkg.Q4_0, blocks, N_ROWS, K_COLS)
+        d_qs, d_sc = torch.from_numpy(qs).to(dev), torch.from_numpy(sc).to(dev)
+        d_t = torch.from_numpy(pkg.repack_tiles(pkg.Q4_0, blocks, N_ROWS, K_COLS)).to(dev)
+        keep.append((d_qs, d_sc, d_t))
+        weights.append(pkg.QMat(pkg.Q4_0, N_ROWS, K_COLS, 32, d_qs.data_ptr(), d_sc.data_ptr(), 0, d_t.data_ptr()))
     x_host = {M: torch.from_numpy(rng.standard_normal((M, K_COLS)).astype(np.float32)).pin_memory() for M in (1,) + EXTRA_M}
     x_dev = {M: x_host[M].to(dev) for M in x_host}
     y_dev = {M: torch.empty((M, N_ROWS), dtype=torch.float32, device=dev) for M in x_host}
     y_host = {M: torch.empty((M, N_ROWS), dtype=torch.float32).pin_memory() for M in x_host}
-    if args.path == "tiles":
-        gemv = lambda W, xp, yp, M, sp: pkg.lib.cmlb200_gemv_tiles(W, xp, yp, M, 0, sp)
-    else:
-        gemv = pkg.lib.cmlb200_gemv
+    gemv = pkg.lib.cmlb200_gemv       # M <= 2: CUDA-core integer-dot kernel; M >= 3: tcgen05 kind::i8 kernel
+
     def sweep(M, sweeps=SWEEPS_PER_STEP):
         xp, yp = x_dev[M].data_ptr(), y_dev[M].data_ptr()
         for _ in range(sweeps):
@@ -334,7 +326,7 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "host fp32 activations -> H2D -> GEMV -> D2H host result, synchronised per call; weights resident"},
-            "gpu_launches": timed_launches,
+            "gpu_launches": 2 * timed_launches,   # activation-digit kernel + GEMV kernel per call
             "clocks": clocks,
         }
         print(json.dumps(line))

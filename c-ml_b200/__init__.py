@@ -20,7 +20,7 @@ lib = C.CDLL(str(LIB_PATH))
 class QMat(C.Structure):
     """cmlb200_qmat (include/cmlb200.h)."""
     _fields_ = [("type", C.c_int), ("rows", C.c_int), ("cols", C.c_int), ("block", C.c_int),
-                ("qs", C.c_void_p), ("scales", C.c_void_p), ("flags", C.c_int)]
+                ("qs", C.c_void_p), ("scales", C.c_void_p), ("flags", C.c_int), ("tiles", C.c_void_p)]
 
 
 def _sig(name, restype, *argtypes):

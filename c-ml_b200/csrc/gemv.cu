@@ -15,10 +15,13 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
 size_t cmlb200_xq_bytes_(int M, int K);
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 
+// gemv_tc.cu: tcgen05 integer tensor-core path over the tile-major copy of the weight
+int cmlb200_gemv_tc_(const cmlb200_qmat* W, const float* x, float* y, int M, int accumulate, cudaStream_t st);
+
 namespace {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
-constexpr int kDp4aMaxM = 4;     // beyond this the per-row integer work outweighs the fp32 path
+constexpr int kDp4aMaxM = 2;     // up to here the CUDA-core integer-dot path is the faster one
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
@@ -246,7 +249,10 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
-    if (W->type != CMLB200_NF4 && M <= kDp4aMaxM) return cmlb200_gemv_dp4a_(W, W2, x, nullptr, y, M, EPI, st);
+    if (W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 &&
+        ((uintptr_t)y & 15) == 0)
+        return cmlb200_gemv_tc_(W, x, y, M, EPI == EPI_ACCUM, st);
+    if (W->type != CMLB200_NF4 && M <= 4) return cmlb200_gemv_dp4a_(W, W2, x, nullptr, y, M, EPI, st);
     switch (W->type) {
         case CMLB200_Q8_0: return gemv_type<CMLB200_Q8_0, EPI>(W, W2, x, y, M, st);
         case CMLB200_Q4_0: return gemv_type<CMLB200_Q4_0, EPI>(W, W2, x, y, M, st);

@@ -53,6 +53,8 @@ typedef struct cmlb200_qmat {
     void* qs;       /* device */
     void* scales;   /* device */
     int flags;      /* CMLB200_QMAT_* bits */
+    void* tiles;    /* device, optional: the same blocks in the tile-major layout (see
+                     * cmlb200_repack_tiles); lets cmlb200_gemv use the tensor-core path for M >= 3 */
 } cmlb200_qmat;
 
 /* Set when some fp16 block scale is subnormal. C-ML's fp16_to_fp32 widens a subnormal half to

@@ -17,19 +17,22 @@ def stream_ptr():
 class DevQMat:
     """A quantized weight uploaded in the repacked device layout."""
 
-    def __init__(self, pkg, dev, qtype, rows, cols, qs, scales, block=32):
+    def __init__(self, pkg, dev, qtype, rows, cols, qs, scales, block=32, tiles=None):
         self.qs = to_dev(qs, dev)
         self.scales = to_dev(scales, dev)
+        self.tiles = to_dev(tiles, dev) if tiles is not None else None
         flags = 0
         if qtype != pkg.NF4:
             sc = np.ascontiguousarray(scales)
             flags = pkg.lib.cmlb200_scales_have_subnormals(pkg.np_ptr(sc), sc.size // 2)
-        self.q = pkg.QMat(qtype, rows, cols, block, self.qs.data_ptr(), self.scales.data_ptr(), flags)
+        self.q = pkg.QMat(qtype, rows, cols, block, self.qs.data_ptr(), self.scales.data_ptr(), flags,
+                          self.tiles.data_ptr() if self.tiles is not None else None)
 
     @classmethod
     def from_gguf(cls, pkg, dev, qtype, blocks, rows, cols):
         qs, sc = pkg.repack_gguf(qtype, blocks, rows, cols)
-        return cls(pkg, dev, qtype, rows, cols, qs, sc)
+        tiles = pkg.repack_tiles(qtype, blocks, rows, cols) if cols % 128 == 0 else None
+        return cls(pkg, dev, qtype, rows, cols, qs, sc, tiles=tiles)
 
     @classmethod
     def from_nf4(cls, pkg, dev, packed, scales, rows, cols, block):

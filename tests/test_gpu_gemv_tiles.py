@@ -18,7 +18,7 @@ def _weight(pkg, synth, ob, orc, dev, rng, kind, N, K):
     blocks = (synth.q8_0_blocks if kind == "q8_0" else synth.q4_0_blocks)(rng, N, K)
     tiles = to_dev(pkg.repack_tiles(qtype, blocks, N, K), dev)
     Wf = ob.dequant_blocks(orc, qtype, blocks, N * K).reshape(N, K)
-    return pkg.QMat(qtype, N, K, 32, tiles.data_ptr(), None, 0), tiles, Wf
+    return pkg.QMat(qtype, N, K, 32, tiles.data_ptr(), None, 0, None), tiles, Wf
 
 
 def _status(pkg):
