@@ -97,3 +97,122 @@ def repack_tiles(qtype: int, blocks, rows: int, cols: int):
     out = np.empty(lib.cmlb200_tiles_bytes(qtype, rows, cols), np.uint8)
     check(lib.cmlb200_repack_tiles(qtype, np_ptr(blocks), rows, cols, np_ptr(out)), "repack_tiles")
     return out
+
+
+# ---- the C-ML-compatible C11 host API (include/cml_quant_api.h) ---------------------------------
+class Tensor(C.Structure):
+    pass
+
+
+Tensor._fields_ = [("shape", C.POINTER(C.c_int)), ("ndim", C.c_int), ("numel", C.c_size_t), ("dtype", C.c_int),
+                   ("device", C.c_int), ("ir_node", C.c_void_p), ("ir_context", C.c_void_p), ("saved_ir_node", C.c_void_p),
+                   ("saved_ir_context", C.c_void_p), ("is_executed", C.c_bool), ("data", C.c_void_p), ("owns_data", C.c_bool),
+                   ("from_buffer_cache", C.c_bool), ("requires_grad", C.c_bool), ("grad", C.c_void_p), ("ref_count", C.c_int),
+                   ("base", C.c_void_p), ("strides", C.POINTER(C.c_size_t)), ("storage_offset", C.c_size_t),
+                   ("is_contiguous", C.c_bool), ("buffer_handle", C.c_void_p), ("user_data", C.c_void_p)]
+
+
+class TensorConfig(C.Structure):
+    _fields_ = [("dtype", C.c_int), ("device", C.c_int), ("has_dtype", C.c_bool), ("has_device", C.c_bool)]
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("vocab_size", "hidden_size", "intermediate_size", "num_layers", "num_heads",
+                                       "num_kv_heads", "max_seq_len")] + \
+               [("rope_theta", C.c_float), ("rms_norm_eps", C.c_float), ("tensor_parallel_size", C.c_int),
+                ("tensor_parallel_rank", C.c_int)]
+
+
+class LlamaModel(C.Structure):
+    _fields_ = [("config", LlamaConfig), ("embed_tokens", C.POINTER(Tensor)), ("norm", C.POINTER(Tensor)),
+                ("lm_head", C.POINTER(Tensor)), ("layers", C.c_void_p), ("num_layers", C.c_int), ("tokenizer", C.c_void_p),
+                ("weights_loaded", C.c_bool), ("current_seq_len", C.c_int)]
+
+
+class GenerationConfig(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int), ("max_new_tokens", C.c_int),
+                ("eos_token_id", C.c_int), ("do_sample", C.c_bool)]
+
+
+class NF4Tensor(C.Structure):
+    _fields_ = [("packed_data", C.POINTER(Tensor)), ("scales", C.POINTER(C.c_float)), ("num_scales", C.c_int),
+                ("block_size", C.c_int), ("original_numel", C.c_size_t), ("original_shape", C.POINTER(C.c_int)),
+                ("original_ndim", C.c_int)]
+
+
+class QLoRALinear(C.Structure):
+    _fields_ = [("in_features", C.c_int), ("out_features", C.c_int), ("rank", C.c_int), ("alpha", C.c_float),
+                ("scaling", C.c_float), ("base_weight_nf4", C.POINTER(NF4Tensor)), ("lora_A", C.POINTER(Tensor)),
+                ("lora_B", C.POINTER(Tensor)), ("enable_double_quant", C.c_bool)]
+
+
+TP = C.POINTER(Tensor)
+MP = C.POINTER(LlamaModel)
+_sig("cml_set_log_level", None, ci)
+_sig("tensor_from_data", TP, vp, C.POINTER(ci), ci, C.POINTER(TensorConfig))
+_sig("tensor_zeros", TP, C.POINTER(ci), ci, C.POINTER(TensorConfig))
+_sig("tensor_free", None, TP)
+_sig("tensor_data_ptr", vp, TP)
+_sig("gguf_type_is_quantized", C.c_bool, ci)
+_sig("gguf_quant_block_size", ci, ci)
+_sig("gguf_quant_type_size", sz, ci)
+_sig("gguf_dequantize", ci, ci, vp, vp, sz)
+_sig("gguf_open_read", vp, C.c_char_p)
+_sig("gguf_close", None, vp)
+_sig("gguf_get_num_tensors", ci, vp)
+_sig("gguf_get_tensor_name", C.c_char_p, vp, ci)
+_sig("gguf_read_tensor", TP, vp, C.c_char_p)
+_sig("cml_quantize_nf4", TP, TP, ci, C.POINTER(C.POINTER(C.c_float)), C.POINTER(ci))
+_sig("cml_dequantize_nf4", TP, TP, C.POINTER(C.c_float), ci, ci, sz)
+_sig("cml_nf4_tensor_create", C.POINTER(NF4Tensor), TP, ci)
+_sig("cml_nf4_tensor_free", None, C.POINTER(NF4Tensor))
+_sig("cml_nf4_tensor_dequantize", TP, C.POINTER(NF4Tensor))
+_sig("cml_qlora_linear_create", C.POINTER(QLoRALinear), TP, ci, C.c_float, ci)
+_sig("cml_qlora_linear_free", None, C.POINTER(QLoRALinear))
+_sig("cml_qlora_linear_forward", TP, C.POINTER(QLoRALinear), TP)
+_sig("cml_qlora_linear_invalidate", None, C.POINTER(QLoRALinear))
+_sig("cml_qlora_memory_usage", sz, C.POINTER(QLoRALinear))
+_sig("cml_qlora_full_memory_usage", sz, ci, ci)
+_sig("cml_llama_config_7b", LlamaConfig)
+_sig("cml_llama_config_13b", LlamaConfig)
+_sig("cml_llama_config_70b", LlamaConfig)
+_sig("cml_generation_default_config", GenerationConfig)
+_sig("cml_llama_create", MP, C.POINTER(LlamaConfig))
+_sig("cml_llama_free", None, MP)
+_sig("cml_llama_load_gguf", ci, MP, C.c_char_p)
+_sig("cml_llama_forward", TP, MP, vp, ci)
+_sig("cml_llama_forward_batch", TP, MP, vp, ci)
+_sig("cml_llama_prefill_sequence", ci, MP, ci, vp, ci)
+_sig("cml_llama_decode_greedy", ci, MP, vp, ci, ci, vp, C.POINTER(C.c_float))
+_sig("cml_llama_generate", vp, MP, C.c_char_p, C.POINTER(GenerationConfig))
+_sig("cml_generation_result_free", None, vp)
+_sig("cml_llama_sample_token", ci, TP, C.POINTER(GenerationConfig))
+_sig("cml_llama_reset", None, MP)
+_sig("cml_llama_print_config", None, C.POINTER(LlamaConfig))
+_sig("cml_llama_set_options", ci, MP, ci, ci)
+_sig("cml_llama_tp_unique_id", ci, vp)
+_sig("cml_llama_tp_init", ci, MP, vp, ci)
+REFERENCE_QUIRKS, KV_FP32, ALL_LOGITS_FP32 = 1, 2, 4
+
+
+def tensor_to_numpy(tp, free=True):
+    """Copy a host Tensor* returned by the library into a numpy array (fp32 / uint8 / fp16)."""
+    import numpy as np
+    t = tp.contents
+    shape = [t.shape[i] for i in range(t.ndim)]
+    np_dtype = {0: np.float32, 8: np.uint8, 5: np.float16, 2: np.int32}[t.dtype]
+    n = int(np.prod(shape))
+    arr = np.frombuffer((C.c_char * (n * np.dtype(np_dtype).itemsize)).from_address(t.data), dtype=np_dtype).reshape(shape).copy()
+    if free:
+        lib.tensor_free(tp)
+    return arr
+
+
+def numpy_to_tensor(a):
+    """A host Tensor* owning a copy of `a` (fp32 or uint8); release with lib.tensor_free."""
+    import numpy as np
+    a = np.ascontiguousarray(a)
+    dt = {np.dtype(np.float32): 0, np.dtype(np.uint8): 8}[a.dtype]
+    cfg = TensorConfig(dt, 0, True, True)
+    shape = (C.c_int * a.ndim)(*a.shape)
+    return lib.tensor_from_data(np_ptr(a), shape, a.ndim, C.byref(cfg))

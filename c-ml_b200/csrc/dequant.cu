@@ -80,6 +80,47 @@ __global__ void dequant_nf4_kernel(const uint8_t* __restrict__ packed, const flo
     }
 }
 
+// NF4 quantisation (src/core/quantization.c:213-312), two passes: block absmax, then codes.
+__global__ void nf4_absmax_kernel(const float* __restrict__ x, size_t numel, int block, float* __restrict__ scales, size_t nblocks) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
+        size_t s = b * (size_t)block, e = s + (size_t)block;
+        if (e > numel) e = numel;
+        float amax = 0.f;
+        for (size_t i = s; i < e; i++) { const float a = fabsf(x[i]); if (a > amax) amax = a; }
+        scales[b] = amax < 1e-10f ? 1e-10f : amax;
+    }
+}
+__device__ __forceinline__ int nf4_nearest(float v) {
+    int best = 0;
+    float bd = fabsf(v - kNF4[0]);
+#pragma unroll
+    for (int c = 1; c < 16; c++) {
+        const float d = fabsf(v - kNF4[c]);
+        if (d < bd) { bd = d; best = c; }
+    }
+    return best;
+}
+__global__ void nf4_codes_kernel(const float* __restrict__ x, size_t numel, int block, const float* __restrict__ scales,
+                                 uint8_t* __restrict__ packed) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t nbytes = (numel + 1) / 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += stride) {
+        int idx[2] = {0, 0};                               // the pad element of an odd tensor keeps code 0
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const size_t e = 2 * i + h;
+            if (e < numel) {
+                float v = __fdiv_rn(x[e], scales[e / (size_t)block]);
+                if (v > 1.0f) v = 1.0f;
+                if (v < -1.0f) v = -1.0f;
+                idx[h] = nf4_nearest(v);
+            }
+        }
+        packed[i] = (uint8_t)((idx[0] << 4) | (idx[1] & 15));
+    }
+}
+
 inline int grid_for(size_t work, int threads) {
     size_t g = (work + threads - 1) / threads;
     size_t cap = (size_t)cmlb_num_sms() * 16;
@@ -136,6 +177,17 @@ extern "C" int cmlb200_dequant_qmat(const cmlb200_qmat* W, float* d_dst, void* s
         default:
             CMLB_REQUIRE(false, "cmlb200_dequant_qmat: unsupported type %d", W->type);
     }
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_quantize_nf4(const float* d_x, size_t numel, int block, uint8_t* d_packed, float* d_scales, void* stream) {
+    CMLB_REQUIRE(d_x && d_packed && d_scales, "cmlb200_quantize_nf4: NULL argument");
+    CMLB_REQUIRE(numel != 0 && block > 0, "cmlb200_quantize_nf4: invalid parameters");
+    const size_t nblocks = (numel + (size_t)block - 1) / (size_t)block;
+    nf4_absmax_kernel<<<grid_for(nblocks, 128), 128, 0, as_stream(stream)>>>(d_x, numel, block, d_scales, nblocks);
+    CMLB_LAUNCH_CHECK();
+    nf4_codes_kernel<<<grid_for((numel + 1) / 2, 256), 256, 0, as_stream(stream)>>>(d_x, numel, block, d_scales, d_packed);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }

@@ -128,7 +128,7 @@ attention_partial_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
         for (int i = 0; i < PER; i++) d = fmaf(qv[i], (float)kp[lane + 32 * i], d);
         d = warp_sum(d) * scale;
         const float mn = fmaxf(m, d);
-        const float corr = __expf(m - mn), p = __expf(d - mn);
+        const float corr = expf(m - mn), p = expf(d - mn);
         const KV* vp = vc + base + (size_t)sk * kvw;
         l = l * corr + p;
 #pragma unroll
@@ -148,7 +148,7 @@ attention_partial_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
         float a = 0.f, lt = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; w++) {
-            const float c = (sm[w] == -INFINITY) ? 0.f : __expf(sm[w] - gm);
+            const float c = (sm[w] == -INFINITY) ? 0.f : expf(sm[w] - gm);
             a = fmaf(sacc[w][threadIdx.x], c, a);
             lt = fmaf(sl[w], c, lt);
         }
@@ -166,13 +166,13 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int ns
     float l = 0.f;
     for (int s = 0; s < nsplit; s++) {
         const float ms = p[s * (HD + 2)];
-        if (ms != -INFINITY) l += p[s * (HD + 2) + 1] * __expf(ms - gm);
+        if (ms != -INFINITY) l += p[s * (HD + 2) + 1] * expf(ms - gm);
     }
     for (int i = threadIdx.x; i < HD; i += blockDim.x) {
         float a = 0.f;
         for (int s = 0; s < nsplit; s++) {
             const float ms = p[s * (HD + 2)];
-            if (ms != -INFINITY) a = fmaf(p[s * (HD + 2) + 2 + i], __expf(ms - gm), a);
+            if (ms != -INFINITY) a = fmaf(p[s * (HD + 2) + 2 + i], expf(ms - gm), a);
         }
         out[rh * HD + i] = a / l;
     }
@@ -212,26 +212,26 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
 }
 
 // ---- row bookkeeping kept on the device so that a decode step can be replayed as a CUDA graph
-// mode 0: one sequence, `rows` consecutive positions starting at cur_len[0] (prefill / single decode)
+// mode 0: sequence `seq`, `rows` consecutive positions starting at cur_len[seq] (prefill / single decode)
 // mode 1: `rows` sequences, one token each at cur_len[b] (batched decode)
 // relative_mask != 0 reproduces C-ML's causal mask on call-relative indices (llm_ops.c:290-298).
-__global__ void prepare_rows_kernel(const int* __restrict__ cur_len, int rows, int mode, int relative_mask,
+__global__ void prepare_rows_kernel(const int* __restrict__ cur_len, int rows, int mode, int relative_mask, int seq,
                                     int* row_seq, int* row_pos, int* row_limit) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     if (mode == 0) {
-        row_seq[r] = 0;
-        row_pos[r] = cur_len[0] + r;
-        row_limit[r] = relative_mask ? r : cur_len[0] + r;
+        row_seq[r] = seq;
+        row_pos[r] = cur_len[seq] + r;
+        row_limit[r] = relative_mask ? r : cur_len[seq] + r;
     } else {
         row_seq[r] = r;
         row_pos[r] = cur_len[r];
         row_limit[r] = relative_mask ? 0 : cur_len[r];
     }
 }
-__global__ void advance_rows_kernel(int* cur_len, int rows, int mode) {
+__global__ void advance_rows_kernel(int* cur_len, int rows, int mode, int seq) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (mode == 0) { if (r == 0) cur_len[0] += rows; }
+    if (mode == 0) { if (r == 0) cur_len[seq] += rows; }
     else if (r < rows) cur_len[r] += 1;
 }
 
@@ -259,6 +259,39 @@ __global__ void swiglu_bf16_kernel(const __nv_bfloat16* __restrict__ g, const __
         const float gv = __bfloat162float(g[i]);
         out[i] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * __bfloat162float(u[i]));
     }
+}
+
+__global__ void swiglu_f32_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float gv = g[i];
+        out[i] = gv / (1.0f + expf(-gv)) * u[i];
+    }
+}
+
+// LoRA low-rank term of the quantized Linear (src/nn/qlora.c:336-361):
+// t[b][r] = sum_i x[b][i] * A[r][i]   then   y[b][o] += scaling * sum_r t[b][r] * B[o][r]
+__global__ void lora_down_kernel(const float* __restrict__ x, const float* __restrict__ A, int K, int rank, float* __restrict__ t) {
+    const int b = blockIdx.y, r = blockIdx.x;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) s = fmaf(x[(size_t)b * K + i], A[(size_t)r * K + i], s);
+    s = warp_sum(s);
+    __shared__ float red[32];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) t[(size_t)b * rank + r] = v;
+    }
+}
+__global__ void lora_up_kernel(const float* __restrict__ t, const float* __restrict__ B, int N, int rank, float scaling,
+                               float* __restrict__ y) {
+    const int b = blockIdx.y;
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= N) return;
+    float s = 0.f;
+    for (int r = 0; r < rank; r++) s = fmaf(t[(size_t)b * rank + r], B[(size_t)o * rank + r], s);
+    y[(size_t)b * N + o] += scaling * s;
 }
 
 inline int ew_grid(size_t n) {
@@ -345,17 +378,17 @@ extern "C" int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d
     return CMLB200_OK;
 }
 
-extern "C" int cmlb200_prepare_rows(const int* d_cur_len, int rows, int mode, int relative_mask, int* d_row_seq,
+extern "C" int cmlb200_prepare_rows(const int* d_cur_len, int rows, int mode, int relative_mask, int seq, int* d_row_seq,
                                     int* d_row_pos, int* d_row_limit, void* stream) {
-    CMLB_REQUIRE(d_cur_len && d_row_seq && d_row_pos && d_row_limit && rows > 0, "cmlb200_prepare_rows: bad argument");
-    prepare_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode, relative_mask, d_row_seq, d_row_pos, d_row_limit);
+    CMLB_REQUIRE(d_cur_len && d_row_seq && d_row_pos && d_row_limit && rows > 0 && seq >= 0, "cmlb200_prepare_rows: bad argument");
+    prepare_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode, relative_mask, seq, d_row_seq, d_row_pos, d_row_limit);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
 
-extern "C" int cmlb200_advance_rows(int* d_cur_len, int rows, int mode, void* stream) {
-    CMLB_REQUIRE(d_cur_len && rows > 0, "cmlb200_advance_rows: bad argument");
-    advance_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode);
+extern "C" int cmlb200_advance_rows(int* d_cur_len, int rows, int mode, int seq, void* stream) {
+    CMLB_REQUIRE(d_cur_len && rows > 0 && seq >= 0, "cmlb200_advance_rows: bad argument");
+    advance_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode, seq);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
@@ -388,6 +421,21 @@ extern "C" int cmlb200_swiglu_bf16(const uint16_t* d_gate, const uint16_t* d_up,
     CMLB_REQUIRE(d_gate && d_up && d_out && n, "cmlb200_swiglu_bf16: bad argument");
     swiglu_bf16_kernel<<<ew_grid(n), 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)d_gate, (const __nv_bfloat16*)d_up,
                                                                (__nv_bfloat16*)d_out, n);
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_swiglu_f32(const float* d_gate, const float* d_up, float* d_out, size_t n, void* stream) {
+    CMLB_REQUIRE(d_gate && d_up && d_out && n, "cmlb200_swiglu_f32: bad argument");
+    swiglu_f32_kernel<<<ew_grid(n), 256, 0, as_stream(stream)>>>(d_gate, d_up, d_out, n);
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_lora_accum(const float* d_x, const float* d_A, const float* d_B, int M, int K, int N, int rank,
+                                  float scaling, float* d_t, float* d_y, void* stream) {
+    CMLB_REQUIRE(d_x && d_A && d_B && d_t && d_y && M > 0 && K > 0 && N > 0 && rank > 0, "cmlb200_lora_accum: bad argument");
+    lora_down_kernel<<<dim3(rank, M), 256, 0, as_stream(stream)>>>(d_x, d_A, K, rank, d_t);
+    CMLB_LAUNCH_CHECK();
+    lora_up_kernel<<<dim3((N + 255) / 256, M), 256, 0, as_stream(stream)>>>(d_t, d_B, N, rank, scaling, d_y);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }

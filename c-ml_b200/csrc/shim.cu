@@ -82,3 +82,49 @@ extern "C" int cmlb200_device_sync(void) {
     CMLB_CUDA(cudaDeviceSynchronize());
     return CMLB200_OK;
 }
+
+extern "C" int cmlb200_graph_begin(void* stream) {
+    CMLB_CUDA(cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeRelaxed));
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_graph_end(void* stream, void** graph_exec) {
+    CMLB_REQUIRE(graph_exec, "cmlb200_graph_end: NULL argument");
+    cudaGraph_t g = nullptr;
+    CMLB_CUDA(cudaStreamEndCapture(as_stream(stream), &g));
+    cudaGraphExec_t e = nullptr;
+    cudaError_t err = cudaGraphInstantiate(&e, g, 0);
+    cudaGraphDestroy(g);
+    CMLB_CUDA(err);
+    *graph_exec = e;
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_graph_launch(void* graph_exec, void* stream) {
+    CMLB_REQUIRE(graph_exec, "cmlb200_graph_launch: NULL argument");
+    CMLB_CUDA(cudaGraphLaunch((cudaGraphExec_t)graph_exec, as_stream(stream)));
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_graph_destroy(void* graph_exec) {
+    if (graph_exec) CMLB_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec));
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_event_create(void** event) {
+    CMLB_REQUIRE(event, "cmlb200_event_create: NULL argument");
+    cudaEvent_t e;
+    CMLB_CUDA(cudaEventCreate(&e));
+    *event = e;
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_event_record(void* event, void* stream) {
+    CMLB_CUDA(cudaEventRecord((cudaEvent_t)event, as_stream(stream)));
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_event_elapsed_ms(void* start, void* stop, float* ms) {
+    CMLB_REQUIRE(ms, "cmlb200_event_elapsed_ms: NULL argument");
+    CMLB_CUDA(cudaEventSynchronize((cudaEvent_t)stop));
+    CMLB_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_event_destroy(void* event) {
+    if (event) CMLB_CUDA(cudaEventDestroy((cudaEvent_t)event));
+    return CMLB200_OK;
+}

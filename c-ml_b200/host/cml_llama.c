@@ -1,0 +1,788 @@
+/*
+ * LLaMA inference entry points on the GPU (C-ML: src/nn/llama.c). The public structs and
+ * functions keep C-ML's shape; the device-side state (packed weights, KV cache, activation
+ * buffers, stream, CUDA graph, NCCL communicator) hangs off the model in a side table keyed
+ * by the model's address, so the public struct layout is untouched.
+ *
+ * Forward pass per layer (src/nn/llama.c:454-548): RMSNorm -> Q/K/V projections -> RoPE ->
+ * append K,V to the cache -> grouped-query attention over the cache -> output projection +
+ * residual -> RMSNorm -> SwiGLU FFN -> down projection + residual. Up to 32 rows run the fp32
+ * decode kernels (dequant-GEMV); longer prompts run the bf16 tcgen05 dequant-GEMM.
+ *
+ * Tensor parallelism (src/distributed/tensor_parallel.c): Q/K/V/gate/up are split by output
+ * rows (column-parallel, whole heads per rank), O/down by input columns (row-parallel); the
+ * partial outputs of the row-parallel projections are summed with an NCCL all-reduce.
+ */
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+#include "cml_internal.h"
+
+#define DEV(call) do { if (CML_DEV_FAIL((call), __func__)) return -1; } while (0)
+#define SKINNY_ROWS 32
+#define ATT_CHUNK 128
+
+typedef struct DevLayer {
+    cmlb200_qmat wq, wk, wv, wo, wg, wu, wd;
+    void *n1, *n2;                         /* fp16 norm weights */
+} DevLayer;
+
+typedef struct DevModel {
+    const CMLLLaMAModel* key;
+    struct DevModel* next;
+    int flags, max_batch, max_rows;
+    int tp, rank, device;
+    void* comm;
+    int hd, heads_l, kvh_l, qw_l, kvw_l, inter_l;
+    DevLayer* L;
+    void *embed, *fnorm;
+    cmlb200_qmat lm_head;
+    void *kc, *vc;                         /* [layers][n_seq][max_seq][kvw_l] */
+    size_t kv_layer_elems;
+    void* stream;
+    float *h, *nrm, *q, *k, *v, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch;
+    uint16_t *b_a, *b_b, *b_c, *b_d;       /* bf16 staging of the prefill path */
+    int *d_tokens, *d_cur, *row_seq, *row_pos, *row_limit, *d_hist;
+    int* h_cur;
+    int att_splits_cap;
+    void* graph;
+    int graph_batch, graph_splits;
+} DevModel;
+
+static DevModel* g_models = NULL;
+
+static DevModel* dm_find(const CMLLLaMAModel* m) {
+    for (DevModel* d = g_models; d; d = d->next) if (d->key == m) return d;
+    return NULL;
+}
+
+/* ---- configuration presets (src/nn/llama.c:14-69) ------------------------------------------- */
+static CMLLLaMAConfig make_cfg(int hidden, int inter, int layers, int heads, int kv, int max_seq) {
+    CMLLLaMAConfig c = {.vocab_size = 32000, .hidden_size = hidden, .intermediate_size = inter, .num_layers = layers,
+                        .num_heads = heads, .num_kv_heads = kv, .max_seq_len = max_seq, .rope_theta = 10000.0f,
+                        .rms_norm_eps = 1e-5f, .tensor_parallel_size = 0, .tensor_parallel_rank = 0};
+    return c;
+}
+CMLLLaMAConfig cml_llama_config_7b(void) { return make_cfg(4096, 11008, 32, 32, 32, 2048); }
+CMLLLaMAConfig cml_llama_config_13b(void) { return make_cfg(5120, 13824, 40, 40, 40, 2048); }
+CMLLLaMAConfig cml_llama_config_70b(void) { return make_cfg(8192, 28672, 80, 64, 8, 4096); }
+
+CMLGenerationConfig cml_generation_default_config(void) {
+    CMLGenerationConfig c = {.temperature = 0.8f, .top_p = 0.9f, .top_k = 40, .max_new_tokens = 256, .eos_token_id = 2, .do_sample = true};
+    return c;
+}
+
+/* ---- create / free ---------------------------------------------------------------------------- */
+CMLLLaMAModel* cml_llama_create(const CMLLLaMAConfig* config) {
+    if (!config) { LOG_ERROR("cml_llama_create: NULL config"); return NULL; }
+    if (config->num_layers <= 0 || config->num_heads <= 0 || config->num_kv_heads <= 0 || config->hidden_size <= 0 ||
+        config->max_seq_len <= 0 || config->hidden_size % config->num_heads || config->num_heads % config->num_kv_heads) {
+        LOG_ERROR("cml_llama_create: invalid configuration");
+        return NULL;
+    }
+    CMLLLaMAModel* m = (CMLLLaMAModel*)calloc(1, sizeof *m);
+    if (!m) { LOG_ERROR("cml_llama_create: allocation failed"); return NULL; }
+    m->config = *config;
+    m->num_layers = config->num_layers;
+    m->layers = (CMLLLaMALayer**)calloc((size_t)config->num_layers, sizeof(CMLLLaMALayer*));
+    if (!m->layers) { free(m); return NULL; }
+    for (int i = 0; i < config->num_layers; i++) {
+        m->layers[i] = (CMLLLaMALayer*)calloc(1, sizeof(CMLLLaMALayer));
+        CMLKVCache* kv = m->layers[i] ? (CMLKVCache*)calloc(1, sizeof(CMLKVCache)) : NULL;
+        if (!kv) { LOG_ERROR("cml_llama_create: layer %d creation failed", i); cml_llama_free(m); return NULL; }
+        kv->max_seq_len = config->max_seq_len;
+        kv->num_kv_heads = config->num_kv_heads;
+        kv->head_dim = config->hidden_size / config->num_heads;
+        m->layers[i]->kv_cache = kv;
+    }
+    LOG_INFO("LLaMA model created: %d layers, hidden=%d, heads=%d, kv_heads=%d", config->num_layers, config->hidden_size,
+             config->num_heads, config->num_kv_heads);
+    return m;
+}
+
+static void qmat_free(cmlb200_qmat* w) {
+    cmlb200_free(w->qs);
+    cmlb200_free(w->scales);
+    cmlb200_free(w->tiles);
+    memset(w, 0, sizeof *w);
+}
+
+static void dm_destroy(DevModel* d) {
+    if (!d) return;
+    if (d->graph) cmlb200_graph_destroy(d->graph);
+    if (d->L) {
+        for (int i = 0; i < d->key->num_layers; i++) {
+            DevLayer* l = &d->L[i];
+            qmat_free(&l->wq); qmat_free(&l->wk); qmat_free(&l->wv); qmat_free(&l->wo);
+            qmat_free(&l->wg); qmat_free(&l->wu); qmat_free(&l->wd);
+            cmlb200_free(l->n1); cmlb200_free(l->n2);
+        }
+        free(d->L);
+    }
+    qmat_free(&d->lm_head);
+    void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->q, d->k, d->v, d->att, d->ffn, d->g, d->u, d->tmp,
+                    d->logits, d->att_scratch, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
+                    d->row_pos, d->row_limit, d->d_hist};
+    for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
+    free(d->h_cur);
+    if (d->comm) cml_nccl_destroy(d->comm);
+    if (d->stream) cmlb200_stream_destroy(d->stream);
+    free(d);
+}
+
+void cml_llama_free(CMLLLaMAModel* model) {
+    if (!model) return;
+    DevModel** pp = &g_models;
+    while (*pp) {
+        if ((*pp)->key == model) { DevModel* d = *pp; *pp = d->next; dm_destroy(d); break; }
+        pp = &(*pp)->next;
+    }
+    if (model->layers) {
+        for (int i = 0; i < model->num_layers; i++) {
+            CMLLLaMALayer* l = model->layers[i];
+            if (!l) continue;
+            Tensor* ts[] = {l->q_proj, l->k_proj, l->v_proj, l->o_proj, l->gate_proj, l->up_proj, l->down_proj,
+                            l->input_layernorm, l->post_attn_layernorm};
+            for (size_t k = 0; k < sizeof ts / sizeof ts[0]; k++) tensor_free(ts[k]);
+            free(l->kv_cache);
+            free(l);
+        }
+        free(model->layers);
+    }
+    if (model->lm_head && model->lm_head != model->embed_tokens) tensor_free(model->lm_head);
+    tensor_free(model->embed_tokens);
+    tensor_free(model->norm);
+    free(model);
+}
+
+/* ---- device state ------------------------------------------------------------------------------ */
+static DevModel* dm_get(CMLLLaMAModel* m) {
+    DevModel* d = dm_find(m);
+    if (d) return d;
+    d = (DevModel*)calloc(1, sizeof *d);
+    if (!d) return NULL;
+    d->key = m;
+    d->max_batch = 1;
+    d->tp = m->config.tensor_parallel_size > 1 ? m->config.tensor_parallel_size : 1;
+    d->rank = d->tp > 1 ? m->config.tensor_parallel_rank : 0;
+    d->device = -1;
+    d->next = g_models;
+    g_models = d;
+    return d;
+}
+
+int cml_llama_set_options(CMLLLaMAModel* model, int flags, int max_batch) {
+    if (!model || max_batch < 1 || max_batch > SKINNY_ROWS) { LOG_ERROR("cml_llama_set_options: invalid arguments (max_batch must be 1..%d)", SKINNY_ROWS); return -1; }
+    DevModel* d = dm_get(model);
+    if (!d) return -1;
+    if (d->h) { LOG_ERROR("cml_llama_set_options: must be called before weights are loaded"); return -1; }
+    d->flags = flags;
+    d->max_batch = max_batch;
+    return 0;
+}
+
+int cml_llama_tp_unique_id(void* id128) { return cml_nccl_unique_id(id128); }
+
+int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
+    if (!model || !id128) { LOG_ERROR("cml_llama_tp_init: NULL argument"); return -1; }
+    DevModel* d = dm_get(model);
+    if (!d) return -1;
+    if (d->tp <= 1) { LOG_ERROR("cml_llama_tp_init: config.tensor_parallel_size is %d", model->config.tensor_parallel_size); return -1; }
+    if (d->rank < 0 || d->rank >= d->tp) { LOG_ERROR("cml_llama_tp_init: rank %d outside 0..%d", d->rank, d->tp - 1); return -1; }
+    DEV(cmlb200_set_device(device));
+    d->device = device;
+    return cml_nccl_init(&d->comm, d->tp, d->rank, id128);
+}
+
+static int dm_alloc_buffers(DevModel* d) {
+    const CMLLLaMAConfig* c = &d->key->config;
+    const int H = c->hidden_size;
+    d->hd = H / c->num_heads;
+    if (c->num_heads % d->tp || c->num_kv_heads % d->tp || c->intermediate_size % d->tp || (c->intermediate_size / d->tp) % 32) {
+        LOG_ERROR("tensor parallel size %d must divide heads (%d), kv heads (%d) and the FFN width (%d) into multiples of 32",
+                  d->tp, c->num_heads, c->num_kv_heads, c->intermediate_size);
+        return -1;
+    }
+    if (d->hd != 32 && d->hd != 64 && d->hd != 128) { LOG_ERROR("head_dim %d not supported (32, 64 or 128)", d->hd); return -1; }
+    d->heads_l = c->num_heads / d->tp;
+    d->kvh_l = c->num_kv_heads / d->tp;
+    d->qw_l = d->heads_l * d->hd;
+    d->kvw_l = d->kvh_l * d->hd;
+    d->inter_l = c->intermediate_size / d->tp;
+    d->max_rows = c->max_seq_len > SKINNY_ROWS ? c->max_seq_len : SKINNY_ROWS;
+    if (d->device >= 0) DEV(cmlb200_set_device(d->device));
+    DEV(cmlb200_stream_create(&d->stream));
+    const size_t R = (size_t)d->max_rows;
+    const int kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
+    d->kv_layer_elems = (size_t)d->max_batch * c->max_seq_len * d->kvw_l;
+    const size_t kv_bytes = d->kv_layer_elems * c->num_layers * (kvf32 ? 4 : 2);
+    DEV(cmlb200_malloc(&d->kc, kv_bytes));
+    DEV(cmlb200_malloc(&d->vc, kv_bytes));
+    DEV(cmlb200_memset(d->kc, 0, kv_bytes, d->stream));
+    DEV(cmlb200_memset(d->vc, 0, kv_bytes, d->stream));
+    const size_t wide = (size_t)(d->inter_l > d->qw_l ? d->inter_l : d->qw_l);
+    DEV(cmlb200_malloc((void**)&d->h, R * H * 4));
+    DEV(cmlb200_malloc((void**)&d->nrm, R * H * 4));
+    DEV(cmlb200_malloc((void**)&d->q, R * d->qw_l * 4));
+    DEV(cmlb200_malloc((void**)&d->k, R * d->kvw_l * 4));
+    DEV(cmlb200_malloc((void**)&d->v, R * d->kvw_l * 4));
+    DEV(cmlb200_malloc((void**)&d->att, R * d->qw_l * 4));
+    DEV(cmlb200_malloc((void**)&d->ffn, (size_t)SKINNY_ROWS * d->inter_l * 4));
+    DEV(cmlb200_malloc((void**)&d->g, (size_t)SKINNY_ROWS * d->inter_l * 4));
+    DEV(cmlb200_malloc((void**)&d->u, (size_t)SKINNY_ROWS * d->inter_l * 4));
+    DEV(cmlb200_malloc((void**)&d->tmp, R * H * 4));
+    DEV(cmlb200_malloc((void**)&d->logits, R * c->vocab_size * 4));
+    DEV(cmlb200_malloc((void**)&d->b_a, R * (wide > (size_t)H ? wide : (size_t)H) * 2));
+    DEV(cmlb200_malloc((void**)&d->b_b, R * (wide > (size_t)c->vocab_size ? wide : (size_t)c->vocab_size) * 2));
+    DEV(cmlb200_malloc((void**)&d->b_c, R * wide * 2));
+    DEV(cmlb200_malloc((void**)&d->b_d, R * wide * 2));
+    d->att_splits_cap = (c->max_seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    DEV(cmlb200_malloc((void**)&d->att_scratch,
+                       cmlb200_attention_scratch_floats(SKINNY_ROWS, d->heads_l, d->hd, d->att_splits_cap) * 4 +
+                           cmlb200_attention_scratch_floats(d->max_rows, d->heads_l, d->hd, 1) * 4));
+    DEV(cmlb200_malloc((void**)&d->d_tokens, R * 4));
+    DEV(cmlb200_malloc((void**)&d->d_cur, (size_t)d->max_batch * 4));
+    DEV(cmlb200_malloc((void**)&d->row_seq, R * 4));
+    DEV(cmlb200_malloc((void**)&d->row_pos, R * 4));
+    DEV(cmlb200_malloc((void**)&d->row_limit, R * 4));
+    DEV(cmlb200_malloc((void**)&d->d_hist, (size_t)c->max_seq_len * d->max_batch * 4));
+    DEV(cmlb200_memset(d->d_cur, 0, (size_t)d->max_batch * 4, d->stream));
+    d->h_cur = (int*)calloc((size_t)d->max_batch, sizeof(int));
+    return d->h_cur ? 0 : -1;
+}
+
+/* GGUF blocks of a [rows, cols] weight -> both device layouts. */
+static int upload_qmat(DevModel* d, int type, const uint8_t* blocks, int rows, int cols, cmlb200_qmat* out) {
+    memset(out, 0, sizeof *out);
+    out->type = type;
+    out->rows = rows;
+    out->cols = cols;
+    out->block = 32;
+    const size_t qb = cmlb200_qs_bytes(type, rows, cols, 32), sb = cmlb200_scale_bytes(type, rows, cols, 32);
+    void *h_qs = malloc(qb), *h_sc = malloc(sb), *h_t = NULL;
+    int rc = -1;
+    if (!h_qs || !h_sc) goto done;
+    if (CML_DEV_FAIL(cmlb200_repack_gguf(type, blocks, rows, cols, h_qs, h_sc), "upload")) goto done;
+    out->flags = cmlb200_scales_have_subnormals(h_sc, sb / 2) ? CMLB200_QMAT_SUBNORMAL_SCALES : 0;
+    if (CML_DEV_FAIL(cmlb200_malloc(&out->qs, qb), "upload") || CML_DEV_FAIL(cmlb200_malloc(&out->scales, sb), "upload")) goto done;
+    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(out->qs, h_qs, qb, d->stream), "upload") ||
+        CML_DEV_FAIL(cmlb200_memcpy_h2d(out->scales, h_sc, sb, d->stream), "upload")) goto done;
+    if (cols % 128 == 0 && d->max_batch > 2) {       /* the tensor-core decode path serves batches of 3..32 */
+        const size_t tb = cmlb200_tiles_bytes(type, rows, cols);
+        h_t = malloc(tb);
+        if (!h_t) goto done;
+        if (CML_DEV_FAIL(cmlb200_repack_tiles(type, blocks, rows, cols, h_t), "upload")) goto done;
+        if (CML_DEV_FAIL(cmlb200_malloc(&out->tiles, tb), "upload")) goto done;
+        if (CML_DEV_FAIL(cmlb200_memcpy_h2d(out->tiles, h_t, tb, d->stream), "upload")) goto done;
+    }
+    if (CML_DEV_FAIL(cmlb200_stream_sync(d->stream), "upload")) goto done;
+    rc = 0;
+done:
+    free(h_qs); free(h_sc); free(h_t);
+    return rc;
+}
+
+/* fp16 (or fp32) host vector -> fp16 device vector */
+static int upload_f16(DevModel* d, const void* raw, GGUFTensorType type, size_t numel, void** out) {
+    uint16_t* tmp = NULL;
+    const void* src = raw;
+    if (type == GGUF_TENSOR_F32) {
+        tmp = (uint16_t*)malloc(numel * 2);
+        if (!tmp) return -1;
+        for (size_t i = 0; i < numel; i++) tmp[i] = cml_f32_to_f16(((const float*)raw)[i]);
+        src = tmp;
+    } else if (type != GGUF_TENSOR_F16) {
+        LOG_ERROR("norm / embedding tensors must be F16 or F32 (got GGUF type %d)", (int)type);
+        return -1;
+    }
+    int rc = -1;
+    if (!CML_DEV_FAIL(cmlb200_malloc(out, numel * 2), "upload") && !CML_DEV_FAIL(cmlb200_memcpy_h2d(*out, src, numel * 2, d->stream), "upload") &&
+        !CML_DEV_FAIL(cmlb200_stream_sync(d->stream), "upload")) rc = 0;
+    free(tmp);
+    return rc;
+}
+
+static Tensor* placeholder(int d0, int d1) {
+    /* shape-only tensor: the weight lives on the device, there is no host copy */
+    Tensor* t = (Tensor*)calloc(1, sizeof(Tensor));
+    if (!t) return NULL;
+    t->ndim = d1 > 0 ? 2 : 1;
+    t->shape = (int*)malloc(2 * sizeof(int));
+    t->strides = (size_t*)malloc(2 * sizeof(size_t));
+    if (!t->shape || !t->strides) { free(t->shape); free(t->strides); free(t); return NULL; }
+    t->shape[0] = d0; t->shape[1] = d1 > 0 ? d1 : 1;
+    t->strides[0] = d1 > 0 ? (size_t)d1 : 1; t->strides[1] = 1;
+    t->numel = (size_t)d0 * (size_t)(d1 > 0 ? d1 : 1);
+    t->dtype = DTYPE_UINT8;
+    t->device = DEVICE_CUDA;
+    t->ref_count = 1;
+    t->is_contiguous = true;
+    return t;
+}
+
+enum { SLOT_NONE, SLOT_EMBED, SLOT_NORM, SLOT_HEAD, SLOT_Q, SLOT_K, SLOT_V, SLOT_O, SLOT_G, SLOT_U, SLOT_D, SLOT_N1, SLOT_N2 };
+
+/* llama.cpp ("blk.N.attn_q.weight") and Hugging Face ("model.layers.N.self_attn.q_proj.weight")
+ * tensor names, as src/nn/llama.c:272-368 recognises them. */
+static int classify(const char* name, int* layer) {
+    *layer = -1;
+    if (!strcmp(name, "token_embd.weight") || !strcmp(name, "model.embed_tokens.weight")) return SLOT_EMBED;
+    if (!strcmp(name, "output_norm.weight") || !strcmp(name, "model.norm.weight")) return SLOT_NORM;
+    if (!strcmp(name, "output.weight") || !strcmp(name, "lm_head.weight")) return SLOT_HEAD;
+    const char* rest = NULL;
+    if (!strncmp(name, "blk.", 4)) rest = name + 4;
+    else if (!strncmp(name, "model.layers.", 13)) rest = name + 13;
+    if (!rest) return SLOT_NONE;
+    char* end;
+    const long l = strtol(rest, &end, 10);
+    if (end == rest || *end != '.') return SLOT_NONE;
+    *layer = (int)l;
+    const char* s = end + 1;
+    static const struct { const char* n; int slot; } map[] = {
+        {"attn_q.weight", SLOT_Q}, {"self_attn.q_proj.weight", SLOT_Q}, {"attn_k.weight", SLOT_K}, {"self_attn.k_proj.weight", SLOT_K},
+        {"attn_v.weight", SLOT_V}, {"self_attn.v_proj.weight", SLOT_V}, {"attn_output.weight", SLOT_O}, {"self_attn.o_proj.weight", SLOT_O},
+        {"ffn_gate.weight", SLOT_G}, {"mlp.gate_proj.weight", SLOT_G}, {"ffn_up.weight", SLOT_U}, {"mlp.up_proj.weight", SLOT_U},
+        {"ffn_down.weight", SLOT_D}, {"mlp.down_proj.weight", SLOT_D}, {"attn_norm.weight", SLOT_N1}, {"input_layernorm.weight", SLOT_N1},
+        {"ffn_norm.weight", SLOT_N2}, {"post_attention_layernorm.weight", SLOT_N2}};
+    for (size_t i = 0; i < sizeof map / sizeof map[0]; i++) if (!strcmp(s, map[i].n)) return map[i].slot;
+    return SLOT_NONE;
+}
+
+/* Cuts this rank's shard out of a full [rows, cols] block array: `by_rows` keeps rows
+ * [rank*rows/tp, ...), otherwise block columns [rank*cols/tp, ...) of every row. */
+static uint8_t* shard_blocks(const uint8_t* full, int type, int rows, int cols, int tp, int rank, int by_rows, int* orow, int* ocol) {
+    const size_t bb = gguf_quant_type_size((GGUFTensorType)type);
+    const int nblk = cols / 32;
+    if (by_rows) {
+        *orow = rows / tp; *ocol = cols;
+        uint8_t* out = (uint8_t*)malloc((size_t)*orow * nblk * bb);
+        if (out) memcpy(out, full + (size_t)rank * *orow * nblk * bb, (size_t)*orow * nblk * bb);
+        return out;
+    }
+    *orow = rows; *ocol = cols / tp;
+    const int lb = nblk / tp;
+    uint8_t* out = (uint8_t*)malloc((size_t)rows * lb * bb);
+    if (out)
+        for (int r = 0; r < rows; r++) memcpy(out + (size_t)r * lb * bb, full + ((size_t)r * nblk + (size_t)rank * lb) * bb, (size_t)lb * bb);
+    return out;
+}
+
+int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
+    if (!model || !filepath) { LOG_ERROR("cml_llama_load_gguf: NULL argument"); return -1; }
+    DevModel* d = dm_get(model);
+    if (!d) return -1;
+    if (d->tp > 1 && !d->comm) { LOG_ERROR("cml_llama_load_gguf: tensor_parallel_size=%d but cml_llama_tp_init was not called", d->tp); return -1; }
+    GGUFContext* ctx = gguf_open_read(filepath);
+    if (!ctx) { LOG_ERROR("cml_llama_load_gguf: failed to open '%s'", filepath); return -1; }
+    if (!d->h && dm_alloc_buffers(d)) { gguf_close(ctx); return -1; }
+    if (!d->L) d->L = (DevLayer*)calloc((size_t)model->num_layers, sizeof(DevLayer));
+    if (!d->L) { gguf_close(ctx); return -1; }
+    const CMLLLaMAConfig* c = &model->config;
+    const int H = c->hidden_size, hdm = d->hd, QW = c->num_heads * hdm, KVW = c->num_kv_heads * hdm, I = c->intermediate_size;
+    int loaded = 0, skipped = 0, failed = 0;
+    const int n = gguf_get_num_tensors(ctx);
+    for (int i = 0; i < n; i++) {
+        const char* name = gguf_get_tensor_name(ctx, i);
+        int layer, slot = name ? classify(name, &layer) : SLOT_NONE;
+        const GGUFTensorInfo* info = cml_gguf_find(ctx, name);
+        if (slot == SLOT_NONE || !info || (layer >= model->num_layers)) {
+            LOG_WARNING("cml_llama_load_gguf: unrecognized tensor name: %s", name ? name : "(null)");
+            skipped++;
+            continue;
+        }
+        void* raw = cml_gguf_read_raw(ctx, info);
+        if (!raw) { failed++; continue; }
+        int rc = -1;
+        if (slot == SLOT_EMBED || slot == SLOT_NORM || slot == SLOT_N1 || slot == SLOT_N2) {
+            size_t numel = 1;
+            for (int k = 0; k < info->ndim; k++) numel *= (size_t)info->shape[k];
+            const size_t want = slot == SLOT_EMBED ? (size_t)c->vocab_size * H : (size_t)H;
+            void** dst = slot == SLOT_EMBED ? &d->embed : slot == SLOT_NORM ? &d->fnorm : slot == SLOT_N1 ? &d->L[layer].n1 : &d->L[layer].n2;
+            Tensor** pub = slot == SLOT_EMBED ? &model->embed_tokens : slot == SLOT_NORM ? &model->norm
+                           : slot == SLOT_N1 ? &model->layers[layer]->input_layernorm : &model->layers[layer]->post_attn_layernorm;
+            if (numel != want) LOG_ERROR("cml_llama_load_gguf: tensor '%s' has %zu elements, expected %zu", name, numel, want);
+            else {
+                cmlb200_free(*dst); *dst = NULL;
+                rc = upload_f16(d, raw, info->type, numel, dst);
+                if (!rc) { tensor_free(*pub); *pub = slot == SLOT_EMBED ? placeholder(c->vocab_size, H) : placeholder(H, 0); }
+            }
+        } else {
+            /* projections: GGUF dims are (in_features, out_features) */
+            int out_f, in_f, by_rows = 1;
+            cmlb200_qmat* dst;
+            Tensor** pub;
+            switch (slot) {
+                case SLOT_Q: out_f = QW; in_f = H; dst = &d->L[layer].wq; pub = &model->layers[layer]->q_proj; break;
+                case SLOT_K: out_f = KVW; in_f = H; dst = &d->L[layer].wk; pub = &model->layers[layer]->k_proj; break;
+                case SLOT_V: out_f = KVW; in_f = H; dst = &d->L[layer].wv; pub = &model->layers[layer]->v_proj; break;
+                case SLOT_O: out_f = H; in_f = QW; by_rows = 0; dst = &d->L[layer].wo; pub = &model->layers[layer]->o_proj; break;
+                case SLOT_G: out_f = I; in_f = H; dst = &d->L[layer].wg; pub = &model->layers[layer]->gate_proj; break;
+                case SLOT_U: out_f = I; in_f = H; dst = &d->L[layer].wu; pub = &model->layers[layer]->up_proj; break;
+                case SLOT_D: out_f = H; in_f = I; by_rows = 0; dst = &d->L[layer].wd; pub = &model->layers[layer]->down_proj; break;
+                default: out_f = c->vocab_size; in_f = H; by_rows = -1; dst = &d->lm_head; pub = &model->lm_head; break;   /* replicated */
+            }
+            if (info->type != GGUF_TENSOR_Q4_0 && info->type != GGUF_TENSOR_Q8_0)
+                LOG_ERROR("cml_llama_load_gguf: tensor '%s' has GGUF type %d; projections must be Q4_0 or Q8_0", name, (int)info->type);
+            else if (info->ndim != 2 || info->shape[0] != in_f || info->shape[1] != out_f)
+                LOG_ERROR("cml_llama_load_gguf: tensor '%s' has dims (%lld, %lld), expected (in=%d, out=%d)", name,
+                          (long long)info->shape[0], (long long)(info->ndim > 1 ? info->shape[1] : 0), in_f, out_f);
+            else {
+                qmat_free(dst);
+                if (d->tp > 1 && by_rows >= 0) {
+                    int lr, lc;
+                    uint8_t* sh = shard_blocks((const uint8_t*)raw, (int)info->type, out_f, in_f, d->tp, d->rank, by_rows, &lr, &lc);
+                    rc = sh ? upload_qmat(d, (int)info->type, sh, lr, lc, dst) : -1;
+                    free(sh);
+                } else rc = upload_qmat(d, (int)info->type, (const uint8_t*)raw, out_f, in_f, dst);
+                if (!rc) { tensor_free(*pub); *pub = placeholder(in_f, out_f); }
+            }
+        }
+        free(raw);
+        if (rc) failed++; else loaded++;
+    }
+    gguf_close(ctx);
+    if (!model->lm_head && model->embed_tokens) LOG_WARNING("cml_llama_load_gguf: no output.weight tensor; tied embeddings are not supported on the quantized path");
+    model->weights_loaded = failed == 0;
+    LOG_INFO("GGUF loading complete: %d loaded, %d skipped, %d failed", loaded, skipped, failed);
+    return failed ? -1 : 0;
+}
+
+/* ---- forward ------------------------------------------------------------------------------------ */
+static int model_ready(const CMLLLaMAModel* m, const DevModel* d) {
+    if (!d || !d->embed || !d->fnorm || !d->lm_head.qs) return 0;
+    for (int i = 0; i < m->num_layers; i++) {
+        const DevLayer* l = &d->L[i];
+        if (!l->wq.qs || !l->wk.qs || !l->wv.qs || !l->wo.qs || !l->wg.qs || !l->wu.qs || !l->wd.qs || !l->n1 || !l->n2) return 0;
+    }
+    return 1;
+}
+
+/* y = x . W^T (accumulate == 0) or y += x . W^T over `rows` rows on the fp32 decode kernels */
+static int lin_f32(DevModel* d, const cmlb200_qmat* W, const float* x, float* y, int rows, int accumulate) {
+    for (int r0 = 0; r0 < rows; r0 += SKINNY_ROWS) {
+        const int m = rows - r0 < SKINNY_ROWS ? rows - r0 : SKINNY_ROWS;
+        const float* xp = x + (size_t)r0 * W->cols;
+        float* yp = y + (size_t)r0 * W->rows;
+        if (accumulate) DEV(cmlb200_gemv_accum(W, xp, yp, m, d->stream));
+        else DEV(cmlb200_gemv(W, xp, yp, m, d->stream));
+    }
+    return 0;
+}
+
+/* Row-parallel projection + residual: h += all_reduce(x . W_shard^T) */
+static int proj_residual_f32(DevModel* d, const cmlb200_qmat* W, const float* x, int rows) {
+    if (d->tp == 1) return lin_f32(d, W, x, d->h, rows, 1);
+    if (lin_f32(d, W, x, d->tmp, rows, 0)) return -1;
+    if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * W->rows, d->stream)) return -1;
+    DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * W->rows, d->stream));
+    return 0;
+}
+
+static int proj_residual_bf16(DevModel* d, const cmlb200_qmat* W, const uint16_t* x, int rows) {
+    DEV(cmlb200_gemm_bf16(W, x, d->b_b, rows, d->stream));
+    const size_t n = (size_t)rows * W->rows;
+    if (d->tp == 1) { DEV(cmlb200_add_bf16(d->h, d->b_b, n, d->stream)); return 0; }
+    DEV(cmlb200_bf16_to_f32(d->b_b, d->tmp, n, d->stream));
+    if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, n, d->stream)) return -1;
+    DEV(cmlb200_add_f32(d->h, d->tmp, n, d->stream));
+    return 0;
+}
+
+/* Enqueues one forward call over `rows` rows whose tokens are in d->d_tokens.
+ * mode 0: one sequence (`seq`), consecutive positions; mode 1: one token for each of `rows`
+ * sequences. plan_limit bounds the cache positions the call may touch (sizes the attention
+ * splits); logits for all rows land in d->logits. */
+static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_limit) {
+    const CMLLLaMAModel* m = d->key;
+    const CMLLLaMAConfig* c = &m->config;
+    const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
+    const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32);
+    void* st = d->stream;
+    DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
+    DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));
+    int splits = 1;
+    if (rows <= SKINNY_ROWS) {
+        const int lim = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
+        splits = (lim + ATT_CHUNK) / ATT_CHUNK;
+        if (splits > d->att_splits_cap) splits = d->att_splits_cap;
+        if (splits < 1) splits = 1;
+    }
+    const int max_limit = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
+    const size_t esz = kvf32 ? 4 : 2;
+    for (int li = 0; li < m->num_layers; li++) {
+        const DevLayer* L = &d->L[li];
+        void* kc = (char*)d->kc + (size_t)li * d->kv_layer_elems * esz;
+        void* vc = (char*)d->vc + (size_t)li * d->kv_layer_elems * esz;
+        if (skinny) {
+            DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
+            if (lin_f32(d, &L->wq, d->nrm, d->q, rows, 0) || lin_f32(d, &L->wk, d->nrm, d->k, rows, 0) || lin_f32(d, &L->wv, d->nrm, d->v, rows, 0)) return -1;
+        } else {
+            DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
+            DEV(cmlb200_gemm_bf16(&L->wq, d->b_a, d->b_b, rows, st));
+            DEV(cmlb200_bf16_to_f32(d->b_b, d->q, (size_t)rows * d->qw_l, st));
+            DEV(cmlb200_gemm_bf16(&L->wk, d->b_a, d->b_b, rows, st));
+            DEV(cmlb200_bf16_to_f32(d->b_b, d->k, (size_t)rows * d->kvw_l, st));
+            DEV(cmlb200_gemm_bf16(&L->wv, d->b_a, d->b_b, rows, st));
+            DEV(cmlb200_bf16_to_f32(d->b_b, d->v, (size_t)rows * d->kvw_l, st));
+        }
+        /* With tensor parallelism head 0 lives on rank 0 only, so the "head 0 only" quirk
+         * rotates nothing on the other ranks. */
+        if (!quirks || d->rank == 0) {
+            DEV(cmlb200_rope(d->q, d->row_pos, rows, d->qw_l, d->hd, c->rope_theta, !quirks, st));
+            DEV(cmlb200_rope(d->k, d->row_pos, rows, d->kvw_l, d->hd, c->rope_theta, !quirks, st));
+        }
+        DEV(cmlb200_kv_append(d->k, d->v, kc, vc, d->row_seq, d->row_pos, rows, d->kvw_l, c->max_seq_len, kvf32, st));
+        DEV(cmlb200_attention(d->q, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd, c->max_seq_len,
+                              max_limit < c->max_seq_len ? max_limit : c->max_seq_len - 1, kvf32, d->att, d->att_scratch, splits, st));
+        if (skinny) {
+            if (proj_residual_f32(d, &L->wo, d->att, rows)) return -1;
+            DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
+            for (int r0 = 0; r0 < rows; r0 += SKINNY_ROWS) {
+                const int mr = rows - r0 < SKINNY_ROWS ? rows - r0 : SKINNY_ROWS;
+                const float* xp = d->nrm + (size_t)r0 * H;
+                if (mr <= 2) DEV(cmlb200_gemv_swiglu(&L->wg, &L->wu, xp, d->ffn, mr, st));
+                else {
+                    DEV(cmlb200_gemv(&L->wg, xp, d->g, mr, st));
+                    DEV(cmlb200_gemv(&L->wu, xp, d->u, mr, st));
+                    DEV(cmlb200_swiglu_f32(d->g, d->u, d->ffn, (size_t)mr * d->inter_l, st));
+                }
+                /* down projection of this chunk, accumulated into its rows of h */
+                if (d->tp == 1) DEV(cmlb200_gemv_accum(&L->wd, d->ffn, d->h + (size_t)r0 * H, mr, st));
+                else {
+                    DEV(cmlb200_gemv(&L->wd, d->ffn, d->tmp, mr, st));
+                    if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)mr * H, st)) return -1;
+                    DEV(cmlb200_add_f32(d->h + (size_t)r0 * H, d->tmp, (size_t)mr * H, st));
+                }
+            }
+        } else {
+            DEV(cmlb200_f32_to_bf16(d->att, d->b_a, (size_t)rows * d->qw_l, st));
+            if (proj_residual_bf16(d, &L->wo, d->b_a, rows)) return -1;
+            DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
+            DEV(cmlb200_gemm_bf16(&L->wg, d->b_a, d->b_c, rows, st));
+            DEV(cmlb200_gemm_bf16(&L->wu, d->b_a, d->b_d, rows, st));
+            DEV(cmlb200_swiglu_bf16(d->b_c, d->b_d, d->b_c, (size_t)rows * d->inter_l, st));
+            if (proj_residual_bf16(d, &L->wd, d->b_c, rows)) return -1;
+        }
+    }
+    if (skinny) {
+        DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
+        if (lin_f32(d, &d->lm_head, d->nrm, d->logits, rows, 0)) return -1;
+    } else {
+        DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
+        DEV(cmlb200_gemm_bf16(&d->lm_head, d->b_a, d->b_b, rows, st));
+        DEV(cmlb200_bf16_to_f32(d->b_b, d->logits, (size_t)rows * c->vocab_size, st));
+    }
+    DEV(cmlb200_advance_rows(d->d_cur, rows, mode, seq, st));
+    return 0;
+}
+
+static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows, int mode, int seq, const char* who) {
+    DevModel* d = dm_find(model);
+    if (!model_ready(model, d)) { LOG_ERROR("%s: weights are not loaded", who); return NULL; }
+    const CMLLLaMAConfig* c = &model->config;
+    int max_pos = 0;
+    if (mode == 0) {
+        if (seq >= d->max_batch) { LOG_ERROR("%s: sequence %d outside the configured batch of %d", who, seq, d->max_batch); return NULL; }
+        max_pos = d->h_cur[seq] + rows;
+    } else {
+        if (rows > d->max_batch) { LOG_ERROR("%s: batch %d exceeds the configured maximum %d", who, rows, d->max_batch); return NULL; }
+        for (int b = 0; b < rows; b++) if (d->h_cur[b] + 1 > max_pos) max_pos = d->h_cur[b] + 1;
+    }
+    if (max_pos > c->max_seq_len) {                     /* cache overflow, as src/nn/llm_ops.c:133-137 */
+        LOG_ERROR("%s: cache overflow (%d > %d)", who, max_pos, c->max_seq_len);
+        return NULL;
+    }
+    int shape[2] = {rows, c->vocab_size};
+    Tensor* out = cml_tensor_alloc(DTYPE_FLOAT32, shape, 2, false);
+    if (!out) return NULL;
+    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_tokens, token_ids, (size_t)rows * 4, d->stream), who) ||
+        enqueue_forward(d, rows, mode, seq, max_pos - 1) ||
+        CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->logits, (size_t)rows * c->vocab_size * 4, d->stream), who) ||
+        CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) {
+        tensor_free(out);
+        return NULL;
+    }
+    int st = 0;
+    if (cmlb200_gemm_status(&st, 1) == CMLB200_OK && st == 0) cmlb200_gemv_tiles_status(&st, 1);
+    if (st) { LOG_ERROR("%s: a bounded device-side wait expired (code %d)", who, st); tensor_free(out); return NULL; }
+    if (mode == 0) d->h_cur[seq] += rows;
+    else for (int b = 0; b < rows; b++) d->h_cur[b] += 1;
+    model->current_seq_len = d->h_cur[0];
+    for (int i = 0; i < model->num_layers; i++) model->layers[i]->kv_cache->current_len = d->h_cur[0];
+    return out;
+}
+
+Tensor* cml_llama_forward(CMLLLaMAModel* model, const int* token_ids, int seq_len) {
+    if (!model || !token_ids || seq_len <= 0) { LOG_ERROR("cml_llama_forward: invalid arguments"); return NULL; }
+    if (!model->embed_tokens) { LOG_ERROR("cml_llama_forward: embed_tokens not loaded"); return NULL; }
+    return run_forward(model, token_ids, seq_len, 0, 0, "cml_llama_forward");
+}
+
+Tensor* cml_llama_forward_batch(CMLLLaMAModel* model, const int* token_ids, int batch) {
+    if (!model || !token_ids || batch <= 0) { LOG_ERROR("cml_llama_forward_batch: invalid arguments"); return NULL; }
+    return run_forward(model, token_ids, batch, 1, 0, "cml_llama_forward_batch");
+}
+
+int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_ids, int seq_len) {
+    if (!model || !token_ids || seq_len <= 0 || seq < 0) { LOG_ERROR("cml_llama_prefill_sequence: invalid arguments"); return -1; }
+    Tensor* t = run_forward(model, token_ids, seq_len, 0, seq, "cml_llama_prefill_sequence");
+    if (!t) return -1;
+    tensor_free(t);
+    return 0;
+}
+
+int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int batch, int steps, int* out_tokens, float* elapsed_ms) {
+    if (!model || !first_tokens || !out_tokens || batch <= 0 || steps <= 0) { LOG_ERROR("cml_llama_decode_greedy: invalid arguments"); return -1; }
+    DevModel* d = dm_find(model);
+    if (!model_ready(model, d)) { LOG_ERROR("cml_llama_decode_greedy: weights are not loaded"); return -1; }
+    const CMLLLaMAConfig* c = &model->config;
+    if (batch > d->max_batch) { LOG_ERROR("cml_llama_decode_greedy: batch %d exceeds the configured maximum %d", batch, d->max_batch); return -1; }
+    int max_pos = 0;
+    for (int b = 0; b < batch; b++) if (d->h_cur[b] + steps > max_pos) max_pos = d->h_cur[b] + steps;
+    if (max_pos > c->max_seq_len) { LOG_ERROR("cml_llama_decode_greedy: cache overflow (%d > %d)", max_pos, c->max_seq_len); return -1; }
+    void* st = d->stream;
+    DEV(cmlb200_memcpy_h2d(d->d_tokens, first_tokens, (size_t)batch * 4, st));
+    const int quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0;
+    int splits = quirks ? 1 : (max_pos - 1 + ATT_CHUNK) / ATT_CHUNK;
+    if (splits > d->att_splits_cap) splits = d->att_splits_cap;
+    /* every step of the loop sees the same attention geometry: `splits` chunks of ATT_CHUNK keys */
+    int plan_limit = splits * ATT_CHUNK - 1;
+    if (plan_limit > c->max_seq_len - 1) plan_limit = c->max_seq_len - 1;
+    void *e0 = NULL, *e1 = NULL;
+    DEV(cmlb200_event_create(&e0));
+    DEV(cmlb200_event_create(&e1));
+    DEV(cmlb200_event_record(e0, st));
+    int s0 = 0;
+    if (!d->graph || d->graph_batch != batch || d->graph_splits != splits) {
+        if (d->graph) { cmlb200_graph_destroy(d->graph); d->graph = NULL; }
+        /* The first step runs eagerly: first-use initialisation inside the kernels' launchers
+         * (function attributes, scratch allocation) must not happen during stream capture. */
+        if (enqueue_forward(d, batch, 1, 0, plan_limit)) return -1;
+        DEV(cmlb200_argmax(d->logits, batch, c->vocab_size, d->d_tokens, st));
+        DEV(cmlb200_memcpy_d2d(d->d_hist, d->d_tokens, (size_t)batch * 4, st));
+        DEV(cmlb200_stream_sync(st));
+        s0 = 1;
+        if (steps > 1) {
+            DEV(cmlb200_graph_begin(st));
+            int rc = enqueue_forward(d, batch, 1, 0, plan_limit);
+            if (!rc && CML_DEV_FAIL(cmlb200_argmax(d->logits, batch, c->vocab_size, d->d_tokens, st), "cml_llama_decode_greedy")) rc = -1;
+            void* g = NULL;
+            if (CML_DEV_FAIL(cmlb200_graph_end(st, &g), "cml_llama_decode_greedy") || rc) { if (g) cmlb200_graph_destroy(g); return -1; }
+            d->graph = g;
+            d->graph_batch = batch;
+            d->graph_splits = splits;
+        }
+    }
+    for (int s = s0; s < steps; s++) {
+        DEV(cmlb200_graph_launch(d->graph, st));
+        DEV(cmlb200_memcpy_d2d(d->d_hist + (size_t)s * batch, d->d_tokens, (size_t)batch * 4, st));
+    }
+    DEV(cmlb200_event_record(e1, st));
+    float ms = 0.f;
+    DEV(cmlb200_event_elapsed_ms(e0, e1, &ms));
+    DEV(cmlb200_memcpy_d2h(out_tokens, d->d_hist, (size_t)steps * batch * 4, st));
+    DEV(cmlb200_stream_sync(st));
+    cmlb200_event_destroy(e0);
+    cmlb200_event_destroy(e1);
+    int stt = 0;
+    if (cmlb200_gemm_status(&stt, 1) == CMLB200_OK && stt == 0) cmlb200_gemv_tiles_status(&stt, 1);
+    if (stt) { LOG_ERROR("cml_llama_decode_greedy: a bounded device-side wait expired (code %d)", stt); return -1; }
+    if (elapsed_ms) *elapsed_ms = ms;
+    for (int b = 0; b < batch; b++) d->h_cur[b] += steps;
+    model->current_seq_len = d->h_cur[0];
+    for (int i = 0; i < model->num_layers; i++) model->layers[i]->kv_cache->current_len = d->h_cur[0];
+    return 0;
+}
+
+/* ---- sampling (src/nn/llama.c:614-737) ----------------------------------------------------------- */
+typedef struct { float value; int index; } LogitEntry;
+static int entry_cmp_desc(const void* a, const void* b) {
+    const float va = ((const LogitEntry*)a)->value, vb = ((const LogitEntry*)b)->value;
+    return va > vb ? -1 : (va < vb ? 1 : 0);
+}
+
+int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config) {
+    if (!logits || !config || !logits->data) return -1;
+    const float* data = (const float*)logits->data;
+    int vocab;
+    const float* row;
+    if (logits->ndim == 2) { vocab = logits->shape[1]; row = data + (size_t)(logits->shape[0] - 1) * vocab; }
+    else if (logits->ndim == 1) { vocab = logits->shape[0]; row = data; }
+    else { LOG_ERROR("cml_llama_sample_token: unexpected logits ndim=%d", logits->ndim); return -1; }
+    if (!config->do_sample || config->temperature <= 0.0f) {        /* greedy: first strict maximum */
+        int best = 0;
+        for (int i = 1; i < vocab; i++) if (row[i] > row[best]) best = i;
+        return best;
+    }
+    LogitEntry* e = (LogitEntry*)malloc((size_t)vocab * sizeof *e);
+    if (!e) return -1;
+    const float inv_t = 1.0f / config->temperature;
+    for (int i = 0; i < vocab; i++) { e[i].value = row[i] * inv_t; e[i].index = i; }
+    qsort(e, (size_t)vocab, sizeof *e, entry_cmp_desc);
+    int k = config->top_k;
+    if (k <= 0 || k > vocab) k = vocab;
+    const float mx = e[0].value;
+    float sum = 0.f;
+    for (int i = 0; i < k; i++) { e[i].value = expf(e[i].value - mx); sum += e[i].value; }
+    for (int i = 0; i < k; i++) e[i].value /= sum;
+    int cutoff = k;
+    if (config->top_p > 0.0f && config->top_p < 1.0f) {
+        float cum = 0.f;
+        for (int i = 0; i < k; i++) { cum += e[i].value; if (cum >= config->top_p) { cutoff = i + 1; break; } }
+    }
+    if (cutoff < k) {
+        float rs = 0.f;
+        for (int i = 0; i < cutoff; i++) rs += e[i].value;
+        if (rs > 0.f) for (int i = 0; i < cutoff; i++) e[i].value /= rs;
+    }
+    const float r = (float)rand() / (float)RAND_MAX;
+    float acc = 0.f;
+    int id = e[0].index;
+    for (int i = 0; i < cutoff; i++) { acc += e[i].value; if (r <= acc) { id = e[i].index; break; } }
+    free(e);
+    return id;
+}
+
+CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config) {
+    if (!model || !prompt || !config) { LOG_ERROR("cml_llama_generate: NULL argument"); return NULL; }
+    /* As in C-ML (src/nn/llama.c:754-762) text generation needs model->tokenizer; the GGUF loader
+     * does not create one. Token-id callers use cml_llama_forward / cml_llama_decode_greedy. */
+    LOG_ERROR("cml_llama_generate: no tokenizer attached to the model");
+    return NULL;
+}
+
+void cml_generation_result_free(CMLGenerationResult* result) {
+    if (!result) return;
+    free(result->token_ids);
+    free(result->text);
+    free(result);
+}
+
+void cml_llama_reset(CMLLLaMAModel* model) {
+    if (!model) return;
+    DevModel* d = dm_find(model);
+    if (d && d->d_cur) {
+        cmlb200_memset(d->d_cur, 0, (size_t)d->max_batch * 4, d->stream);
+        cmlb200_stream_sync(d->stream);
+        memset(d->h_cur, 0, (size_t)d->max_batch * sizeof(int));
+    }
+    for (int i = 0; i < model->num_layers; i++)
+        if (model->layers[i] && model->layers[i]->kv_cache) model->layers[i]->kv_cache->current_len = 0;
+    model->current_seq_len = 0;
+}
+
+void cml_llama_print_config(const CMLLLaMAConfig* config) {
+    if (!config) return;
+    const int hd = config->hidden_size / config->num_heads;
+    const long long layer = (long long)config->hidden_size * config->num_heads * hd + 2LL * config->hidden_size * config->num_kv_heads * hd +
+                            3LL * config->hidden_size * config->intermediate_size;
+    const long long total = config->num_layers * layer + 2LL * config->vocab_size * config->hidden_size;
+    printf("LLaMA Configuration:\n  vocab_size:        %d\n  hidden_size:       %d\n  intermediate_size: %d\n  num_layers:        %d\n"
+           "  num_heads:         %d\n  num_kv_heads:      %d\n  head_dim:          %d\n  max_seq_len:       %d\n  rope_theta:        %.1f\n"
+           "  rms_norm_eps:      %.1e\n  est. parameters:   %.1fB\n",
+           config->vocab_size, config->hidden_size, config->intermediate_size, config->num_layers, config->num_heads,
+           config->num_kv_heads, hd, config->max_seq_len, config->rope_theta, config->rms_norm_eps, total / 1e9);
+}

@@ -37,3 +37,67 @@ def bf16_round(a):
 
 def bf16_to_f32(u16):
     return (np.ascontiguousarray(u16, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# ---- GGUF v3 writer for synthetic models (little-endian; tensor data 32-byte aligned) ------------
+def write_gguf(path, tensors):
+    """tensors: list of (name, dims, gguf_type, raw_bytes). dims are written in the given order
+    (for weights: (in_features, out_features), the GGUF convention)."""
+    import struct
+    infos, blobs, off = [], [], 0
+    for name, dims, gtype, raw in tensors:
+        raw = bytes(raw)
+        infos.append((name.encode(), dims, gtype, off))
+        pad = (-len(raw)) % 32
+        blobs.append(raw + b"\0" * pad)
+        off += len(raw) + pad
+    out = bytearray()
+    out += struct.pack("<IIQQ", 0x46475547, 3, len(tensors), 1)
+    key = b"general.architecture"
+    out += struct.pack("<Q", len(key)) + key + struct.pack("<I", 8) + struct.pack("<Q", 5) + b"llama"
+    for name, dims, gtype, o in infos:
+        out += struct.pack("<Q", len(name)) + name + struct.pack("<I", len(dims))
+        for d in dims:
+            out += struct.pack("<Q", d)
+        out += struct.pack("<IQ", gtype, o)
+    out += b"\0" * ((-len(out)) % 32)
+    with open(path, "wb") as f:
+        f.write(out)
+        for b in blobs:
+            f.write(b)
+
+
+def make_llama(rng, cfg, quantize, qtype=2, wscale=0.05):
+    """Random LLaMA weights quantized with `quantize(fp32 [out,in]) -> GGUF block bytes`.
+    Returns (gguf tensor list, dict of quantized block arrays + fp16 vectors)."""
+    V, H, I, L = cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"]
+    hd = H // cfg["heads"]
+    QW, KVW = cfg["heads"] * hd, cfg["kv_heads"] * hd
+    tensors, store = [], {}
+
+    def proj(name, out_f, in_f):
+        w = (rng.standard_normal((out_f, in_f)) * wscale).astype(np.float32)
+        blocks = quantize(w)
+        store[name] = (blocks, out_f, in_f)
+        tensors.append((name, (in_f, out_f), qtype, blocks.tobytes()))
+
+    def vec(name, n, base=1.0, rows=None):
+        shape = (rows, n) if rows else (n,)
+        v = (base + 0.1 * rng.standard_normal(shape)).astype(np.float16) if base else (rng.standard_normal(shape) * 0.5).astype(np.float16)
+        store[name] = v
+        tensors.append((name, tuple(reversed(shape)), 1, v.tobytes()))
+
+    vec("token_embd.weight", H, base=0.0, rows=V)
+    for l in range(L):
+        vec(f"blk.{l}.attn_norm.weight", H)
+        proj(f"blk.{l}.attn_q.weight", QW, H)
+        proj(f"blk.{l}.attn_k.weight", KVW, H)
+        proj(f"blk.{l}.attn_v.weight", KVW, H)
+        proj(f"blk.{l}.attn_output.weight", H, QW)
+        vec(f"blk.{l}.ffn_norm.weight", H)
+        proj(f"blk.{l}.ffn_gate.weight", I, H)
+        proj(f"blk.{l}.ffn_up.weight", I, H)
+        proj(f"blk.{l}.ffn_down.weight", H, I)
+    vec("output_norm.weight", H)
+    proj("output.weight", V, H)
+    return tensors, store

@@ -1,0 +1,284 @@
+/*
+ * cml_quant_api.h -- the C11 host API of the quantized-LLM path, with the names, argument
+ * meaning, ownership and error behaviour of C-ML's public headers, so that callers of that
+ * path (examples/llama_inference.c, src/nn/openai_api.c, the speculative-decoding forward
+ * callback) can link against this library instead. Behind it everything runs on the GPU
+ * through the cmlb200 C-ABI (cmlb200.h); there is no CPU fallback.
+ *
+ * Struct layouts are part of C-ML's ABI because its callers and tests read and write the
+ * fields directly; they are reproduced field for field. Each declaration cites the C-ML
+ * header (relative to the C-ML source tree) it stands in for.
+ *
+ * Errors: pointer-returning functions return NULL, int-returning ones -1 (0 = success), and
+ * every failure logs through cml_log_message at LOG_LEVEL_ERROR, as in C-ML.
+ */
+#ifndef CML_QUANT_API_H
+#define CML_QUANT_API_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- include/core/logging.h:6-27 ------------------------------------------------------- */
+typedef enum { LOG_LEVEL_DEBUG = 0, LOG_LEVEL_INFO = 1, LOG_LEVEL_WARNING = 2, LOG_LEVEL_ERROR = 3 } LogLevel;
+extern LogLevel g_log_level;
+void cml_set_log_level(LogLevel level);
+void cml_log_message(LogLevel level, const char* file, int line, const char* func, const char* format, ...);
+#define LOG_DEBUG(...) cml_log_message(LOG_LEVEL_DEBUG, __FILE__, __LINE__, __func__, __VA_ARGS__)
+#define LOG_INFO(...) cml_log_message(LOG_LEVEL_INFO, __FILE__, __LINE__, __func__, __VA_ARGS__)
+#define LOG_WARNING(...) cml_log_message(LOG_LEVEL_WARNING, __FILE__, __LINE__, __func__, __VA_ARGS__)
+#define LOG_ERROR(...) cml_log_message(LOG_LEVEL_ERROR, __FILE__, __LINE__, __func__, __VA_ARGS__)
+
+/* ---- include/backend/device.h:13-21, include/tensor/tensor.h:16-34,40-75,88-93 ----------- */
+typedef enum { DEVICE_CPU, DEVICE_CUDA, DEVICE_METAL, DEVICE_ROCM, DEVICE_OPENCL, DEVICE_SIM_GPU, DEVICE_AUTO } DeviceType;
+
+typedef enum {
+    DTYPE_FLOAT32, DTYPE_FLOAT64, DTYPE_INT32, DTYPE_INT64, DTYPE_BOOL, DTYPE_FLOAT16, DTYPE_BFLOAT16,
+    DTYPE_INT8, DTYPE_UINT8, DTYPE_INT16, DTYPE_UINT16, DTYPE_UINT32, DTYPE_UINT64,
+    DTYPE_FLOAT8_E4M3, DTYPE_FLOAT8_E5M2, DTYPE_FLOAT8_E4M3_FNUZ, DTYPE_FLOAT8_E5M2_FNUZ
+} DType;
+
+struct IRNode;
+struct CMLGraph;
+struct CMLBackendBuffer;
+
+/* Host tensors handed across this API are always realised (is_executed, data != NULL,
+ * contiguous); the lazy-graph fields exist for layout compatibility and stay NULL. */
+typedef struct Tensor {
+    int* shape;
+    int ndim;
+    size_t numel;
+    DType dtype;
+    DeviceType device;
+    struct IRNode* ir_node;
+    struct CMLGraph* ir_context;
+    struct IRNode* saved_ir_node;
+    struct CMLGraph* saved_ir_context;
+    bool is_executed;
+    void* data;
+    bool owns_data;
+    bool from_buffer_cache;
+    bool requires_grad;
+    struct Tensor* grad;
+    int ref_count;
+    struct Tensor* base;
+    size_t* strides;
+    size_t storage_offset;
+    bool is_contiguous;
+    struct CMLBackendBuffer* buffer_handle;
+    void* user_data;
+} Tensor;
+
+typedef struct TensorConfig {
+    DType dtype;
+    DeviceType device;
+    bool has_dtype;
+    bool has_device;
+} TensorConfig;
+
+size_t cml_dtype_size(DType dtype);
+Tensor* tensor_empty(int* shape, int ndim, const TensorConfig* config);
+Tensor* tensor_zeros(int* shape, int ndim, const TensorConfig* config);
+Tensor* tensor_from_data(const void* data, int* shape, int ndim, const TensorConfig* config);
+void tensor_free(Tensor* t);
+void* tensor_data_ptr(Tensor* t);
+int tensor_ensure_executed(Tensor* t);
+
+/* ---- include/core/gguf.h:11-50, include/core/gguf_quant.h:14-62 --------------------------- */
+#define GGUF_MAGIC 0x46475547
+typedef enum {
+    GGUF_TENSOR_F32 = 0, GGUF_TENSOR_F16 = 1, GGUF_TENSOR_Q4_0 = 2, GGUF_TENSOR_Q4_1 = 3, GGUF_TENSOR_Q8_0 = 7,
+    GGUF_TENSOR_Q4_K = 12, GGUF_TENSOR_Q5_K = 13, GGUF_TENSOR_Q6_K = 14, GGUF_TENSOR_I8 = 16, GGUF_TENSOR_I16 = 17,
+    GGUF_TENSOR_I32 = 18
+} GGUFTensorType;
+
+#define QK4_0 32
+typedef struct { uint16_t d; uint8_t qs[QK4_0 / 2]; } BlockQ4_0;
+#define QK8_0 32
+typedef struct { uint16_t d; int8_t qs[QK8_0]; } BlockQ8_0;
+
+bool gguf_type_is_quantized(GGUFTensorType type);
+int gguf_quant_block_size(GGUFTensorType type);
+size_t gguf_quant_type_size(GGUFTensorType type);
+/* Host pointers in, host fp32 out, computed on the device; -1 on NULL, numel == 0, a type
+ * without a device kernel (only Q4_0 and Q8_0 have one) or numel % block != 0. */
+int gguf_dequantize(GGUFTensorType type, const void* src, float* dst, size_t numel);
+
+typedef struct GGUFContext GGUFContext;
+GGUFContext* gguf_open_read(const char* filepath);
+void gguf_close(GGUFContext* ctx);
+int gguf_get_num_tensors(GGUFContext* ctx);
+const char* gguf_get_tensor_name(GGUFContext* ctx, int index);
+/* As in C-ML: quantized tensors come back dequantized to fp32, others in their own dtype. */
+Tensor* gguf_read_tensor(GGUFContext* ctx, const char* name);
+
+/* ---- include/core/quantization.h:28-38, include/nn/qlora.h:18-60 -------------------------- */
+extern const float CML_NF4_TABLE[16];
+Tensor* cml_quantize_nf4(Tensor* tensor, int block_size, float** out_scales, int* out_num_scales);
+Tensor* cml_dequantize_nf4(Tensor* nf4_tensor, const float* scales, int num_scales, int block_size, size_t original_numel);
+
+typedef struct CMLNF4Tensor {
+    Tensor* packed_data;
+    float* scales;
+    int num_scales;
+    int block_size;
+    size_t original_numel;
+    int* original_shape;
+    int original_ndim;
+} CMLNF4Tensor;
+
+typedef struct CMLQLoRALinear {
+    int in_features;
+    int out_features;
+    int rank;
+    float alpha;
+    float scaling;
+    CMLNF4Tensor* base_weight_nf4;
+    Tensor* lora_A;
+    Tensor* lora_B;
+    bool enable_double_quant;
+} CMLQLoRALinear;
+
+CMLNF4Tensor* cml_nf4_tensor_create(Tensor* float_tensor, int block_size);
+void cml_nf4_tensor_free(CMLNF4Tensor* nf4);
+Tensor* cml_nf4_tensor_dequantize(const CMLNF4Tensor* nf4);
+CMLQLoRALinear* cml_qlora_linear_create(Tensor* base_weight, int rank, float alpha, int block_size);
+void cml_qlora_linear_free(CMLQLoRALinear* qlora);
+/* y = x . dequant(W)^T + scaling * (x . A^T) . B^T. The packed base weight is uploaded on the
+ * first call and kept on the device; after editing packed_data or scales in place call
+ * cml_qlora_linear_invalidate. lora_A / lora_B are re-read on every call. M <= 32 rows use the
+ * fp32 decode kernel, larger batches the bf16 tensor-core kernel. */
+Tensor* cml_qlora_linear_forward(CMLQLoRALinear* qlora, Tensor* input);
+void cml_qlora_linear_invalidate(CMLQLoRALinear* qlora);      /* addition: no C-ML counterpart */
+size_t cml_qlora_memory_usage(const CMLQLoRALinear* qlora);
+size_t cml_qlora_full_memory_usage(int in_features, int out_features);
+
+/* ---- include/nn/llm_ops.h:13-32 (the cache object the model structs point at) -------------- */
+typedef struct CMLKVCache {
+    Tensor* key_cache;      /* NULL here: keys and values live on the device */
+    Tensor* value_cache;
+    int max_seq_len;
+    int current_len;
+    int num_kv_heads;
+    int head_dim;
+} CMLKVCache;
+typedef struct CMLTokenizer CMLTokenizer;
+
+/* ---- include/nn/llama.h:13-106 -------------------------------------------------------------- */
+typedef struct CMLLLaMAConfig {
+    int vocab_size;
+    int hidden_size;
+    int intermediate_size;
+    int num_layers;
+    int num_heads;
+    int num_kv_heads;
+    int max_seq_len;
+    float rope_theta;
+    float rms_norm_eps;
+    int tensor_parallel_size;
+    int tensor_parallel_rank;
+} CMLLLaMAConfig;
+
+CMLLLaMAConfig cml_llama_config_7b(void);
+CMLLLaMAConfig cml_llama_config_13b(void);
+CMLLLaMAConfig cml_llama_config_70b(void);
+
+typedef struct CMLLLaMALayer {
+    Tensor* q_proj;
+    Tensor* k_proj;
+    Tensor* v_proj;
+    Tensor* o_proj;
+    Tensor* gate_proj;
+    Tensor* up_proj;
+    Tensor* down_proj;
+    Tensor* input_layernorm;
+    Tensor* post_attn_layernorm;
+    CMLKVCache* kv_cache;
+} CMLLLaMALayer;
+
+typedef struct CMLLLaMAModel {
+    CMLLLaMAConfig config;
+    Tensor* embed_tokens;
+    Tensor* norm;
+    Tensor* lm_head;
+    CMLLLaMALayer** layers;
+    int num_layers;
+    CMLTokenizer* tokenizer;
+    bool weights_loaded;
+    int current_seq_len;
+} CMLLLaMAModel;
+
+typedef struct CMLGenerationConfig {
+    float temperature;
+    float top_p;
+    int top_k;
+    int max_new_tokens;
+    int eos_token_id;
+    bool do_sample;
+} CMLGenerationConfig;
+
+typedef struct CMLGenerationResult {
+    int* token_ids;
+    int num_tokens;
+    char* text;
+    float total_time_ms;
+    float tokens_per_second;
+} CMLGenerationResult;
+
+CMLGenerationConfig cml_generation_default_config(void);
+CMLLLaMAModel* cml_llama_create(const CMLLLaMAConfig* config);
+void cml_llama_free(CMLLLaMAModel* model);
+/* Reads a GGUF v3 file whose projection tensors are Q4_0 or Q8_0 and whose norms / embeddings
+ * are F16 (or F32), keeps the blocks quantized, repacks them once and uploads them. Tensor
+ * dimensions follow the GGUF convention: dims = (in_features, out_features), i.e. `out` rows of
+ * `in` contiguous elements with quantization blocks along `in`. The Tensor* fields of the model
+ * are set to small placeholder tensors (shape only) so that callers' NULL checks keep working.
+ * With config.tensor_parallel_size > 1 only this rank's shard is uploaded. */
+int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath);
+/* Logits [seq_len, vocab] as a host fp32 tensor the caller frees, one sequence, positions
+ * continuing at model->current_seq_len. */
+Tensor* cml_llama_forward(CMLLLaMAModel* model, const int* token_ids, int seq_len);
+CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config);
+void cml_generation_result_free(CMLGenerationResult* result);
+int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config);
+void cml_llama_reset(CMLLLaMAModel* model);
+void cml_llama_print_config(const CMLLLaMAConfig* config);
+
+/* ---- additions (no C-ML counterpart) ---------------------------------------------------------- */
+/* Behaviour switches of a model, to be set after cml_llama_create and before the first forward:
+ *   CML_B200_REFERENCE_QUIRKS  reproduce two properties of C-ML's forward pass exactly: RoPE
+ *       rotates only head 0 (src/nn/llama.c:483-484 passes 2-D tensors to cml_rope_forward) and
+ *       the causal mask compares call-relative indices (src/nn/llm_ops.c:290-298), so a cached
+ *       decode step attends to cache slot 0 only. Off (default): every head is rotated and the
+ *       mask uses absolute positions.
+ *   CML_B200_KV_FP32           keep the KV cache in fp32 (default fp16).
+ *   CML_B200_ALL_LOGITS_FP32   prompts longer than 32 tokens normally run the bf16 tensor-core
+ *       path; with this flag every forward uses the fp32 decode kernels (slow, for parity runs). */
+#define CML_B200_REFERENCE_QUIRKS 1
+#define CML_B200_KV_FP32 2
+#define CML_B200_ALL_LOGITS_FP32 4
+int cml_llama_set_options(CMLLLaMAModel* model, int flags, int max_batch);
+/* One decode step for `batch` independent sequences (each with its own cache and position),
+ * one new token each; logits [batch, vocab]. C-ML's forward is single-sequence only. */
+Tensor* cml_llama_forward_batch(CMLLLaMAModel* model, const int* token_ids, int batch);
+/* Prefill sequence `seq` of a batch with its prompt (positions start at 0 for that sequence). */
+int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_ids, int seq_len);
+/* Greedy decoding kept on the device: feeds each step's arg-max back as the next input for
+ * `steps` steps (all `batch` sequences), writes the chosen ids [steps, batch] to out_tokens and
+ * the wall time of the loop to *elapsed_ms. The step is captured once as a CUDA graph. */
+int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int batch, int steps, int* out_tokens,
+                            float* elapsed_ms);
+/* Tensor parallelism over NCCL: every rank creates its model with tensor_parallel_size/rank
+ * set, rank 0 obtains an id with cml_llama_tp_unique_id and sends the 128 bytes to the other
+ * ranks by any means, then every rank calls cml_llama_tp_init before loading weights. */
+int cml_llama_tp_unique_id(void* id128);
+int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CML_QUANT_API_H */

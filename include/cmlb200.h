@@ -152,6 +152,60 @@ int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, ui
  * expired since the last reset (0 = none). C-ML has no counterpart: its path cannot stall. */
 int cmlb200_gemm_status(int* status, int reset);
 
+/* ---- NF4 quantisation on the device: cml_quantize_nf4 (src/core/quantization.c:213-312):
+ * per-block absmax floored at 1e-10, x/absmax clamped to [-1,1], nearest code with the first
+ * minimum winning, even element in the high nibble. d_packed gets (numel+1)/2 bytes, d_scales
+ * ceil(numel/block) floats. Bit-identical to the CPU routine. */
+int cmlb200_quantize_nf4(const float* d_x, size_t numel, int block, uint8_t* d_packed, float* d_scales, void* stream);
+
+/* ---- the non-matmul pieces of the LLaMA forward pass ------------------------------------------
+ * "rows" are the activation rows of one forward call; row r belongs to sequence row_seq[r], sits
+ * at absolute position row_pos[r] and may attend to cache slots 0..row_limit[r]. */
+/* embed_tokens_lookup (src/nn/llama.c:421-452), fp16 table, out-of-range ids read row 0. */
+int cmlb200_embed_f16(const uint16_t* d_table_f16, const int* d_tokens, int rows, int hidden, int vocab, float* d_out, void* stream);
+/* rms_norm (src/nn/llama.c:71-124): x * 1/sqrt(mean(x^2)+eps) * w; fp16 weight; writes fp32
+ * (d_out_f32) or bf16 (d_out_bf16), whichever is non-NULL. */
+int cmlb200_rmsnorm(const float* d_x, const uint16_t* d_w_f16, int rows, int dim, float eps, float* d_out_f32, uint16_t* d_out_bf16, void* stream);
+/* cml_rope_forward (src/nn/llm_ops.c:702-805), in place on [rows, width]; all_heads == 0 rotates
+ * only the first head_dim columns of each row, which is what C-ML's forward pass does. */
+int cmlb200_rope(float* d_x, const int* d_row_pos, int rows, int width, int head_dim, float base, int all_heads, void* stream);
+/* cml_kv_cache_append (src/nn/llm_ops.c:118-157) into a [n_seq, max_seq, kvw] cache (fp16 or fp32). */
+int cmlb200_kv_append(const float* d_k, const float* d_v, void* d_kcache, void* d_vcache, const int* d_row_seq, const int* d_row_pos, int rows, int kvw, int max_seq, int kv_is_f32, void* stream);
+/* cml_gqa_forward (src/nn/llm_ops.c:194-361) over the cache, split over the key range and merged.
+ * max_limit = the largest row_limit of the call (sizes the splits); d_scratch needs
+ * cmlb200_attention_scratch_floats(rows, heads, head_dim, splits) floats. */
+size_t cmlb200_attention_scratch_floats(int rows, int heads, int head_dim, int splits);
+int cmlb200_attention(const float* d_q, const void* d_kcache, const void* d_vcache, const int* d_row_seq, const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq, int max_limit, int kv_is_f32, float* d_out, float* d_scratch, int splits, void* stream);
+/* Greedy branch of cml_llama_sample_token (src/nn/llama.c:650-660): first index of the maximum. */
+int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream);
+/* Row bookkeeping kept on the device so that a decode step replays as a CUDA graph.
+ * mode 0: sequence `seq`, rows consecutive positions from cur_len[seq]; mode 1: rows sequences,
+ * one token each at cur_len[b]. relative_mask reproduces C-ML's call-relative causal mask. */
+int cmlb200_prepare_rows(const int* d_cur_len, int rows, int mode, int relative_mask, int seq, int* d_row_seq, int* d_row_pos, int* d_row_limit, void* stream);
+int cmlb200_advance_rows(int* d_cur_len, int rows, int mode, int seq, void* stream);
+/* Element-wise helpers (uop_add src/ops/uops.c:37, silu*mul of src/nn/llama.c:126-155). */
+int cmlb200_bf16_to_f32(const uint16_t* d_in, float* d_out, size_t n, void* stream);
+int cmlb200_f32_to_bf16(const float* d_in, uint16_t* d_out, size_t n, void* stream);
+int cmlb200_add_bf16(float* d_acc, const uint16_t* d_in, size_t n, void* stream);
+int cmlb200_add_f32(float* d_acc, const float* d_in, size_t n, void* stream);
+int cmlb200_swiglu_bf16(const uint16_t* d_gate, const uint16_t* d_up, uint16_t* d_out, size_t n, void* stream);
+int cmlb200_swiglu_f32(const float* d_gate, const float* d_up, float* d_out, size_t n, void* stream);
+
+/* LoRA term of the quantized Linear (src/nn/qlora.c:336-361): y[M,N] += scaling * (x.A^T).B^T
+ * with A [rank,K], B [N,rank]; d_t is M*rank floats of scratch. */
+int cmlb200_lora_accum(const float* d_x, const float* d_A, const float* d_B, int M, int K, int N, int rank, float scaling, float* d_t, float* d_y, void* stream);
+
+/* ---- CUDA graph capture of a launch sequence (used for the decode step) ----------------------- */
+int cmlb200_graph_begin(void* stream);
+int cmlb200_graph_end(void* stream, void** graph_exec);
+int cmlb200_graph_launch(void* graph_exec, void* stream);
+int cmlb200_graph_destroy(void* graph_exec);
+/* Wall-clock helpers on the device timeline. */
+int cmlb200_event_create(void** event);
+int cmlb200_event_record(void* event, void* stream);
+int cmlb200_event_elapsed_ms(void* start, void* stop, float* ms);
+int cmlb200_event_destroy(void* event);
+
 #ifdef __cplusplus
 }
 #endif
