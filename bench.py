@@ -140,6 +140,45 @@ def cpu_reference_leg(budget_s=12.0):
             "host_cores_available": os.cpu_count(), "ms_per_call": 1e3 * per_call}
 
 
+LLAMA_7B = dict(vocab=32000, hidden=4096, inter=11008, layers=32, heads=32, kv_heads=32, max_seq=1024)
+
+
+def llama_leg(pkg, synth, prompt_len=512, new_tokens=128, batches=(1, 8), cfg=LLAMA_7B, tag="llama7b_q4_0"):
+    """LLaMA-7B-architecture decode on one GPU: random Q4_0 weights (fp16 norms and embeddings)
+    written as a GGUF file and loaded through cml_llama_load_gguf, a random 512-token prompt per
+    sequence, then 128 greedy tokens generated on the device (fp16 KV cache)."""
+    import tempfile
+    out = {}
+    rng = np.random.default_rng(99)
+    with tempfile.TemporaryDirectory(prefix="cmlb200_") as tmp:
+        path = os.path.join(tmp, "model.gguf")
+        t0 = time.perf_counter()
+        nbytes = synth.write_random_llama_gguf(path, rng, cfg)
+        out[f"{tag}_gguf_bytes"] = nbytes
+        out[f"{tag}_generate_s"] = time.perf_counter() - t0
+        for B in batches:
+            c = pkg.LlamaConfig(cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv_heads"],
+                                cfg["max_seq"], 10000.0, 1e-5, 0, 0)
+            m = pkg.lib.cml_llama_create(C.byref(c))
+            assert m and pkg.lib.cml_llama_set_options(m, 0, B) == 0
+            t0 = time.perf_counter()
+            assert pkg.lib.cml_llama_load_gguf(m, path.encode()) == 0, "cml_llama_load_gguf failed"
+            out[f"{tag}_load_s_b{B}"] = time.perf_counter() - t0
+            prompts = rng.integers(0, cfg["vocab"], (B, prompt_len)).astype(np.int32)
+            t0 = time.perf_counter()
+            for b in range(B):
+                assert pkg.lib.cml_llama_prefill_sequence(m, b, pkg.np_ptr(prompts[b]), prompt_len) == 0
+            out[f"{tag}_prefill_tok_s_b{B}"] = B * prompt_len / (time.perf_counter() - t0)
+            first = rng.integers(0, cfg["vocab"], B).astype(np.int32)
+            toks = np.zeros((new_tokens, B), np.int32)
+            ms = C.c_float(0)
+            assert pkg.lib.cml_llama_decode_greedy(m, pkg.np_ptr(first), B, new_tokens, pkg.np_ptr(toks), C.byref(ms)) == 0
+            out[f"{tag}_decode_tok_s_b{B}"] = B * new_tokens / (ms.value * 1e-3)
+            out[f"{tag}_decode_ms_per_step_b{B}"] = ms.value / new_tokens
+            pkg.lib.cml_llama_free(m)
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -167,6 +206,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--copies", type=int, default=COPIES)
+    ap.add_argument("--skip-llama", action="store_true", help="skip the LLaMA-7B decode leg")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
     args = ap.parse_args()
@@ -306,6 +346,14 @@ def main():
         extra[f"M{M}_gbs"] = alg_bytes(M) / (msM * 1e-3 / (sM * copies * SWEEPS_PER_STEP)) / 1e9 * world
     e2e_dt, h2d, d2h = e2e_timed(1, max(2, args.steps // 4), 3)
     e2e_gbs = alg_bytes(1) * copies * max(2, args.steps // 4) / e2e_dt / 1e9 * world
+
+    if rank == 0 and world == 1 and not args.skip_llama:
+        del weights, keep
+        torch.cuda.empty_cache()
+        try:
+            extra.update(llama_leg(pkg, synth))
+        except Exception as exc:                     # the GEMV headline stands on its own
+            extra["llama7b_q4_0_error"] = repr(exc)[:300]
 
     if rank == 0:
         peak, peak_kind = measured_peaks()

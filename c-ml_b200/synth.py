@@ -101,3 +101,63 @@ def make_llama(rng, cfg, quantize, qtype=2, wscale=0.05):
     vec("output_norm.weight", H)
     proj("output.weight", V, H)
     return tensors, store
+
+
+def write_random_llama_gguf(path, rng, cfg, qtype=2, weight_std=0.02):
+    """A LLaMA-shaped GGUF with random Q4_0/Q8_0 blocks (uniform quants, fp16 scales chosen so
+    that the dequantised weights have roughly `weight_std`), fp16 norms near 1 and fp16
+    embeddings. Generated tensor by tensor straight into the file, so 7B-sized models need no
+    fp32 staging; every layer reuses the random bytes drawn for layer 0 (the file still holds
+    each layer separately). Returns the number of bytes written."""
+    import struct
+    V, H, I, L = cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"]
+    hd = H // cfg["heads"]
+    QW, KVW = cfg["heads"] * hd, cfg["kv_heads"] * hd
+    bb, qstd = (18, 4.6) if qtype == 2 else (34, 73.0)
+    d0 = weight_std / qstd
+    spec = [("token_embd.weight", (H, V), 1)]
+    for l in range(L):
+        spec += [(f"blk.{l}.attn_norm.weight", (H,), 1), (f"blk.{l}.attn_q.weight", (H, QW), qtype),
+                 (f"blk.{l}.attn_k.weight", (H, KVW), qtype), (f"blk.{l}.attn_v.weight", (H, KVW), qtype),
+                 (f"blk.{l}.attn_output.weight", (QW, H), qtype), (f"blk.{l}.ffn_norm.weight", (H,), 1),
+                 (f"blk.{l}.ffn_gate.weight", (H, I), qtype), (f"blk.{l}.ffn_up.weight", (H, I), qtype),
+                 (f"blk.{l}.ffn_down.weight", (I, H), qtype)]
+    spec += [("output_norm.weight", (H,), 1), ("output.weight", (H, V), qtype)]
+
+    def nbytes(dims, t):
+        n = int(np.prod(dims))
+        return n * 2 if t == 1 else n // 32 * bb
+
+    head = bytearray(struct.pack("<IIQQ", 0x46475547, 3, len(spec), 0))
+    off = 0
+    for name, dims, t in spec:
+        nb = name.encode()
+        head += struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(dims))
+        for d in dims:
+            head += struct.pack("<Q", d)
+        head += struct.pack("<IQ", t, off)
+        off += (nbytes(dims, t) + 31) // 32 * 32
+    head += b"\0" * ((-len(head)) % 32)
+    cache = {}          # layers share their random bytes: one draw per (tensor kind, shape)
+    with open(path, "wb") as f:
+        f.write(head)
+        for name, dims, t in spec:
+            n = int(np.prod(dims))
+            kind = (name.split(".", 2)[2] if name.startswith("blk.") else name, dims, t)
+            if kind in cache:
+                raw = cache[kind]
+            elif t == 1:
+                if len(dims) == 1:
+                    raw = (1.0 + 0.05 * rng.standard_normal(n)).astype(np.float16).tobytes()
+                else:
+                    raw = (0.5 * rng.standard_normal(n, dtype=np.float32)).astype(np.float16).tobytes()
+            else:
+                nblk = n // 32
+                blk = np.empty((nblk, bb), np.uint8)
+                blk[:, :2] = rng.uniform(0.5 * d0, 1.5 * d0, nblk).astype(np.float16).view(np.uint8).reshape(nblk, 2)
+                blk[:, 2:] = rng.integers(0, 256, (nblk, bb - 2), dtype=np.uint8)
+                raw = blk.tobytes()
+            cache[kind] = raw
+            f.write(raw)
+            f.write(b"\0" * ((-len(raw)) % 32))
+    return len(head) + off
