@@ -55,6 +55,7 @@ _sig("cmlb200_gguf_dequantize", ci, ci, vp, vp, sz, vp)
 _sig("cmlb200_dequant_qmat", ci, C.POINTER(QMat), vp, vp)
 _sig("cmlb200_dequantize_nf4", ci, vp, vp, ci, ci, sz, vp, vp)
 _sig("cmlb200_gemv", ci, C.POINTER(QMat), vp, vp, ci, vp)
+_sig("cmlb200_gemv_noalloc", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_accum", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_swiglu", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_tiles_bytes", sz, ci, ci, ci)

@@ -353,3 +353,51 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
     if (quirk) return q8 ? run_epi<CMLB200_Q8_0, true>(W, W2, xq, y, M, epi, st) : run_epi<CMLB200_Q4_0, true>(W, W2, xq, y, M, epi, st);
     return q8 ? run_epi<CMLB200_Q8_0, false>(W, W2, xq, y, M, epi, st) : run_epi<CMLB200_Q4_0, false>(W, W2, xq, y, M, epi, st);
 }
+
+// ---- allocation-free variant -------------------------------------------------------------------
+// Some hosts of this library must not allocate device memory once they are running: an inference
+// server that has handed the whole GPU to its own arena, a real-time loop that may not take the
+// allocator's lock, a sandboxed plug-in whose CUDA allocation calls are filtered. For them the
+// activation digits of the decode GEMV live in a fixed array that is part of the library image
+// (every GPU that loads the library carries these 512 KiB until the process exits).
+constexpr size_t kStaticScratchBytes = 512u << 10;
+static __device__ __align__(256) uint32_t g_static_xq[kStaticScratchBytes / sizeof(uint32_t)];
+
+// `g_static_xq` as written in host code is only the host-side handle of the symbol, never a
+// device address; the address a kernel may use is looked up once per device, with that device
+// current, and cached here.
+static uint32_t* g_static_xq_ptr[16] = {};
+
+static int static_scratch(uint32_t** out) {
+    int dev = 0;
+    CMLB_CUDA(cudaGetDevice(&dev));
+    CMLB_REQUIRE(dev >= 0 && dev < 16, "cmlb200_gemv_noalloc: device index %d out of range", dev);
+    if (!g_static_xq_ptr[dev]) {
+        void* p = nullptr;
+        CMLB_CUDA(cudaGetSymbolAddress(&p, g_static_xq));
+        g_static_xq_ptr[dev] = static_cast<uint32_t*>(p);
+    }
+    *out = g_static_xq_ptr[dev];
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_gemv_noalloc(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream) {
+    CMLB_REQUIRE(W && W->qs && W->scales && d_x && d_y, "cmlb200_gemv_noalloc: NULL argument");
+    CMLB_REQUIRE(W->type == CMLB200_Q4_0 || W->type == CMLB200_Q8_0, "cmlb200_gemv_noalloc: weight type %d is not Q4_0 or Q8_0", W->type);
+    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "cmlb200_gemv_noalloc: weight shape %dx%d (cols must be a multiple of 32)", W->rows, W->cols);
+    CMLB_REQUIRE(M >= 1 && M <= 4, "cmlb200_gemv_noalloc: M=%d outside 1..4", M);
+    CMLB_REQUIRE(((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)d_x & 15) == 0, "cmlb200_gemv_noalloc: weight planes and x must be 16-byte aligned");
+    const size_t need = cmlb200_xq_bytes_(M, W->cols);
+    CMLB_REQUIRE(need <= kStaticScratchBytes,
+                 "cmlb200_gemv_noalloc: M*cols = %d*%d needs %zu bytes of activation scratch, the built-in array holds %zu "
+                 "(M*cols <= 149796); use cmlb200_gemv for larger problems",
+                 M, W->cols, need, kStaticScratchBytes);
+    uint32_t* xq = nullptr;
+    int rc = static_scratch(&xq);
+    if (rc) return rc;
+    // Every word a later kernel reads is rewritten here for this call's x, so nothing in the
+    // array has to start at zero and the previous call's contents are harmless.
+    rc = cmlb200_x_digits_(d_x, M, W->cols, xq, as_stream(stream));
+    if (rc) return rc;
+    return cmlb200_gemv_dp4a_(W, nullptr, d_x, xq, d_y, M, EPI_STORE, as_stream(stream));
+}

@@ -120,6 +120,18 @@ int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const fl
 /* y += x . W^T (residual add fused; src/nn/llama.c:523-530 and :538-543). */
 int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
 
+/* The decode GEMV for callers that cannot allocate device memory at run time (a serving process
+ * that gave the whole GPU to its own arena, a real-time loop that must not take the allocator
+ * lock, a sandbox that filters CUDA allocation calls). It has no counterpart in C-ML. Same result
+ * as cmlb200_gemv for Q4_0 / Q8_0 weights in the planes layout and M <= 4, but the activation
+ * scratch is a fixed 512 KiB array inside the library image (resident on every GPU that loads the
+ * library until the process exits) and the call performs no cudaMalloc / cudaFree. Limit:
+ * M * cols <= 149,796 (e.g. M = 4 with cols = 28672); larger requests fail with CMLB200_EINVAL and
+ * a message. The first call on a device looks up the array's device address; make that call
+ * before starting any stream capture. All calls on a device share the array: calls whose kernels
+ * could overlap on the GPU (different streams) race on it and must be ordered by the caller. */
+int cmlb200_gemv_noalloc(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
+
 /* ---- tile-major weights for the tensor-core decode path ----------------------------------
  * The same GGUF blocks regrouped as "units": for row tile t (128 rows, the last one zero
  * padded) and block column b one contiguous unit holds the 128 rows' quants of block b
