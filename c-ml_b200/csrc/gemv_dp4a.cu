@@ -30,8 +30,8 @@ enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
-constexpr int XW = 28;            // words per block of x digits: 3 planes x 8 words + scale + block sum + 2 pad
-constexpr int XFULL = (1 << 20) - 1;
+constexpr int XW = kXqWords;      // words per block of x digits: 3 planes x 8 words + scale + block sum + 2 pad
+constexpr int XFULL = kXqFull;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -400,4 +400,109 @@ extern "C" int cmlb200_gemv_noalloc(const cmlb200_qmat* W, const float* d_x, flo
     rc = cmlb200_x_digits_(d_x, M, W->cols, xq, as_stream(stream));
     if (rc) return rc;
     return cmlb200_gemv_dp4a_(W, nullptr, d_x, xq, d_y, M, EPI_STORE, as_stream(stream));
+}
+
+// ---- digits produced by the kernel that makes the activations ------------------------------------
+// In the LLaMA decode step the GEMV input comes out of RMSNorm; producing the digit planes there
+// saves a launch per projection group (Q/K/V share one set, gate/up another).
+namespace {
+
+// 8 lanes (sub = 0..7) turn the 32 values of one block, 4 per lane, into its XW-word record.
+__device__ __forceinline__ void emit_block_digits(const float (&e)[4], int sub, unsigned gmask, uint32_t* dst) {
+    float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+    const float inv = amax > 0.f ? (float)XFULL / amax : 0.f;
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    int xsum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int X = __float2int_rn(e[i] * inv);
+        X = max(-XFULL, min(XFULL, X));
+        xsum += X;
+        const int d2 = ((X + 64) & 127) - 64;
+        const int X1 = (X - d2) >> 7;
+        const int d1 = ((X1 + 64) & 127) - 64;
+        const int d0 = (X1 - d1) >> 7;
+        w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+        w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+        w2 |= (uint32_t)(d2 & 0xFF) << (8 * i);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) xsum += __shfl_xor_sync(gmask, xsum, o);
+    dst[sub] = w0;
+    dst[8 + sub] = w1;
+    dst[16 + sub] = w2;
+    if (sub == 0) {
+        dst[24] = __float_as_uint(amax / (float)XFULL);
+        dst[25] = (uint32_t)xsum;
+    }
+}
+
+// RMSNorm (src/nn/llama.c:71-124) of one row per CTA; writes the normalised row as fp32 (if asked)
+// and as digit records. dim % 32 == 0.
+__global__ void __launch_bounds__(256)
+rmsnorm_digits_kernel(const float* __restrict__ x, const __half* __restrict__ w, int dim, float eps, float* __restrict__ out,
+                      uint32_t* __restrict__ xq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float red[8];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)r * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < dim; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)dim + eps);
+    const int sub = threadIdx.x & 7;
+    const unsigned gmask = 0xffu << (threadIdx.x & 24);
+    const int nblk = dim / 32;
+    for (int b = threadIdx.x >> 3; b < nblk; b += 32) {
+        const int i = b * 32 + sub * 4;
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        const float e[4] = {v.x * inv * __half2float(w[i]), v.y * inv * __half2float(w[i + 1]),
+                            v.z * inv * __half2float(w[i + 2]), v.w * inv * __half2float(w[i + 3])};
+        if (out) *reinterpret_cast<float4*>(out + (size_t)r * dim + i) = make_float4(e[0], e[1], e[2], e[3]);
+        emit_block_digits(e, sub, gmask, xq + ((size_t)r * nblk + b) * XW);
+    }
+}
+
+}  // namespace
+
+extern "C" size_t cmlb200_xq_bytes(int M, int K) { return cmlb200_xq_bytes_(M, K); }
+
+extern "C" int cmlb200_x_digits(const float* d_x, int M, int K, void* d_xq, void* stream) {
+    CMLB_REQUIRE(d_x && d_xq && M >= 1 && K > 0 && K % 32 == 0, "cmlb200_x_digits: bad argument");
+    CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_xq & 15) == 0, "cmlb200_x_digits: pointers must be 16-byte aligned");
+    return cmlb200_x_digits_(d_x, M, K, (uint32_t*)d_xq, as_stream(stream));
+}
+
+extern "C" int cmlb200_rmsnorm_digits(const float* d_x, const uint16_t* d_w_f16, int rows, int dim, float eps, float* d_out_f32,
+                                      void* d_xq, void* stream) {
+    CMLB_REQUIRE(d_x && d_w_f16 && d_xq && rows >= 1 && dim > 0 && dim % 32 == 0, "cmlb200_rmsnorm_digits: bad argument");
+    CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_xq & 15) == 0 && ((uintptr_t)d_out_f32 & 15) == 0,
+                 "cmlb200_rmsnorm_digits: pointers must be 16-byte aligned");
+    return launch_pdl(rmsnorm_digits_kernel, dim3(rows), dim3(256), 0, as_stream(stream), d_x, (const __half*)d_w_f16, dim, eps,
+                      d_out_f32, (uint32_t*)d_xq);
+}
+
+// epi: 0 store, 1 accumulate into y, 2 SwiGLU of (W, W2)
+extern "C" int cmlb200_gemv_xq(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* d_xq, float* d_y, int M, int epi,
+                               void* stream) {
+    CMLB_REQUIRE(W && W->qs && W->scales && d_xq && d_y, "cmlb200_gemv_xq: NULL argument");
+    CMLB_REQUIRE(W->type == CMLB200_Q4_0 || W->type == CMLB200_Q8_0, "cmlb200_gemv_xq: weight type %d is not Q4_0 or Q8_0", W->type);
+    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "cmlb200_gemv_xq: bad weight shape %dx%d", W->rows, W->cols);
+    CMLB_REQUIRE(M >= 1 && M <= 4 && epi >= 0 && epi <= 2, "cmlb200_gemv_xq: M=%d must be 1..4 and epi=%d one of 0, 1, 2", M, epi);
+    if (epi == EPI_SWIGLU)
+        CMLB_REQUIRE(W2 && W2->qs && W2->scales && W2->type == W->type && W2->rows == W->rows && W2->cols == W->cols,
+                     "cmlb200_gemv_xq: SwiGLU needs a second weight of the same type and shape");
+    return cmlb200_gemv_dp4a_(W, epi == EPI_SWIGLU ? W2 : nullptr, nullptr, (const uint32_t*)d_xq, d_y, M, epi, as_stream(stream));
 }

@@ -104,7 +104,9 @@ template <typename KV, int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_partial_kernel(const float* __restrict__ q, const KV* __restrict__ kc, const KV* __restrict__ vc,
                          const int* __restrict__ row_seq, const int* __restrict__ row_limit, int heads, int kv_heads,
-                         int max_seq, int chunk, float* __restrict__ partial) {
+                         int max_seq, int chunk, float* __restrict__ partial, int q_stride) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int PER = HD / 32;                       // head-dim elements per lane
     const int h = blockIdx.x, r = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -117,22 +119,45 @@ attention_partial_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
     const float scale = 1.0f / sqrtf((float)HD);
     float qv[PER];
 #pragma unroll
-    for (int i = 0; i < PER; i++) qv[i] = q[((size_t)r * heads + h) * HD + lane + 32 * i];
+    for (int i = 0; i < PER; i++) qv[i] = q[(size_t)r * q_stride + (size_t)h * HD + lane + 32 * i];
     float m = -INFINITY, l = 0.f, acc[PER];
 #pragma unroll
     for (int i = 0; i < PER; i++) acc[i] = 0.f;
-    for (int sk = k_begin + warp; sk < k_end; sk += NW) {
-        const KV* kp = kc + base + (size_t)sk * kvw;
-        float d = 0.f;
+    // A warp takes KB consecutive keys per step and requests all their K and V rows before it
+    // consumes any, so one memory round trip serves KB keys.
+    constexpr int KB = 8;
+    for (int sk0 = k_begin + warp * KB; sk0 < k_end; sk0 += NW * KB) {
+        float kr[KB][PER], vr[KB][PER];
 #pragma unroll
-        for (int i = 0; i < PER; i++) d = fmaf(qv[i], (float)kp[lane + 32 * i], d);
-        d = warp_sum(d) * scale;
-        const float mn = fmaxf(m, d);
-        const float corr = expf(m - mn), p = expf(d - mn);
-        const KV* vp = vc + base + (size_t)sk * kvw;
-        l = l * corr + p;
+        for (int j = 0; j < KB; j++) {
+            const int sk = min(sk0 + j, k_end - 1);
+            const KV* kp = kc + base + (size_t)sk * kvw;
+            const KV* vp = vc + base + (size_t)sk * kvw;
 #pragma unroll
-        for (int i = 0; i < PER; i++) acc[i] = acc[i] * corr + p * (float)vp[lane + 32 * i];
+            for (int i = 0; i < PER; i++) { kr[j][i] = (float)kp[lane + 32 * i]; vr[j][i] = (float)vp[lane + 32 * i]; }
+        }
+        float d[KB];
+        float bm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; i++) t = fmaf(qv[i], kr[j][i], t);
+            d[j] = (sk0 + j < k_end) ? warp_sum(t) * scale : -INFINITY;
+            bm = fmaxf(bm, d[j]);
+        }
+        const float mn = fmaxf(m, bm);
+        const float corr = expf(m - mn);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] *= corr;
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            const float p = expf(d[j] - mn);               // exp(-inf) = 0 for keys past the end
+            l += p;
+#pragma unroll
+            for (int i = 0; i < PER; i++) acc[i] = fmaf(p, vr[j][i], acc[i]);
+        }
         m = mn;
     }
     __shared__ float sm[NW], sl[NW], sacc[NW][HD];
@@ -157,8 +182,13 @@ attention_partial_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
     }
 }
 
+// Combines the splits of one (row, head). blockDim = HD. With xq != NULL the head's HD outputs are
+// also written as activation digits (HD/32 block records) for the output projection that follows.
 template <int HD>
-__global__ void attention_merge_kernel(const float* __restrict__ partial, int nsplit, float* __restrict__ out) {
+__global__ void attention_merge_kernel(const float* __restrict__ partial, int nsplit, float* __restrict__ out,
+                                       uint32_t* __restrict__ xq, int heads) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t rh = blockIdx.x;                      // row * heads + head
     const float* p = partial + rh * nsplit * (HD + 2);
     float gm = -INFINITY;
@@ -168,14 +198,56 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int ns
         const float ms = p[s * (HD + 2)];
         if (ms != -INFINITY) l += p[s * (HD + 2) + 1] * expf(ms - gm);
     }
-    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
-        float a = 0.f;
-        for (int s = 0; s < nsplit; s++) {
-            const float ms = p[s * (HD + 2)];
-            if (ms != -INFINITY) a = fmaf(p[s * (HD + 2) + 2 + i], expf(ms - gm), a);
-        }
-        out[rh * HD + i] = a / l;
+    const int i = threadIdx.x;
+    float a = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+        const float ms = p[s * (HD + 2)];
+        if (ms != -INFINITY) a = fmaf(p[s * (HD + 2) + 2 + i], expf(ms - gm), a);
     }
+    const float v = a / l;
+    out[rh * HD + i] = v;
+    if (xq) {
+        const size_t row = rh / heads, h = rh % heads;
+        const size_t blk = (row * heads + h) * (HD / 32) + (i >> 5);     // block index within [rows][heads*HD/32]
+        xq_emit_warp(v, i & 31, xq + blk * kXqWords);
+    }
+}
+
+// RoPE on the Q and K parts of a fused [rows][q|k|v] buffer, then K and V into the cache
+// (cml_rope_forward src/nn/llm_ops.c:702-805 + cml_kv_cache_append :118-157 in one pass).
+// rotate_heads = 1 rotates only head 0 of Q and of K (C-ML's behaviour), -1 rotates all.
+template <typename KV>
+__global__ void qkv_rope_append_kernel(float* __restrict__ qkv, int stride, const int* __restrict__ row_seq,
+                                       const int* __restrict__ row_pos, int heads, int kv_heads, int hd, float base,
+                                       int rotate_all, int rotate_any, KV* __restrict__ kc, KV* __restrict__ vc, int max_seq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int r = blockIdx.x;
+    const int qw = heads * hd, kvw = kv_heads * hd, half = hd / 2;
+    float* row = qkv + (size_t)r * stride;
+    const float pos = (float)row_pos[r];
+    const size_t dst = ((size_t)row_seq[r] * max_seq + row_pos[r]) * kvw;
+    // pairs of Q and K: index space [0, (heads + kv_heads) * half)
+    for (int idx = threadIdx.x; idx < (heads + kv_heads) * half; idx += blockDim.x) {
+        const int hh = idx / half, i = idx - hh * half;
+        const bool is_k = hh >= heads;
+        const int h = is_k ? hh - heads : hh;
+        float* v = row + (is_k ? qw : 0) + (size_t)h * hd + 2 * i;
+        float a = v[0], b = v[1];
+        if (rotate_any && (rotate_all || h == 0)) {
+            const float freq = 1.0f / powf(base, (float)(2 * i) / (float)hd);
+            const float th = pos * freq;
+            const float c = cosf(th), s = sinf(th);
+            const float na = a * c - b * s, nb = a * s + b * c;
+            a = na; b = nb;
+            v[0] = a; v[1] = b;
+        }
+        if (is_k) {
+            kc[dst + (size_t)h * hd + 2 * i] = (KV)a;
+            kc[dst + (size_t)h * hd + 2 * i + 1] = (KV)b;
+        }
+    }
+    for (int i = threadIdx.x; i < kvw; i += blockDim.x) vc[dst + i] = (KV)row[qw + kvw + i];
 }
 
 // ---- greedy pick: first index holding the strict maximum of each row
@@ -346,9 +418,9 @@ extern "C" size_t cmlb200_attention_scratch_floats(int rows, int heads, int head
     return (size_t)rows * heads * splits * (head_dim + 2);
 }
 
-extern "C" int cmlb200_attention(const float* d_q, const void* d_kcache, const void* d_vcache, const int* d_row_seq,
-                                 const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq,
-                                 int max_limit, int kv_is_f32, float* d_out, float* d_scratch, int splits, void* stream) {
+static int attention_impl(const float* d_q, int q_stride, const void* d_kcache, const void* d_vcache, const int* d_row_seq,
+                          const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq,
+                          int max_limit, int kv_is_f32, float* d_out, uint32_t* d_xq, float* d_scratch, int splits, void* stream) {
     CMLB_REQUIRE(d_q && d_kcache && d_vcache && d_row_seq && d_row_limit && d_out && d_scratch, "cmlb200_attention: NULL argument");
     CMLB_REQUIRE(rows > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "cmlb200_attention: num_heads (%d) must be divisible by num_kv_heads (%d)", heads, kv_heads);
     CMLB_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 32, "cmlb200_attention: head_dim %d not in {32, 64, 128}", head_dim);
@@ -356,11 +428,16 @@ extern "C" int cmlb200_attention(const float* d_q, const void* d_kcache, const v
     const int chunk = (max_limit + 1 + splits - 1) / splits;
     dim3 grid(heads, rows, splits);
     cudaStream_t st = as_stream(stream);
-#define ATT_LAUNCH(KV, HD)                                                                                            \
-    attention_partial_kernel<KV, HD><<<grid, ATT_THREADS, 0, st>>>(d_q, (const KV*)d_kcache, (const KV*)d_vcache,   \
-                                                                   d_row_seq, d_row_limit, heads, kv_heads, max_seq, \
-                                                                   chunk, d_scratch);                                \
-    attention_merge_kernel<HD><<<rows * heads, HD, 0, st>>>(d_scratch, splits, d_out)
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t c1 = {}, c2 = {};
+    c1.gridDim = grid; c1.blockDim = dim3(ATT_THREADS); c1.stream = st; c1.attrs = pdl; c1.numAttrs = 1;
+    c2.gridDim = dim3(rows * heads); c2.blockDim = dim3(head_dim); c2.stream = st; c2.attrs = pdl; c2.numAttrs = 1;
+#define ATT_LAUNCH(KV, HD)                                                                                               \
+    CMLB_CUDA(cudaLaunchKernelEx(&c1, attention_partial_kernel<KV, HD>, d_q, (const KV*)d_kcache, (const KV*)d_vcache,  \
+                                 d_row_seq, d_row_limit, heads, kv_heads, max_seq, chunk, d_scratch, q_stride));        \
+    CMLB_CUDA(cudaLaunchKernelEx(&c2, attention_merge_kernel<HD>, (const float*)d_scratch, splits, d_out, d_xq, heads))
     if (kv_is_f32) {
         if (head_dim == 128) { ATT_LAUNCH(float, 128); } else if (head_dim == 64) { ATT_LAUNCH(float, 64); } else { ATT_LAUNCH(float, 32); }
     } else {
@@ -368,6 +445,51 @@ extern "C" int cmlb200_attention(const float* d_q, const void* d_kcache, const v
     }
 #undef ATT_LAUNCH
     CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_attention(const float* d_q, const void* d_kcache, const void* d_vcache, const int* d_row_seq,
+                                 const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq,
+                                 int max_limit, int kv_is_f32, float* d_out, float* d_scratch, int splits, void* stream) {
+    return attention_impl(d_q, heads * head_dim, d_kcache, d_vcache, d_row_seq, d_row_limit, rows, heads, kv_heads, head_dim,
+                          max_seq, max_limit, kv_is_f32, d_out, nullptr, d_scratch, splits, stream);
+}
+
+// Same with Q rows `q_stride` floats apart (Q inside a fused q|k|v buffer) and, when d_xq is not
+// NULL, the attention output also written as activation digits for cmlb200_gemv_xq.
+extern "C" int cmlb200_attention_ex(const float* d_q, int q_stride, const void* d_kcache, const void* d_vcache,
+                                    const int* d_row_seq, const int* d_row_limit, int rows, int heads, int kv_heads,
+                                    int head_dim, int max_seq, int max_limit, int kv_is_f32, float* d_out, void* d_xq,
+                                    float* d_scratch, int splits, void* stream) {
+    CMLB_REQUIRE(q_stride >= heads * head_dim, "cmlb200_attention_ex: q_stride %d smaller than a row of Q", q_stride);
+    return attention_impl(d_q, q_stride, d_kcache, d_vcache, d_row_seq, d_row_limit, rows, heads, kv_heads, head_dim, max_seq,
+                          max_limit, kv_is_f32, d_out, (uint32_t*)d_xq, d_scratch, splits, stream);
+}
+
+extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* d_row_seq, const int* d_row_pos, int rows,
+                                       int heads, int kv_heads, int head_dim, float base, int rotate_heads, void* d_kcache,
+                                       void* d_vcache, int max_seq, int kv_is_f32, void* stream) {
+    CMLB_REQUIRE(d_qkv && d_row_seq && d_row_pos && d_kcache && d_vcache, "cmlb200_qkv_rope_append: NULL argument");
+    CMLB_REQUIRE(rows > 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && head_dim % 2 == 0 && max_seq > 0 &&
+                     row_stride >= (heads + 2 * kv_heads) * head_dim,
+                 "cmlb200_qkv_rope_append: bad shape");
+    if (base <= 0.f) base = 10000.0f;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(256);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int rotate_any = rotate_heads != 0, rotate_all = rotate_heads < 0;
+    if (kv_is_f32)
+        CMLB_CUDA(cudaLaunchKernelEx(&cfg, qkv_rope_append_kernel<float>, d_qkv, row_stride, d_row_seq, d_row_pos, heads, kv_heads,
+                                     head_dim, base, rotate_all, rotate_any, (float*)d_kcache, (float*)d_vcache, max_seq));
+    else
+        CMLB_CUDA(cudaLaunchKernelEx(&cfg, qkv_rope_append_kernel<__half>, d_qkv, row_stride, d_row_seq, d_row_pos, heads, kv_heads,
+                                     head_dim, base, rotate_all, rotate_any, (__half*)d_kcache, (__half*)d_vcache, max_seq));
     return CMLB200_OK;
 }
 

@@ -23,11 +23,13 @@
 
 #define DEV(call) do { if (CML_DEV_FAIL((call), __func__)) return -1; } while (0)
 #define SKINNY_ROWS 32
-#define ATT_CHUNK 128
+#define ATT_CHUNK 64
 
 typedef struct DevLayer {
-    cmlb200_qmat wq, wk, wv, wo, wg, wu, wd;
+    cmlb200_qmat wqkv, wo, wg, wu, wd;     /* Q, K and V rows are stacked into one matrix at load */
     void *n1, *n2;                         /* fp16 norm weights */
+    uint8_t* pend[3];                      /* host blocks of q, k, v waiting for each other */
+    int pend_type;
 } DevLayer;
 
 typedef struct DevModel {
@@ -43,7 +45,9 @@ typedef struct DevModel {
     void *kc, *vc;                         /* [layers][n_seq][max_seq][kvw_l] */
     size_t kv_layer_elems;
     void* stream;
-    float *h, *nrm, *q, *k, *v, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch;
+    int qkv_w;                             /* qw_l + 2 * kvw_l */
+    float *h, *nrm, *qkv, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch;
+    void *xq_a, *xq_b, *xq_c;              /* activation digits: hidden-wide, attention-wide, FFN-wide */
     uint16_t *b_a, *b_b, *b_c, *b_d;       /* bf16 staging of the prefill path */
     int *d_tokens, *d_cur, *row_seq, *row_pos, *row_limit, *d_hist;
     int* h_cur;
@@ -116,16 +120,17 @@ static void dm_destroy(DevModel* d) {
     if (d->L) {
         for (int i = 0; i < d->key->num_layers; i++) {
             DevLayer* l = &d->L[i];
-            qmat_free(&l->wq); qmat_free(&l->wk); qmat_free(&l->wv); qmat_free(&l->wo);
+            qmat_free(&l->wqkv); qmat_free(&l->wo);
             qmat_free(&l->wg); qmat_free(&l->wu); qmat_free(&l->wd);
             cmlb200_free(l->n1); cmlb200_free(l->n2);
+            for (int k = 0; k < 3; k++) free(l->pend[k]);
         }
         free(d->L);
     }
     qmat_free(&d->lm_head);
-    void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->q, d->k, d->v, d->att, d->ffn, d->g, d->u, d->tmp,
+    void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->qkv, d->att, d->ffn, d->g, d->u, d->tmp,
                     d->logits, d->att_scratch, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
-                    d->row_pos, d->row_limit, d->d_hist};
+                    d->row_pos, d->row_limit, d->d_hist, d->xq_a, d->xq_b, d->xq_c};
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
     if (d->comm) cml_nccl_destroy(d->comm);
@@ -212,6 +217,7 @@ static int dm_alloc_buffers(DevModel* d) {
     d->qw_l = d->heads_l * d->hd;
     d->kvw_l = d->kvh_l * d->hd;
     d->inter_l = c->intermediate_size / d->tp;
+    d->qkv_w = d->qw_l + 2 * d->kvw_l;
     d->max_rows = c->max_seq_len > SKINNY_ROWS ? c->max_seq_len : SKINNY_ROWS;
     if (d->device >= 0) DEV(cmlb200_set_device(d->device));
     DEV(cmlb200_stream_create(&d->stream));
@@ -223,12 +229,13 @@ static int dm_alloc_buffers(DevModel* d) {
     DEV(cmlb200_malloc(&d->vc, kv_bytes));
     DEV(cmlb200_memset(d->kc, 0, kv_bytes, d->stream));
     DEV(cmlb200_memset(d->vc, 0, kv_bytes, d->stream));
-    const size_t wide = (size_t)(d->inter_l > d->qw_l ? d->inter_l : d->qw_l);
+    const size_t wide = (size_t)(d->inter_l > d->qkv_w ? d->inter_l : d->qkv_w);
     DEV(cmlb200_malloc((void**)&d->h, R * H * 4));
     DEV(cmlb200_malloc((void**)&d->nrm, R * H * 4));
-    DEV(cmlb200_malloc((void**)&d->q, R * d->qw_l * 4));
-    DEV(cmlb200_malloc((void**)&d->k, R * d->kvw_l * 4));
-    DEV(cmlb200_malloc((void**)&d->v, R * d->kvw_l * 4));
+    DEV(cmlb200_malloc((void**)&d->qkv, R * d->qkv_w * 4));
+    DEV(cmlb200_malloc(&d->xq_a, cmlb200_xq_bytes(4, H)));
+    DEV(cmlb200_malloc(&d->xq_b, cmlb200_xq_bytes(4, d->qw_l)));
+    DEV(cmlb200_malloc(&d->xq_c, cmlb200_xq_bytes(4, d->inter_l)));
     DEV(cmlb200_malloc((void**)&d->att, R * d->qw_l * 4));
     DEV(cmlb200_malloc((void**)&d->ffn, (size_t)SKINNY_ROWS * d->inter_l * 4));
     DEV(cmlb200_malloc((void**)&d->g, (size_t)SKINNY_ROWS * d->inter_l * 4));
@@ -411,13 +418,13 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
             }
         } else {
             /* projections: GGUF dims are (in_features, out_features) */
-            int out_f, in_f, by_rows = 1;
-            cmlb200_qmat* dst;
+            int out_f, in_f, by_rows = 1, qkv_slot = -1;
+            cmlb200_qmat* dst = NULL;
             Tensor** pub;
             switch (slot) {
-                case SLOT_Q: out_f = QW; in_f = H; dst = &d->L[layer].wq; pub = &model->layers[layer]->q_proj; break;
-                case SLOT_K: out_f = KVW; in_f = H; dst = &d->L[layer].wk; pub = &model->layers[layer]->k_proj; break;
-                case SLOT_V: out_f = KVW; in_f = H; dst = &d->L[layer].wv; pub = &model->layers[layer]->v_proj; break;
+                case SLOT_Q: out_f = QW; in_f = H; qkv_slot = 0; pub = &model->layers[layer]->q_proj; break;
+                case SLOT_K: out_f = KVW; in_f = H; qkv_slot = 1; pub = &model->layers[layer]->k_proj; break;
+                case SLOT_V: out_f = KVW; in_f = H; qkv_slot = 2; pub = &model->layers[layer]->v_proj; break;
                 case SLOT_O: out_f = H; in_f = QW; by_rows = 0; dst = &d->L[layer].wo; pub = &model->layers[layer]->o_proj; break;
                 case SLOT_G: out_f = I; in_f = H; dst = &d->L[layer].wg; pub = &model->layers[layer]->gate_proj; break;
                 case SLOT_U: out_f = I; in_f = H; dst = &d->L[layer].wu; pub = &model->layers[layer]->up_proj; break;
@@ -429,7 +436,38 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
             else if (info->ndim != 2 || info->shape[0] != in_f || info->shape[1] != out_f)
                 LOG_ERROR("cml_llama_load_gguf: tensor '%s' has dims (%lld, %lld), expected (in=%d, out=%d)", name,
                           (long long)info->shape[0], (long long)(info->ndim > 1 ? info->shape[1] : 0), in_f, out_f);
-            else {
+            else if (qkv_slot >= 0) {
+                /* Q, K, V: keep this rank's rows on the host until all three are there, then
+                 * upload them stacked as one [q | k | v] matrix (one GEMV instead of three). */
+                DevLayer* L = &d->L[layer];
+                int lr = out_f, lc = in_f;
+                uint8_t* sh = shard_blocks((const uint8_t*)raw, (int)info->type, out_f, in_f, d->tp, d->rank, 1, &lr, &lc);
+                const int have_other = L->pend[0] || L->pend[1] || L->pend[2];
+                if (sh && have_other && L->pend_type != (int)info->type) {
+                    LOG_ERROR("cml_llama_load_gguf: layer %d mixes block types across attn_q/k/v", layer);
+                    free(sh);
+                } else if (sh) {
+                    free(L->pend[qkv_slot]);
+                    L->pend[qkv_slot] = sh;
+                    L->pend_type = (int)info->type;
+                    rc = 0;
+                    if (L->pend[0] && L->pend[1] && L->pend[2]) {
+                        const size_t bb = gguf_quant_type_size(info->type), rowb = (size_t)(H / 32) * bb;
+                        const size_t qb = (size_t)d->qw_l * rowb, kb = (size_t)d->kvw_l * rowb;
+                        uint8_t* all = (uint8_t*)malloc(qb + 2 * kb);
+                        if (all) {
+                            memcpy(all, L->pend[0], qb);
+                            memcpy(all + qb, L->pend[1], kb);
+                            memcpy(all + qb + kb, L->pend[2], kb);
+                            qmat_free(&L->wqkv);
+                            rc = upload_qmat(d, (int)info->type, all, d->qkv_w, H, &L->wqkv);
+                            free(all);
+                        } else rc = -1;
+                        for (int k = 0; k < 3; k++) { free(L->pend[k]); L->pend[k] = NULL; }
+                    }
+                    if (!rc) { tensor_free(*pub); *pub = placeholder(in_f, out_f); }
+                }
+            } else {
                 qmat_free(dst);
                 if (d->tp > 1 && by_rows >= 0) {
                     int lr, lc;
@@ -455,7 +493,7 @@ static int model_ready(const CMLLLaMAModel* m, const DevModel* d) {
     if (!d || !d->embed || !d->fnorm || !d->lm_head.qs) return 0;
     for (int i = 0; i < m->num_layers; i++) {
         const DevLayer* l = &d->L[i];
-        if (!l->wq.qs || !l->wk.qs || !l->wv.qs || !l->wo.qs || !l->wg.qs || !l->wu.qs || !l->wd.qs || !l->n1 || !l->n2) return 0;
+        if (!l->wqkv.qs || !l->wo.qs || !l->wg.qs || !l->wu.qs || !l->wd.qs || !l->n1 || !l->n2) return 0;
     }
     return 1;
 }
@@ -500,56 +538,68 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
     const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32);
+    const int tiny = rows <= 2;                 /* integer-dot GEMV with digits shared between projections */
     void* st = d->stream;
     DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
     DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));
+    const int max_limit_raw = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
+    const int max_limit = max_limit_raw < c->max_seq_len ? max_limit_raw : c->max_seq_len - 1;
     int splits = 1;
     if (rows <= SKINNY_ROWS) {
-        const int lim = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
-        splits = (lim + ATT_CHUNK) / ATT_CHUNK;
+        splits = (max_limit + ATT_CHUNK) / ATT_CHUNK;
         if (splits > d->att_splits_cap) splits = d->att_splits_cap;
         if (splits < 1) splits = 1;
     }
-    const int max_limit = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
+    /* With tensor parallelism head 0 lives on rank 0 only, so C-ML's "head 0 only" rotation
+     * touches nothing on the other ranks. */
+    const int rotate = quirks ? (d->rank == 0 ? 1 : 0) : -1;
     const size_t esz = kvf32 ? 4 : 2;
     for (int li = 0; li < m->num_layers; li++) {
         const DevLayer* L = &d->L[li];
         void* kc = (char*)d->kc + (size_t)li * d->kv_layer_elems * esz;
         void* vc = (char*)d->vc + (size_t)li * d->kv_layer_elems * esz;
-        if (skinny) {
+        /* ---- attention block: norm -> fused QKV projection -> RoPE + cache append -> attention */
+        if (tiny) {
+            DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
+            DEV(cmlb200_gemv_xq(&L->wqkv, NULL, d->xq_a, d->qkv, rows, 0, st));
+        } else if (skinny) {
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
-            if (lin_f32(d, &L->wq, d->nrm, d->q, rows, 0) || lin_f32(d, &L->wk, d->nrm, d->k, rows, 0) || lin_f32(d, &L->wv, d->nrm, d->v, rows, 0)) return -1;
+            if (lin_f32(d, &L->wqkv, d->nrm, d->qkv, rows, 0)) return -1;
         } else {
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
-            DEV(cmlb200_gemm_bf16(&L->wq, d->b_a, d->b_b, rows, st));
-            DEV(cmlb200_bf16_to_f32(d->b_b, d->q, (size_t)rows * d->qw_l, st));
-            DEV(cmlb200_gemm_bf16(&L->wk, d->b_a, d->b_b, rows, st));
-            DEV(cmlb200_bf16_to_f32(d->b_b, d->k, (size_t)rows * d->kvw_l, st));
-            DEV(cmlb200_gemm_bf16(&L->wv, d->b_a, d->b_b, rows, st));
-            DEV(cmlb200_bf16_to_f32(d->b_b, d->v, (size_t)rows * d->kvw_l, st));
+            DEV(cmlb200_gemm_bf16(&L->wqkv, d->b_a, d->b_b, rows, st));
+            DEV(cmlb200_bf16_to_f32(d->b_b, d->qkv, (size_t)rows * d->qkv_w, st));
         }
-        /* With tensor parallelism head 0 lives on rank 0 only, so the "head 0 only" quirk
-         * rotates nothing on the other ranks. */
-        if (!quirks || d->rank == 0) {
-            DEV(cmlb200_rope(d->q, d->row_pos, rows, d->qw_l, d->hd, c->rope_theta, !quirks, st));
-            DEV(cmlb200_rope(d->k, d->row_pos, rows, d->kvw_l, d->hd, c->rope_theta, !quirks, st));
-        }
-        DEV(cmlb200_kv_append(d->k, d->v, kc, vc, d->row_seq, d->row_pos, rows, d->kvw_l, c->max_seq_len, kvf32, st));
-        DEV(cmlb200_attention(d->q, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd, c->max_seq_len,
-                              max_limit < c->max_seq_len ? max_limit : c->max_seq_len - 1, kvf32, d->att, d->att_scratch, splits, st));
-        if (skinny) {
+        DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
+                                    rotate, kc, vc, c->max_seq_len, kvf32, st));
+        DEV(cmlb200_attention_ex(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd,
+                                 c->max_seq_len, max_limit, kvf32, d->att, tiny ? d->xq_b : NULL, d->att_scratch, splits, st));
+        /* ---- output projection + residual, FFN + residual */
+        if (tiny) {
+            if (d->tp == 1) DEV(cmlb200_gemv_xq(&L->wo, NULL, d->xq_b, d->h, rows, 1, st));
+            else {
+                DEV(cmlb200_gemv_xq(&L->wo, NULL, d->xq_b, d->tmp, rows, 0, st));
+                if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * H, st)) return -1;
+                DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * H, st));
+            }
+            DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
+            DEV(cmlb200_gemv_xq(&L->wg, &L->wu, d->xq_a, d->ffn, rows, 2, st));
+            DEV(cmlb200_x_digits(d->ffn, rows, d->inter_l, d->xq_c, st));
+            if (d->tp == 1) DEV(cmlb200_gemv_xq(&L->wd, NULL, d->xq_c, d->h, rows, 1, st));
+            else {
+                DEV(cmlb200_gemv_xq(&L->wd, NULL, d->xq_c, d->tmp, rows, 0, st));
+                if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * H, st)) return -1;
+                DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * H, st));
+            }
+        } else if (skinny) {
             if (proj_residual_f32(d, &L->wo, d->att, rows)) return -1;
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
             for (int r0 = 0; r0 < rows; r0 += SKINNY_ROWS) {
                 const int mr = rows - r0 < SKINNY_ROWS ? rows - r0 : SKINNY_ROWS;
                 const float* xp = d->nrm + (size_t)r0 * H;
-                if (mr <= 2) DEV(cmlb200_gemv_swiglu(&L->wg, &L->wu, xp, d->ffn, mr, st));
-                else {
-                    DEV(cmlb200_gemv(&L->wg, xp, d->g, mr, st));
-                    DEV(cmlb200_gemv(&L->wu, xp, d->u, mr, st));
-                    DEV(cmlb200_swiglu_f32(d->g, d->u, d->ffn, (size_t)mr * d->inter_l, st));
-                }
-                /* down projection of this chunk, accumulated into its rows of h */
+                DEV(cmlb200_gemv(&L->wg, xp, d->g, mr, st));
+                DEV(cmlb200_gemv(&L->wu, xp, d->u, mr, st));
+                DEV(cmlb200_swiglu_f32(d->g, d->u, d->ffn, (size_t)mr * d->inter_l, st));
                 if (d->tp == 1) DEV(cmlb200_gemv_accum(&L->wd, d->ffn, d->h + (size_t)r0 * H, mr, st));
                 else {
                     DEV(cmlb200_gemv(&L->wd, d->ffn, d->tmp, mr, st));
@@ -567,7 +617,10 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
             if (proj_residual_bf16(d, &L->wd, d->b_c, rows)) return -1;
         }
     }
-    if (skinny) {
+    if (tiny) {
+        DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
+        DEV(cmlb200_gemv_xq(&d->lm_head, NULL, d->xq_a, d->logits, rows, 0, st));
+    } else if (skinny) {
         DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
         if (lin_f32(d, &d->lm_head, d->nrm, d->logits, rows, 0)) return -1;
     } else {

@@ -120,6 +120,19 @@ int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const fl
 /* y += x . W^T (residual add fused; src/nn/llama.c:523-530 and :538-543). */
 int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
 
+/* The same kernels with the activation "digits" (the block-fixed-point form of x the integer-dot
+ * GEMV consumes) made explicit, so that one set of digits serves several projections of the same
+ * activations (Q/K/V, gate/up) and can be produced by the kernel that makes the activations:
+ *   cmlb200_xq_bytes        bytes of digit scratch for M rows of K values
+ *   cmlb200_x_digits        x[M,K] fp32 -> digits
+ *   cmlb200_rmsnorm_digits  rms_norm (src/nn/llama.c:71-124) writing fp32 (optional) and digits
+ *   cmlb200_gemv_xq         y (= | += | swiglu) from digits; M <= 4; epi 0 store, 1 accumulate,
+ *                           2 SwiGLU with W2 as the up projection */
+size_t cmlb200_xq_bytes(int M, int K);
+int cmlb200_x_digits(const float* d_x, int M, int K, void* d_xq, void* stream);
+int cmlb200_rmsnorm_digits(const float* d_x, const uint16_t* d_w_f16, int rows, int dim, float eps, float* d_out_f32, void* d_xq, void* stream);
+int cmlb200_gemv_xq(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* d_xq, float* d_y, int M, int epi, void* stream);
+
 /* The decode GEMV for callers that cannot allocate device memory at run time (a serving process
  * that gave the whole GPU to its own arena, a real-time loop that must not take the allocator
  * lock, a sandbox that filters CUDA allocation calls). It has no counterpart in C-ML. Same result
@@ -188,6 +201,12 @@ int cmlb200_kv_append(const float* d_k, const float* d_v, void* d_kcache, void* 
  * cmlb200_attention_scratch_floats(rows, heads, head_dim, splits) floats. */
 size_t cmlb200_attention_scratch_floats(int rows, int heads, int head_dim, int splits);
 int cmlb200_attention(const float* d_q, const void* d_kcache, const void* d_vcache, const int* d_row_seq, const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq, int max_limit, int kv_is_f32, float* d_out, float* d_scratch, int splits, void* stream);
+/* Fused variants used by the decode step: Q rows `q_stride` floats apart (Q inside a fused q|k|v
+ * buffer), attention output optionally also written as activation digits (d_xq, may be NULL); and
+ * RoPE on the Q and K parts of such a buffer followed by the K/V cache append in one launch.
+ * rotate_heads: 0 none, 1 head 0 of Q and K only (C-ML's behaviour), -1 every head. */
+int cmlb200_attention_ex(const float* d_q, int q_stride, const void* d_kcache, const void* d_vcache, const int* d_row_seq, const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq, int max_limit, int kv_is_f32, float* d_out, void* d_xq, float* d_scratch, int splits, void* stream);
+int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* d_row_seq, const int* d_row_pos, int rows, int heads, int kv_heads, int head_dim, float base, int rotate_heads, void* d_kcache, void* d_vcache, int max_seq, int kv_is_f32, void* stream);
 /* Greedy branch of cml_llama_sample_token (src/nn/llama.c:650-660): first index of the maximum. */
 int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream);
 /* Row bookkeeping kept on the device so that a decode step replays as a CUDA graph.
