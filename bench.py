@@ -207,6 +207,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--copies", type=int, default=COPIES)
     ap.add_argument("--skip-llama", action="store_true", help="skip the LLaMA-7B decode leg")
+    ap.add_argument("--profile-llama", action="store_true",
+                    help="small run for ncu: 4-layer LLaMA-7B-shaped model, 512-token prefill, 6 decode steps, batch 1")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
     args = ap.parse_args()
@@ -226,6 +228,11 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.profile_llama:
+        cfg = dict(LLAMA_7B, layers=4)
+        print(json.dumps({"profile_run": True, **llama_leg(pkg, synth, new_tokens=6, batches=(1,), cfg=cfg, tag="llama7b_4layers")}))
+        return
 
     rng = np.random.default_rng(1234 + rank)
     copies = args.copies

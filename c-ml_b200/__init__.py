@@ -191,6 +191,7 @@ _sig("cml_llama_sample_token", ci, TP, C.POINTER(GenerationConfig))
 _sig("cml_llama_reset", None, MP)
 _sig("cml_llama_print_config", None, C.POINTER(LlamaConfig))
 _sig("cml_llama_set_options", ci, MP, ci, ci)
+_sig("cml_tp_shard_qblocks", ci, ci, vp, ci, ci, ci, ci, ci, vp)
 _sig("cml_llama_tp_unique_id", ci, vp)
 _sig("cml_llama_tp_init", ci, MP, vp, ci)
 REFERENCE_QUIRKS, KV_FP32, ALL_LOGITS_FP32 = 1, 2, 4

@@ -441,16 +441,16 @@ __device__ __forceinline__ void emit_block_digits(const float (&e)[4], int sub, 
 
 // RMSNorm (src/nn/llama.c:71-124) of one row per CTA; writes the normalised row as fp32 (if asked)
 // and as digit records. dim % 32 == 0.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rmsnorm_digits_kernel(const float* __restrict__ x, const __half* __restrict__ w, int dim, float eps, float* __restrict__ out,
                       uint32_t* __restrict__ xq) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    __shared__ float red[8];
+    __shared__ float red[32];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)r * dim;
     float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < dim; i += 1024) {
+    for (int i = threadIdx.x * 4; i < dim; i += 4096) {
         const float4 v = *reinterpret_cast<const float4*>(xr + i);
         ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
     }
@@ -460,12 +460,12 @@ rmsnorm_digits_kernel(const float* __restrict__ x, const __half* __restrict__ w,
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) tot += red[i];
+    for (int i = 0; i < 32; i++) tot += red[i];
     const float inv = 1.0f / sqrtf(tot / (float)dim + eps);
     const int sub = threadIdx.x & 7;
     const unsigned gmask = 0xffu << (threadIdx.x & 24);
     const int nblk = dim / 32;
-    for (int b = threadIdx.x >> 3; b < nblk; b += 32) {
+    for (int b = threadIdx.x >> 3; b < nblk; b += 128) {
         const int i = b * 32 + sub * 4;
         const float4 v = *reinterpret_cast<const float4*>(xr + i);
         const float e[4] = {v.x * inv * __half2float(w[i]), v.y * inv * __half2float(w[i + 1]),
@@ -490,7 +490,7 @@ extern "C" int cmlb200_rmsnorm_digits(const float* d_x, const uint16_t* d_w_f16,
     CMLB_REQUIRE(d_x && d_w_f16 && d_xq && rows >= 1 && dim > 0 && dim % 32 == 0, "cmlb200_rmsnorm_digits: bad argument");
     CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_xq & 15) == 0 && ((uintptr_t)d_out_f32 & 15) == 0,
                  "cmlb200_rmsnorm_digits: pointers must be 16-byte aligned");
-    return launch_pdl(rmsnorm_digits_kernel, dim3(rows), dim3(256), 0, as_stream(stream), d_x, (const __half*)d_w_f16, dim, eps,
+    return launch_pdl(rmsnorm_digits_kernel, dim3(rows), dim3(1024), 0, as_stream(stream), d_x, (const __half*)d_w_f16, dim, eps,
                       d_out_f32, (uint32_t*)d_xq);
 }
 

@@ -222,32 +222,34 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ qkv, int stride, cons
                                        int rotate_all, int rotate_any, KV* __restrict__ kc, KV* __restrict__ vc, int max_seq) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int r = blockIdx.x;
-    const int qw = heads * hd, kvw = kv_heads * hd, half = hd / 2;
+    // grid = (rows, heads + 2*kv_heads): one CTA per Q head, K head or V head; thread i owns pair i
+    const int r = blockIdx.x, hh = blockIdx.y, i = threadIdx.x;
+    const int qw = heads * hd, kvw = kv_heads * hd;
     float* row = qkv + (size_t)r * stride;
-    const float pos = (float)row_pos[r];
     const size_t dst = ((size_t)row_seq[r] * max_seq + row_pos[r]) * kvw;
-    // pairs of Q and K: index space [0, (heads + kv_heads) * half)
-    for (int idx = threadIdx.x; idx < (heads + kv_heads) * half; idx += blockDim.x) {
-        const int hh = idx / half, i = idx - hh * half;
-        const bool is_k = hh >= heads;
-        const int h = is_k ? hh - heads : hh;
-        float* v = row + (is_k ? qw : 0) + (size_t)h * hd + 2 * i;
-        float a = v[0], b = v[1];
-        if (rotate_any && (rotate_all || h == 0)) {
-            const float freq = 1.0f / powf(base, (float)(2 * i) / (float)hd);
-            const float th = pos * freq;
-            const float c = cosf(th), s = sinf(th);
-            const float na = a * c - b * s, nb = a * s + b * c;
-            a = na; b = nb;
-            v[0] = a; v[1] = b;
-        }
-        if (is_k) {
-            kc[dst + (size_t)h * hd + 2 * i] = (KV)a;
-            kc[dst + (size_t)h * hd + 2 * i + 1] = (KV)b;
-        }
+    if (hh >= heads + kv_heads) {                                   // V head: straight copy into the cache
+        const int h = hh - heads - kv_heads;
+        const float* v = row + qw + kvw + (size_t)h * hd + 2 * i;
+        vc[dst + (size_t)h * hd + 2 * i] = (KV)v[0];
+        vc[dst + (size_t)h * hd + 2 * i + 1] = (KV)v[1];
+        return;
     }
-    for (int i = threadIdx.x; i < kvw; i += blockDim.x) vc[dst + i] = (KV)row[qw + kvw + i];
+    const bool is_k = hh >= heads;
+    const int h = is_k ? hh - heads : hh;
+    float* v = row + (is_k ? qw : 0) + (size_t)h * hd + 2 * i;
+    float a = v[0], b = v[1];
+    if (rotate_any && (rotate_all || h == 0)) {
+        const float freq = 1.0f / powf(base, (float)(2 * i) / (float)hd);
+        const float th = (float)row_pos[r] * freq;
+        const float c = cosf(th), sn = sinf(th);
+        const float na = a * c - b * sn, nb = a * sn + b * c;
+        a = na; b = nb;
+        v[0] = a; v[1] = b;
+    }
+    if (is_k) {
+        kc[dst + (size_t)h * hd + 2 * i] = (KV)a;
+        kc[dst + (size_t)h * hd + 2 * i + 1] = (KV)b;
+    }
 }
 
 // ---- greedy pick: first index holding the strict maximum of each row
@@ -475,8 +477,8 @@ extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* 
                  "cmlb200_qkv_rope_append: bad shape");
     if (base <= 0.f) base = 10000.0f;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rows);
-    cfg.blockDim = dim3(256);
+    cfg.gridDim = dim3(rows, heads + 2 * kv_heads);
+    cfg.blockDim = dim3(head_dim / 2);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -358,22 +358,36 @@ static int classify(const char* name, int* layer) {
     return SLOT_NONE;
 }
 
-/* Cuts this rank's shard out of a full [rows, cols] block array: `by_rows` keeps rows
- * [rank*rows/tp, ...), otherwise block columns [rank*cols/tp, ...) of every row. */
-static uint8_t* shard_blocks(const uint8_t* full, int type, int rows, int cols, int tp, int rank, int by_rows, int* orow, int* ocol) {
+/* cml_tp_shard_weight (src/distributed/tensor_parallel.c:25-101) on quantized blocks: dim 0 keeps
+ * rows [rank*rows/tp, (rank+1)*rows/tp), dim 1 keeps columns [rank*cols/tp, (rank+1)*cols/tp) of
+ * every row, which must fall on block boundaries. Same argument checks, -1 on failure. */
+int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int dim, int tp_size, int tp_rank, void* out) {
     const size_t bb = gguf_quant_type_size((GGUFTensorType)type);
+    if (!blocks || !out) { LOG_ERROR("cml_tp_shard_qblocks: NULL argument"); return -1; }
+    if (!bb || gguf_quant_block_size((GGUFTensorType)type) != 32) { LOG_ERROR("cml_tp_shard_qblocks: type %d is not a 32-element block type", type); return -1; }
+    if (dim != 0 && dim != 1) { LOG_ERROR("cml_tp_shard_qblocks: dim must be 0 or 1, got %d", dim); return -1; }
+    if (tp_size <= 0 || tp_rank < 0 || tp_rank >= tp_size) { LOG_ERROR("cml_tp_shard_qblocks: invalid tp_size=%d or tp_rank=%d", tp_size, tp_rank); return -1; }
+    if (rows <= 0 || cols <= 0 || cols % 32) { LOG_ERROR("cml_tp_shard_qblocks: bad shape %dx%d", rows, cols); return -1; }
     const int nblk = cols / 32;
-    if (by_rows) {
-        *orow = rows / tp; *ocol = cols;
-        uint8_t* out = (uint8_t*)malloc((size_t)*orow * nblk * bb);
-        if (out) memcpy(out, full + (size_t)rank * *orow * nblk * bb, (size_t)*orow * nblk * bb);
-        return out;
+    const uint8_t* full = (const uint8_t*)blocks;
+    uint8_t* dst = (uint8_t*)out;
+    if (dim == 0) {
+        if (rows % tp_size) { LOG_ERROR("cml_tp_shard_qblocks: rows (%d) not divisible by tp_size (%d)", rows, tp_size); return -1; }
+        const size_t n = (size_t)(rows / tp_size) * nblk * bb;
+        memcpy(dst, full + (size_t)tp_rank * n, n);
+    } else {
+        if (cols % tp_size || (cols / tp_size) % 32) { LOG_ERROR("cml_tp_shard_qblocks: cols (%d) must split into %d multiples of 32", cols, tp_size); return -1; }
+        const int lb = nblk / tp_size;
+        for (int r = 0; r < rows; r++) memcpy(dst + (size_t)r * lb * bb, full + ((size_t)r * nblk + (size_t)tp_rank * lb) * bb, (size_t)lb * bb);
     }
-    *orow = rows; *ocol = cols / tp;
-    const int lb = nblk / tp;
-    uint8_t* out = (uint8_t*)malloc((size_t)rows * lb * bb);
-    if (out)
-        for (int r = 0; r < rows; r++) memcpy(out + (size_t)r * lb * bb, full + ((size_t)r * nblk + (size_t)rank * lb) * bb, (size_t)lb * bb);
+    return 0;
+}
+
+static uint8_t* shard_blocks(const uint8_t* full, int type, int rows, int cols, int tp, int rank, int by_rows, int* orow, int* ocol) {
+    *orow = by_rows ? rows / tp : rows;
+    *ocol = by_rows ? cols : cols / tp;
+    uint8_t* out = (uint8_t*)malloc((size_t)*orow * (*ocol / 32) * gguf_quant_type_size((GGUFTensorType)type));
+    if (out && cml_tp_shard_qblocks(type, full, rows, cols, by_rows ? 0 : 1, tp, rank, out)) { free(out); out = NULL; }
     return out;
 }
 
