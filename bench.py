@@ -382,7 +382,7 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "host fp32 activations -> H2D -> GEMV -> D2H host result, synchronised per call; weights resident"},
-            "gpu_launches": 2 * timed_launches,   # activation-digit kernel + GEMV kernel per call
+            "gpu_launches": timed_launches,       # one kernel per call (activation digits are made inside it)
             "clocks": clocks,
         }
         print(json.dumps(line))

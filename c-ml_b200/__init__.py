@@ -58,11 +58,17 @@ _sig("cmlb200_gemv", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_noalloc", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_accum", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_swiglu", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, ci, vp)
+_sig("cmlb200_xq_bytes", sz, ci, ci)
+_sig("cmlb200_x_digits", ci, vp, ci, ci, vp, vp)
+_sig("cmlb200_rmsnorm_digits", ci, vp, vp, ci, ci, C.c_float, vp, vp, vp)
+_sig("cmlb200_gemv_xq", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, ci, ci, vp)
+_sig("cmlb200_gemv_rmsnorm", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, C.c_float, vp, ci, ci, vp)
 _sig("cmlb200_tiles_bytes", sz, ci, ci, ci)
 _sig("cmlb200_repack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_unrepack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_gemv_tiles", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemv_tiles_status", ci, C.POINTER(ci), ci)
+_sig("cmlb200_gemv_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_gemm_bf16", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemm_bf16_splitk", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemm_status", ci, C.POINTER(ci), ci)

@@ -45,10 +45,20 @@ __device__ __forceinline__ float cml_half_to_float(uint16_t h) {
 }
 
 // Activation "digits" consumed by the integer-dot GEMV: per 32-element block of x a record of
-// kXqWords 32-bit words: three planes of 8 words (signed 7-bit digits d0, d1, d2 of the 21-bit
-// block-fixed-point value, 4 per word), the block scale (fp32 bits), the block sum (int32), 2 pad.
+// kXqWords 32-bit words: three planes of 8 words (signed 8-bit digits d0, d1, d2 of the 24-bit
+// block-fixed-point value X = d0*65536 + d1*256 + d2, 4 elements per word), the block scale
+// (fp32 bits) and 3 pad words (records stay 16-byte aligned; the 28-word stride is
+// bank-conflict-free for 128-bit shared-memory reads by consecutive lanes).
 constexpr int kXqWords = 28;
-constexpr int kXqFull = (1 << 20) - 1;
+constexpr int kXqFull = 127 * 65536 + 127 * 256 + 127;      // largest |X| whose balanced digits all fit int8
+
+// X = d0*65536 + d1*256 + d2 with d1, d2 in [-128, 127]; |X| <= kXqFull keeps d0 in [-127, 127].
+__device__ __forceinline__ void xq_split(int X, int& d0, int& d1, int& d2) {
+    d2 = ((X + 128) & 255) - 128;
+    const int X1 = (X - d2) >> 8;
+    d1 = ((X1 + 128) & 255) - 128;
+    d0 = (X1 - d1) >> 8;
+}
 
 // One warp = one block: lane l holds element l. Writes the block's record at dst.
 __device__ __forceinline__ void xq_emit_warp(float v, int lane, uint32_t* dst) {
@@ -58,15 +68,10 @@ __device__ __forceinline__ void xq_emit_warp(float v, int lane, uint32_t* dst) {
     const float inv = amax > 0.f ? (float)kXqFull / amax : 0.f;
     int X = __float2int_rn(v * inv);
     X = max(-kXqFull, min(kXqFull, X));
-    const int d2 = ((X + 64) & 127) - 64;
-    const int X1 = (X - d2) >> 7;
-    const int d1 = ((X1 + 64) & 127) - 64;
-    const int d0 = (X1 - d1) >> 7;
-    int xsum = X;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) xsum += __shfl_xor_sync(0xffffffffu, xsum, o);
-    uint32_t b0 = (uint32_t)(d0 & 0xFF) << (8 * (lane & 3)), b1 = (uint32_t)(d1 & 0xFF) << (8 * (lane & 3)),
-             b2 = (uint32_t)(d2 & 0xFF) << (8 * (lane & 3));
+    int d0, d1, d2;
+    xq_split(X, d0, d1, d2);
+    const int sh = 8 * (lane & 3);
+    uint32_t b0 = (uint32_t)(d0 & 0xFF) << sh, b1 = (uint32_t)(d1 & 0xFF) << sh, b2 = (uint32_t)(d2 & 0xFF) << sh;
 #pragma unroll
     for (int o = 1; o < 4; o <<= 1) {
         b0 |= __shfl_xor_sync(0xffffffffu, b0, o);
@@ -78,10 +83,31 @@ __device__ __forceinline__ void xq_emit_warp(float v, int lane, uint32_t* dst) {
         dst[8 + (lane >> 2)] = b1;
         dst[16 + (lane >> 2)] = b2;
     }
-    if (lane == 0) {
-        dst[24] = __float_as_uint(amax / (float)kXqFull);
-        dst[25] = (uint32_t)xsum;
+    if (lane == 0) dst[24] = __float_as_uint(amax / (float)kXqFull);
+}
+
+// 8 lanes (sub = 0..7; gmask = their lane mask) turn the 32 values of one block, 4 per lane, into
+// its record at dst (global or shared memory).
+__device__ __forceinline__ void xq_emit_oct(const float (&e)[4], int sub, unsigned gmask, uint32_t* dst) {
+    float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+    const float inv = amax > 0.f ? (float)kXqFull / amax : 0.f;
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int X = __float2int_rn(e[i] * inv);
+        X = max(-kXqFull, min(kXqFull, X));
+        int d0, d1, d2;
+        xq_split(X, d0, d1, d2);
+        w0 |= (uint32_t)(d0 & 0xFF) << (8 * i);
+        w1 |= (uint32_t)(d1 & 0xFF) << (8 * i);
+        w2 |= (uint32_t)(d2 & 0xFF) << (8 * i);
     }
+    dst[sub] = w0;
+    dst[8 + sub] = w1;
+    dst[16 + sub] = w2;
+    if (sub == 0) dst[24] = __float_as_uint(amax / (float)kXqFull);
 }
 
 static inline int cmlb_num_sms() {

@@ -10,8 +10,8 @@
 #include "common.cuh"
 
 // gemv_dp4a.cu: the integer-dot kernels for Q4_0 / Q8_0 at small M
-int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint32_t* xq, float* y,
-                       int M, int epi, cudaStream_t st);
+int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
+                       const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
 size_t cmlb200_xq_bytes_(int M, int K);
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 
@@ -252,7 +252,7 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     if (W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 &&
         ((uintptr_t)y & 15) == 0)
         return cmlb200_gemv_tc_(W, x, y, M, EPI == EPI_ACCUM, st);
-    if (W->type != CMLB200_NF4 && M <= 4) return cmlb200_gemv_dp4a_(W, W2, x, nullptr, y, M, EPI, st);
+    if (W->type != CMLB200_NF4 && M <= 4) return cmlb200_gemv_dp4a_(W, W2, x, nullptr, 0.f, nullptr, y, M, EPI, st);
     switch (W->type) {
         case CMLB200_Q8_0: return gemv_type<CMLB200_Q8_0, EPI>(W, W2, x, y, M, st);
         case CMLB200_Q4_0: return gemv_type<CMLB200_Q4_0, EPI>(W, W2, x, y, M, st);

@@ -127,11 +127,20 @@ int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int 
  *   cmlb200_x_digits        x[M,K] fp32 -> digits
  *   cmlb200_rmsnorm_digits  rms_norm (src/nn/llama.c:71-124) writing fp32 (optional) and digits
  *   cmlb200_gemv_xq         y (= | += | swiglu) from digits; M <= 4; epi 0 store, 1 accumulate,
- *                           2 SwiGLU with W2 as the up projection */
+ *                           2 SwiGLU with W2 as the up projection
+ *   cmlb200_gemv_rmsnorm    the same from fp32 x that is RMS-normalised (src/nn/llama.c:71-124)
+ *                           inside the GEMV launch: rms_norm followed by a projection
+ *                           (src/nn/llama.c:461-470, 535-537, 580-583) in one kernel */
 size_t cmlb200_xq_bytes(int M, int K);
 int cmlb200_x_digits(const float* d_x, int M, int K, void* d_xq, void* stream);
 int cmlb200_rmsnorm_digits(const float* d_x, const uint16_t* d_w_f16, int rows, int dim, float eps, float* d_out_f32, void* d_xq, void* stream);
 int cmlb200_gemv_xq(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* d_xq, float* d_y, int M, int epi, void* stream);
+int cmlb200_gemv_rmsnorm(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* d_x, const uint16_t* d_norm_w_f16, float eps,
+                         float* d_y, int M, int epi, void* stream);
+/* The M <= 4 kernels wait for their shared-memory copies with a bounded spin. Synchronises the
+ * device and stores 0 in *status if every wait so far completed, else which buffer gave up (the
+ * outputs of that launch are then invalid); reset != 0 clears the word. */
+int cmlb200_gemv_status(int* status, int reset);
 
 /* The decode GEMV for callers that cannot allocate device memory at run time (a serving process
  * that gave the whole GPU to its own arena, a real-time loop that must not take the allocator

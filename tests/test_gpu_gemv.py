@@ -9,6 +9,8 @@ from conftest import rel_err, rel_err_inf
 from gpu_util import make_weight, stream_ptr, to_dev
 
 pytestmark = pytest.mark.gpu
+# M <= 4 rounds x to 24 bits relative to each 32-block maximum: as good as fp32 accumulation
+DIGIT_TOL = 1e-5
 TOL = 2e-3
 
 
@@ -46,7 +48,7 @@ def test_gemv_config_shapes_sampled_rows(pkg, synth, ob, orc, torch_dev, kind, N
     rows = rng.choice(N, 96, replace=False)
     want = ob.linear_nt(orc, x, Wf[rows])
     scale = np.abs(x @ Wf.T).max()
-    assert np.abs(got[:, rows] - want).max() / scale <= 1e-5
+    assert np.abs(got[:, rows] - want).max() / scale <= DIGIT_TOL
     assert rel_err(got[:, rows], want) <= TOL
 
 
@@ -60,12 +62,12 @@ def test_gemv_linearity_at_full_size(pkg, synth, ob, orc, torch_dev):
     y1 = _run(pkg, pkg.lib.cmlb200_gemv, W, x1, N, torch_dev)
     y2 = _run(pkg, pkg.lib.cmlb200_gemv, W, x2, N, torch_dev)
     y3 = _run(pkg, pkg.lib.cmlb200_gemv, W, (np.float32(0.5) * x1 + x2), N, torch_dev)
-    assert rel_err_inf(y3, 0.5 * y1 + y2) <= 1e-5
+    assert rel_err_inf(y3, 0.5 * y1 + y2) <= DIGIT_TOL
     # batching is row-independent: M=8 output rows equal eight M=1 calls
     X = rng.standard_normal((8, K)).astype(np.float32)
     Y = _run(pkg, pkg.lib.cmlb200_gemv, W, X, N, torch_dev)
     for m in (0, 3, 7):
-        assert rel_err_inf(Y[m:m + 1], _run(pkg, pkg.lib.cmlb200_gemv, W, X[m:m + 1], N, torch_dev)) <= 1e-5
+        assert rel_err_inf(Y[m:m + 1], _run(pkg, pkg.lib.cmlb200_gemv, W, X[m:m + 1], N, torch_dev)) <= DIGIT_TOL
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
@@ -103,7 +105,7 @@ def test_gemv_matches_stored_reference_output(pkg, golden, torch_dev):
         blocks[~finite, :2] = 0                       # the generator zeroed non-finite weights
         W = DevQMat.from_gguf(pkg, torch_dev, qtype, np.ascontiguousarray(blocks.reshape(-1)), 8, 256)
         got = _run(pkg, pkg.lib.cmlb200_gemv, W, golden[f"{name}_x"], 8, torch_dev)
-        assert rel_err_inf(got, golden[f"{name}_linear_y"]) <= 1e-5
+        assert rel_err_inf(got, golden[f"{name}_linear_y"]) <= DIGIT_TOL
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
@@ -123,3 +125,46 @@ def test_gemv_with_subnormal_scales_follows_reference_quirk(pkg, synth, ob, orc,
     for M in (1, 2, 8):
         x = rng.standard_normal((M, K)).astype(np.float32)
         assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev), ob.linear_nt(orc, x, Wf)) <= TOL
+
+
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("K", [512, 1056])                 # streaming kernel (K % 256 == 0) and register kernel
+def test_gemv_digit_entry_points_and_fused_rmsnorm(pkg, synth, ob, orc, torch_dev, kind, K):
+    """x_digits + gemv_xq, rmsnorm_digits + gemv_xq and gemv_rmsnorm agree with the oracle's
+    rms_norm followed by its linear; the kernels' bounded waits all completed."""
+    import ctypes as C
+    rng = np.random.default_rng(11)
+    N, eps = 301, 1e-5
+    Wg, Wgf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    Wu, Wuf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    nw = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    for M in (1, 2, 3):
+        x = (3.0 * rng.standard_normal((M, K))).astype(np.float32)
+        normed = np.zeros_like(x)
+        nwf = nw.astype(np.float32)
+        orc.orc_rmsnorm(x.ctypes.data, nwf.ctypes.data, M, K, eps, normed.ctypes.data)
+        d_x, d_nw = to_dev(x, torch_dev), to_dev(nw.view(np.uint16), torch_dev)
+        d_xq = torch.zeros(pkg.lib.cmlb200_xq_bytes(M, K), dtype=torch.uint8, device=torch_dev)
+        d_y = torch.zeros((M, N), dtype=torch.float32, device=torch_dev)
+        # plain digits
+        pkg.check(pkg.lib.cmlb200_x_digits(d_x.data_ptr(), M, K, d_xq.data_ptr(), stream_ptr()), "x_digits")
+        pkg.check(pkg.lib.cmlb200_gemv_xq(Wg.q, None, d_xq.data_ptr(), d_y.data_ptr(), M, 0, stream_ptr()), "gemv_xq")
+        assert rel_err(d_y.cpu().numpy(), ob.linear_nt(orc, x, Wgf)) <= TOL
+        # digits out of RMSNorm, fp32 copy of the normalised rows on the side
+        d_n = torch.zeros_like(d_x)
+        pkg.check(pkg.lib.cmlb200_rmsnorm_digits(d_x.data_ptr(), d_nw.data_ptr(), M, K, eps, d_n.data_ptr(), d_xq.data_ptr(), stream_ptr()), "rmsnorm_digits")
+        assert rel_err(d_n.cpu().numpy(), normed) <= 1e-5
+        y0 = rng.standard_normal((M, N)).astype(np.float32)
+        d_y.copy_(to_dev(y0, torch_dev))
+        pkg.check(pkg.lib.cmlb200_gemv_xq(Wg.q, None, d_xq.data_ptr(), d_y.data_ptr(), M, 1, stream_ptr()), "gemv_xq accum")
+        want = ob.linear_nt(orc, normed, Wgf)
+        assert rel_err(d_y.cpu().numpy(), y0 + want) <= TOL
+        # normalisation inside the GEMV launch: store and SwiGLU
+        pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, None, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 0, stream_ptr()), "gemv_rmsnorm")
+        assert rel_err(d_y.cpu().numpy(), want) <= TOL
+        pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, Wu.q, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 2, stream_ptr()), "gemv_rmsnorm swiglu")
+        u = ob.linear_nt(orc, normed, Wuf)
+        assert rel_err(d_y.cpu().numpy(), (want / (1.0 + np.exp(-want.astype(np.float64)))).astype(np.float32) * u) <= TOL
+    st = C.c_int(-1)
+    pkg.check(pkg.lib.cmlb200_gemv_status(C.byref(st), 0), "gemv_status")
+    assert st.value == 0
