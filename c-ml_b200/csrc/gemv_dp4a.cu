@@ -711,18 +711,6 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
     return q8 ? run_epi<CMLB200_Q8_0, false>(W, W2, x, nw, eps, xq, ws, y, M, epi, st) : run_epi<CMLB200_Q4_0, false>(W, W2, x, nw, eps, xq, ws, y, M, epi, st);
 }
 
-#ifdef CMLB200_TRACE
-extern "C" int cmlb200_trace_read_(void* out, int reset) {
-    CMLB_CUDA(cudaDeviceSynchronize());
-    CMLB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
-    if (reset) {
-        static unsigned int zero[160] = {};
-        CMLB_CUDA(cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero)));
-    }
-    return CMLB200_OK;
-}
-#endif
-
 // Device-side health word of the streaming kernel: 0 while every bounded wait has completed.
 extern "C" int cmlb200_gemv_status(int* status, int reset) {
     CMLB_REQUIRE(status, "cmlb200_gemv_status: NULL argument");

@@ -3,7 +3,7 @@
 //
 // At HBM speed an SM receives a 32-weight block every ~0.8 clocks. dp4a shares the 64-lane
 // integer pipe with the nibble unpacking, so three exact 8-bit digit planes of x cost about as
-// many integer-pipe cycles as the memory system leaves (measured: the dp4a kernels issue ~125
+// many integer-pipe cycles as the memory system leaves (measured: the dp4a kernels execute ~125
 // thread instructions per block and stall on that pipe). One MMA does 16 rows x 32 weights x 8
 // columns; with the digit planes of x as columns (3 digits + a zero column per row of x, so two
 // rows of x fit) the whole dot-product work is one tensor instruction per 512 weights, and the
@@ -14,38 +14,61 @@
 //     (low nibbles 4t..4t+3, high nibbles 16+4t..), so one ldmatrix over 16-byte block rows in
 //     shared memory delivers each thread its word, and three logic operations turn it into the
 //     two int8x4 registers 16*(q-8). Q8_0 bytes are used as they are.
-//   * B operand = digit planes of the block-fixed-point form of x (common.cuh), kept in
-//     registers for the whole kernel when every warp owns a single 8-block slice of K.
-//   * The accumulator comes back as int32; started at 0x4B400000 its bit pattern read as fp32 is
-//     12582912 + sum, so one subtraction converts it exactly, and a fused multiply-add applies
-//     the fp16 block scale times the block scale of x. Digit columns are combined at the end.
+//   * B operand = digit planes of the block-fixed-point form of x (common.cuh). Every warp makes
+//     the digits of its own slice of K itself (no CTA-wide barrier) and, when the slice is a
+//     single unit, keeps the fragments in registers for the whole kernel.
+//   * A thread's two accumulator columns are neighbouring digits, so (c_even << 8) + c_odd is
+//     their exact int32 combination; one conversion and one fused multiply-add apply the fp16
+//     block scale times the block scale of x. The two column pairs of a row of x are combined
+//     at the end of an item.
 //
-// Work split: item = 16 consecutive weight rows over all of K; the 16 warps of a CTA split K in
-// slices of 8 blocks, each warp streaming its slice of successive items through its own ring of
+// Work split: item = 16 consecutive weight rows over all of K; the 8 warps of a CTA split K in
+// slices of KU blocks, each warp streaming its slice of successive items through its own ring of
 // cp.async buffers (issued before griddepcontrol.wait: weights do not depend on the previous
-// kernel), and the CTA sums the 16 partial results of an item in a fixed order. One CTA per SM,
-// items dealt round-robin. Replaces C-ML's dequantize-then-fp32-matmul (src/core/gguf.c:271-295
-// + src/ops/ir/execution.c:989-1052, 3090-3134) like the other GEMV kernels.
+// kernel), and the CTA sums the partial results of an item in a fixed order. Grid = one CTA per
+// SM, items dealt round-robin; a CTA needs less than half an SM's shared memory and registers,
+// so the next launch's CTAs become resident and prefetch while this one computes. Replaces
+// C-ML's dequantize-then-fp32-matmul (src/core/gguf.c:271-295 + src/ops/ir/execution.c:989-1052,
+// 3090-3134) like the other GEMV kernels.
 #include "common.cuh"
 
 namespace {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
-constexpr int SW = 16;                 // warps per CTA
-constexpr int KU = 8;                  // blocks per unit (one warp, one item, one ring buffer)
+constexpr int SW = 8;                  // warps per CTA
 constexpr int XW = kXqWords;
-constexpr uint32_t MAGIC = 0x4B400000u;
-constexpr float MAGICF = 12582912.0f;
 
-template <int TYPE, int NW>
+#ifdef CMLB200_TRACE
+// Diagnostic build only: per CTA and launch, global-timer stamps at kernel entry, after the
+// dependency wait, after the digits are in place and at exit.
+__device__ unsigned long long g_trace[16][160][4];
+__device__ unsigned int g_trace_cnt[160];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE_SLOT() unsigned tr_slot = 0; if (threadIdx.x == 0) { tr_slot = atomicAdd(&g_trace_cnt[blockIdx.x], 1u) % 16; }
+#define TRACE(k) if (threadIdx.x == 0) g_trace[tr_slot][blockIdx.x][k] = gtime();
+#else
+#define TRACE_SLOT()
+#define TRACE(k)
+#endif
+
+// One unit = 16 rows x KU blocks of one weight: what one warp takes from one item.
+template <int TYPE, int KU, int NW>
 struct Cfg {
     static constexpr int QB = (TYPE == CMLB200_Q8_0) ? 32 : 16;     // quant bytes per block
-    static constexpr int PPR = KU * QB / 16;                         // 16-byte pieces per row of a unit
+    static constexpr int PPR = KU * QB / 16;                         // 16-byte pieces per row
+    static constexpr int RPP = 32 / PPR;                             // rows one warp-wide copy covers
+    static constexpr int PASSES = 16 / RPP;
     static constexpr int ROW_STRIDE = KU * QB + 16;                  // padded: 8 rows hit 8 different bank groups
     static constexpr int QS_BYTES = 16 * ROW_STRIDE;
-    static constexpr int SC_STRIDE = 48;                             // 8 fp16 scales + pad, conflict-free for 128-bit reads
+    static constexpr int SC_PIECES = KU / 8;                         // 16-byte pieces of fp16 scales per row
+    static constexpr int SC_STRIDE = 48;                             // conflict-free for 128-bit reads of 8 rows
     static constexpr int MAT_BYTES = QS_BYTES + 16 * SC_STRIDE;
     static constexpr int UNIT_BYTES = NW * MAT_BYTES;
+    static_assert(PPR <= 32 && 32 % PPR == 0, "a row must fit one warp-wide copy");
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -59,38 +82,46 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
 }
-// D = A(16x32 s8, row) * B(32x8 s8, col) + MAGIC in every lane of the accumulator
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+// D = A(16x32 s8, row) * B(32x8 s8, col)
 __device__ __forceinline__ void mma_s8(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
                                        int& d0, int& d1, int& d2, int& d3) {
+    const int z = 0;
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(MAGIC));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
 }
-__device__ __forceinline__ float unmagic(int c) { return __int_as_float(c) - MAGICF; }
 
+// The two fp16 scales packed in one word, widened (with C-ML's subnormal rule when QUIRK).
 template <bool QUIRK>
-__device__ __forceinline__ float scale_of(uint32_t packed, int odd) {
-    const uint16_t h = (uint16_t)(odd ? (packed >> 16) : (packed & 0xFFFFu));
-    return QUIRK ? cml_half_to_float(h) : __half2float(__ushort_as_half(h));
+__device__ __forceinline__ float2 scales_of(uint32_t packed) {
+    if (QUIRK) return make_float2(cml_half_to_float((uint16_t)(packed & 0xFFFFu)), cml_half_to_float((uint16_t)(packed >> 16)));
+    return __half22float2(*reinterpret_cast<const __half2*>(&packed));
 }
 
-// xin: digit records [MT][K/32][XW] (XMODE 0), fp32 activations [MT][K] (XMODE 1), or fp32
-// activations RMS-normalised with the fp16 weight nw first (XMODE 2; src/nn/llama.c:71-124).
-// y: [MT][N]. K % 256 == 0. BREG: K/256 <= SW, every warp keeps its B fragments in registers.
-// NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi selects store or accumulate.
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
-__global__ void __launch_bounds__(SW * 32, 1)
+// xin: digit records [MT][K/32][XW] (xmode 0), fp32 activations [MT][K] (xmode 1), or fp32
+// activations RMS-normalised with the fp16 weight nw first (xmode 2; src/nn/llama.c:71-124).
+// y: [MT][N]. K % (32*KU) == 0. KU == 16: every warp owns at most one unit per item and keeps its
+// B fragments in registers. NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi selects store
+// or accumulate.
+template <int TYPE, int MT, int NW, bool QUIRK, int KU, int NBUF>
+__global__ void __launch_bounds__(SW * 32, 2)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
                 const void* __restrict__ xin, const __half* __restrict__ nw, float eps, float* __restrict__ y, int N, int K,
-                int XMODE, int epi) {
-    using C = Cfg<TYPE, NW>;
+                int xmode, int epi) {
+    using C = Cfg<TYPE, KU, NW>;
     constexpr int QB = C::QB, NC = 4 * MT;
+    constexpr bool BREG = (KU == 16);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[SW][MT];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int nblk = K / 32, nocts = nblk / KU;
+    const int nblk = K / 32, nun = nblk / KU;
     // shared memory: B table [nblk][NC][8 words] | xs [MT][nblk] | partials [2][SW][NW][MT][16] | rings
     uint32_t* table = reinterpret_cast<uint32_t*>(smem);
     float* xs_all = reinterpret_cast<float*>(smem + (size_t)nblk * NC * 32);
@@ -99,62 +130,79 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     const uint32_t ring0 = smem_u32(ring);
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    TRACE_SLOT();
+    TRACE(0);
 
-    // this warp's slice of K (in units of KU blocks) and this CTA's items
-    const int q = nocts / SW, rem = nocts % SW;
-    const int my_noct = q + (warp < rem ? 1 : 0);
-    const int oct0 = warp * q + min(warp, rem);
+    // this warp's slice of K (units of KU blocks) and this CTA's items
+    const int q = nun / SW, rem = nun % SW;
+    const int my_nun = q + (warp < rem ? 1 : 0);
+    const int un0 = warp * q + min(warp, rem);
     const int items = (N + 15) / 16;
     const int my_items = ((int)blockIdx.x < items) ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int n_units = my_items * my_noct;
     const size_t row_bytes = (size_t)nblk * QB;
 
-    auto issue = [&](int u, int buf) {
-        const int it = u / my_noct, oct = oct0 + (u - it * my_noct);
-        const int row0 = ((int)blockIdx.x + it * (int)gridDim.x) * 16;
-        const uint32_t dst = ring0 + buf * C::UNIT_BYTES;
+    // per-lane constants of the copy pattern: pass k moves rows k*RPP .. k*RPP+RPP-1 of the unit
+    const size_t src_off_l = (size_t)(lane / C::PPR) * row_bytes + (size_t)(lane % C::PPR) * 16;
+    const uint32_t dst_off_l = (uint32_t)((lane / C::PPR) * C::ROW_STRIDE + (lane % C::PPR) * 16);
+    const size_t src_step = (size_t)C::RPP * row_bytes;
+    const int sc_row = lane / C::SC_PIECES, sc_piece = lane % C::SC_PIECES;
+
+    int iss_it = 0, iss_o = 0;           // the next unit to request
+    auto issue_next = [&](int buf) {
+        if (iss_it < my_items && my_nun > 0) {
+            const int row0 = ((int)blockIdx.x + iss_it * (int)gridDim.x) * 16;
+            const int un = un0 + iss_o;
+            const uint32_t dst = ring0 + buf * C::UNIT_BYTES;
 #pragma unroll
-        for (int a = 0; a < NW; a++) {
-            const uint8_t* wq = a ? qs2 : qs;
-            const uint16_t* ws = a ? scales2 : scales;
+            for (int a = 0; a < NW; a++) {
+                const uint8_t* wq = (a ? qs2 : qs) + (size_t)un * (KU * QB);
+                const uint16_t* ws = (a ? scales2 : scales) + (size_t)un * KU;
+                if (row0 + 16 <= N) {
+                    const uint8_t* src = wq + (size_t)row0 * row_bytes + src_off_l;
 #pragma unroll
-            for (int p = lane; p < 16 * C::PPR; p += 32) {
-                const int row = p / C::PPR, off = p - row * C::PPR;
-                const int srow = min(row0 + row, N - 1);             // rows past N repeat the last row; never written
-                cp_async16(dst + a * C::MAT_BYTES + row * C::ROW_STRIDE + off * 16,
-                           wq + (size_t)srow * row_bytes + (size_t)oct * (KU * QB) + off * 16);
+                    for (int k = 0; k < C::PASSES; k++)
+                        cp_async16(dst + a * C::MAT_BYTES + dst_off_l + k * (C::RPP * C::ROW_STRIDE), src + k * src_step);
+                } else {                                              // last item: rows past N repeat row N-1; never written
+#pragma unroll
+                    for (int k = 0; k < C::PASSES; k++) {
+                        const int srow = min(row0 + k * C::RPP + lane / C::PPR, N - 1);
+                        cp_async16(dst + a * C::MAT_BYTES + dst_off_l + k * (C::RPP * C::ROW_STRIDE),
+                                   wq + (size_t)srow * row_bytes + (size_t)(lane % C::PPR) * 16);
+                    }
+                }
+                if (lane < 16 * C::SC_PIECES) {
+                    const int srow = min(row0 + sc_row, N - 1);
+                    cp_async16(dst + a * C::MAT_BYTES + C::QS_BYTES + sc_row * C::SC_STRIDE + sc_piece * 16,
+                               ws + (size_t)srow * nblk + sc_piece * 8);
+                }
             }
-            if (lane < 16) {
-                const int srow = min(row0 + lane, N - 1);
-                cp_async16(dst + a * C::MAT_BYTES + C::QS_BYTES + lane * C::SC_STRIDE, ws + (size_t)srow * nblk + (size_t)oct * KU);
-            }
+            if (++iss_o == my_nun) { iss_o = 0; iss_it++; }
         }
+        cp_async_commit();
     };
 
     // Weights do not depend on the preceding kernel: fill the ring before the dependency wait.
 #pragma unroll
-    for (int i = 0; i < NBUF; i++) {
-        if (i < n_units) issue(i, i);
-        cp_async_commit();
-    }
+    for (int i = 0; i < NBUF; i++) issue_next(i);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    TRACE(1);
 
-    // ---- digits of x into the B table
+    // ---- digits of this warp's slice of x into the B table (8 lanes per block, 4 blocks per pass)
     {
-        const int sub = threadIdx.x & 7;
-        const unsigned gmask = 0xffu << (threadIdx.x & 24);
-        if (XMODE != 0) {
+        const int sub = lane & 7;
+        const unsigned gmask = 0xffu << (lane & 24);
+        const int b_lo = un0 * KU, b_cnt = my_nun * KU;            // this warp's blocks
+        if (xmode != 0) {
             const float* x = static_cast<const float*>(xin);
             float inv[MT];
 #pragma unroll
             for (int m = 0; m < MT; m++) inv[m] = 1.f;
-            if (XMODE == 2) {
-                
+            if (xmode == 2) {                                        // sum of squares: every warp its slice, then all
 #pragma unroll
                 for (int m = 0; m < MT; m++) {
                     float ss = 0.f;
-                    for (int i = threadIdx.x * 4; i < K; i += SW * 128) {
-                        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + i);
+                    for (int i = lane * 4; i < b_cnt * 32; i += 128) {
+                        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + b_lo * 32 + i);
                         ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
                     }
 #pragma unroll
@@ -172,11 +220,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
             }
 #pragma unroll
             for (int m = 0; m < MT; m++)
-                for (int b = threadIdx.x >> 3; b < nblk; b += SW * 4) {
+#pragma unroll 4
+                for (int bb = lane >> 3; bb < b_cnt; bb += 4) {
+                    const int b = b_lo + bb;
                     const int i = b * 32 + sub * 4;
                     const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + i);
                     float e[4] = {v.x, v.y, v.z, v.w};
-                    if (XMODE == 2) {
+                    if (xmode == 2) {
                         const uint2 wr = *reinterpret_cast<const uint2*>(nw + i);
                         const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
                         const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
@@ -204,16 +254,20 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 }
         } else {
             const uint32_t* xq = static_cast<const uint32_t*>(xin);
-            for (int idx = threadIdx.x; idx < MT * nblk * 8; idx += SW * 32) {
-                const int s8 = idx & 7, mb = idx >> 3, m = mb / nblk, b = mb - m * nblk;
-                const uint32_t* rec = xq + (size_t)mb * XW;
-                uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (s8 & 3) * 2 + (s8 >> 2);
-                dst[0] = rec[s8]; dst[8] = rec[8 + s8]; dst[16] = rec[16 + s8]; dst[24] = 0u;
-                if (s8 == 0) xs_all[m * nblk + b] = __uint_as_float(rec[24]);
-            }
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+#pragma unroll 4
+                for (int bb = lane >> 3; bb < b_cnt; bb += 4) {
+                    const int b = b_lo + bb;
+                    const uint32_t* rec = xq + ((size_t)m * nblk + b) * XW;
+                    uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (sub & 3) * 2 + (sub >> 2);
+                    dst[0] = rec[sub]; dst[8] = rec[8 + sub]; dst[16] = rec[16 + sub]; dst[24] = 0u;
+                    if (sub == 0) xs_all[m * nblk + b] = __uint_as_float(rec[24]);
+                }
         }
     }
-    __syncthreads();
+    __syncwarp();
+    TRACE(2);
 
     // B fragment of block b for this thread: column g (n index), words t and 4+t of the plane
     auto load_b = [&](int b, uint32_t& b0, uint32_t& b1) {
@@ -226,81 +280,77 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 
     uint32_t breg[BREG ? KU : 1][2];
     float xsr[BREG ? KU : 1];
-    if (BREG && my_noct > 0) {
+    if (BREG && my_nun > 0) {
 #pragma unroll
         for (int i = 0; i < (BREG ? KU : 1); i++) {
-            load_b(oct0 * KU + i, breg[i][0], breg[i][1]);
-            xsr[i] = xs_all[xm * nblk + oct0 * KU + i];
+            load_b(un0 * KU + i, breg[i][0], breg[i][1]);
+            xsr[i] = xs_all[xm * nblk + un0 * KU + i];
         }
     }
 
     const uint32_t ld_off = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * C::ROW_STRIDE + (lane >> 4) * 16);
     int u = 0;
     for (int it = 0; it < my_items; it++) {
-        float acc[NW][4];
+        float acc[NW][2];            // rows g and g+8: sum over blocks of scale * (c_even * 256 + c_odd)
 #pragma unroll
-        for (int a = 0; a < NW; a++)
-#pragma unroll
-            for (int k = 0; k < 4; k++) acc[a][k] = 0.f;
+        for (int a = 0; a < NW; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
 
-        for (int o = 0; o < my_noct; o++, u++) {
+        for (int o = 0; o < my_nun; o++, u++) {
             const int buf = u % NBUF;
             cp_async_wait<NBUF - 1>();
             __syncwarp();
             const uint32_t ub = ring0 + buf * C::UNIT_BYTES;
-            const int blk0 = (oct0 + o) * KU;
+            const int blk0 = (un0 + o) * KU;
 #pragma unroll
             for (int a = 0; a < NW; a++) {
                 const uint32_t mb = ub + a * C::MAT_BYTES;
-                uint4 sg, sg8;       // fp16 scales of rows g and g+8, 8 blocks each
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(sg.x), "=r"(sg.y), "=r"(sg.z), "=r"(sg.w) : "r"(mb + C::QS_BYTES + g * C::SC_STRIDE));
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(sg8.x), "=r"(sg8.y), "=r"(sg8.z), "=r"(sg8.w) : "r"(mb + C::QS_BYTES + (g + 8) * C::SC_STRIDE));
-                const uint32_t sgw[4] = {sg.x, sg.y, sg.z, sg.w}, sg8w[4] = {sg8.x, sg8.y, sg8.z, sg8.w};
-                auto one_block = [&](int i, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+                uint32_t sgw[KU / 2], sg8w[KU / 2];     // fp16 scales of rows g and g+8, two blocks per word
+#pragma unroll
+                for (int h = 0; h < KU / 8; h++) {
+                    const uint4 v = lds128(mb + C::QS_BYTES + g * C::SC_STRIDE + h * 16);
+                    const uint4 w = lds128(mb + C::QS_BYTES + (g + 8) * C::SC_STRIDE + h * 16);
+                    sgw[4 * h] = v.x; sgw[4 * h + 1] = v.y; sgw[4 * h + 2] = v.z; sgw[4 * h + 3] = v.w;
+                    sg8w[4 * h] = w.x; sg8w[4 * h + 1] = w.y; sg8w[4 * h + 2] = w.z; sg8w[4 * h + 3] = w.w;
+                }
+                auto one_block = [&](int i, float d_lo, float d_hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
                     uint32_t b0, b1;
                     float xs;
                     if (BREG) { b0 = breg[BREG ? i : 0][0]; b1 = breg[BREG ? i : 0][1]; xs = xsr[BREG ? i : 0]; }
                     else { load_b(blk0 + i, b0, b1); xs = xs_all[xm * nblk + blk0 + i]; }
                     int c0, c1, c2, c3;
                     mma_s8(a0, a1, a2, a3, b0, b1, c0, c1, c2, c3);
-                    const float s_lo = scale_of<QUIRK>(sgw[i >> 1], i & 1) * xs;
-                    const float s_hi = scale_of<QUIRK>(sg8w[i >> 1], i & 1) * xs;
-                    acc[a][0] = fmaf(unmagic(c0), s_lo, acc[a][0]);
-                    acc[a][1] = fmaf(unmagic(c1), s_lo, acc[a][1]);
-                    acc[a][2] = fmaf(unmagic(c2), s_hi, acc[a][2]);
-                    acc[a][3] = fmaf(unmagic(c3), s_hi, acc[a][3]);
+                    acc[a][0] = fmaf((float)((c0 << 8) + c1), d_lo * xs, acc[a][0]);
+                    acc[a][1] = fmaf((float)((c2 << 8) + c3), d_hi * xs, acc[a][1]);
                 };
-                if (TYPE == CMLB200_Q4_0) {
 #pragma unroll
-                    for (int p = 0; p < KU / 2; p++) {       // two blocks per ldmatrix: [rows 0-7 | 8-15] x [block 2p | 2p+1]
-                        uint32_t r0, r1, r2, r3;
+                for (int p = 0; p < KU / 2; p++) {
+                    const float2 dlo = scales_of<QUIRK>(sgw[p]), dhi = scales_of<QUIRK>(sg8w[p]);
+                    uint32_t r0, r1, r2, r3;
+                    if (TYPE == CMLB200_Q4_0) {          // one ldmatrix: [rows 0-7 | 8-15] x [block 2p | 2p+1]
                         ldmatrix_x4(mb + ld_off + p * 32, r0, r1, r2, r3);
                         // nibble n in the top half of a byte, top bit flipped, reads as the int8 16*(n-8)
-                        one_block(2 * p, ((r0 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r1 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
+                        one_block(2 * p, dlo.x, dhi.x, ((r0 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r1 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
                                   (r0 & 0xF0F0F0F0u) ^ 0x80808080u, (r1 & 0xF0F0F0F0u) ^ 0x80808080u);
-                        one_block(2 * p + 1, ((r2 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r3 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
+                        one_block(2 * p + 1, dlo.y, dhi.y, ((r2 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r3 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
                                   (r2 & 0xF0F0F0F0u) ^ 0x80808080u, (r3 & 0xF0F0F0F0u) ^ 0x80808080u);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < KU; i++) {           // one block per ldmatrix: [rows 0-7 | 8-15] x [bytes 0-15 | 16-31]
-                        uint32_t r0, r1, r2, r3;
-                        ldmatrix_x4(mb + ld_off + i * 32, r0, r1, r2, r3);
-                        one_block(i, r0, r1, r2, r3);
+                    } else {                             // one ldmatrix per block: [rows 0-7 | 8-15] x [bytes 0-15 | 16-31]
+                        ldmatrix_x4(mb + ld_off + (2 * p) * 32, r0, r1, r2, r3);
+                        one_block(2 * p, dlo.x, dhi.x, r0, r1, r2, r3);
+                        ldmatrix_x4(mb + ld_off + (2 * p + 1) * 32, r0, r1, r2, r3);
+                        one_block(2 * p + 1, dlo.y, dhi.y, r0, r1, r2, r3);
                     }
                 }
             }
             __syncwarp();                                    // every lane is done with this buffer
-            if (u + NBUF < n_units) issue(u + NBUF, buf);
-            cp_async_commit();
+            issue_next(buf);
         }
 
-        // ---- combine digit columns, then the 16 K-slices of the CTA
+        // ---- combine the column pairs (t even: d0*256 + d1, t odd: d2*256), then the CTA's K slices
         const int par = it & 1;
+        const float wgt = (t & 1) ? (1.0f / 256.0f) : 256.0f;
 #pragma unroll
         for (int a = 0; a < NW; a++) {
-            float p_lo = (t & 1) ? acc[a][0] : fmaf(acc[a][0], 65536.0f, acc[a][1] * 256.0f);     // row g
-            float p_hi = (t & 1) ? acc[a][2] : fmaf(acc[a][2], 65536.0f, acc[a][3] * 256.0f);     // row g + 8
+            float p_lo = acc[a][0] * wgt, p_hi = acc[a][1] * wgt;
             p_lo += __shfl_xor_sync(0xffffffffu, p_lo, 1);
             p_hi += __shfl_xor_sync(0xffffffffu, p_hi, 1);
             if ((t & 1) == 0 && (t >> 1) < MT) {
@@ -330,7 +380,22 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         }
     }
     cp_async_wait<0>();
+    TRACE(3);
 }
+
+#ifdef CMLB200_TRACE
+}  // namespace
+extern "C" int cmlb200_trace_read_(void* out, int reset) {
+    CMLB_CUDA(cudaDeviceSynchronize());
+    CMLB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
+    if (reset) {
+        static unsigned int zero[160] = {};
+        CMLB_CUDA(cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero)));
+    }
+    return CMLB200_OK;
+}
+namespace {
+#endif
 
 template <typename Kern, typename... Args>
 int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -349,19 +414,20 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A
 }
 
 constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemHalf = 112 * 1024;       // two CTAs (this launch's and the next one's) per SM
 
-template <int TYPE, int NW>
+template <int TYPE, int KU, int NW>
 size_t smem_bytes(int MT, int nblk, int nbuf) {
     return (size_t)nblk * 4 * MT * 32 + ((((size_t)MT * nblk + 31) & ~(size_t)31) + 2 * SW * NW * MT * 16) * sizeof(float) +
-           (size_t)SW * nbuf * Cfg<TYPE, NW>::UNIT_BYTES;
+           (size_t)SW * nbuf * Cfg<TYPE, KU, NW>::UNIT_BYTES;
 }
 
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
+template <int TYPE, int MT, int NW, bool QUIRK, int KU, int NBUF>
 int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
                cudaStream_t st) {
     const int N = W->rows, K = W->cols;
-    const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
-    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF>;
+    const size_t smem = smem_bytes<TYPE, KU, NW>(MT, K / 32, NBUF);
+    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, KU, NBUF>;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
         CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -373,20 +439,36 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
                       W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi);
 }
 
+// Ring depth: the deepest of 4, 3, 2 that still lets two CTAs share an SM; failing that, the
+// deepest that fits at all.
+int g_nbuf_pref = 0;       // tuning hook: a ring depth to try first (0 = none)
+
+template <int TYPE, int KU, int NW>
+int pick_nbuf(int MT, int nblk) {
+    if (g_nbuf_pref >= 2 && g_nbuf_pref <= 4 && smem_bytes<TYPE, KU, NW>(MT, nblk, g_nbuf_pref) <= kSmemLimit) return g_nbuf_pref;
+    for (int n = 4; n >= 2; n--)
+        if (smem_bytes<TYPE, KU, NW>(MT, nblk, n) <= kSmemHalf) return n;
+    for (int n = 4; n >= 2; n--)
+        if (smem_bytes<TYPE, KU, NW>(MT, nblk, n) <= kSmemLimit) return n;
+    return 0;
+}
+
+template <int TYPE, int MT, int NW, bool QUIRK, int KU>
+int launch_ku(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
+              cudaStream_t st) {
+    const int nbuf = pick_nbuf<TYPE, KU, NW>(MT, W->cols / 32);
+    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, KU, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, KU, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    CMLB_REQUIRE(nbuf == 2, "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
+    return launch_cfg<TYPE, MT, NW, QUIRK, KU, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
+}
+
 template <int TYPE, int MT, int NW, bool QUIRK>
 int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
            cudaStream_t st) {
     const int nblk = W->cols / 32;
-    const bool breg = nblk / KU <= SW;
-    const int nbuf = smem_bytes<TYPE, NW>(MT, nblk, 4) <= kSmemLimit ? 4 : smem_bytes<TYPE, NW>(MT, nblk, 3) <= kSmemLimit ? 3 : 2;
-    if (breg) {
-        if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, true, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
-        if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, true, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
-        return launch_cfg<TYPE, MT, NW, QUIRK, true, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    }
-    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, false, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, false, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    return launch_cfg<TYPE, MT, NW, QUIRK, false, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    if (nblk % 16 == 0 && nblk / 16 <= SW) return launch_ku<TYPE, MT, NW, QUIRK, 16>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    return launch_ku<TYPE, MT, NW, QUIRK, 8>(W, W2, xin, nw, eps, y, xmode, epi, st);
 }
 
 // Rows of x two at a time (one launch streams the weight once for both), then one.
@@ -414,7 +496,16 @@ int run_x(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const _
     return run_m<TYPE, 1, QUIRK>(W, W2, xin, xrb, nw, eps, y, M, xmode, epi, st);
 }
 
+template <int TYPE>
+bool fits(int nblk, int epi) {
+    if (nblk % 16 == 0 && nblk / 16 <= SW)
+        return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 16, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 16, 1>(2, nblk) > 0;
+    return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 8, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 8, 1>(2, nblk) > 0;
+}
+
 }  // namespace
+
+extern "C" void cmlb200_gemv_mma_tune_(int nbuf) { g_nbuf_pref = nbuf; }
 
 // Shapes the tensor-core decode kernel takes: whole 8-block slices of K with 16-byte aligned
 // scale rows, and room in shared memory for the digit table of two rows of x next to the rings.
@@ -422,10 +513,7 @@ bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi) {
     if (W->type != CMLB200_Q4_0 && W->type != CMLB200_Q8_0) return false;
     if (W->cols % 256 != 0 || ((uintptr_t)W->qs & 15) || ((uintptr_t)W->scales & 15)) return false;
     const int nblk = W->cols / 32;
-    const bool q8 = W->type == CMLB200_Q8_0;
-    const size_t need = epi == EPI_SWIGLU ? (q8 ? smem_bytes<CMLB200_Q8_0, 2>(2, nblk, 2) : smem_bytes<CMLB200_Q4_0, 2>(2, nblk, 2))
-                                          : (q8 ? smem_bytes<CMLB200_Q8_0, 1>(2, nblk, 2) : smem_bytes<CMLB200_Q4_0, 1>(2, nblk, 2));
-    return need <= kSmemLimit;
+    return W->type == CMLB200_Q8_0 ? fits<CMLB200_Q8_0>(nblk, epi) : fits<CMLB200_Q4_0>(nblk, epi);
 }
 
 // y[M, rows] (= | += | swiglu) for M <= 4. Exactly one of xq (digit records) and x (fp32, with
