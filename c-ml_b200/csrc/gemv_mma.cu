@@ -12,31 +12,35 @@
 //   * A operand straight from the file format: thread (g, t) of the MMA needs k = 4t..4t+3 and
 //     k = 16+4t..16+4t+3 of rows g and g+8. Word t of a Q4_0 block holds exactly those elements
 //     (low nibbles 4t..4t+3, high nibbles 16+4t..), so one ldmatrix over 16-byte block rows in
-//     shared memory delivers each thread its word, and three logic operations turn it into the
-//     two int8x4 registers 16*(q-8). Q8_0 bytes are used as they are.
-//   * B operand = digit planes of the block-fixed-point form of x (common.cuh). Every warp makes
-//     the digits of its own slice of K itself (no CTA-wide barrier) and, when the slice is a
-//     single unit, keeps the fragments in registers for the whole kernel.
+//     shared memory delivers each thread its word, and one shift plus two 3-input logic
+//     operations turn it into the two int8x4 registers 16*(q-8). Q8_0 bytes are used as they are.
+//   * B operand = digit planes of a fixed-point form of x: every warp takes its own slice of K
+//     (8 blocks), finds the slice maximum, writes x_k ~= s * X_k with X_k a signed 24-bit integer
+//     split in three balanced 8-bit digits, and keeps the fragments in registers for the whole
+//     kernel when the slice is its only one. No CTA-wide barrier is involved (except the sum of
+//     squares when the RMSNorm is applied here). The rounding of x to 24 bits of its slice maximum
+//     is of the order of the rounding an fp32 accumulation commits.
 //   * A thread's two accumulator columns are neighbouring digits, so (c_even << 8) + c_odd is
 //     their exact int32 combination; one conversion and one fused multiply-add apply the fp16
-//     block scale times the block scale of x. The two column pairs of a row of x are combined
-//     at the end of an item.
+//     block scale, the slice scale of x is applied once per unit, and the two column pairs of a
+//     row of x are combined at the end of an item.
 //
-// Work split: item = 16 consecutive weight rows over all of K; the 8 warps of a CTA split K in
-// slices of KU blocks, each warp streaming its slice of successive items through its own ring of
+// Work split: item = 16 consecutive weight rows over all of K; the 16 warps of a CTA split K in
+// units of 8 blocks, each warp streaming its units of successive items through its own ring of
 // cp.async buffers (issued before griddepcontrol.wait: weights do not depend on the previous
 // kernel), and the CTA sums the partial results of an item in a fixed order. Grid = one CTA per
-// SM, items dealt round-robin; a CTA needs less than half an SM's shared memory and registers,
-// so the next launch's CTAs become resident and prefetch while this one computes. Replaces
-// C-ML's dequantize-then-fp32-matmul (src/core/gguf.c:271-295 + src/ops/ir/execution.c:989-1052,
-// 3090-3134) like the other GEMV kernels.
+// SM, items dealt round-robin. Replaces C-ML's dequantize-then-fp32-matmul
+// (src/core/gguf.c:271-295 + src/ops/ir/execution.c:989-1052, 3090-3134) like the other GEMV
+// kernels.
 #include "common.cuh"
 
 namespace {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
-constexpr int SW = 8;                  // warps per CTA
+constexpr int SW = 16;                 // warps per CTA
+constexpr int KU = 8;                  // blocks per unit: what one warp takes from one item at a time
 constexpr int XW = kXqWords;
+constexpr int XFULL = kXqFull - 1;     // |X| <= XFULL + 1 after rounding, which still splits into int8 digits
 
 #ifdef CMLB200_TRACE
 // Diagnostic build only: per CTA and launch, global-timer stamps at kernel entry, after the
@@ -55,8 +59,8 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define TRACE(k)
 #endif
 
-// One unit = 16 rows x KU blocks of one weight: what one warp takes from one item.
-template <int TYPE, int KU, int NW>
+// One unit = 16 rows x KU blocks of one weight.
+template <int TYPE, int NW>
 struct Cfg {
     static constexpr int QB = (TYPE == CMLB200_Q8_0) ? 32 : 16;     // quant bytes per block
     static constexpr int PPR = KU * QB / 16;                         // 16-byte pieces per row
@@ -64,11 +68,8 @@ struct Cfg {
     static constexpr int PASSES = 16 / RPP;
     static constexpr int ROW_STRIDE = KU * QB + 16;                  // padded: 8 rows hit 8 different bank groups
     static constexpr int QS_BYTES = 16 * ROW_STRIDE;
-    static constexpr int SC_PIECES = KU / 8;                         // 16-byte pieces of fp16 scales per row
-    static constexpr int SC_STRIDE = 48;                             // conflict-free for 128-bit reads of 8 rows
-    static constexpr int MAT_BYTES = QS_BYTES + 16 * SC_STRIDE;
+    static constexpr int MAT_BYTES = QS_BYTES + 16 * 16;             // + 8 fp16 scales per row
     static constexpr int UNIT_BYTES = NW * MAT_BYTES;
-    static_assert(PPR <= 32 && 32 % PPR == 0, "a row must fit one warp-wide copy");
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -86,6 +87,12 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
+}
+// (a & m) ^ c in one logic instruction
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t m, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(m), "r"(c));
+    return d;
 }
 // D = A(16x32 s8, row) * B(32x8 s8, col)
 __device__ __forceinline__ void mma_s8(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
@@ -105,27 +112,26 @@ __device__ __forceinline__ float2 scales_of(uint32_t packed) {
 
 // xin: digit records [MT][K/32][XW] (xmode 0), fp32 activations [MT][K] (xmode 1), or fp32
 // activations RMS-normalised with the fp16 weight nw first (xmode 2; src/nn/llama.c:71-124).
-// y: [MT][N]. K % (32*KU) == 0. KU == 16: every warp owns at most one unit per item and keeps its
-// B fragments in registers. NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi selects store
-// or accumulate.
-template <int TYPE, int MT, int NW, bool QUIRK, int KU, int NBUF>
-__global__ void __launch_bounds__(SW * 32, 2)
+// y: [MT][N]. K % 256 == 0. BREG: K/256 <= SW, every warp owns at most one unit per item and
+// keeps its B fragments in registers. NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi
+// selects store or accumulate.
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
+__global__ void __launch_bounds__(SW * 32, 1)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
                 const void* __restrict__ xin, const __half* __restrict__ nw, float eps, float* __restrict__ y, int N, int K,
                 int xmode, int epi) {
-    using C = Cfg<TYPE, KU, NW>;
+    using C = Cfg<TYPE, NW>;
     constexpr int QB = C::QB, NC = 4 * MT;
-    constexpr bool BREG = (KU == 16);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[SW][MT];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nblk = K / 32, nun = nblk / KU;
-    // shared memory: B table [nblk][NC][8 words] | xs [MT][nblk] | partials [2][SW][NW][MT][16] | rings
+    // shared memory: B table [nblk][NC][8 words] | unit scales [MT][nun] | partials [2][SW][NW][MT][16] | rings
     uint32_t* table = reinterpret_cast<uint32_t*>(smem);
     float* xs_all = reinterpret_cast<float*>(smem + (size_t)nblk * NC * 32);
-    float* partial = xs_all + (((size_t)MT * nblk + 31) & ~(size_t)31);
+    float* partial = xs_all + (((size_t)MT * nun + 31) & ~(size_t)31);
     uint8_t* ring = reinterpret_cast<uint8_t*>(partial + 2 * SW * NW * MT * 16) + (size_t)warp * NBUF * C::UNIT_BYTES;
     const uint32_t ring0 = smem_u32(ring);
 
@@ -133,7 +139,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     TRACE_SLOT();
     TRACE(0);
 
-    // this warp's slice of K (units of KU blocks) and this CTA's items
+    // this warp's units of K and this CTA's items
     const int q = nun / SW, rem = nun % SW;
     const int my_nun = q + (warp < rem ? 1 : 0);
     const int un0 = warp * q + min(warp, rem);
@@ -145,7 +151,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     const size_t src_off_l = (size_t)(lane / C::PPR) * row_bytes + (size_t)(lane % C::PPR) * 16;
     const uint32_t dst_off_l = (uint32_t)((lane / C::PPR) * C::ROW_STRIDE + (lane % C::PPR) * 16);
     const size_t src_step = (size_t)C::RPP * row_bytes;
-    const int sc_row = lane / C::SC_PIECES, sc_piece = lane % C::SC_PIECES;
 
     int iss_it = 0, iss_o = 0;           // the next unit to request
     auto issue_next = [&](int buf) {
@@ -170,10 +175,9 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                                    wq + (size_t)srow * row_bytes + (size_t)(lane % C::PPR) * 16);
                     }
                 }
-                if (lane < 16 * C::SC_PIECES) {
-                    const int srow = min(row0 + sc_row, N - 1);
-                    cp_async16(dst + a * C::MAT_BYTES + C::QS_BYTES + sc_row * C::SC_STRIDE + sc_piece * 16,
-                               ws + (size_t)srow * nblk + sc_piece * 8);
+                if (lane < 16) {
+                    const int srow = min(row0 + lane, N - 1);
+                    cp_async16(dst + a * C::MAT_BYTES + C::QS_BYTES + lane * 16, ws + (size_t)srow * nblk);
                 }
             }
             if (++iss_o == my_nun) { iss_o = 0; iss_it++; }
@@ -187,83 +191,87 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
 
-    // ---- digits of this warp's slice of x into the B table (8 lanes per block, 4 blocks per pass)
+    // ---- digits of this warp's units of x into the B table. Lane = (block lane>>3 (+4), elements
+    // 4*(lane&7)..+3); a unit is 8 blocks = two such passes, loaded together.
     {
         const int sub = lane & 7;
-        const unsigned gmask = 0xffu << (lane & 24);
-        const int b_lo = un0 * KU, b_cnt = my_nun * KU;            // this warp's blocks
-        if (xmode != 0) {
+        float inv[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) inv[m] = 1.f;
+        if (xmode == 2) {                                            // sum of squares: every warp its units, then all
             const float* x = static_cast<const float*>(xin);
-            float inv[MT];
 #pragma unroll
-            for (int m = 0; m < MT; m++) inv[m] = 1.f;
-            if (xmode == 2) {                                        // sum of squares: every warp its slice, then all
-#pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    float ss = 0.f;
-                    for (int i = lane * 4; i < b_cnt * 32; i += 128) {
-                        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + b_lo * 32 + i);
-                        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                    if (lane == 0) red[warp][m] = ss;
+            for (int m = 0; m < MT; m++) {
+                float ss = 0.f;
+                for (int i = lane * 4; i < my_nun * KU * 32; i += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + (size_t)un0 * KU * 32 + i);
+                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
                 }
-                __syncthreads();
 #pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    float tot = 0.f;
-#pragma unroll
-                    for (int w = 0; w < SW; w++) tot += red[w][m];
-                    inv[m] = 1.0f / sqrtf(tot / (float)K + eps);
-                }
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) red[warp][m] = ss;
             }
+            __syncthreads();
 #pragma unroll
-            for (int m = 0; m < MT; m++)
-#pragma unroll 4
-                for (int bb = lane >> 3; bb < b_cnt; bb += 4) {
-                    const int b = b_lo + bb;
-                    const int i = b * 32 + sub * 4;
-                    const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + i);
-                    float e[4] = {v.x, v.y, v.z, v.w};
-                    if (xmode == 2) {
-                        const uint2 wr = *reinterpret_cast<const uint2*>(nw + i);
-                        const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
-                        const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
-                        e[0] = e[0] * inv[m] * w01.x; e[1] = e[1] * inv[m] * w01.y;
-                        e[2] = e[2] * inv[m] * w23.x; e[3] = e[3] * inv[m] * w23.y;
+            for (int m = 0; m < MT; m++) {
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < SW; w++) tot += red[w][m];
+                inv[m] = 1.0f / sqrtf(tot / (float)K + eps);
+            }
+        }
+        for (int uo = 0; uo < my_nun; uo++) {
+            const int un = un0 + uo;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                float e[2][4];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int b = un * KU + (lane >> 3) + 4 * h;
+                    if (xmode == 0) {                                // rebuild the values from block-scaled records
+                        const uint32_t* rec = static_cast<const uint32_t*>(xin) + ((size_t)m * nblk + b) * XW;
+                        const uint32_t w0 = rec[sub], w1 = rec[8 + sub], w2 = rec[16 + sub];
+                        const float bs = __uint_as_float(rec[24]);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const int X = ((int)(int8_t)(w0 >> (8 * k))) * 65536 + ((int)(int8_t)(w1 >> (8 * k))) * 256 + (int)(int8_t)(w2 >> (8 * k));
+                            e[h][k] = (float)X * bs;
+                        }
+                    } else {
+                        const int i = b * 32 + sub * 4;
+                        const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(xin) + (size_t)m * K + i);
+                        e[h][0] = v.x; e[h][1] = v.y; e[h][2] = v.z; e[h][3] = v.w;
+                        if (xmode == 2) {
+                            const uint2 wr = *reinterpret_cast<const uint2*>(nw + i);
+                            const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
+                            const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
+                            e[h][0] = e[h][0] * inv[m] * w01.x; e[h][1] = e[h][1] * inv[m] * w01.y;
+                            e[h][2] = e[h][2] * inv[m] * w23.x; e[h][3] = e[h][3] * inv[m] * w23.y;
+                        }
                     }
-                    float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
-#pragma unroll
-                    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
-                    const float sc = amax > 0.f ? (float)kXqFull / amax : 0.f;
-                    uint32_t w[3] = {0, 0, 0};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        int X = __float2int_rn(e[k] * sc);
-                        X = max(-kXqFull, min(kXqFull, X));
-                        int d0, d1, d2;
-                        xq_split(X, d0, d1, d2);
-                        w[0] |= (uint32_t)(d0 & 0xFF) << (8 * k);
-                        w[1] |= (uint32_t)(d1 & 0xFF) << (8 * k);
-                        w[2] |= (uint32_t)(d2 & 0xFF) << (8 * k);
-                    }
-                    uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (sub & 3) * 2 + (sub >> 2);
-                    dst[0] = w[0]; dst[8] = w[1]; dst[16] = w[2]; dst[24] = 0u;
-                    if (sub == 0) xs_all[m * nblk + b] = amax / (float)kXqFull;
                 }
-        } else {
-            const uint32_t* xq = static_cast<const uint32_t*>(xin);
+                float amax = 0.f;
 #pragma unroll
-            for (int m = 0; m < MT; m++)
-#pragma unroll 4
-                for (int bb = lane >> 3; bb < b_cnt; bb += 4) {
-                    const int b = b_lo + bb;
-                    const uint32_t* rec = xq + ((size_t)m * nblk + b) * XW;
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++) amax = fmaxf(amax, fabsf(e[h][k]));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                const float sc = amax > 0.f ? (float)XFULL / amax : 0.f;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int b = un * KU + (lane >> 3) + 4 * h;
+                    int d[3][4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) xq_split(__float2int_rn(e[h][k] * sc), d[0][k], d[1][k], d[2][k]);
                     uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (sub & 3) * 2 + (sub >> 2);
-                    dst[0] = rec[sub]; dst[8] = rec[8 + sub]; dst[16] = rec[16 + sub]; dst[24] = 0u;
-                    if (sub == 0) xs_all[m * nblk + b] = __uint_as_float(rec[24]);
+#pragma unroll
+                    for (int j = 0; j < 3; j++)
+                        dst[8 * j] = __byte_perm(__byte_perm(d[j][0], d[j][1], 0x0040), __byte_perm(d[j][2], d[j][3], 0x0040), 0x5410);
+                    dst[24] = 0u;
                 }
+                if (lane == 0) xs_all[m * nun + un] = amax / (float)XFULL;
+            }
         }
     }
     __syncwarp();
@@ -279,19 +287,18 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     const int xm = (MT == 2) ? (t >> 1) : 0;                 // row of x this thread's accumulator columns belong to
 
     uint32_t breg[BREG ? KU : 1][2];
-    float xsr[BREG ? KU : 1];
+    float xs_reg = 0.f;
     if (BREG && my_nun > 0) {
 #pragma unroll
-        for (int i = 0; i < (BREG ? KU : 1); i++) {
-            load_b(un0 * KU + i, breg[i][0], breg[i][1]);
-            xsr[i] = xs_all[xm * nblk + un0 * KU + i];
-        }
+        for (int i = 0; i < (BREG ? KU : 1); i++) load_b(un0 * KU + i, breg[i][0], breg[i][1]);
+        xs_reg = xs_all[xm * nun + un0];
     }
 
     const uint32_t ld_off = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * C::ROW_STRIDE + (lane >> 4) * 16);
+    const uint32_t nib_mask = 0xF0F0F0F0u, nib_flip = 0x80808080u;
     int u = 0;
     for (int it = 0; it < my_items; it++) {
-        float acc[NW][2];            // rows g and g+8: sum over blocks of scale * (c_even * 256 + c_odd)
+        float acc[NW][2];            // rows g and g+8: sum over blocks of scales * (c_even * 256 + c_odd)
 #pragma unroll
         for (int a = 0; a < NW; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
 
@@ -301,26 +308,21 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
             __syncwarp();
             const uint32_t ub = ring0 + buf * C::UNIT_BYTES;
             const int blk0 = (un0 + o) * KU;
+            const float xs = BREG ? xs_reg : xs_all[xm * nun + un0 + o];
 #pragma unroll
             for (int a = 0; a < NW; a++) {
                 const uint32_t mb = ub + a * C::MAT_BYTES;
-                uint32_t sgw[KU / 2], sg8w[KU / 2];     // fp16 scales of rows g and g+8, two blocks per word
-#pragma unroll
-                for (int h = 0; h < KU / 8; h++) {
-                    const uint4 v = lds128(mb + C::QS_BYTES + g * C::SC_STRIDE + h * 16);
-                    const uint4 w = lds128(mb + C::QS_BYTES + (g + 8) * C::SC_STRIDE + h * 16);
-                    sgw[4 * h] = v.x; sgw[4 * h + 1] = v.y; sgw[4 * h + 2] = v.z; sgw[4 * h + 3] = v.w;
-                    sg8w[4 * h] = w.x; sg8w[4 * h + 1] = w.y; sg8w[4 * h + 2] = w.z; sg8w[4 * h + 3] = w.w;
-                }
+                const uint4 sv = lds128(mb + C::QS_BYTES + g * 16), sw = lds128(mb + C::QS_BYTES + (g + 8) * 16);
+                const uint32_t sgw[4] = {sv.x, sv.y, sv.z, sv.w}, sg8w[4] = {sw.x, sw.y, sw.z, sw.w};
+                float au0 = 0.f, au1 = 0.f;      // this unit, before the scale of x
                 auto one_block = [&](int i, float d_lo, float d_hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
                     uint32_t b0, b1;
-                    float xs;
-                    if (BREG) { b0 = breg[BREG ? i : 0][0]; b1 = breg[BREG ? i : 0][1]; xs = xsr[BREG ? i : 0]; }
-                    else { load_b(blk0 + i, b0, b1); xs = xs_all[xm * nblk + blk0 + i]; }
+                    if (BREG) { b0 = breg[BREG ? i : 0][0]; b1 = breg[BREG ? i : 0][1]; }
+                    else load_b(blk0 + i, b0, b1);
                     int c0, c1, c2, c3;
                     mma_s8(a0, a1, a2, a3, b0, b1, c0, c1, c2, c3);
-                    acc[a][0] = fmaf((float)((c0 << 8) + c1), d_lo * xs, acc[a][0]);
-                    acc[a][1] = fmaf((float)((c2 << 8) + c3), d_hi * xs, acc[a][1]);
+                    au0 = fmaf((float)((c0 << 8) + c1), d_lo, au0);
+                    au1 = fmaf((float)((c2 << 8) + c3), d_hi, au1);
                 };
 #pragma unroll
                 for (int p = 0; p < KU / 2; p++) {
@@ -329,10 +331,10 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                     if (TYPE == CMLB200_Q4_0) {          // one ldmatrix: [rows 0-7 | 8-15] x [block 2p | 2p+1]
                         ldmatrix_x4(mb + ld_off + p * 32, r0, r1, r2, r3);
                         // nibble n in the top half of a byte, top bit flipped, reads as the int8 16*(n-8)
-                        one_block(2 * p, dlo.x, dhi.x, ((r0 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r1 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
-                                  (r0 & 0xF0F0F0F0u) ^ 0x80808080u, (r1 & 0xF0F0F0F0u) ^ 0x80808080u);
-                        one_block(2 * p + 1, dlo.y, dhi.y, ((r2 << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((r3 << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
-                                  (r2 & 0xF0F0F0F0u) ^ 0x80808080u, (r3 & 0xF0F0F0F0u) ^ 0x80808080u);
+                        one_block(2 * p, dlo.x, dhi.x, and_xor(r0 << 4, nib_mask, nib_flip), and_xor(r1 << 4, nib_mask, nib_flip),
+                                  and_xor(r0, nib_mask, nib_flip), and_xor(r1, nib_mask, nib_flip));
+                        one_block(2 * p + 1, dlo.y, dhi.y, and_xor(r2 << 4, nib_mask, nib_flip), and_xor(r3 << 4, nib_mask, nib_flip),
+                                  and_xor(r2, nib_mask, nib_flip), and_xor(r3, nib_mask, nib_flip));
                     } else {                             // one ldmatrix per block: [rows 0-7 | 8-15] x [bytes 0-15 | 16-31]
                         ldmatrix_x4(mb + ld_off + (2 * p) * 32, r0, r1, r2, r3);
                         one_block(2 * p, dlo.x, dhi.x, r0, r1, r2, r3);
@@ -340,6 +342,8 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                         one_block(2 * p + 1, dlo.y, dhi.y, r0, r1, r2, r3);
                     }
                 }
+                acc[a][0] = fmaf(au0, xs, acc[a][0]);
+                acc[a][1] = fmaf(au1, xs, acc[a][1]);
             }
             __syncwarp();                                    // every lane is done with this buffer
             issue_next(buf);
@@ -414,20 +418,19 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A
 }
 
 constexpr size_t kSmemLimit = 227 * 1024;
-constexpr size_t kSmemHalf = 112 * 1024;       // two CTAs (this launch's and the next one's) per SM
 
-template <int TYPE, int KU, int NW>
+template <int TYPE, int NW>
 size_t smem_bytes(int MT, int nblk, int nbuf) {
-    return (size_t)nblk * 4 * MT * 32 + ((((size_t)MT * nblk + 31) & ~(size_t)31) + 2 * SW * NW * MT * 16) * sizeof(float) +
-           (size_t)SW * nbuf * Cfg<TYPE, KU, NW>::UNIT_BYTES;
+    return (size_t)nblk * 4 * MT * 32 + ((((size_t)MT * (nblk / KU) + 31) & ~(size_t)31) + 2 * SW * NW * MT * 16) * sizeof(float) +
+           (size_t)SW * nbuf * Cfg<TYPE, NW>::UNIT_BYTES;
 }
 
-template <int TYPE, int MT, int NW, bool QUIRK, int KU, int NBUF>
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
 int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
                cudaStream_t st) {
     const int N = W->rows, K = W->cols;
-    const size_t smem = smem_bytes<TYPE, KU, NW>(MT, K / 32, NBUF);
-    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, KU, NBUF>;
+    const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
+    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF>;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
         CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -439,36 +442,32 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
                       W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi);
 }
 
-// Ring depth: the deepest of 4, 3, 2 that still lets two CTAs share an SM; failing that, the
-// deepest that fits at all.
 int g_nbuf_pref = 0;       // tuning hook: a ring depth to try first (0 = none)
 
-template <int TYPE, int KU, int NW>
+// Ring depth: the deepest of 4, 3, 2 that fits next to the digit table.
+template <int TYPE, int NW>
 int pick_nbuf(int MT, int nblk) {
-    if (g_nbuf_pref >= 2 && g_nbuf_pref <= 4 && smem_bytes<TYPE, KU, NW>(MT, nblk, g_nbuf_pref) <= kSmemLimit) return g_nbuf_pref;
+    if (g_nbuf_pref >= 2 && g_nbuf_pref <= 4 && smem_bytes<TYPE, NW>(MT, nblk, g_nbuf_pref) <= kSmemLimit) return g_nbuf_pref;
     for (int n = 4; n >= 2; n--)
-        if (smem_bytes<TYPE, KU, NW>(MT, nblk, n) <= kSmemHalf) return n;
-    for (int n = 4; n >= 2; n--)
-        if (smem_bytes<TYPE, KU, NW>(MT, nblk, n) <= kSmemLimit) return n;
+        if (smem_bytes<TYPE, NW>(MT, nblk, n) <= kSmemLimit) return n;
     return 0;
 }
 
-template <int TYPE, int MT, int NW, bool QUIRK, int KU>
-int launch_ku(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
-              cudaStream_t st) {
-    const int nbuf = pick_nbuf<TYPE, KU, NW>(MT, W->cols / 32);
-    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, KU, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, KU, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG>
+int launch_b(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
+             cudaStream_t st) {
+    const int nbuf = pick_nbuf<TYPE, NW>(MT, W->cols / 32);
+    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
     CMLB_REQUIRE(nbuf == 2, "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
-    return launch_cfg<TYPE, MT, NW, QUIRK, KU, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
 }
 
 template <int TYPE, int MT, int NW, bool QUIRK>
 int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
            cudaStream_t st) {
-    const int nblk = W->cols / 32;
-    if (nblk % 16 == 0 && nblk / 16 <= SW) return launch_ku<TYPE, MT, NW, QUIRK, 16>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    return launch_ku<TYPE, MT, NW, QUIRK, 8>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    if (W->cols / (32 * KU) <= SW) return launch_b<TYPE, MT, NW, QUIRK, true>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    return launch_b<TYPE, MT, NW, QUIRK, false>(W, W2, xin, nw, eps, y, xmode, epi, st);
 }
 
 // Rows of x two at a time (one launch streams the weight once for both), then one.
@@ -498,9 +497,7 @@ int run_x(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const _
 
 template <int TYPE>
 bool fits(int nblk, int epi) {
-    if (nblk % 16 == 0 && nblk / 16 <= SW)
-        return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 16, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 16, 1>(2, nblk) > 0;
-    return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 8, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 8, 1>(2, nblk) > 0;
+    return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 1>(2, nblk) > 0;
 }
 
 }  // namespace
