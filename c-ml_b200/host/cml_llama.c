@@ -47,7 +47,6 @@ typedef struct DevModel {
     void* stream;
     int qkv_w;                             /* qw_l + 2 * kvw_l */
     float *h, *nrm, *qkv, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch;
-    void *xq_a, *xq_b, *xq_c;              /* activation digits: hidden-wide, attention-wide, FFN-wide */
     uint16_t *b_a, *b_b, *b_c, *b_d;       /* bf16 staging of the prefill path */
     int *d_tokens, *d_cur, *row_seq, *row_pos, *row_limit, *d_hist;
     int* h_cur;
@@ -130,7 +129,7 @@ static void dm_destroy(DevModel* d) {
     qmat_free(&d->lm_head);
     void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->qkv, d->att, d->ffn, d->g, d->u, d->tmp,
                     d->logits, d->att_scratch, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
-                    d->row_pos, d->row_limit, d->d_hist, d->xq_a, d->xq_b, d->xq_c};
+                    d->row_pos, d->row_limit, d->d_hist};
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
     if (d->comm) cml_nccl_destroy(d->comm);
@@ -233,9 +232,6 @@ static int dm_alloc_buffers(DevModel* d) {
     DEV(cmlb200_malloc((void**)&d->h, R * H * 4));
     DEV(cmlb200_malloc((void**)&d->nrm, R * H * 4));
     DEV(cmlb200_malloc((void**)&d->qkv, R * d->qkv_w * 4));
-    DEV(cmlb200_malloc(&d->xq_a, cmlb200_xq_bytes(4, H)));
-    DEV(cmlb200_malloc(&d->xq_b, cmlb200_xq_bytes(4, d->qw_l)));
-    DEV(cmlb200_malloc(&d->xq_c, cmlb200_xq_bytes(4, d->inter_l)));
     DEV(cmlb200_malloc((void**)&d->att, R * d->qw_l * 4));
     DEV(cmlb200_malloc((void**)&d->ffn, (size_t)SKINNY_ROWS * d->inter_l * 4));
     DEV(cmlb200_malloc((void**)&d->g, (size_t)SKINNY_ROWS * d->inter_l * 4));
@@ -552,7 +548,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
     const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32);
-    const int tiny = rows <= 2;                 /* integer-dot GEMV with digits shared between projections */
+    const int tiny = rows <= 2;                 /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
     void* st = d->stream;
     DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
     DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));
@@ -574,8 +570,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
         void* vc = (char*)d->vc + (size_t)li * d->kv_layer_elems * esz;
         /* ---- attention block: norm -> fused QKV projection -> RoPE + cache append -> attention */
         if (tiny) {
-            DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
-            DEV(cmlb200_gemv_xq(&L->wqkv, NULL, d->xq_a, d->qkv, rows, 0, st));
+            DEV(cmlb200_gemv_rmsnorm(&L->wqkv, NULL, d->h, (const uint16_t*)L->n1, c->rms_norm_eps, d->qkv, rows, 0, st));
         } else if (skinny) {
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
             if (lin_f32(d, &L->wqkv, d->nrm, d->qkv, rows, 0)) return -1;
@@ -587,24 +582,12 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
         DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
                                     rotate, kc, vc, c->max_seq_len, kvf32, st));
         DEV(cmlb200_attention_ex(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd,
-                                 c->max_seq_len, max_limit, kvf32, d->att, tiny ? d->xq_b : NULL, d->att_scratch, splits, st));
+                                 c->max_seq_len, max_limit, kvf32, d->att, NULL, d->att_scratch, splits, st));
         /* ---- output projection + residual, FFN + residual */
         if (tiny) {
-            if (d->tp == 1) DEV(cmlb200_gemv_xq(&L->wo, NULL, d->xq_b, d->h, rows, 1, st));
-            else {
-                DEV(cmlb200_gemv_xq(&L->wo, NULL, d->xq_b, d->tmp, rows, 0, st));
-                if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * H, st)) return -1;
-                DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * H, st));
-            }
-            DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
-            DEV(cmlb200_gemv_xq(&L->wg, &L->wu, d->xq_a, d->ffn, rows, 2, st));
-            DEV(cmlb200_x_digits(d->ffn, rows, d->inter_l, d->xq_c, st));
-            if (d->tp == 1) DEV(cmlb200_gemv_xq(&L->wd, NULL, d->xq_c, d->h, rows, 1, st));
-            else {
-                DEV(cmlb200_gemv_xq(&L->wd, NULL, d->xq_c, d->tmp, rows, 0, st));
-                if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * H, st)) return -1;
-                DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * H, st));
-            }
+            if (proj_residual_f32(d, &L->wo, d->att, rows)) return -1;
+            DEV(cmlb200_gemv_rmsnorm(&L->wg, &L->wu, d->h, (const uint16_t*)L->n2, c->rms_norm_eps, d->ffn, rows, 2, st));
+            if (proj_residual_f32(d, &L->wd, d->ffn, rows)) return -1;
         } else if (skinny) {
             if (proj_residual_f32(d, &L->wo, d->att, rows)) return -1;
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
@@ -632,8 +615,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
         }
     }
     if (tiny) {
-        DEV(cmlb200_rmsnorm_digits(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, NULL, d->xq_a, st));
-        DEV(cmlb200_gemv_xq(&d->lm_head, NULL, d->xq_a, d->logits, rows, 0, st));
+        DEV(cmlb200_gemv_rmsnorm(&d->lm_head, NULL, d->h, (const uint16_t*)d->fnorm, c->rms_norm_eps, d->logits, rows, 0, st));
     } else if (skinny) {
         DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
         if (lin_f32(d, &d->lm_head, d->nrm, d->logits, rows, 0)) return -1;
