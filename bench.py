@@ -179,6 +179,55 @@ def llama_leg(pkg, synth, prompt_len=512, new_tokens=128, batches=(1, 8), cfg=LL
     return out
 
 
+def llama_tp_leg(pkg, synth, dist, torch, dev, rank, world, prompt_len=512, new_tokens=128, cfg=LLAMA_7B, tag="llama7b_q4_0"):
+    """The same LLaMA-7B-architecture decode with the weights sharded over all ranks (Q/K/V and
+    gate/up by rows, attention-out and FFN-down by columns, NCCL all-reduce after the two
+    row-parallel projections): batch 1, 512-token prompt, 128 greedy tokens. Every rank runs it;
+    the step time is the maximum over ranks."""
+    import tempfile
+    out = {}
+    rng = np.random.default_rng(99)
+    path = os.path.join(tempfile.gettempdir(), f"cmlb200_tp_{os.environ.get('MASTER_PORT', '0')}.gguf")
+    if rank == 0:
+        synth.write_random_llama_gguf(path, rng, cfg)
+    dist.barrier()
+    try:
+        ident = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            assert pkg.lib.cml_llama_tp_unique_id(buf) == 0
+            ident = torch.tensor(list(buf), dtype=torch.uint8, device=dev)
+        dist.broadcast(ident, 0)
+        idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
+        c = pkg.LlamaConfig(cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv_heads"],
+                            cfg["max_seq"], 10000.0, 1e-5, world, rank)
+        m = pkg.lib.cml_llama_create(C.byref(c))
+        assert m and pkg.lib.cml_llama_set_options(m, 0, 1) == 0
+        assert pkg.lib.cml_llama_tp_init(m, idb, dev.index) == 0, "cml_llama_tp_init failed"
+        assert pkg.lib.cml_llama_load_gguf(m, path.encode()) == 0, "cml_llama_load_gguf failed"
+        prng = np.random.default_rng(7)
+        prompt = prng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+        t0 = time.perf_counter()
+        assert pkg.lib.cml_llama_prefill_sequence(m, 0, pkg.np_ptr(prompt), prompt_len) == 0
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        first = np.array([5], np.int32)
+        toks = np.zeros((new_tokens, 1), np.int32)
+        ms = C.c_float(0)
+        assert pkg.lib.cml_llama_decode_greedy(m, pkg.np_ptr(first), 1, new_tokens, pkg.np_ptr(toks), C.byref(ms)) == 0
+        t = torch.tensor([ms.value, prefill_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[f"{tag}_tp{world}_decode_tok_s_b1"] = new_tokens / (float(t[0]) * 1e-3)
+        out[f"{tag}_tp{world}_decode_ms_per_step_b1"] = float(t[0]) / new_tokens
+        out[f"{tag}_tp{world}_prefill_tok_s_b1"] = prompt_len / float(t[1])
+        pkg.lib.cml_llama_free(m)
+    finally:
+        dist.barrier()
+        if rank == 0 and os.path.exists(path):
+            os.remove(path)
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -228,6 +277,14 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        if not os.environ.get("CML_NCCL_LIB"):      # the library's dlopen should find the NCCL torch itself uses
+            try:
+                import nvidia.nccl
+                cand = os.path.join(list(nvidia.nccl.__path__)[0], "lib", "libnccl.so.2")
+                if os.path.exists(cand):
+                    os.environ["CML_NCCL_LIB"] = cand
+            except ImportError:
+                pass
 
     if args.profile_llama:
         cfg = dict(LLAMA_7B, layers=4)
@@ -361,6 +418,15 @@ def main():
             extra.update(llama_leg(pkg, synth))
         except Exception as exc:                     # the GEMV headline stands on its own
             extra["llama7b_q4_0_error"] = repr(exc)[:300]
+    if world > 1 and not args.skip_llama:
+        del weights, keep
+        torch.cuda.empty_cache()
+        try:
+            tp_out = llama_tp_leg(pkg, synth, dist, torch, dev, rank, world)
+            if rank == 0:
+                extra.update(tp_out)
+        except Exception as exc:
+            extra[f"llama7b_q4_0_tp{world}_error"] = repr(exc)[:300]
 
     if rank == 0:
         peak, peak_kind = measured_peaks()

@@ -272,13 +272,13 @@ int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_i
  * the wall time of the loop to *elapsed_ms. The step is captured once as a CUDA graph. */
 int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int batch, int steps, int* out_tokens,
                             float* elapsed_ms);
-/* Tensor parallelism over NCCL: every rank creates its model with tensor_parallel_size/rank
- * set, rank 0 obtains an id with cml_llama_tp_unique_id and sends the 128 bytes to the other
- * ranks by any means, then every rank calls cml_llama_tp_init before loading weights. */
 /* cml_tp_shard_weight (include/distributed/tensor_parallel.h:59) for a weight that stays
  * quantized: the shard of a [rows, cols] array of 32-element GGUF blocks along dim 0 (rows) or
  * dim 1 (columns, on block boundaries) into `out`. -1 when the split is uneven. */
 int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int dim, int tp_size, int tp_rank, void* out);
+/* Tensor parallelism over NCCL: every rank creates its model with tensor_parallel_size/rank
+ * set, rank 0 obtains an id with cml_llama_tp_unique_id and sends the 128 bytes to the other
+ * ranks by any means, then every rank calls cml_llama_tp_init before loading weights. */
 int cml_llama_tp_unique_id(void* id128);
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device);
 
