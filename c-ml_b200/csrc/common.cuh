@@ -110,6 +110,43 @@ __device__ __forceinline__ void xq_emit_oct(const float (&e)[4], int sub, unsign
     if (sub == 0) dst[24] = __float_as_uint(amax / (float)kXqFull);
 }
 
+// Workspace of the tensor-parallel all-reduce over peer memory (one per rank, mapped into every
+// other rank through CUDA IPC). Two independent channels: 0 = the stand-alone kernel
+// (tp_allreduce.cu, kTpCtas slices), 1 = the epilogue of the decode GEMV (gemv_mma.cu, one slice
+// per CTA of its grid). Per channel: a sequence counter per slice, a flag word per (peer, slice)
+// and two alternating inboxes with room for max_floats values from each of 8 ranks.
+//   +0      u32 seq0[16]      +64    u32 status
+//   +1024   u32 flags0[8][16]
+//   +2048   u32 seq1[192]     +4096  u32 flags1[8][192]
+//   +16384  float inbox[channel][parity][from][max_floats]
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpCtas = 16;
+constexpr int kTpGemvSlices = 192;
+constexpr size_t kTpHeaderBytes = 16384;
+struct TpPeers {
+    uint8_t* ws[kTpMaxRanks];        // every rank's workspace as mapped in this process (ws[rank] = own)
+    float* h;                        // the residual the sum is added to (GEMV epilogue channel)
+    size_t max_floats;
+    int tp, rank;                    // tp == 0: no all-reduce
+};
+__device__ __forceinline__ uint32_t* tpws_seq(uint8_t* ws, int ch) { return reinterpret_cast<uint32_t*>(ws + (ch ? 2048 : 0)); }
+__device__ __forceinline__ uint32_t* tpws_status(uint8_t* ws) { return reinterpret_cast<uint32_t*>(ws + 64); }
+__device__ __forceinline__ uint32_t* tpws_flags(uint8_t* ws, int ch, int from) {
+    return reinterpret_cast<uint32_t*>(ws + (ch ? 4096 : 1024)) + from * (ch ? kTpGemvSlices : kTpCtas);
+}
+__device__ __forceinline__ float* tpws_inbox(uint8_t* ws, int ch, int parity, int from, size_t max_floats) {
+    return reinterpret_cast<float*>(ws + kTpHeaderBytes) + (((size_t)ch * 2 + parity) * kTpMaxRanks + from) * max_floats;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+constexpr int kTpSpinLimit = 1 << 22;
+
 static inline int cmlb_num_sms() {
     static int sms = 0;
     if (!sms) {

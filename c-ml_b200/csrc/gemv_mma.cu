@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(SW * 32, 1)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
                 const void* __restrict__ xin, const __half* __restrict__ nw, float eps, float* __restrict__ y, int N, int K,
-                int xmode, int epi) {
+                int xmode, int epi, TpPeers tpa) {
     using C = Cfg<TYPE, NW>;
     constexpr int QB = C::QB, NC = 4 * MT;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -218,6 +218,9 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     for (int i = 0; i < NBUF; i++) issue_next(i);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
+    // tensor-parallel epilogue: sequence number of this all-reduce and the inbox buffer it uses
+    const uint32_t tp_seq = tpa.tp ? tpws_seq(tpa.ws[tpa.rank], 1)[blockIdx.x] + 1 : 0u;
+    const int tp_par = (int)(tp_seq & 1u);
 
     // ---- digits of this warp's units of x into the B table. Lane = (block lane>>3 (+4), elements
     // 4*(lane&7)..+3); a unit is 8 blocks = two such passes, loaded together.
@@ -382,7 +385,9 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 }
                 float* out = y + (size_t)m * N + row;
                 if (NW == 2) *out = (sum[0] / (1.0f + expf(-sum[0]))) * sum[NW - 1];
-                else if (epi == EPI_ACCUM) *out += sum[0];
+                else if (tpa.tp) {                           // this rank's share goes to every rank's inbox, its own included
+                    for (int qr = 0; qr < tpa.tp; qr++) tpws_inbox(tpa.ws[qr], 1, tp_par, tpa.rank, tpa.max_floats)[(size_t)m * N + row] = sum[0];
+                } else if (epi == EPI_ACCUM) *out += sum[0];
                 else *out = sum[0];
             }
         }
@@ -431,6 +436,36 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         if (slot == FB - 1 || it == my_items - 1) flush(it - slot, slot + 1);
     }
     cp_async_wait<0>();
+    if (tpa.tp) {
+        // All rows of this CTA are on their way to the peers. Tell every peer (flag word of this rank
+        // and CTA), wait for theirs, then add all ranks' shares in rank order onto the residual.
+        __shared__ int tp_ok;
+        uint8_t* mine = tpa.ws[tpa.rank];
+        if (threadIdx.x == 0) tp_ok = 1;
+        __threadfence_system();
+        __syncthreads();
+        if ((int)threadIdx.x < tpa.tp && (int)threadIdx.x != tpa.rank) {
+            st_release_sys(tpws_flags(tpa.ws[threadIdx.x], 1, tpa.rank) + blockIdx.x, tp_seq);
+            const uint32_t* f = tpws_flags(mine, 1, threadIdx.x) + blockIdx.x;
+            int i = 0;
+            while ((int32_t)(ld_acquire_sys(f) - tp_seq) < 0 && ++i < kTpSpinLimit) {}
+            if (i >= kTpSpinLimit) { tp_ok = 0; atomicExch(tpws_status(mine), 1u + threadIdx.x); }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) tpws_seq(mine, 1)[blockIdx.x] = tp_seq;
+        if (tp_ok) {
+            for (int idx = threadIdx.x; idx < my_items * MT * 16; idx += SW * 32) {
+                const int r = idx & 15, m = (idx >> 4) % MT, it = idx / (16 * MT);
+                const int row = ((int)blockIdx.x + it * (int)gridDim.x) * 16 + r;
+                if (row < N) {
+                    const size_t at = (size_t)m * N + row;
+                    float v = 0.f;
+                    for (int qr = 0; qr < tpa.tp; qr++) v += tpws_inbox(mine, 1, tp_par, qr, tpa.max_floats)[at];
+                    tpa.h[at] += v;
+                }
+            }
+        }
+    }
     TRACE(3);
 }
 
@@ -478,7 +513,7 @@ size_t smem_bytes(int MT, int nblk, int nbuf) {
 
 template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
 int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
-               cudaStream_t st) {
+               const TpPeers& tpa, cudaStream_t st) {
     const int N = W->rows, K = W->cols;
     const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
     auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF>;
@@ -490,7 +525,7 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
     const int grid = min(cmlb_num_sms(), (N + 15) / 16);
     return launch_pdl(kern, dim3(grid), dim3(SW * 32), smem, st, (const uint8_t*)W->qs, (const uint16_t*)W->scales,
                       W2 ? (const uint8_t*)W2->qs : (const uint8_t*)nullptr,
-                      W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi);
+                      W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi, tpa);
 }
 
 int g_nbuf_pref = 0;       // tuning hook: a ring depth to try first (0 = none)
@@ -506,44 +541,46 @@ int pick_nbuf(int MT, int nblk) {
 
 template <int TYPE, int MT, int NW, bool QUIRK, bool BREG>
 int launch_b(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
-             cudaStream_t st) {
+             const TpPeers& tpa, cudaStream_t st) {
     const int nbuf = pick_nbuf<TYPE, NW>(MT, W->cols / 32);
-    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 4>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 3>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 4>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 3>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
     CMLB_REQUIRE(nbuf == 2, "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
-    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 2>(W, W2, xin, nw, eps, y, xmode, epi, st);
+    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 2>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
 }
 
 template <int TYPE, int MT, int NW, bool QUIRK>
 int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
-           cudaStream_t st) {
-    if (W->cols / (32 * KU) <= SW) return launch_b<TYPE, MT, NW, QUIRK, true>(W, W2, xin, nw, eps, y, xmode, epi, st);
-    return launch_b<TYPE, MT, NW, QUIRK, false>(W, W2, xin, nw, eps, y, xmode, epi, st);
+           const TpPeers& tpa, cudaStream_t st) {
+    if (W->cols / (32 * KU) <= SW) return launch_b<TYPE, MT, NW, QUIRK, true>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    return launch_b<TYPE, MT, NW, QUIRK, false>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
 }
 
 // Rows of x two at a time (one launch streams the weight once for both), then one.
 template <int TYPE, int NW, bool QUIRK>
 int run_m(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, size_t x_row_bytes, const __half* nw, float eps, float* y, int M,
-          int xmode, int epi, cudaStream_t st) {
+          int xmode, int epi, const TpPeers& tp0, cudaStream_t st) {
     int m0 = 0, rc = 0;
     while (m0 < M && rc == 0) {
         const void* xm = static_cast<const uint8_t*>(xin) + (size_t)m0 * x_row_bytes;
         float* ym = y + (size_t)m0 * W->rows;
-        if (M - m0 >= 2) { rc = launch<TYPE, 2, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, st); m0 += 2; }
-        else { rc = launch<TYPE, 1, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, st); m0 += 1; }
+        TpPeers tpa = tp0;
+        if (tpa.tp) tpa.h = tp0.h + (size_t)m0 * W->rows;
+        if (M - m0 >= 2) { rc = launch<TYPE, 2, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 2; }
+        else { rc = launch<TYPE, 1, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 1; }
     }
     return rc;
 }
 
 template <int TYPE, bool QUIRK>
 int run_x(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const __half* nw, float eps, const uint32_t* xq, float* y, int M,
-          int epi, cudaStream_t st) {
+          int epi, const TpPeers& tpa, cudaStream_t st) {
     const int K = W->cols;
     const void* xin = xq ? (const void*)xq : (const void*)x;
     const size_t xrb = xq ? (size_t)(K / 32) * XW * 4 : (size_t)K * 4;
     const int xmode = xq ? 0 : (nw ? 2 : 1);
-    if (epi == EPI_SWIGLU) return run_m<TYPE, 2, QUIRK>(W, W2, xin, xrb, nw, eps, y, M, xmode, epi, st);
-    return run_m<TYPE, 1, QUIRK>(W, W2, xin, xrb, nw, eps, y, M, xmode, epi, st);
+    if (epi == EPI_SWIGLU) return run_m<TYPE, 2, QUIRK>(W, W2, xin, xrb, nw, eps, y, M, xmode, epi, tpa, st);
+    return run_m<TYPE, 1, QUIRK>(W, W2, xin, xrb, nw, eps, y, M, xmode, epi, tpa, st);
 }
 
 template <int TYPE>
@@ -566,11 +603,44 @@ bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi) {
 
 // y[M, rows] (= | += | swiglu) for M <= 4. Exactly one of xq (digit records) and x (fp32, with
 // optional RMSNorm weight norm_w) is given. Arguments are validated by the callers.
-int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
-                      const uint32_t* xq, float* y, int M, int epi, cudaStream_t st) {
+static int run_all(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
+                   const uint32_t* xq, float* y, int M, int epi, const TpPeers& tpa, cudaStream_t st) {
     const __half* nw = reinterpret_cast<const __half*>(norm_w);
     const bool quirk = (W->flags & CMLB200_QMAT_SUBNORMAL_SCALES) || (W2 && (W2->flags & CMLB200_QMAT_SUBNORMAL_SCALES));
     const bool q8 = W->type == CMLB200_Q8_0;
-    if (quirk) return q8 ? run_x<CMLB200_Q8_0, true>(W, W2, x, nw, eps, xq, y, M, epi, st) : run_x<CMLB200_Q4_0, true>(W, W2, x, nw, eps, xq, y, M, epi, st);
-    return q8 ? run_x<CMLB200_Q8_0, false>(W, W2, x, nw, eps, xq, y, M, epi, st) : run_x<CMLB200_Q4_0, false>(W, W2, x, nw, eps, xq, y, M, epi, st);
+    if (quirk) return q8 ? run_x<CMLB200_Q8_0, true>(W, W2, x, nw, eps, xq, y, M, epi, tpa, st) : run_x<CMLB200_Q4_0, true>(W, W2, x, nw, eps, xq, y, M, epi, tpa, st);
+    return q8 ? run_x<CMLB200_Q8_0, false>(W, W2, x, nw, eps, xq, y, M, epi, tpa, st) : run_x<CMLB200_Q4_0, false>(W, W2, x, nw, eps, xq, y, M, epi, tpa, st);
+}
+
+int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
+                      const uint32_t* xq, float* y, int M, int epi, cudaStream_t st) {
+    return run_all(W, W2, x, norm_w, eps, xq, y, M, epi, TpPeers{}, st);
+}
+
+// Row-parallel projection of a tensor-parallel layer with the all-reduce in its epilogue:
+// h[M, rows] += sum over ranks of x_rank . dequant(W_rank)^T (src/nn/llama.c:523-530, 538-543 with
+// src/distributed/tensor_parallel.c:195-260 in between). One launch per rank: every CTA sends
+// the rows it finishes to all ranks' inboxes, then exchanges one flag per peer and adds the
+// shares in rank order. All projections that use one workspace must have the same `rows`, since
+// the flags are kept per CTA and the CTA-to-rows mapping depends on rows alone.
+extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x, float* d_h, int M, int tp, int rank, void* const* ws,
+                                         size_t max_floats, void* stream) {
+    CMLB_REQUIRE(W && W->qs && W->scales && d_x && d_h && ws, "cmlb200_gemv_tp_allreduce: NULL argument");
+    CMLB_REQUIRE(M >= 1 && M <= 4, "cmlb200_gemv_tp_allreduce: M=%d outside 1..4", M);
+    CMLB_REQUIRE(tp >= 2 && tp <= kTpMaxRanks && rank >= 0 && rank < tp, "cmlb200_gemv_tp_allreduce: tp=%d rank=%d (tp must be 2..8)", tp, rank);
+    CMLB_REQUIRE(cmlb200_gemv_mma_ok_(W, EPI_STORE), "cmlb200_gemv_tp_allreduce: weight %dx%d type %d is outside the tensor-core decode kernel", W->rows, W->cols, W->type);
+    CMLB_REQUIRE((size_t)M * W->rows <= max_floats && (W->rows + 15) / 16 <= kTpGemvSlices * 64, "cmlb200_gemv_tp_allreduce: M*rows = %zu exceeds the workspace", (size_t)M * W->rows);
+    CMLB_REQUIRE(cmlb_num_sms() <= kTpGemvSlices, "cmlb200_gemv_tp_allreduce: more than %d SMs", kTpGemvSlices);
+    CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0, "cmlb200_gemv_tp_allreduce: x must be 16-byte aligned");
+    TpPeers p = {};
+    for (int r = 0; r < tp; r++) {
+        CMLB_REQUIRE(ws[r], "cmlb200_gemv_tp_allreduce: workspace of rank %d missing", r);
+        p.ws[r] = static_cast<uint8_t*>(ws[r]);
+    }
+    p.tp = tp; p.rank = rank; p.max_floats = max_floats; p.h = d_h;
+    return run_all(W, nullptr, d_x, nullptr, 0.f, nullptr, d_h, M, EPI_STORE, p, as_stream(stream));
+}
+
+extern "C" int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W) {
+    return W && W->qs && W->scales && cmlb200_gemv_mma_ok_(W, EPI_STORE) && cmlb_num_sms() <= kTpGemvSlices ? 1 : 0;
 }

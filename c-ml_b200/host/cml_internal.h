@@ -31,6 +31,7 @@ float cml_f16_to_f32(uint16_t h);
 int cml_nccl_unique_id(void* id128);
 int cml_nccl_init(void** comm, int nranks, int rank, const void* id128);
 int cml_nccl_allreduce_sum_f32(void* comm, float* d_buf, size_t count, void* stream);
+int cml_nccl_allgather_bytes(void* comm, const void* d_send, void* d_recv, size_t bytes, void* stream);
 void cml_nccl_destroy(void* comm);
 
 #endif

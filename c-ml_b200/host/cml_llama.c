@@ -38,6 +38,11 @@ typedef struct DevModel {
     int flags, max_batch, max_rows;
     int tp, rank, device;
     void* comm;
+    /* peer-memory all-reduce for decode-sized rows: every rank's workspace as mapped here
+     * (ar_ws[rank] is this rank's own allocation), NULL when only NCCL is available */
+    void* ar_ws[8];
+    size_t ar_max_floats;
+    int ar_ok;
     int hd, heads_l, kvh_l, qw_l, kvw_l, inter_l;
     DevLayer* L;
     void *embed, *fnorm;
@@ -132,6 +137,11 @@ static void dm_destroy(DevModel* d) {
                     d->row_pos, d->row_limit, d->d_hist};
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
+    for (int r = 0; r < 8; r++) {
+        if (!d->ar_ws[r]) continue;
+        if (r == d->rank) cmlb200_free(d->ar_ws[r]);
+        else cmlb200_ipc_close(d->ar_ws[r]);
+    }
     if (d->comm) cml_nccl_destroy(d->comm);
     if (d->stream) cmlb200_stream_destroy(d->stream);
     free(d);
@@ -190,6 +200,33 @@ int cml_llama_set_options(CMLLLaMAModel* model, int flags, int max_batch) {
 
 int cml_llama_tp_unique_id(void* id128) { return cml_nccl_unique_id(id128); }
 
+/* Maps every rank's all-reduce workspace into this process: own allocation, CUDA IPC handles
+ * exchanged with one ncclAllGather. Ranks must be separate processes on GPUs with peer access;
+ * anything else leaves ar_ok = 0 and the NCCL path in charge. */
+static int tp_peer_setup(DevModel* d) {
+    const int H = d->key->config.hidden_size;
+    void *d_mine = NULL, *d_all = NULL;
+    unsigned char mine[64], all[8 * 64];
+    int rc = -1;
+    if (d->tp > 8) return -1;
+    d->ar_max_floats = (size_t)SKINNY_ROWS * H;
+    const size_t bytes = cmlb200_tp_ar_workspace_bytes(d->ar_max_floats);
+    if (cmlb200_malloc(&d->ar_ws[d->rank], bytes) || cmlb200_memset(d->ar_ws[d->rank], 0, bytes, NULL) || cmlb200_device_sync()) goto done;
+    if (cmlb200_ipc_get_handle(d->ar_ws[d->rank], mine)) goto done;
+    if (cmlb200_malloc(&d_mine, 64) || cmlb200_malloc(&d_all, 64 * (size_t)d->tp)) goto done;
+    if (cmlb200_memcpy_h2d(d_mine, mine, 64, NULL) || cmlb200_device_sync()) goto done;
+    if (cml_nccl_allgather_bytes(d->comm, d_mine, d_all, 64, NULL) || cmlb200_device_sync()) goto done;
+    if (cmlb200_memcpy_d2h(all, d_all, 64 * (size_t)d->tp, NULL) || cmlb200_device_sync()) goto done;
+    rc = 0;
+    for (int r = 0; r < d->tp && rc == 0; r++)
+        if (r != d->rank && cmlb200_ipc_open(all + 64 * r, &d->ar_ws[r])) rc = -1;
+done:
+    cmlb200_free(d_mine);
+    cmlb200_free(d_all);
+    d->ar_ok = rc == 0;
+    return rc;
+}
+
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     if (!model || !id128) { LOG_ERROR("cml_llama_tp_init: NULL argument"); return -1; }
     DevModel* d = dm_get(model);
@@ -198,7 +235,10 @@ int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     if (d->rank < 0 || d->rank >= d->tp) { LOG_ERROR("cml_llama_tp_init: rank %d outside 0..%d", d->rank, d->tp - 1); return -1; }
     DEV(cmlb200_set_device(device));
     d->device = device;
-    return cml_nccl_init(&d->comm, d->tp, d->rank, id128);
+    if (cml_nccl_init(&d->comm, d->tp, d->rank, id128)) return -1;
+    const char* only = getenv("CML_B200_TP_NCCL_ONLY");
+    if (!(only && only[0] == '1') && tp_peer_setup(d)) LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size");
+    return 0;
 }
 
 static int dm_alloc_buffers(DevModel* d) {
@@ -523,7 +563,16 @@ static int lin_f32(DevModel* d, const cmlb200_qmat* W, const float* x, float* y,
 /* Row-parallel projection + residual: h += all_reduce(x . W_shard^T) */
 static int proj_residual_f32(DevModel* d, const cmlb200_qmat* W, const float* x, int rows) {
     if (d->tp == 1) return lin_f32(d, W, x, d->h, rows, 1);
+    if (d->ar_ok && rows <= 4 && W->rows == d->key->config.hidden_size && (size_t)rows * W->rows <= d->ar_max_floats &&
+        cmlb200_gemv_tp_fused_ok(W)) {       /* projection and all-reduce in one launch */
+        DEV(cmlb200_gemv_tp_allreduce(W, x, d->h, rows, d->tp, d->rank, d->ar_ws, d->ar_max_floats, d->stream));
+        return 0;
+    }
     if (lin_f32(d, W, x, d->tmp, rows, 0)) return -1;
+    if (d->ar_ok && (size_t)rows * W->rows <= d->ar_max_floats && ((size_t)rows * W->rows) % 4 == 0) {
+        DEV(cmlb200_tp_allreduce_add(d->h, d->tmp, (size_t)rows * W->rows, d->tp, d->rank, d->ar_ws, d->ar_max_floats, d->stream));
+        return 0;
+    }
     if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, (size_t)rows * W->rows, d->stream)) return -1;
     DEV(cmlb200_add_f32(d->h, d->tmp, (size_t)rows * W->rows, d->stream));
     return 0;

@@ -15,6 +15,7 @@ typedef struct { char internal[128]; } nccl_uid;
 typedef int (*fn_get_uid)(nccl_uid*);
 typedef int (*fn_init_rank)(void**, int, nccl_uid, int);
 typedef int (*fn_allreduce)(const void*, void*, size_t, int, int, void*, void*);
+typedef int (*fn_allgather)(const void*, void*, size_t, int, void*, void*);
 typedef int (*fn_destroy)(void*);
 typedef const char* (*fn_errstr)(int);
 
@@ -23,6 +24,7 @@ static struct {
     fn_get_uid get_uid;
     fn_init_rank init_rank;
     fn_allreduce allreduce;
+    fn_allgather allgather;
     fn_destroy destroy;
     fn_errstr errstr;
 } g_nccl;
@@ -39,6 +41,7 @@ static int load_nccl(void) {
     g_nccl.get_uid = (fn_get_uid)dlsym(g_nccl.lib, "ncclGetUniqueId");
     g_nccl.init_rank = (fn_init_rank)dlsym(g_nccl.lib, "ncclCommInitRank");
     g_nccl.allreduce = (fn_allreduce)dlsym(g_nccl.lib, "ncclAllReduce");
+    g_nccl.allgather = (fn_allgather)dlsym(g_nccl.lib, "ncclAllGather");
     g_nccl.destroy = (fn_destroy)dlsym(g_nccl.lib, "ncclCommDestroy");
     g_nccl.errstr = (fn_errstr)dlsym(g_nccl.lib, "ncclGetErrorString");
     if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.destroy) {
@@ -71,6 +74,12 @@ int cml_nccl_init(void** comm, int nranks, int rank, const void* id128) {
 int cml_nccl_allreduce_sum_f32(void* comm, float* d_buf, size_t count, void* stream) {
     if (!comm || !d_buf) return -1;
     return check(g_nccl.allreduce(d_buf, d_buf, count, 7 /* ncclFloat32 */, 0 /* ncclSum */, comm, stream), "ncclAllReduce");
+}
+
+/* Every rank contributes `bytes` bytes at d_send; d_recv receives nranks * bytes in rank order. */
+int cml_nccl_allgather_bytes(void* comm, const void* d_send, void* d_recv, size_t bytes, void* stream) {
+    if (!comm || !d_send || !d_recv || !g_nccl.allgather) return -1;
+    return check(g_nccl.allgather(d_send, d_recv, bytes, 0 /* ncclInt8 */, comm, stream), "ncclAllGather");
 }
 
 void cml_nccl_destroy(void* comm) {

@@ -246,6 +246,31 @@ int cmlb200_event_record(void* event, void* stream);
 int cmlb200_event_elapsed_ms(void* start, void* stop, float* ms);
 int cmlb200_event_destroy(void* event);
 
+/* ---- tensor-parallel all-reduce over peer memory -------------------------------------------
+ * h[0..n) += sum over ranks of partial[0..n) in one launch per rank, for the decode-sized
+ * messages after the row-parallel projections (C-ML: cml_tp_all_reduce_sum,
+ * src/distributed/tensor_parallel.c:195-260). Each rank owns a workspace of
+ * cmlb200_tp_ar_workspace_bytes(max_floats) bytes from cmlb200_malloc, zero-filled once, and
+ * maps the other ranks' workspaces through CUDA IPC (ranks are separate processes on GPUs with
+ * peer access). ws[r] is rank r's workspace as seen by the caller, ws[rank] its own. n % 4 == 0,
+ * n <= max_floats, 2 <= tp <= 8. Every rank makes the same sequence of calls; the ranks' results
+ * are bit-identical. Waits are bounded: cmlb200_tp_ar_status reports 1 + the peer a launch gave
+ * up on (its h is then untouched), 0 otherwise. */
+size_t cmlb200_tp_ar_workspace_bytes(size_t max_floats);
+int cmlb200_tp_allreduce_add(float* d_h, const float* d_partial, size_t n, int tp, int rank, void* const* ws, size_t max_floats, void* stream);
+int cmlb200_tp_ar_status(const void* own_ws, int* status);
+/* The row-parallel projection and its all-reduce in one launch per rank, for M <= 4 and weights
+ * the tensor-core decode kernel takes (Q4_0 / Q8_0 planes, cols % 256 == 0):
+ * h[M, rows] += sum over ranks of x_rank . dequant(W_rank)^T (src/nn/llama.c:523-530, 538-543 with
+ * src/distributed/tensor_parallel.c:195-260). Same workspaces as above (it uses its own part of
+ * them); all projections sharing a workspace must have the same `rows`. */
+int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x, float* d_h, int M, int tp, int rank, void* const* ws,
+                              size_t max_floats, void* stream);
+int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W);
+int cmlb200_ipc_get_handle(void* d_ptr, void* handle64);
+int cmlb200_ipc_open(const void* handle64, void** d_ptr);
+int cmlb200_ipc_close(void* d_ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,9 @@ for toks in (prompt, np.array([7], np.int32), np.array([11], np.int32)):     # a
     assert got is not None and want is not None
     err = float(np.abs(got - want).max() / np.abs(want).max())
     worst = max(worst, err)
+    both = [None, None]
+    dist.all_gather_object(both, got.tobytes())
+    assert both[0] == both[1], "ranks disagree on the logits"
 assert worst < 2e-3, worst
 dist.barrier()
 pkg.lib.cml_llama_free(m)
@@ -63,15 +66,16 @@ print(f"rank {rank} ok {worst:.2e}")
 '''
 
 
-def test_two_gpu_tensor_parallel_matches_oracle(tmp_path):
+@pytest.mark.parametrize("nccl_only", ["0", "1"])           # peer-memory all-reduce, then NCCL for every size
+def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, nccl_only):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", CML_B200_TP_NCCL_ONLY=nccl_only)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29541", str(script), str(ROOT), str(tmp_path)]
+           "--master-port", "2954" + nccl_only, str(script), str(ROOT), str(tmp_path)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
