@@ -443,7 +443,7 @@ def main():
             "extra": extra,
             "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
                          "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
-                         "traffic": 25397760,   # dram__bytes_read+write per launch, ncu capture in profiles/
+                         "traffic": 25412864,   # dram__bytes_read+write per launch, ncu capture in profiles/
                          "algorithmic_bytes_per_launch": alg_bytes(1), "us_per_launch": per_launch_s * 1e6},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
