@@ -31,7 +31,7 @@
 
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 // gemv_mma.cu: the tensor-core kernel for the shapes it takes
-bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi);
+bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M);
 int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                       const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
 
@@ -696,7 +696,7 @@ int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t s
 // norm_w first when that is not NULL.
 int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                        const uint32_t* xq, float* y, int M, int epi, cudaStream_t st) {
-    if (cmlb200_gemv_mma_ok_(W, epi)) return cmlb200_gemv_mma_(W, W2, xq ? nullptr : x, norm_w, eps, xq, y, M, epi, st);
+    if (cmlb200_gemv_mma_ok_(W, epi, M)) return cmlb200_gemv_mma_(W, W2, xq ? nullptr : x, norm_w, eps, xq, y, M, epi, st);
     uint32_t* ws = nullptr;
     if (xq) x = nullptr;
     else if (!stream_ok(W, 2)) {      // the register kernel may be needed: it reads digits from the library's scratch

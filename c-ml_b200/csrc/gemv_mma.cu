@@ -40,7 +40,8 @@ enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 constexpr int SW = 16;                 // warps per CTA
 constexpr int KU = 8;                  // blocks per unit: what one warp takes from one item at a time
 constexpr int XW = kXqWords;
-constexpr int FB = 4;                  // items whose partial results wait in shared memory for one CTA barrier
+// items whose partial results wait in shared memory for one CTA barrier
+__host__ __device__ constexpr int flush_batch(int nw, int mt) { return (void)nw, (void)mt, 4; }
 constexpr int XFULL = kXqFull - 1;     // |X| <= XFULL + 1 after rounding, which still splits into int8 digits
 
 #ifdef CMLB200_TRACE
@@ -121,14 +122,14 @@ __device__ __forceinline__ float2 scales_of(uint32_t packed) {
 // y: [MT][N]. K % 256 == 0. BREG: K/256 <= SW, every warp owns at most one unit per item and
 // keeps its B fragments in registers. NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi
 // selects store or accumulate.
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, bool TP>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
                 const void* __restrict__ xin, const __half* __restrict__ nw, float eps, float* __restrict__ y, int N, int K,
                 int xmode, int epi, TpPeers tpa) {
     using C = Cfg<TYPE, NW>;
-    constexpr int QB = C::QB, NC = 4 * MT;
+    constexpr int QB = C::QB, NC = 4 * MT, FB = flush_batch(NW, MT);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[SW][MT];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -219,7 +220,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
     // tensor-parallel epilogue: sequence number of this all-reduce and the inbox buffer it uses
-    const uint32_t tp_seq = tpa.tp ? tpws_seq(tpa.ws[tpa.rank], 1)[blockIdx.x] + 1 : 0u;
+    const uint32_t tp_seq = TP ? tpws_seq(tpa.ws[tpa.rank], 1)[blockIdx.x] + 1 : 0u;
     const int tp_par = (int)(tp_seq & 1u);
 
     // ---- digits of this warp's units of x into the B table. Lane = (block lane>>3 (+4), elements
@@ -385,7 +386,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 }
                 float* out = y + (size_t)m * N + row;
                 if (NW == 2) *out = (sum[0] / (1.0f + expf(-sum[0]))) * sum[NW - 1];
-                else if (tpa.tp) {                           // this rank's share goes to every rank's inbox, its own included
+                else if (TP) {                               // this rank's share goes to every rank's inbox, its own included
                     for (int qr = 0; qr < tpa.tp; qr++) tpws_inbox(tpa.ws[qr], 1, tp_par, tpa.rank, tpa.max_floats)[(size_t)m * N + row] = sum[0];
                 } else if (epi == EPI_ACCUM) *out += sum[0];
                 else *out = sum[0];
@@ -394,14 +395,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         __syncthreads();
     };
 
-    int u = 0;
+    int buf = 0, slot = 0;
     for (int it = 0; it < my_items; it++) {
         float acc[NW][2];            // rows g and g+8: sum over blocks of scales * (c_even * 256 + c_odd)
 #pragma unroll
         for (int a = 0; a < NW; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
 
-        for (int o = 0; o < (BREG ? min(my_nun, 1) : my_nun); o++, u++) {
-            const int buf = u % NBUF;
+        for (int o = 0; o < (BREG ? min(my_nun, 1) : my_nun); o++) {
             cp_async_wait<NBUF - 1>();
             __syncwarp();
             const uint32_t ub = ring0 + buf * C::UNIT_BYTES;
@@ -417,11 +417,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
             }
             __syncwarp();                                    // every lane is done with this buffer
             issue_next(buf);
+            buf = (buf + 1 == NBUF) ? 0 : buf + 1;
         }
 
         // ---- combine the column pairs (t even: d0*256 + d1, t odd: d2*256) and park the item
         if (DBG_SKIP(2)) continue;
-        const int slot = it % FB;
 #pragma unroll
         for (int a = 0; a < NW; a++) {
             float p_lo = acc[a][0] * wgt, p_hi = acc[a][1] * wgt;
@@ -433,10 +433,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 dst[8] = p_hi;
             }
         }
-        if (slot == FB - 1 || it == my_items - 1) flush(it - slot, slot + 1);
+        if (slot == FB - 1 || it == my_items - 1) { flush(it - slot, slot + 1); slot = 0; }
+        else slot++;
     }
     cp_async_wait<0>();
-    if (tpa.tp) {
+    if (TP) {
         // All rows of this CTA are on their way to the peers. Tell every peer (flag word of this rank
         // and CTA), wait for theirs, then add all ranks' shares in rank order onto the residual.
         __shared__ int tp_ok;
@@ -507,16 +508,16 @@ constexpr size_t kSmemLimit = 227 * 1024;
 
 template <int TYPE, int NW>
 size_t smem_bytes(int MT, int nblk, int nbuf) {
-    return (size_t)nblk * 4 * MT * 32 + ((((size_t)MT * (nblk / KU) + 31) & ~(size_t)31) + FB * SW * NW * MT * 16) * sizeof(float) +
+    return (size_t)nblk * 4 * MT * 32 + ((((size_t)MT * (nblk / KU) + 31) & ~(size_t)31) + flush_batch(NW, MT) * SW * NW * MT * 16) * sizeof(float) +
            (size_t)SW * nbuf * Cfg<TYPE, NW>::UNIT_BYTES;
 }
 
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF>
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, bool TP>
 int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
                const TpPeers& tpa, cudaStream_t st) {
     const int N = W->rows, K = W->cols;
     const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
-    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF>;
+    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF, TP>;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
         CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -528,25 +529,20 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
                       W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi, tpa);
 }
 
-int g_nbuf_pref = 0;       // tuning hook: a ring depth to try first (0 = none)
-
 // Ring depth. Two buffers per warp measured fastest on the 11008 x 4096 case (6.35 us against
 // 6.68 and 7.17 with three and four): 32 KB of copies per SM are requested before the dependency
 // wait and a deeper ring only lengthens that prologue, which sits on the launch-to-launch path.
+constexpr int kNbuf = 2;
+
 template <int TYPE, int NW>
-int pick_nbuf(int MT, int nblk) {
-    if (g_nbuf_pref >= 2 && g_nbuf_pref <= 4 && smem_bytes<TYPE, NW>(MT, nblk, g_nbuf_pref) <= kSmemLimit) return g_nbuf_pref;
-    return smem_bytes<TYPE, NW>(MT, nblk, 2) <= kSmemLimit ? 2 : 0;
-}
+bool fits_smem(int MT, int nblk) { return smem_bytes<TYPE, NW>(MT, nblk, kNbuf) <= kSmemLimit; }
 
 template <int TYPE, int MT, int NW, bool QUIRK, bool BREG>
 int launch_b(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
              const TpPeers& tpa, cudaStream_t st) {
-    const int nbuf = pick_nbuf<TYPE, NW>(MT, W->cols / 32);
-    if (nbuf == 4) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 4>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
-    if (nbuf == 3) return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 3>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
-    CMLB_REQUIRE(nbuf == 2, "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
-    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, 2>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    CMLB_REQUIRE((fits_smem<TYPE, NW>(MT, W->cols / 32)), "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
+    if (NW == 1 && tpa.tp) return launch_cfg<TYPE, MT, 1, QUIRK, BREG, kNbuf, true>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, kNbuf, false>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
 }
 
 template <int TYPE, int MT, int NW, bool QUIRK>
@@ -584,21 +580,20 @@ int run_x(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const _
 }
 
 template <int TYPE>
-bool fits(int nblk, int epi) {
-    return epi == EPI_SWIGLU ? pick_nbuf<TYPE, 2>(2, nblk) > 0 : pick_nbuf<TYPE, 1>(2, nblk) > 0;
+bool fits(int nblk, int epi, int mt) {
+    return epi == EPI_SWIGLU ? fits_smem<TYPE, 2>(mt, nblk) : fits_smem<TYPE, 1>(mt, nblk);
 }
 
 }  // namespace
 
-extern "C" void cmlb200_gemv_mma_tune_(int nbuf) { g_nbuf_pref = nbuf; }
-
 // Shapes the tensor-core decode kernel takes: whole 8-block slices of K with 16-byte aligned
 // scale rows, and room in shared memory for the digit table of two rows of x next to the rings.
-bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi) {
+bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M) {
     if (W->type != CMLB200_Q4_0 && W->type != CMLB200_Q8_0) return false;
     if (W->cols % 256 != 0 || ((uintptr_t)W->qs & 15) || ((uintptr_t)W->scales & 15)) return false;
     const int nblk = W->cols / 32;
-    return W->type == CMLB200_Q8_0 ? fits<CMLB200_Q8_0>(nblk, epi) : fits<CMLB200_Q4_0>(nblk, epi);
+    const int mt = M >= 2 ? 2 : 1;             // rows of x go two per launch, then one
+    return W->type == CMLB200_Q8_0 ? fits<CMLB200_Q8_0>(nblk, epi, mt) : fits<CMLB200_Q4_0>(nblk, epi, mt);
 }
 
 // y[M, rows] (= | += | swiglu) for M <= 4. Exactly one of xq (digit records) and x (fp32, with
@@ -628,7 +623,7 @@ extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x
     CMLB_REQUIRE(W && W->qs && W->scales && d_x && d_h && ws, "cmlb200_gemv_tp_allreduce: NULL argument");
     CMLB_REQUIRE(M >= 1 && M <= 4, "cmlb200_gemv_tp_allreduce: M=%d outside 1..4", M);
     CMLB_REQUIRE(tp >= 2 && tp <= kTpMaxRanks && rank >= 0 && rank < tp, "cmlb200_gemv_tp_allreduce: tp=%d rank=%d (tp must be 2..8)", tp, rank);
-    CMLB_REQUIRE(cmlb200_gemv_mma_ok_(W, EPI_STORE), "cmlb200_gemv_tp_allreduce: weight %dx%d type %d is outside the tensor-core decode kernel", W->rows, W->cols, W->type);
+    CMLB_REQUIRE(cmlb200_gemv_mma_ok_(W, EPI_STORE, M), "cmlb200_gemv_tp_allreduce: weight %dx%d type %d is outside the tensor-core decode kernel", W->rows, W->cols, W->type);
     CMLB_REQUIRE((size_t)M * W->rows <= max_floats && (W->rows + 15) / 16 <= kTpGemvSlices * 64, "cmlb200_gemv_tp_allreduce: M*rows = %zu exceeds the workspace", (size_t)M * W->rows);
     CMLB_REQUIRE(cmlb_num_sms() <= kTpGemvSlices, "cmlb200_gemv_tp_allreduce: more than %d SMs", kTpGemvSlices);
     CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0, "cmlb200_gemv_tp_allreduce: x must be 16-byte aligned");
@@ -641,6 +636,6 @@ extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x
     return run_all(W, nullptr, d_x, nullptr, 0.f, nullptr, d_h, M, EPI_STORE, p, as_stream(stream));
 }
 
-extern "C" int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W) {
-    return W && W->qs && W->scales && cmlb200_gemv_mma_ok_(W, EPI_STORE) && cmlb_num_sms() <= kTpGemvSlices ? 1 : 0;
+extern "C" int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W, int M) {
+    return W && W->qs && W->scales && M >= 1 && M <= 4 && cmlb200_gemv_mma_ok_(W, EPI_STORE, M) && cmlb_num_sms() <= kTpGemvSlices ? 1 : 0;
 }

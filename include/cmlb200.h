@@ -266,7 +266,7 @@ int cmlb200_tp_ar_status(const void* own_ws, int* status);
  * them); all projections sharing a workspace must have the same `rows`. */
 int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x, float* d_h, int M, int tp, int rank, void* const* ws,
                               size_t max_floats, void* stream);
-int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W);
+int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W, int M);
 int cmlb200_ipc_get_handle(void* d_ptr, void* handle64);
 int cmlb200_ipc_open(const void* handle64, void** d_ptr);
 int cmlb200_ipc_close(void* d_ptr);
