@@ -395,13 +395,14 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         __syncthreads();
     };
 
-    int buf = 0, slot = 0;
+    int u = 0;
     for (int it = 0; it < my_items; it++) {
         float acc[NW][2];            // rows g and g+8: sum over blocks of scales * (c_even * 256 + c_odd)
 #pragma unroll
         for (int a = 0; a < NW; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
 
-        for (int o = 0; o < (BREG ? min(my_nun, 1) : my_nun); o++) {
+        for (int o = 0; o < (BREG ? min(my_nun, 1) : my_nun); o++, u++) {
+            const int buf = u % NBUF;
             cp_async_wait<NBUF - 1>();
             __syncwarp();
             const uint32_t ub = ring0 + buf * C::UNIT_BYTES;
@@ -417,11 +418,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
             }
             __syncwarp();                                    // every lane is done with this buffer
             issue_next(buf);
-            buf = (buf + 1 == NBUF) ? 0 : buf + 1;
         }
 
         // ---- combine the column pairs (t even: d0*256 + d1, t odd: d2*256) and park the item
         if (DBG_SKIP(2)) continue;
+        const int slot = it % FB;
 #pragma unroll
         for (int a = 0; a < NW; a++) {
             float p_lo = acc[a][0] * wgt, p_hi = acc[a][1] * wgt;
@@ -433,8 +434,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 dst[8] = p_hi;
             }
         }
-        if (slot == FB - 1 || it == my_items - 1) { flush(it - slot, slot + 1); slot = 0; }
-        else slot++;
+        if (slot == FB - 1 || it == my_items - 1) flush(it - slot, slot + 1);
     }
     cp_async_wait<0>();
     if (TP) {
