@@ -252,6 +252,163 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ qkv, int stride, cons
     }
 }
 
+// ---- decode attention in one launch: RoPE of the new token's Q and K, cache append, split-KV
+// attention and the merge of the splits (cml_rope_forward src/nn/llm_ops.c:702-805,
+// cml_kv_cache_append :118-157, cml_gqa_forward :243-372 for one new token per sequence).
+// grid = (heads, rows, splits), 128 threads. Every CTA rotates its own head of Q; the CTA whose
+// key range holds the new token's position takes that key and value from the q|k|v buffer (rotated,
+// rounded to the cache type) instead of the cache, and the first Q head of each KV group also
+// writes them into the cache for later steps, so no CTA reads a cache row another CTA writes.
+// Each CTA leaves an unnormalised partial (max, sum, acc[hd]); the last CTA of a (row, head) to
+// arrive (atomic counter, reset for the next launch) merges the splits in split order.
+// Requires that all other attended keys are in the cache already: one row per sequence.
+template <typename KV, int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restrict__ kc, KV* __restrict__ vc,
+                        const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ row_limit,
+                        int heads, int kv_heads, int max_seq, int chunk, float rope_base, float* __restrict__ partial,
+                        unsigned int* __restrict__ counters, float* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int PER = HD / 32;                       // contiguous head-dim elements per lane
+    constexpr int NW = ATT_THREADS / 32;
+    const int h = blockIdx.x, r = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int qw = heads * HD, kvw = kv_heads * HD, group = heads / kv_heads;
+    const int kh = h / group;
+    const int limit = row_limit[r], pos = row_pos[r];
+    const int k_begin = split * chunk, k_end = min(limit + 1, k_begin + chunk);
+    const size_t base = (size_t)row_seq[r] * max_seq * kvw + (size_t)kh * HD;
+    const float* row = qkv + (size_t)r * stride;
+    const bool has_new = pos >= k_begin && pos < k_end;           // the new token's key belongs to this CTA
+
+    __shared__ float qs[HD], knew[HD], vnew[HD];
+    __shared__ float sm[NW], sl[NW], sacc[NW][HD];
+    __shared__ unsigned int s_last;
+    if (threadIdx.x < HD / 2) {
+        const int i = threadIdx.x;
+        const float freq = 1.0f / powf(rope_base, (float)(2 * i) / (float)HD);
+        const float th = (float)pos * freq;
+        const float c = cosf(th), sn = sinf(th);
+        const float qa = row[(size_t)h * HD + 2 * i], qb = row[(size_t)h * HD + 2 * i + 1];
+        const float scale = 1.0f / sqrtf((float)HD);
+        qs[2 * i] = (qa * c - qb * sn) * scale;
+        qs[2 * i + 1] = (qa * sn + qb * c) * scale;
+        if (has_new) {
+            const float ka = row[qw + (size_t)kh * HD + 2 * i], kb = row[qw + (size_t)kh * HD + 2 * i + 1];
+            const KV k0 = (KV)(ka * c - kb * sn), k1 = (KV)(ka * sn + kb * c);
+            const KV v0 = (KV)row[qw + kvw + (size_t)kh * HD + 2 * i], v1 = (KV)row[qw + kvw + (size_t)kh * HD + 2 * i + 1];
+            knew[2 * i] = (float)k0; knew[2 * i + 1] = (float)k1;
+            vnew[2 * i] = (float)v0; vnew[2 * i + 1] = (float)v1;
+            if (h % group == 0) {
+                const size_t dst = base + (size_t)pos * kvw;
+                kc[dst + 2 * i] = k0; kc[dst + 2 * i + 1] = k1;
+                vc[dst + 2 * i] = v0; vc[dst + 2 * i + 1] = v1;
+            }
+        }
+    }
+    __syncthreads();
+    float qv[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) qv[i] = qs[lane * PER + i];
+    float m = -INFINITY, l = 0.f, acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) acc[i] = 0.f;
+    // A warp takes KB consecutive keys per step and requests all their K and V rows (one vector load
+    // per lane and row) before it consumes any.
+    constexpr int KB = 8;
+    for (int sk0 = k_begin + warp * KB; sk0 < k_end; sk0 += NW * KB) {
+        float kr[KB][PER], vr[KB][PER];
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            const int sk = min(sk0 + j, k_end - 1);
+            const KV* kp = kc + base + (size_t)sk * kvw + lane * PER;
+            const KV* vp = vc + base + (size_t)sk * kvw + lane * PER;
+            if (sizeof(KV) == 2 && PER == 4) {
+                const uint2 ku = *reinterpret_cast<const uint2*>(kp), vu = *reinterpret_cast<const uint2*>(vp);
+                const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&ku.x)), k23 = __half22float2(*reinterpret_cast<const __half2*>(&ku.y));
+                const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vu.x)), v23 = __half22float2(*reinterpret_cast<const __half2*>(&vu.y));
+                kr[j][0] = k01.x; kr[j][1] = k01.y; kr[j][2 % PER] = k23.x; kr[j][3 % PER] = k23.y;
+                vr[j][0] = v01.x; vr[j][1] = v01.y; vr[j][2 % PER] = v23.x; vr[j][3 % PER] = v23.y;
+            } else {
+#pragma unroll
+                for (int i = 0; i < PER; i++) { kr[j][i] = (float)kp[i]; vr[j][i] = (float)vp[i]; }
+            }
+            if (sk == pos) {                            // the row being written by another CTA: take the values from the buffer
+#pragma unroll
+                for (int i = 0; i < PER; i++) { kr[j][i] = knew[lane * PER + i]; vr[j][i] = vnew[lane * PER + i]; }
+            }
+        }
+        float d[KB];
+        float bm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; i++) t = fmaf(qv[i], kr[j][i], t);
+            d[j] = (sk0 + j < k_end) ? warp_sum(t) : -INFINITY;
+            bm = fmaxf(bm, d[j]);
+        }
+        const float mn = fmaxf(m, bm);
+        const float corr = expf(m - mn);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] *= corr;
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            const float p = expf(d[j] - mn);               // exp(-inf) = 0 for keys past the end
+            l += p;
+#pragma unroll
+            for (int i = 0; i < PER; i++) acc[i] = fmaf(p, vr[j][i], acc[i]);
+        }
+        m = mn;
+    }
+    if (lane == 0) { sm[warp] = m; sl[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < PER; i++) sacc[warp][lane * PER + i] = acc[i];
+    __syncthreads();
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; w++) gm = fmaxf(gm, sm[w]);
+    const size_t rh = (size_t)r * heads + h;
+    float* mine = partial + (rh * nsplit + split) * (HD + 2);
+    if (threadIdx.x < HD) {
+        float a = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) {
+            const float c = (sm[w] == -INFINITY) ? 0.f : expf(sm[w] - gm);
+            a = fmaf(sacc[w][threadIdx.x], c, a);
+            lt = fmaf(sl[w], c, lt);
+        }
+        mine[2 + threadIdx.x] = a;
+        if (threadIdx.x == 0) { mine[0] = gm; mine[1] = lt; }
+    }
+    // ---- the last split of this (row, head) to finish merges all of them
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&counters[rh], 1u) == (unsigned)nsplit - 1) ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[rh] = 0u;            // ready for the next launch
+    const float* p = partial + rh * nsplit * (HD + 2);
+    float mg = -INFINITY;
+    for (int s2 = 0; s2 < nsplit; s2++) mg = fmaxf(mg, __ldcg(p + s2 * (HD + 2)));
+    float lg = 0.f;
+    for (int s2 = 0; s2 < nsplit; s2++) {
+        const float ms = __ldcg(p + s2 * (HD + 2));
+        if (ms != -INFINITY) lg += __ldcg(p + s2 * (HD + 2) + 1) * expf(ms - mg);
+    }
+    if (threadIdx.x < HD) {
+        float a = 0.f;
+        for (int s2 = 0; s2 < nsplit; s2++) {
+            const float ms = __ldcg(p + s2 * (HD + 2));
+            if (ms != -INFINITY) a = fmaf(__ldcg(p + s2 * (HD + 2) + 2 + threadIdx.x), expf(ms - mg), a);
+        }
+        out[rh * HD + threadIdx.x] = a / lg;
+    }
+}
+
 // ---- greedy pick: first index holding the strict maximum of each row
 __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
     __shared__ float sv[32];
@@ -466,6 +623,50 @@ extern "C" int cmlb200_attention_ex(const float* d_q, int q_stride, const void* 
     CMLB_REQUIRE(q_stride >= heads * head_dim, "cmlb200_attention_ex: q_stride %d smaller than a row of Q", q_stride);
     return attention_impl(d_q, q_stride, d_kcache, d_vcache, d_row_seq, d_row_limit, rows, heads, kv_heads, head_dim, max_seq,
                           max_limit, kv_is_f32, d_out, (uint32_t*)d_xq, d_scratch, splits, stream);
+}
+
+// Scratch of cmlb200_attention_decode: 16 KB of per-(row, head) arrival counters (rows*heads <= 4096),
+// then the partials.
+constexpr size_t kAttCounterBytes = 16384;
+extern "C" size_t cmlb200_attention_decode_scratch_bytes(int rows, int heads, int head_dim, int splits) {
+    return kAttCounterBytes + cmlb200_attention_scratch_floats(rows, heads, head_dim, splits) * sizeof(float);
+}
+
+// Decode attention for rows that are one new token per sequence: d_qkv holds [rows][q|k|v] as the
+// projection left it (row_stride floats apart, nothing rotated yet). Rotates Q and K of every head
+// at row_pos, appends K and V to the cache, attends keys 0..row_limit (row_limit[r] >= row_pos[r]
+// is not required, but the new key is only used when row_pos[r] <= row_limit[r]) and writes
+// [rows][heads*head_dim] fp32. d_scratch: cmlb200_attention_decode_scratch_bytes bytes whose
+// first 16 KB (the counters) are zero before the first call; the kernel leaves them zero.
+extern "C" int cmlb200_attention_decode(const float* d_qkv, int row_stride, void* d_kcache, void* d_vcache, const int* d_row_seq,
+                                        const int* d_row_pos, const int* d_row_limit, int rows, int heads, int kv_heads,
+                                        int head_dim, int max_seq, int max_limit, int kv_is_f32, float rope_base, float* d_out,
+                                        void* d_scratch, int splits, void* stream) {
+    CMLB_REQUIRE(d_qkv && d_kcache && d_vcache && d_row_seq && d_row_pos && d_row_limit && d_out && d_scratch, "cmlb200_attention_decode: NULL argument");
+    CMLB_REQUIRE(rows > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "cmlb200_attention_decode: num_heads (%d) must be divisible by num_kv_heads (%d)", heads, kv_heads);
+    CMLB_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 32, "cmlb200_attention_decode: head_dim %d not in {32, 64, 128}", head_dim);
+    CMLB_REQUIRE(row_stride >= (heads + 2 * kv_heads) * head_dim, "cmlb200_attention_decode: row_stride %d smaller than a q|k|v row", row_stride);
+    CMLB_REQUIRE(splits >= 1 && max_limit >= 0 && max_limit < max_seq, "cmlb200_attention_decode: bad splits/max_limit");
+    if (rope_base <= 0.f) rope_base = 10000.0f;
+    const int chunk = (max_limit + 1 + splits - 1) / splits;
+    CMLB_REQUIRE((size_t)rows * heads * sizeof(unsigned int) <= kAttCounterBytes, "cmlb200_attention_decode: rows*heads = %d exceeds 4096", rows * heads);
+    unsigned int* counters = static_cast<unsigned int*>(d_scratch);
+    float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(d_scratch) + kAttCounterBytes);
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t c1 = {};
+    c1.gridDim = dim3(heads, rows, splits); c1.blockDim = dim3(ATT_THREADS); c1.stream = as_stream(stream); c1.attrs = pdl; c1.numAttrs = 1;
+#define ATT_LAUNCH(KV, HD)                                                                                                    \
+    CMLB_CUDA(cudaLaunchKernelEx(&c1, attention_decode_kernel<KV, HD>, d_qkv, row_stride, (KV*)d_kcache, (KV*)d_vcache, d_row_seq, \
+                                 d_row_pos, d_row_limit, heads, kv_heads, max_seq, chunk, rope_base, partial, counters, d_out))
+    if (kv_is_f32) {
+        if (head_dim == 128) { ATT_LAUNCH(float, 128); } else if (head_dim == 64) { ATT_LAUNCH(float, 64); } else { ATT_LAUNCH(float, 32); }
+    } else {
+        if (head_dim == 128) { ATT_LAUNCH(__half, 128); } else if (head_dim == 64) { ATT_LAUNCH(__half, 64); } else { ATT_LAUNCH(__half, 32); }
+    }
+#undef ATT_LAUNCH
+    return CMLB200_OK;
 }
 
 extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* d_row_seq, const int* d_row_pos, int rows,

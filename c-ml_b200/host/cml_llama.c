@@ -283,9 +283,12 @@ static int dm_alloc_buffers(DevModel* d) {
     DEV(cmlb200_malloc((void**)&d->b_c, R * wide * 2));
     DEV(cmlb200_malloc((void**)&d->b_d, R * wide * 2));
     d->att_splits_cap = (c->max_seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
-    DEV(cmlb200_malloc((void**)&d->att_scratch,
-                       cmlb200_attention_scratch_floats(SKINNY_ROWS, d->heads_l, d->hd, d->att_splits_cap) * 4 +
-                           cmlb200_attention_scratch_floats(d->max_rows, d->heads_l, d->hd, 1) * 4));
+    {   /* the larger of: split partials for a skinny call (+ the decode kernel's counters), one split for a prefill call */
+        const size_t bytes = cmlb200_attention_decode_scratch_bytes(SKINNY_ROWS, d->heads_l, d->hd, d->att_splits_cap) +
+                             cmlb200_attention_scratch_floats(d->max_rows, d->heads_l, d->hd, 1) * 4;
+        DEV(cmlb200_malloc((void**)&d->att_scratch, bytes));
+        DEV(cmlb200_memset(d->att_scratch, 0, bytes, NULL));
+    }
     DEV(cmlb200_malloc((void**)&d->d_tokens, R * 4));
     DEV(cmlb200_malloc((void**)&d->d_cur, (size_t)d->max_batch * 4));
     DEV(cmlb200_malloc((void**)&d->row_seq, R * 4));
@@ -612,6 +615,8 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     /* With tensor parallelism head 0 lives on rank 0 only, so C-ML's "head 0 only" rotation
      * touches nothing on the other ranks. */
     const int rotate = quirks ? (d->rank == 0 ? 1 : 0) : -1;
+    /* one new token per sequence, position-correct behaviour: RoPE, cache append, attention and merge in one launch */
+    const int fused_att = !quirks && rows <= SKINNY_ROWS && (mode == 1 || rows == 1) && rows * d->heads_l <= 4096;
     const size_t esz = kvf32 ? 4 : 2;
     for (int li = 0; li < m->num_layers; li++) {
         const DevLayer* L = &d->L[li];
@@ -628,10 +633,15 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
             DEV(cmlb200_gemm_bf16(&L->wqkv, d->b_a, d->b_b, rows, st));
             DEV(cmlb200_bf16_to_f32(d->b_b, d->qkv, (size_t)rows * d->qkv_w, st));
         }
-        DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
-                                    rotate, kc, vc, c->max_seq_len, kvf32, st));
-        DEV(cmlb200_attention_ex(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd,
-                                 c->max_seq_len, max_limit, kvf32, d->att, NULL, d->att_scratch, splits, st));
+        if (fused_att) {
+            DEV(cmlb200_attention_decode(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_pos, d->row_limit, rows, d->heads_l, d->kvh_l,
+                                         d->hd, c->max_seq_len, max_limit, kvf32, c->rope_theta, d->att, d->att_scratch, splits, st));
+        } else {
+            DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
+                                        rotate, kc, vc, c->max_seq_len, kvf32, st));
+            DEV(cmlb200_attention_ex(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd,
+                                     c->max_seq_len, max_limit, kvf32, d->att, NULL, (float*)d->att_scratch + 4096, splits, st));
+        }
         /* ---- output projection + residual, FFN + residual */
         if (tiny) {
             if (proj_residual_f32(d, &L->wo, d->att, rows)) return -1;
