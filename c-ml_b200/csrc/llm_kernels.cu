@@ -262,16 +262,31 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ qkv, int stride, cons
 // Each CTA leaves an unnormalised partial (max, sum, acc[hd]); the last CTA of a (row, head) to
 // arrive (atomic counter, reset for the next launch) merges the splits in split order.
 // Requires that all other attended keys are in the cache already: one row per sequence.
+// cos/sin of every rotation pair at each row's position: cs[row][i] = (cos, sin)(pos * base^(-2i/hd)),
+// computed once per decode step and read by every layer's attention launch.
+__global__ void rope_table_kernel(const int* __restrict__ row_pos, int hd, float base, float2* __restrict__ cs) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int r = blockIdx.x, i = threadIdx.x;
+    if (i < hd / 2) {
+        const float freq = 1.0f / powf(base, (float)(2 * i) / (float)hd);
+        const float th = (float)row_pos[r] * freq;
+        cs[(size_t)r * (hd / 2) + i] = make_float2(cosf(th), sinf(th));
+    }
+}
+
+constexpr int ATTD_THREADS = 128;
+constexpr int ATTD_MAX_SPLITS = 256;       // key splits per (row, head) the merge has room for
 template <typename KV, int HD>
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATTD_THREADS)
 attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restrict__ kc, KV* __restrict__ vc,
                         const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ row_limit,
-                        int heads, int kv_heads, int max_seq, int chunk, float rope_base, float* __restrict__ partial,
-                        unsigned int* __restrict__ counters, float* __restrict__ out) {
+                        int heads, int kv_heads, int max_seq, int chunk, const float2* __restrict__ rope_cs,
+                        float* __restrict__ partial, unsigned int* __restrict__ counters, float* __restrict__ out) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int PER = HD / 32;                       // contiguous head-dim elements per lane
-    constexpr int NW = ATT_THREADS / 32;
+    constexpr int NW = ATTD_THREADS / 32;
     const int h = blockIdx.x, r = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int qw = heads * HD, kvw = kv_heads * HD, group = heads / kv_heads;
@@ -287,17 +302,17 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
     __shared__ unsigned int s_last;
     if (threadIdx.x < HD / 2) {
         const int i = threadIdx.x;
-        const float freq = 1.0f / powf(rope_base, (float)(2 * i) / (float)HD);
-        const float th = (float)pos * freq;
-        const float c = cosf(th), sn = sinf(th);
-        const float qa = row[(size_t)h * HD + 2 * i], qb = row[(size_t)h * HD + 2 * i + 1];
+        const float2 cs = rope_cs[(size_t)r * (HD / 2) + i];
+        const float c = cs.x, sn = cs.y;
+        const float2 qp = *reinterpret_cast<const float2*>(row + (size_t)h * HD + 2 * i);
         const float scale = 1.0f / sqrtf((float)HD);
-        qs[2 * i] = (qa * c - qb * sn) * scale;
-        qs[2 * i + 1] = (qa * sn + qb * c) * scale;
+        qs[2 * i] = (qp.x * c - qp.y * sn) * scale;
+        qs[2 * i + 1] = (qp.x * sn + qp.y * c) * scale;
         if (has_new) {
-            const float ka = row[qw + (size_t)kh * HD + 2 * i], kb = row[qw + (size_t)kh * HD + 2 * i + 1];
-            const KV k0 = (KV)(ka * c - kb * sn), k1 = (KV)(ka * sn + kb * c);
-            const KV v0 = (KV)row[qw + kvw + (size_t)kh * HD + 2 * i], v1 = (KV)row[qw + kvw + (size_t)kh * HD + 2 * i + 1];
+            const float2 kp = *reinterpret_cast<const float2*>(row + qw + (size_t)kh * HD + 2 * i);
+            const float2 vp = *reinterpret_cast<const float2*>(row + qw + kvw + (size_t)kh * HD + 2 * i);
+            const KV k0 = (KV)(kp.x * c - kp.y * sn), k1 = (KV)(kp.x * sn + kp.y * c);
+            const KV v0 = (KV)vp.x, v1 = (KV)vp.y;
             knew[2 * i] = (float)k0; knew[2 * i + 1] = (float)k1;
             vnew[2 * i] = (float)v0; vnew[2 * i + 1] = (float)v1;
             if (h % group == 0) {
@@ -315,7 +330,7 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
 #pragma unroll
     for (int i = 0; i < PER; i++) acc[i] = 0.f;
     // A warp takes KB consecutive keys per step and requests all their K and V rows (one vector load
-    // per lane and row) before it consumes any.
+    // per lane and row) before it consumes any; with a chunk of 32 keys every warp makes one step.
     constexpr int KB = 8;
     for (int sk0 = k_begin + warp * KB; sk0 < k_end; sk0 += NW * KB) {
         float kr[KB][PER], vr[KB][PER];
@@ -391,20 +406,36 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
     if (!s_last) return;
     __threadfence();
     if (threadIdx.x == 0) counters[rh] = 0u;            // ready for the next launch
+    // Two rounds of loads, each issued as one batch: the splits' (max, sum) pairs by one thread each,
+    // then every output element's share of all splits.
     const float* p = partial + rh * nsplit * (HD + 2);
-    float mg = -INFINITY;
-    for (int s2 = 0; s2 < nsplit; s2++) mg = fmaxf(mg, __ldcg(p + s2 * (HD + 2)));
-    float lg = 0.f;
-    for (int s2 = 0; s2 < nsplit; s2++) {
-        const float ms = __ldcg(p + s2 * (HD + 2));
-        if (ms != -INFINITY) lg += __ldcg(p + s2 * (HD + 2) + 1) * expf(ms - mg);
+    __shared__ float s_w[ATTD_MAX_SPLITS], s_l[ATTD_MAX_SPLITS];
+    for (int s2 = threadIdx.x; s2 < nsplit; s2 += ATTD_THREADS) {
+        s_w[s2] = __ldcg(p + s2 * (HD + 2));
+        s_l[s2] = __ldcg(p + s2 * (HD + 2) + 1);
     }
+    __syncthreads();
+    float mg = -INFINITY;
+    for (int s2 = 0; s2 < nsplit; s2++) mg = fmaxf(mg, s_w[s2]);
+    __syncthreads();
+    for (int s2 = threadIdx.x; s2 < nsplit; s2 += ATTD_THREADS) s_w[s2] = (s_w[s2] == -INFINITY) ? 0.f : expf(s_w[s2] - mg);
+    __syncthreads();
     if (threadIdx.x < HD) {
-        float a = 0.f;
-        for (int s2 = 0; s2 < nsplit; s2++) {
-            const float ms = __ldcg(p + s2 * (HD + 2));
-            if (ms != -INFINITY) a = fmaf(__ldcg(p + s2 * (HD + 2) + 2 + threadIdx.x), expf(ms - mg), a);
+        float a = 0.f, lg = 0.f;
+        int s2 = 0;
+        for (; s2 + 8 <= nsplit; s2 += 8) {
+            float as[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) as[k] = __ldcg(p + (s2 + k) * (HD + 2) + 2 + threadIdx.x);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { a = fmaf(as[k], s_w[s2 + k], a); lg = fmaf(s_l[s2 + k], s_w[s2 + k], lg); }
         }
+        float as[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) as[k] = (s2 + k < nsplit) ? __ldcg(p + (s2 + k) * (HD + 2) + 2 + threadIdx.x) : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            if (s2 + k < nsplit) { a = fmaf(as[k], s_w[s2 + k], a); lg = fmaf(s_l[s2 + k], s_w[s2 + k], lg); }
         out[rh * HD + threadIdx.x] = a / lg;
     }
 }
@@ -632,22 +663,35 @@ extern "C" size_t cmlb200_attention_decode_scratch_bytes(int rows, int heads, in
     return kAttCounterBytes + cmlb200_attention_scratch_floats(rows, heads, head_dim, splits) * sizeof(float);
 }
 
+// (cos, sin) of every rotation pair at each row's position: d_cs[rows][head_dim/2][2], for
+// cmlb200_attention_decode. One launch per decode step serves all layers.
+extern "C" int cmlb200_rope_table(const int* d_row_pos, int rows, int head_dim, float base, float* d_cs, void* stream) {
+    CMLB_REQUIRE(d_row_pos && d_cs && rows > 0 && head_dim > 0 && head_dim % 2 == 0 && head_dim <= 2048, "cmlb200_rope_table: bad argument");
+    if (base <= 0.f) base = 10000.0f;
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows); cfg.blockDim = dim3((head_dim / 2 + 31) / 32 * 32); cfg.stream = as_stream(stream); cfg.attrs = pdl; cfg.numAttrs = 1;
+    CMLB_CUDA(cudaLaunchKernelEx(&cfg, rope_table_kernel, d_row_pos, head_dim, base, reinterpret_cast<float2*>(d_cs)));
+    return CMLB200_OK;
+}
+
 // Decode attention for rows that are one new token per sequence: d_qkv holds [rows][q|k|v] as the
 // projection left it (row_stride floats apart, nothing rotated yet). Rotates Q and K of every head
-// at row_pos, appends K and V to the cache, attends keys 0..row_limit (row_limit[r] >= row_pos[r]
+// with the (cos, sin) table of cmlb200_rope_table for the same row_pos, appends K and V to the cache, attends keys 0..row_limit (row_limit[r] >= row_pos[r]
 // is not required, but the new key is only used when row_pos[r] <= row_limit[r]) and writes
 // [rows][heads*head_dim] fp32. d_scratch: cmlb200_attention_decode_scratch_bytes bytes whose
 // first 16 KB (the counters) are zero before the first call; the kernel leaves them zero.
 extern "C" int cmlb200_attention_decode(const float* d_qkv, int row_stride, void* d_kcache, void* d_vcache, const int* d_row_seq,
                                         const int* d_row_pos, const int* d_row_limit, int rows, int heads, int kv_heads,
-                                        int head_dim, int max_seq, int max_limit, int kv_is_f32, float rope_base, float* d_out,
+                                        int head_dim, int max_seq, int max_limit, int kv_is_f32, const float* d_rope_cs, float* d_out,
                                         void* d_scratch, int splits, void* stream) {
-    CMLB_REQUIRE(d_qkv && d_kcache && d_vcache && d_row_seq && d_row_pos && d_row_limit && d_out && d_scratch, "cmlb200_attention_decode: NULL argument");
+    CMLB_REQUIRE(d_qkv && d_kcache && d_vcache && d_row_seq && d_row_pos && d_row_limit && d_rope_cs && d_out && d_scratch, "cmlb200_attention_decode: NULL argument");
     CMLB_REQUIRE(rows > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "cmlb200_attention_decode: num_heads (%d) must be divisible by num_kv_heads (%d)", heads, kv_heads);
     CMLB_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 32, "cmlb200_attention_decode: head_dim %d not in {32, 64, 128}", head_dim);
     CMLB_REQUIRE(row_stride >= (heads + 2 * kv_heads) * head_dim, "cmlb200_attention_decode: row_stride %d smaller than a q|k|v row", row_stride);
-    CMLB_REQUIRE(splits >= 1 && max_limit >= 0 && max_limit < max_seq, "cmlb200_attention_decode: bad splits/max_limit");
-    if (rope_base <= 0.f) rope_base = 10000.0f;
+    CMLB_REQUIRE(splits >= 1 && splits <= ATTD_MAX_SPLITS && max_limit >= 0 && max_limit < max_seq, "cmlb200_attention_decode: bad splits/max_limit (splits <= 256)");
     const int chunk = (max_limit + 1 + splits - 1) / splits;
     CMLB_REQUIRE((size_t)rows * heads * sizeof(unsigned int) <= kAttCounterBytes, "cmlb200_attention_decode: rows*heads = %d exceeds 4096", rows * heads);
     unsigned int* counters = static_cast<unsigned int*>(d_scratch);
@@ -656,10 +700,10 @@ extern "C" int cmlb200_attention_decode(const float* d_qkv, int row_stride, void
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t c1 = {};
-    c1.gridDim = dim3(heads, rows, splits); c1.blockDim = dim3(ATT_THREADS); c1.stream = as_stream(stream); c1.attrs = pdl; c1.numAttrs = 1;
+    c1.gridDim = dim3(heads, rows, splits); c1.blockDim = dim3(ATTD_THREADS); c1.stream = as_stream(stream); c1.attrs = pdl; c1.numAttrs = 1;
 #define ATT_LAUNCH(KV, HD)                                                                                                    \
     CMLB_CUDA(cudaLaunchKernelEx(&c1, attention_decode_kernel<KV, HD>, d_qkv, row_stride, (KV*)d_kcache, (KV*)d_vcache, d_row_seq, \
-                                 d_row_pos, d_row_limit, heads, kv_heads, max_seq, chunk, rope_base, partial, counters, d_out))
+                                 d_row_pos, d_row_limit, heads, kv_heads, max_seq, chunk, reinterpret_cast<const float2*>(d_rope_cs), partial, counters, d_out))
     if (kv_is_f32) {
         if (head_dim == 128) { ATT_LAUNCH(float, 128); } else if (head_dim == 64) { ATT_LAUNCH(float, 64); } else { ATT_LAUNCH(float, 32); }
     } else {

@@ -23,6 +23,7 @@
 
 #define DEV(call) do { if (CML_DEV_FAIL((call), __func__)) return -1; } while (0)
 #define SKINNY_ROWS 32
+#define ATT_DECODE_CHUNK 32
 #define ATT_CHUNK 64
 
 typedef struct DevLayer {
@@ -51,7 +52,7 @@ typedef struct DevModel {
     size_t kv_layer_elems;
     void* stream;
     int qkv_w;                             /* qw_l + 2 * kvw_l */
-    float *h, *nrm, *qkv, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch;
+    float *h, *nrm, *qkv, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch, *rope_cs;
     uint16_t *b_a, *b_b, *b_c, *b_d;       /* bf16 staging of the prefill path */
     int *d_tokens, *d_cur, *row_seq, *row_pos, *row_limit, *d_hist;
     int* h_cur;
@@ -133,7 +134,7 @@ static void dm_destroy(DevModel* d) {
     }
     qmat_free(&d->lm_head);
     void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->qkv, d->att, d->ffn, d->g, d->u, d->tmp,
-                    d->logits, d->att_scratch, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
+                    d->logits, d->att_scratch, d->rope_cs, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
                     d->row_pos, d->row_limit, d->d_hist};
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
@@ -284,10 +285,11 @@ static int dm_alloc_buffers(DevModel* d) {
     DEV(cmlb200_malloc((void**)&d->b_d, R * wide * 2));
     d->att_splits_cap = (c->max_seq_len + ATT_CHUNK - 1) / ATT_CHUNK;
     {   /* the larger of: split partials for a skinny call (+ the decode kernel's counters), one split for a prefill call */
-        const size_t bytes = cmlb200_attention_decode_scratch_bytes(SKINNY_ROWS, d->heads_l, d->hd, d->att_splits_cap) +
+        const size_t bytes = cmlb200_attention_decode_scratch_bytes(SKINNY_ROWS, d->heads_l, d->hd, 2 * d->att_splits_cap) +
                              cmlb200_attention_scratch_floats(d->max_rows, d->heads_l, d->hd, 1) * 4;
         DEV(cmlb200_malloc((void**)&d->att_scratch, bytes));
         DEV(cmlb200_memset(d->att_scratch, 0, bytes, NULL));
+        DEV(cmlb200_malloc((void**)&d->rope_cs, (size_t)SKINNY_ROWS * d->hd * sizeof(float)));
     }
     DEV(cmlb200_malloc((void**)&d->d_tokens, R * 4));
     DEV(cmlb200_malloc((void**)&d->d_cur, (size_t)d->max_batch * 4));
@@ -615,8 +617,15 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     /* With tensor parallelism head 0 lives on rank 0 only, so C-ML's "head 0 only" rotation
      * touches nothing on the other ranks. */
     const int rotate = quirks ? (d->rank == 0 ? 1 : 0) : -1;
-    /* one new token per sequence, position-correct behaviour: RoPE, cache append, attention and merge in one launch */
+    /* one new token per sequence, position-correct behaviour: RoPE, cache append, attention and merge in one launch,
+     * one CTA of four warps per 32 keys */
     const int fused_att = !quirks && rows <= SKINNY_ROWS && (mode == 1 || rows == 1) && rows * d->heads_l <= 4096;
+    if (fused_att) {
+        splits = (max_limit + ATT_DECODE_CHUNK) / ATT_DECODE_CHUNK;
+        if (splits > 2 * d->att_splits_cap) splits = 2 * d->att_splits_cap;
+        if (splits > 256) splits = 256;
+    }
+    if (fused_att) DEV(cmlb200_rope_table(d->row_pos, rows, d->hd, c->rope_theta, d->rope_cs, st));
     const size_t esz = kvf32 ? 4 : 2;
     for (int li = 0; li < m->num_layers; li++) {
         const DevLayer* L = &d->L[li];
@@ -635,7 +644,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
         }
         if (fused_att) {
             DEV(cmlb200_attention_decode(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_pos, d->row_limit, rows, d->heads_l, d->kvh_l,
-                                         d->hd, c->max_seq_len, max_limit, kvf32, c->rope_theta, d->att, d->att_scratch, splits, st));
+                                         d->hd, c->max_seq_len, max_limit, kvf32, d->rope_cs, d->att, d->att_scratch, splits, st));
         } else {
             DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
                                         rotate, kc, vc, c->max_seq_len, kvf32, st));

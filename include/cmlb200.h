@@ -219,15 +219,18 @@ int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* d_row_seq, 
 /* The decode step's attention in one launch, for rows that are one new token per sequence
  * (cml_rope_forward src/nn/llm_ops.c:702-805 on Q and K, cml_kv_cache_append :118-157,
  * cml_gqa_forward :243-372): d_qkv holds [rows][q|k|v] as the fused projection left it, nothing
- * rotated. Every head of Q and K is rotated at row_pos, K and V of the new token go into the cache,
+ * rotated. Every head of Q and K is rotated at row_pos (table from cmlb200_rope_table), K and V of the new token go into the cache,
  * keys 0..row_limit are attended (split over `splits` CTAs per head, merged by the last to finish)
  * and [rows][heads*head_dim] fp32 is written. d_scratch: cmlb200_attention_decode_scratch_bytes
  * bytes, its first 16 KB zero before the first call (the kernel leaves them zero). */
 size_t cmlb200_attention_decode_scratch_bytes(int rows, int heads, int head_dim, int splits);
 int cmlb200_attention_decode(const float* d_qkv, int row_stride, void* d_kcache, void* d_vcache, const int* d_row_seq,
                              const int* d_row_pos, const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim,
-                             int max_seq, int max_limit, int kv_is_f32, float rope_base, float* d_out, void* d_scratch, int splits,
-                             void* stream);
+                             int max_seq, int max_limit, int kv_is_f32, const float* d_rope_cs, float* d_out, void* d_scratch,
+                             int splits, void* stream);
+/* d_cs[rows][head_dim/2][2] = (cos, sin)(row_pos * base^(-2i/head_dim)): the rotation table
+ * cmlb200_attention_decode reads; one launch per decode step serves every layer. */
+int cmlb200_rope_table(const int* d_row_pos, int rows, int head_dim, float base, float* d_cs, void* stream);
 /* Greedy branch of cml_llama_sample_token (src/nn/llama.c:650-660): first index of the maximum. */
 int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream);
 /* Row bookkeeping kept on the device so that a decode step replays as a CUDA graph.

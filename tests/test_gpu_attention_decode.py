@@ -57,10 +57,12 @@ def test_attention_decode_matches_unfused_path_and_formulas(pkg, torch_dev, kv_f
     d_qkv, d_kc, d_vc = to_dev(qkv, torch_dev), to_dev(kc, torch_dev), to_dev(vc, torch_dev)
     d_out = torch.zeros((rows, qw), dtype=torch.float32, device=torch_dev)
     scratch = torch.zeros(pkg.lib.cmlb200_attention_decode_scratch_bytes(rows, heads, hd, splits), dtype=torch.uint8, device=torch_dev)
+    d_cs = torch.zeros((rows, hd // 2, 2), dtype=torch.float32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_rope_table(d_pos.data_ptr(), rows, hd, base, d_cs.data_ptr(), stream_ptr()), "rope_table")
     for _ in range(2):                                         # twice: the arrival counters must come back to zero
         pkg.check(pkg.lib.cmlb200_attention_decode(d_qkv.data_ptr(), stride, d_kc.data_ptr(), d_vc.data_ptr(), d_seq.data_ptr(),
                                                    d_pos.data_ptr(), d_pos.data_ptr(), rows, heads, kvh, hd, max_seq, max_limit, kv_f32,
-                                                   base, d_out.data_ptr(), scratch.data_ptr(), splits, stream_ptr()), "attention_decode")
+                                                   d_cs.data_ptr(), d_out.data_ptr(), scratch.data_ptr(), splits, stream_ptr()), "attention_decode")
     torch.cuda.synchronize()
     got = d_out.cpu().numpy()
     assert np.abs(got - want).max() / np.abs(want).max() <= 2e-3
