@@ -15,6 +15,11 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
 size_t cmlb200_xq_bytes_(int M, int K);
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 
+// gemv_mma.cu: the tensor-core decode kernel (mma.sync int8) for up to 4 rows of x per launch
+bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M);
+int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
+                      const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
+
 // gemv_tc.cu: tcgen05 integer tensor-core path over the tile-major copy of the weight
 int cmlb200_gemv_tc_(const cmlb200_qmat* W, const float* x, float* y, int M, int accumulate, cudaStream_t st);
 
@@ -22,6 +27,7 @@ namespace {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 constexpr int kDp4aMaxM = 2;     // up to here the CUDA-core integer-dot path is the faster one
+constexpr int kMmaMaxM = 8;      // up to here the mma.sync kernel (4 rows of x per launch) beats the tcgen05 one
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
@@ -249,6 +255,8 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
+    if (W->type != CMLB200_NF4 && M <= kMmaMaxM && cmlb200_gemv_mma_ok_(W, EPI, M))
+        return cmlb200_gemv_mma_(W, W2, x, nullptr, 0.f, nullptr, y, M, EPI, st);
     if (W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 &&
         ((uintptr_t)y & 15) == 0)
         return cmlb200_gemv_tc_(W, x, y, M, EPI == EPI_ACCUM, st);

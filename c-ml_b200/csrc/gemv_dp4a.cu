@@ -855,7 +855,7 @@ extern "C" int cmlb200_gemv_rmsnorm(const cmlb200_qmat* W, const cmlb200_qmat* W
     CMLB_REQUIRE(W && W->qs && W->scales && d_x && d_norm_w_f16 && d_y, "cmlb200_gemv_rmsnorm: NULL argument");
     CMLB_REQUIRE(W->type == CMLB200_Q4_0 || W->type == CMLB200_Q8_0, "cmlb200_gemv_rmsnorm: weight type %d is not Q4_0 or Q8_0", W->type);
     CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "cmlb200_gemv_rmsnorm: bad weight shape %dx%d", W->rows, W->cols);
-    CMLB_REQUIRE(M >= 1 && M <= 4 && epi >= 0 && epi <= 2, "cmlb200_gemv_rmsnorm: M=%d must be 1..4 and epi=%d one of 0, 1, 2", M, epi);
+    CMLB_REQUIRE(M >= 1 && M <= 8 && epi >= 0 && epi <= 2, "cmlb200_gemv_rmsnorm: M=%d must be 1..8 and epi=%d one of 0, 1, 2", M, epi);
     CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_norm_w_f16 & 7) == 0, "cmlb200_gemv_rmsnorm: x must be 16-byte, norm_w 8-byte aligned");
     if (epi == EPI_SWIGLU)
         CMLB_REQUIRE(W2 && W2->qs && W2->scales && W2->type == W->type && W2->rows == W->rows && W2->cols == W->cols,

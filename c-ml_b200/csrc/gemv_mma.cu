@@ -130,6 +130,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 int xmode, int epi, TpPeers tpa) {
     using C = Cfg<TYPE, NW>;
     constexpr int QB = C::QB, NC = 4 * MT, FB = flush_batch(NW, MT);
+    constexpr int NM = (MT + 1) / 2;          // MMAs per block: two rows of x (8 digit columns) each
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[SW][MT];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -312,37 +313,47 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     __syncwarp();
     TRACE(2);
 
-    // B fragment of block b for this thread: column g (n index), words t and 4+t of the plane
-    auto load_b = [&](int b, uint32_t& b0, uint32_t& b1) {
-        if (g < NC) {
-            const uint2 v = *reinterpret_cast<const uint2*>(table + ((size_t)b * NC + g) * 8 + t * 2);
+    // B fragment of block b for MMA j and this thread: column 8j+g (n index), words t and 4+t of the plane
+    auto load_b = [&](int b, int j, uint32_t& b0, uint32_t& b1) {
+        if (8 * j + g < NC) {
+            const uint2 v = *reinterpret_cast<const uint2*>(table + ((size_t)b * NC + 8 * j + g) * 8 + t * 2);
             b0 = v.x; b1 = v.y;
         } else { b0 = 0u; b1 = 0u; }
     };
-    const int xm = (MT == 2) ? (t >> 1) : 0;                 // row of x this thread's accumulator columns belong to
+    // row of x the accumulator columns of this thread belong to in MMA j: 2j + (t >> 1)
+    const int xm0 = (MT >= 2) ? (t >> 1) : 0;
 
-    uint32_t breg[BREG ? KU : 1][2];
-    float xs_reg = 0.f;
+    uint32_t breg[BREG ? KU : 1][NM][2];
+    float xs_reg[NM];
+#pragma unroll
+    for (int j = 0; j < NM; j++) xs_reg[j] = 0.f;
     if (BREG && my_nun > 0) {
 #pragma unroll
-        for (int i = 0; i < (BREG ? KU : 1); i++) load_b(un0 * KU + i, breg[i][0], breg[i][1]);
-        xs_reg = xs_all[xm * nun + un0];
+        for (int i = 0; i < (BREG ? KU : 1); i++)
+#pragma unroll
+            for (int j = 0; j < NM; j++) load_b(un0 * KU + i, j, breg[i][j][0], breg[i][j][1]);
+#pragma unroll
+        for (int j = 0; j < NM; j++) xs_reg[j] = xs_all[min(2 * j + xm0, MT - 1) * nun + un0];
     }
 
     const uint32_t ld_off = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * C::ROW_STRIDE + (lane >> 4) * 16);
     const uint32_t nib_mask = 0xF0F0F0F0u, nib_flip = 0x80808080u;
-    // One unit: 8 MMAs per weight; returns the unit's sums for rows g and g+8 before the scale of x.
-    auto unit_mmas = [&](uint32_t mb, int blk0, float& au0, float& au1) {
+    // One unit: 8 blocks x NM MMAs per weight; au[j][0/1] = the unit's sums of MMA j for rows g and g+8
+    // before the scale of x.
+    auto unit_mmas = [&](uint32_t mb, int blk0, float (&au)[NM][2]) {
         const uint4 sv = lds128(mb + C::QS_BYTES + g * 16), sw = lds128(mb + C::QS_BYTES + (g + 8) * 16);
         const uint32_t sgw[4] = {sv.x, sv.y, sv.z, sv.w}, sg8w[4] = {sw.x, sw.y, sw.z, sw.w};
         auto one_block = [&](int i, float d_lo, float d_hi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
-            uint32_t b0, b1;
-            if (BREG) { b0 = breg[BREG ? i : 0][0]; b1 = breg[BREG ? i : 0][1]; }
-            else load_b(blk0 + i, b0, b1);
-            int c0, c1, c2, c3;
-            mma_s8(a0, a1, a2, a3, b0, b1, c0, c1, c2, c3);
-            au0 = fmaf((float)((c0 << 8) + c1), d_lo, au0);
-            au1 = fmaf((float)((c2 << 8) + c3), d_hi, au1);
+#pragma unroll
+            for (int j = 0; j < NM; j++) {
+                uint32_t b0, b1;
+                if (BREG) { b0 = breg[BREG ? i : 0][j][0]; b1 = breg[BREG ? i : 0][j][1]; }
+                else load_b(blk0 + i, j, b0, b1);
+                int c0, c1, c2, c3;
+                mma_s8(a0, a1, a2, a3, b0, b1, c0, c1, c2, c3);
+                au[j][0] = fmaf((float)((c0 << 8) + c1), d_lo, au[j][0]);
+                au[j][1] = fmaf((float)((c2 << 8) + c3), d_hi, au[j][1]);
+            }
         };
 #pragma unroll
         for (int p = 0; p < KU / 2; p++) {
@@ -367,8 +378,8 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     // Results of FB items are parked in shared memory and the CTA meets once per FB items: the
     // threads of the first warps then add the 16 K-slices of every row in warp order and write y.
     const float wgt = ((t & 1) ? (1.0f / 256.0f) : 256.0f) * ((TYPE == CMLB200_Q4_0) ? 0.0625f : 1.0f);
-    float* my_part = partial + (size_t)warp * (NW * MT * 16) + (t >> 1) * 16 + g;     // + slot * SW*NW*MT*16 + a * MT*16
-    const bool part_writer = (t & 1) == 0 && (t >> 1) < MT;
+    float* my_part = partial + (size_t)warp * (NW * MT * 16) + xm0 * 16 + g;     // + slot * SW*NW*MT*16 + a * MT*16 + 2j * 16
+    const bool even_t = (t & 1) == 0;
     auto flush = [&](int it_first, int count) {              // items it_first .. it_first+count-1 sit in slots 0..count-1
         __syncthreads();
         for (int idx = threadIdx.x; idx < count * MT * 16; idx += SW * 32) {
@@ -397,23 +408,32 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 
     int u = 0;
     for (int it = 0; it < my_items; it++) {
-        float acc[NW][2];            // rows g and g+8: sum over blocks of scales * (c_even * 256 + c_odd)
+        float acc[NW][NM][2];        // rows g and g+8 of MMA j: sum over blocks of scales * (c_even * 256 + c_odd)
 #pragma unroll
-        for (int a = 0; a < NW; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
+        for (int a = 0; a < NW; a++)
+#pragma unroll
+            for (int j = 0; j < NM; j++) { acc[a][j][0] = 0.f; acc[a][j][1] = 0.f; }
 
         for (int o = 0; o < (BREG ? min(my_nun, 1) : my_nun); o++, u++) {
             const int buf = u % NBUF;
             cp_async_wait<NBUF - 1>();
             __syncwarp();
             const uint32_t ub = ring0 + buf * C::UNIT_BYTES;
-            const float xs = BREG ? xs_reg : xs_all[xm * nun + un0 + o];
+            float xs[NM];
+#pragma unroll
+            for (int j = 0; j < NM; j++) xs[j] = BREG ? xs_reg[j] : xs_all[min(2 * j + xm0, MT - 1) * nun + un0 + o];
             if (!DBG_SKIP(3)) {
 #pragma unroll
                 for (int a = 0; a < NW; a++) {
-                    float au0 = 0.f, au1 = 0.f;
-                    unit_mmas(ub + a * C::MAT_BYTES, (un0 + o) * KU, au0, au1);
-                    acc[a][0] = fmaf(au0, xs, acc[a][0]);
-                    acc[a][1] = fmaf(au1, xs, acc[a][1]);
+                    float au[NM][2];
+#pragma unroll
+                    for (int j = 0; j < NM; j++) { au[j][0] = 0.f; au[j][1] = 0.f; }
+                    unit_mmas(ub + a * C::MAT_BYTES, (un0 + o) * KU, au);
+#pragma unroll
+                    for (int j = 0; j < NM; j++) {
+                        acc[a][j][0] = fmaf(au[j][0], xs[j], acc[a][j][0]);
+                        acc[a][j][1] = fmaf(au[j][1], xs[j], acc[a][j][1]);
+                    }
                 }
             }
             __syncwarp();                                    // every lane is done with this buffer
@@ -424,16 +444,18 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         if (DBG_SKIP(2)) continue;
         const int slot = it % FB;
 #pragma unroll
-        for (int a = 0; a < NW; a++) {
-            float p_lo = acc[a][0] * wgt, p_hi = acc[a][1] * wgt;
-            p_lo += __shfl_xor_sync(0xffffffffu, p_lo, 1);
-            p_hi += __shfl_xor_sync(0xffffffffu, p_hi, 1);
-            if (part_writer) {
-                float* dst = my_part + (size_t)slot * (SW * NW * MT * 16) + a * (MT * 16);
-                dst[0] = p_lo;
-                dst[8] = p_hi;
+        for (int a = 0; a < NW; a++)
+#pragma unroll
+            for (int j = 0; j < NM; j++) {
+                float p_lo = acc[a][j][0] * wgt, p_hi = acc[a][j][1] * wgt;
+                p_lo += __shfl_xor_sync(0xffffffffu, p_lo, 1);
+                p_hi += __shfl_xor_sync(0xffffffffu, p_hi, 1);
+                if (even_t && 2 * j + xm0 < MT) {
+                    float* dst = my_part + (size_t)slot * (SW * NW * MT * 16) + a * (MT * 16) + 2 * j * 16;
+                    dst[0] = p_lo;
+                    dst[8] = p_hi;
+                }
             }
-        }
         if (slot == FB - 1 || it == my_items - 1) flush(it - slot, slot + 1);
     }
     cp_async_wait<0>();
@@ -552,7 +574,8 @@ int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const
     return launch_b<TYPE, MT, NW, QUIRK, false>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
 }
 
-// Rows of x two at a time (one launch streams the weight once for both), then one.
+// Rows of x four at a time when the digit table fits (one launch streams the weight once for
+// all of them), then two, then one.
 template <int TYPE, int NW, bool QUIRK>
 int run_m(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, size_t x_row_bytes, const __half* nw, float eps, float* y, int M,
           int xmode, int epi, const TpPeers& tp0, cudaStream_t st) {
@@ -562,6 +585,9 @@ int run_m(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, size_t
         float* ym = y + (size_t)m0 * W->rows;
         TpPeers tpa = tp0;
         if (tpa.tp) tpa.h = tp0.h + (size_t)m0 * W->rows;
+        if (M - m0 >= 3 && fits_smem<TYPE, NW>(4, W->cols / 32)) {
+            if (M - m0 >= 4) { rc = launch<TYPE, 4, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 4; continue; }
+        }
         if (M - m0 >= 2) { rc = launch<TYPE, 2, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 2; }
         else { rc = launch<TYPE, 1, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 1; }
     }

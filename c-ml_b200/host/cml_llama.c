@@ -602,7 +602,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
     const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32);
-    const int tiny = rows <= 2;                 /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
+    const int tiny = rows <= 8;                 /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
     void* st = d->stream;
     DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
     DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));

@@ -128,7 +128,7 @@ int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int 
  *   cmlb200_rmsnorm_digits  rms_norm (src/nn/llama.c:71-124) writing fp32 (optional) and digits
  *   cmlb200_gemv_xq         y (= | += | swiglu) from digits; M <= 4; epi 0 store, 1 accumulate,
  *                           2 SwiGLU with W2 as the up projection
- *   cmlb200_gemv_rmsnorm    the same from fp32 x that is RMS-normalised (src/nn/llama.c:71-124)
+ *   cmlb200_gemv_rmsnorm    (M <= 8) the same from fp32 x that is RMS-normalised (src/nn/llama.c:71-124)
  *                           inside the GEMV launch: rms_norm followed by a projection
  *                           (src/nn/llama.c:461-470, 535-537, 580-583) in one kernel */
 size_t cmlb200_xq_bytes(int M, int K);
