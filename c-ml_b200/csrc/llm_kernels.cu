@@ -28,6 +28,8 @@ __device__ __forceinline__ float warp_max(float v) {
 // ---- embedding gather: fp16 table -> fp32 rows; out-of-range ids read row 0 (llama.c:440-444)
 __global__ void embed_kernel(const __half* __restrict__ table, const int* __restrict__ tokens, int hidden, int vocab,
                              float* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int r = blockIdx.x;
     int t = tokens[r];
     if (t < 0 || t >= vocab) t = 0;
@@ -99,6 +101,18 @@ __global__ void kv_append_kernel(const float* __restrict__ k, const float* __res
 // (max, sum, acc[hd]); attention_merge_kernel combines the splits. Keys beyond row_limit are the
 // causally masked ones: C-ML gives them -1e9 before the softmax, i.e. weight exp(-1e9 - max) = 0
 // in fp32, so skipping them yields the same result.
+// Launch with programmatic stream serialization: the kernel may become resident while its
+// predecessor drains; every kernel launched this way starts with griddepcontrol.wait.
+template <typename Kern, typename... Args>
+static cudaError_t launch_dep(Kern kern, dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 constexpr int ATT_THREADS = 128;
 template <typename KV, int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
@@ -442,6 +456,8 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
 
 // ---- greedy pick: first index holding the strict maximum of each row
 __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -479,6 +495,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
 // relative_mask != 0 reproduces C-ML's causal mask on call-relative indices (llm_ops.c:290-298).
 __global__ void prepare_rows_kernel(const int* __restrict__ cur_len, int rows, int mode, int relative_mask, int seq,
                                     int* row_seq, int* row_pos, int* row_limit) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     if (mode == 0) {
@@ -492,6 +510,8 @@ __global__ void prepare_rows_kernel(const int* __restrict__ cur_len, int rows, i
     }
 }
 __global__ void advance_rows_kernel(int* cur_len, int rows, int mode, int seq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (mode == 0) { if (r == 0) cur_len[seq] += rows; }
     else if (r < rows) cur_len[r] += 1;
@@ -567,7 +587,7 @@ inline int ew_grid(size_t n) {
 extern "C" int cmlb200_embed_f16(const uint16_t* d_table_f16, const int* d_tokens, int rows, int hidden, int vocab,
                                  float* d_out, void* stream) {
     CMLB_REQUIRE(d_table_f16 && d_tokens && d_out && rows > 0 && hidden > 0 && vocab > 0, "cmlb200_embed_f16: bad argument");
-    embed_kernel<<<rows, 256, 0, as_stream(stream)>>>((const __half*)d_table_f16, d_tokens, hidden, vocab, d_out);
+    CMLB_CUDA(launch_dep(embed_kernel, dim3(rows), dim3(256), as_stream(stream), (const __half*)d_table_f16, d_tokens, hidden, vocab, d_out));
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
@@ -742,7 +762,7 @@ extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* 
 
 extern "C" int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream) {
     CMLB_REQUIRE(d_logits && d_out && rows > 0 && vocab > 0, "cmlb200_argmax: bad argument");
-    argmax_kernel<<<rows, 1024, 0, as_stream(stream)>>>(d_logits, vocab, d_out);
+    CMLB_CUDA(launch_dep(argmax_kernel, dim3(rows), dim3(1024), as_stream(stream), d_logits, vocab, d_out));
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
@@ -750,14 +770,14 @@ extern "C" int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d
 extern "C" int cmlb200_prepare_rows(const int* d_cur_len, int rows, int mode, int relative_mask, int seq, int* d_row_seq,
                                     int* d_row_pos, int* d_row_limit, void* stream) {
     CMLB_REQUIRE(d_cur_len && d_row_seq && d_row_pos && d_row_limit && rows > 0 && seq >= 0, "cmlb200_prepare_rows: bad argument");
-    prepare_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode, relative_mask, seq, d_row_seq, d_row_pos, d_row_limit);
+    CMLB_CUDA(launch_dep(prepare_rows_kernel, dim3((rows + 127) / 128), dim3(128), as_stream(stream), d_cur_len, rows, mode, relative_mask, seq, d_row_seq, d_row_pos, d_row_limit));
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
 
 extern "C" int cmlb200_advance_rows(int* d_cur_len, int rows, int mode, int seq, void* stream) {
     CMLB_REQUIRE(d_cur_len && rows > 0 && seq >= 0, "cmlb200_advance_rows: bad argument");
-    advance_rows_kernel<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_cur_len, rows, mode, seq);
+    CMLB_CUDA(launch_dep(advance_rows_kernel, dim3((rows + 127) / 128), dim3(128), as_stream(stream), d_cur_len, rows, mode, seq));
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }

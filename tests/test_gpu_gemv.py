@@ -168,3 +168,25 @@ def test_gemv_digit_entry_points_and_fused_rmsnorm(pkg, synth, ob, orc, torch_de
     st = C.c_int(-1)
     pkg.check(pkg.lib.cmlb200_gemv_status(C.byref(st), 0), "gemv_status")
     assert st.value == 0
+
+
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("N,K", [(5, 256), (16, 512), (33, 4096), (301, 2816)])
+def test_gemv_tensor_core_kernel_edges(pkg, synth, ob, orc, torch_dev, kind, N, K):
+    """Shapes around the tensor-core decode kernel's tiling: fewer rows than one 16-row item, a single
+    8-block unit (most warps idle), K that leaves the last warps without a unit, every M up to 8
+    (4 + 2 + 1 rows per launch), all three epilogues."""
+    rng = np.random.default_rng(12)
+    Wg, Wgf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    Wu, Wuf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    for M in (1, 2, 3, 4, 5, 7, 8):
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        x[0, :32] = 0.0                                   # an all-zero block
+        x[M - 1, 40] = 1e4                                # one huge element in a slice
+        g, u = ob.linear_nt(orc, x, Wgf), ob.linear_nt(orc, x, Wuf)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv, Wg, x, N, torch_dev), g) <= TOL
+        y0 = rng.standard_normal((M, N)).astype(np.float32)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv_accum, Wg, x, N, torch_dev, y0=y0), y0 + g) <= TOL
+        with np.errstate(over="ignore"):                  # exp(-g) may overflow to inf for the huge element: silu -> 0
+            want = (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv_swiglu, Wg, x, N, torch_dev, W2=Wu), want) <= TOL
