@@ -113,8 +113,9 @@ __device__ __forceinline__ void xq_emit_oct(const float (&e)[4], int sub, unsign
 // Workspace of the tensor-parallel all-reduce over peer memory (one per rank, mapped into every
 // other rank through CUDA IPC). Two independent channels: 0 = the stand-alone kernel
 // (tp_allreduce.cu, kTpCtas slices), 1 = the epilogue of the decode GEMV (gemv_mma.cu, one slice
-// per CTA of its grid). Per channel: a sequence counter per slice, a flag word per (peer, slice)
-// and two alternating inboxes with room for max_floats values from each of 8 ranks.
+// per CTA of its grid). Per channel: a sequence counter per slice, a flag word per (peer, slice;
+// channel 0 only) and two alternating inboxes with room for max_floats values from each of 8
+// ranks (channel 1 stores 8-byte (value, sequence) packets there, so it holds max_floats / 2).
 //   +0      u32 seq0[16]      +64    u32 status
 //   +1024   u32 flags0[8][16]
 //   +2048   u32 seq1[192]     +4096  u32 flags1[8][192]
@@ -146,6 +147,17 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 constexpr int kTpSpinLimit = 1 << 22;
+// (value, sequence number) packets: one 8-byte store carries a result and the proof that it
+// belongs to this all-reduce, so the receiver polls the data words themselves and no fence or
+// separate flag is needed between ranks.
+__device__ __forceinline__ void st_packet_sys(uint2* p, float v, uint32_t seq) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_packet_sys(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 static inline int cmlb_num_sms() {
     static int sms = 0;

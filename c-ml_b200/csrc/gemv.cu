@@ -16,7 +16,7 @@ size_t cmlb200_xq_bytes_(int M, int K);
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 
 // gemv_mma.cu: the tensor-core decode kernel (mma.sync int8) for up to 4 rows of x per launch
-bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M);
+int cmlb200_gemv_mma_rows_(const cmlb200_qmat* W, int epi);
 int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                       const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
 
@@ -255,8 +255,13 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
-    if (W->type != CMLB200_NF4 && M <= kMmaMaxM && cmlb200_gemv_mma_ok_(W, EPI, M))
-        return cmlb200_gemv_mma_(W, W2, x, nullptr, 0.f, nullptr, y, M, EPI, st);
+    const bool tc_ok = W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 && ((uintptr_t)y & 15) == 0;
+    if (W->type != CMLB200_NF4 && M <= kMmaMaxM) {
+        // the mma.sync kernel streams the weight once per launch: take it while two launches cover M
+        // (or when there is no tile-major copy for the tcgen05 kernel)
+        const int per = cmlb200_gemv_mma_rows_(W, EPI);
+        if (per > 0 && ((M + per - 1) / per <= 2 || !tc_ok)) return cmlb200_gemv_mma_(W, W2, x, nullptr, 0.f, nullptr, y, M, EPI, st);
+    }
     if (W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 &&
         ((uintptr_t)y & 15) == 0)
         return cmlb200_gemv_tc_(W, x, y, M, EPI == EPI_ACCUM, st);

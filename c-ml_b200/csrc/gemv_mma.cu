@@ -398,7 +398,8 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 float* out = y + (size_t)m * N + row;
                 if (NW == 2) *out = (sum[0] / (1.0f + expf(-sum[0]))) * sum[NW - 1];
                 else if (TP) {                               // this rank's share goes to every rank's inbox, its own included
-                    for (int qr = 0; qr < tpa.tp; qr++) tpws_inbox(tpa.ws[qr], 1, tp_par, tpa.rank, tpa.max_floats)[(size_t)m * N + row] = sum[0];
+                    for (int qr = 0; qr < tpa.tp; qr++)
+                        st_packet_sys(reinterpret_cast<uint2*>(tpws_inbox(tpa.ws[qr], 1, tp_par, tpa.rank, tpa.max_floats)) + (size_t)m * N + row, sum[0], tp_seq);
                 } else if (epi == EPI_ACCUM) *out += sum[0];
                 else *out = sum[0];
             }
@@ -460,34 +461,29 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     }
     cp_async_wait<0>();
     if (TP) {
-        // All rows of this CTA are on their way to the peers. Tell every peer (flag word of this rank
-        // and CTA), wait for theirs, then add all ranks' shares in rank order onto the residual.
-        __shared__ int tp_ok;
+        // All rows of this CTA are on their way to every rank as (value, sequence) packets. Collect
+        // the packets of all ranks for the same rows (they carry this all-reduce's sequence number
+        // once they have landed) and add them in rank order onto the residual.
         uint8_t* mine = tpa.ws[tpa.rank];
-        if (threadIdx.x == 0) tp_ok = 1;
-        __threadfence_system();
-        __syncthreads();
-        if ((int)threadIdx.x < tpa.tp && (int)threadIdx.x != tpa.rank) {
-            st_release_sys(tpws_flags(tpa.ws[threadIdx.x], 1, tpa.rank) + blockIdx.x, tp_seq);
-            const uint32_t* f = tpws_flags(mine, 1, threadIdx.x) + blockIdx.x;
-            int i = 0;
-            while ((int32_t)(ld_acquire_sys(f) - tp_seq) < 0 && ++i < kTpSpinLimit) {}
-            if (i >= kTpSpinLimit) { tp_ok = 0; atomicExch(tpws_status(mine), 1u + threadIdx.x); }
+        for (int idx = threadIdx.x; idx < my_items * MT * 16; idx += SW * 32) {
+            const int r = idx & 15, m = (idx >> 4) % MT, it = idx / (16 * MT);
+            const int row = ((int)blockIdx.x + it * (int)gridDim.x) * 16 + r;
+            if (row < N) {
+                const size_t at = (size_t)m * N + row;
+                float v = 0.f;
+                bool ok = true;
+                for (int qr = 0; qr < tpa.tp && ok; qr++) {
+                    const uint2* src = reinterpret_cast<const uint2*>(tpws_inbox(mine, 1, tp_par, qr, tpa.max_floats)) + at;
+                    uint2 pkt = ld_packet_sys(src);
+                    for (int i = 0; pkt.y != tp_seq && i < kTpSpinLimit; i++) pkt = ld_packet_sys(src);
+                    if (pkt.y != tp_seq) { ok = false; atomicExch(tpws_status(mine), 1u + qr); }
+                    v += __uint_as_float(pkt.x);
+                }
+                if (ok) tpa.h[at] += v;
+            }
         }
         __syncthreads();
         if (threadIdx.x == 0) tpws_seq(mine, 1)[blockIdx.x] = tp_seq;
-        if (tp_ok) {
-            for (int idx = threadIdx.x; idx < my_items * MT * 16; idx += SW * 32) {
-                const int r = idx & 15, m = (idx >> 4) % MT, it = idx / (16 * MT);
-                const int row = ((int)blockIdx.x + it * (int)gridDim.x) * 16 + r;
-                if (row < N) {
-                    const size_t at = (size_t)m * N + row;
-                    float v = 0.f;
-                    for (int qr = 0; qr < tpa.tp; qr++) v += tpws_inbox(mine, 1, tp_par, qr, tpa.max_floats)[at];
-                    tpa.h[at] += v;
-                }
-            }
-        }
     }
     TRACE(3);
 }
@@ -585,10 +581,9 @@ int run_m(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, size_t
         float* ym = y + (size_t)m0 * W->rows;
         TpPeers tpa = tp0;
         if (tpa.tp) tpa.h = tp0.h + (size_t)m0 * W->rows;
-        if (M - m0 >= 3 && fits_smem<TYPE, NW>(4, W->cols / 32)) {
-            if (M - m0 >= 4) { rc = launch<TYPE, 4, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 4; continue; }
-        }
-        if (M - m0 >= 2) { rc = launch<TYPE, 2, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 2; }
+        const int nblk = W->cols / 32, left = M - m0;
+        if (left >= 4 && fits_smem<TYPE, NW>(4, nblk)) { rc = launch<TYPE, 4, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 4; }
+        else if (left >= 2 && fits_smem<TYPE, NW>(2, nblk)) { rc = launch<TYPE, 2, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 2; }
         else { rc = launch<TYPE, 1, NW, QUIRK>(W, W2, xm, nw, eps, ym, xmode, epi, tpa, st); m0 += 1; }
     }
     return rc;
@@ -618,8 +613,19 @@ bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M) {
     if (W->type != CMLB200_Q4_0 && W->type != CMLB200_Q8_0) return false;
     if (W->cols % 256 != 0 || ((uintptr_t)W->qs & 15) || ((uintptr_t)W->scales & 15)) return false;
     const int nblk = W->cols / 32;
-    const int mt = M >= 2 ? 2 : 1;             // rows of x go two per launch, then one
-    return W->type == CMLB200_Q8_0 ? fits<CMLB200_Q8_0>(nblk, epi, mt) : fits<CMLB200_Q4_0>(nblk, epi, mt);
+    (void)M;                                   // rows of x go four, two or one per launch, whatever fits
+    return W->type == CMLB200_Q8_0 ? fits<CMLB200_Q8_0>(nblk, epi, 1) : fits<CMLB200_Q4_0>(nblk, epi, 1);
+}
+
+// Rows of x one launch of the tensor-core decode kernel takes for this weight: 4, 2, 1, or 0 when
+// the shape is outside the kernel.
+int cmlb200_gemv_mma_rows_(const cmlb200_qmat* W, int epi) {
+    if (!cmlb200_gemv_mma_ok_(W, epi, 1)) return 0;
+    const int nblk = W->cols / 32;
+    const bool q8 = W->type == CMLB200_Q8_0;
+    for (int mt = 4; mt >= 2; mt >>= 1)
+        if (q8 ? fits<CMLB200_Q8_0>(nblk, epi, mt) : fits<CMLB200_Q4_0>(nblk, epi, mt)) return mt;
+    return 1;
 }
 
 // y[M, rows] (= | += | swiglu) for M <= 4. Exactly one of xq (digit records) and x (fp32, with
@@ -641,8 +647,8 @@ int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float
 // Row-parallel projection of a tensor-parallel layer with the all-reduce in its epilogue:
 // h[M, rows] += sum over ranks of x_rank . dequant(W_rank)^T (src/nn/llama.c:523-530, 538-543 with
 // src/distributed/tensor_parallel.c:195-260 in between). One launch per rank: every CTA sends
-// the rows it finishes to all ranks' inboxes, then exchanges one flag per peer and adds the
-// shares in rank order. All projections that use one workspace must have the same `rows`, since
+// the rows it finishes to all ranks' inboxes as (value, sequence) packets and, once its items
+// are done, adds the packets of all ranks for its rows in rank order. All projections that use one workspace must have the same `rows`, since
 // the flags are kept per CTA and the CTA-to-rows mapping depends on rows alone.
 extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x, float* d_h, int M, int tp, int rank, void* const* ws,
                                          size_t max_floats, void* stream) {
@@ -650,7 +656,7 @@ extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x
     CMLB_REQUIRE(M >= 1 && M <= 4, "cmlb200_gemv_tp_allreduce: M=%d outside 1..4", M);
     CMLB_REQUIRE(tp >= 2 && tp <= kTpMaxRanks && rank >= 0 && rank < tp, "cmlb200_gemv_tp_allreduce: tp=%d rank=%d (tp must be 2..8)", tp, rank);
     CMLB_REQUIRE(cmlb200_gemv_mma_ok_(W, EPI_STORE, M), "cmlb200_gemv_tp_allreduce: weight %dx%d type %d is outside the tensor-core decode kernel", W->rows, W->cols, W->type);
-    CMLB_REQUIRE((size_t)M * W->rows <= max_floats && (W->rows + 15) / 16 <= kTpGemvSlices * 64, "cmlb200_gemv_tp_allreduce: M*rows = %zu exceeds the workspace", (size_t)M * W->rows);
+    CMLB_REQUIRE((size_t)M * W->rows * 2 <= max_floats, "cmlb200_gemv_tp_allreduce: M*rows = %zu exceeds the workspace (max_floats / 2)", (size_t)M * W->rows);
     CMLB_REQUIRE(cmlb_num_sms() <= kTpGemvSlices, "cmlb200_gemv_tp_allreduce: more than %d SMs", kTpGemvSlices);
     CMLB_REQUIRE(((uintptr_t)d_x & 15) == 0, "cmlb200_gemv_tp_allreduce: x must be 16-byte aligned");
     TpPeers p = {};

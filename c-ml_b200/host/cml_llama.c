@@ -568,7 +568,7 @@ static int lin_f32(DevModel* d, const cmlb200_qmat* W, const float* x, float* y,
 /* Row-parallel projection + residual: h += all_reduce(x . W_shard^T) */
 static int proj_residual_f32(DevModel* d, const cmlb200_qmat* W, const float* x, int rows) {
     if (d->tp == 1) return lin_f32(d, W, x, d->h, rows, 1);
-    if (d->ar_ok && rows <= 4 && W->rows == d->key->config.hidden_size && (size_t)rows * W->rows <= d->ar_max_floats &&
+    if (d->ar_ok && rows <= 4 && W->rows == d->key->config.hidden_size && (size_t)rows * W->rows * 2 <= d->ar_max_floats &&
         cmlb200_gemv_tp_fused_ok(W, rows)) {       /* projection and all-reduce in one launch */
         DEV(cmlb200_gemv_tp_allreduce(W, x, d->h, rows, d->tp, d->rank, d->ar_ws, d->ar_max_floats, d->stream));
         return 0;
