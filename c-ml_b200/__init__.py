@@ -74,7 +74,6 @@ _sig("cmlb200_repack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_unrepack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_gemv_tiles", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemv_tiles_status", ci, C.POINTER(ci), ci)
-_sig("cmlb200_gemv_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_gemm_bf16", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemm_bf16_splitk", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemm_status", ci, C.POINTER(ci), ci)

@@ -7,7 +7,7 @@
 //     x_k  ~=  s_b * X_k,   X_k a signed 16-bit integer,  s_b = max|x_block| / 32639,
 // and X_k is split into two signed 8-bit digits X_k = d0*256 + d1 held as int8x4 words. The
 // block dot product  sum_k q_k * X_k  then is two exact integer dot products on dp4a (4
-// multiply-adds per lane-operation), recombined in int32 and scaled by d_b * s_b in fp32;
+// multiply-adds per lane-operation), recombined in fp32 and scaled by d_b * s_b;
 // blocks are accumulated in fp32. Q4_0 nibbles are turned into the signed bytes 16*(q-8) with
 // one shift and two 3-input logic operations per 8 weights, so the "-8" offset costs nothing
 // and the factor 16 is taken out once per output. The only approximation is the rounding of x
@@ -17,16 +17,10 @@
 // Replaces, like gemv.cu, C-ML's dequantize-then-fp32-matmul (src/core/gguf.c:271-295 +
 // src/ops/ir/execution.c:989-1052, 3090-3134).
 //
-// Two kernels:
-//   * gemv_stream_kernel (K % 256 == 0): one persistent CTA per SM. Every warp runs its own
-//     ring of NBUF shared-memory buffers filled by bulk copies (cp.async.bulk + mbarrier), one
-//     buffer = R weight rows x up to KC blocks with their scales, so each SM keeps
-//     WARPS*NBUF buffers in flight from launch to exit; the digits of x sit in shared memory
-//     and are either produced in the kernel from fp32 x or copied from a record array made by
-//     the kernel that produced the activations. Weight copies are issued before
-//     griddepcontrol.wait (programmatic dependent launch), x is touched only after it.
-//   * gemv_dp4a_kernel (any K % 32 == 0): register path, each warp loads its rows straight
-//     from global memory; digits come from a record array.
+// This file holds the register-path kernel, which takes any K % 32 == 0: each warp loads its rows
+// straight from global memory and digits come from a record array. The tensor-core kernel in
+// gemv_mma.cu takes the shapes it can (K % 256 == 0 and a digit table that fits shared memory) and
+// is tried first.
 #include "common.cuh"
 
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
@@ -267,338 +261,6 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A
     return CMLB200_OK;
 }
 
-// ---- streaming kernel ---------------------------------------------------------------------------
-constexpr int SPIN_LIMIT = 1 << 22;
-__device__ int g_stream_status = 0;          // 0 ok; else 1 + index of the buffer whose wait expired
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the phase did not complete within SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < SPIN_LIMIT; i++)
-        if (mbar_try(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-#ifdef CMLB200_TRACE
-// Diagnostic build only: per CTA and launch, global-timer stamps at kernel entry, after the
-// dependency wait, after the digits are in place and at exit.
-__device__ unsigned long long g_trace[16][160][4];
-__device__ unsigned int g_trace_cnt[160];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE_SLOT() unsigned tr_slot = 0; if (threadIdx.x == 0) { tr_slot = atomicAdd(&g_trace_cnt[blockIdx.x], 1u) % 16; }
-#define TRACE(k) if (threadIdx.x == 0) g_trace[tr_slot][blockIdx.x][k] = gtime();
-#else
-#define TRACE_SLOT()
-#define TRACE(k)
-#endif
-
-template <int TYPE, int NW, int R, bool DREG>
-struct StreamCfg {
-    static constexpr int QB = (TYPE == CMLB200_Q8_0) ? 32 : 16;      // quant bytes per block
-    static constexpr int KC = 128;                                   // blocks per buffer and row
-    static constexpr int QS_BYTES = NW * R * KC * QB;
-    static constexpr int BUF_BYTES = QS_BYTES + NW * R * KC * 2;     // + fp16 scales
-    // shared memory left for the rings once the digit records are placed
-    static constexpr int BUDGET = DREG ? 200 * 1024 : 150 * 1024;
-    static constexpr int SW0 = DREG ? 12 : 16;
-    static constexpr int SW = (BUDGET / (SW0 * BUF_BYTES) >= 2) ? SW0 : 8;       // warps per CTA
-    static constexpr int NBUF = (BUDGET / (SW * BUF_BYTES) >= 4) ? 4 : BUDGET / (SW * BUF_BYTES);
-    static_assert(NBUF >= 2, "ring too small");
-    static constexpr int BAR_BYTES = 128 * ((SW * NBUF * 8 + 127) / 128);
-    __host__ __device__ static size_t digit_bytes(int MT, int nblk) { return 128 * (((size_t)MT * nblk * XW * 4 + 127) / 128); }
-};
-
-// xin: digit records [MT][K/32][XW] (XMODE 0), fp32 activations [MT][K] (XMODE 1), or fp32
-// activations to be RMS-normalised with the fp16 weight nw first (XMODE 2; src/nn/llama.c:71-124:
-// x * (1 / sqrt(mean(x^2) + eps)) * w, every CTA normalising its own copy). y: [MT][N].
-// Work unit = (group of R consecutive rows, chunk of KC blocks); warp w of the grid owns groups
-// w, w + total_warps, ... and walks their chunks in order. Buffer i of a warp holds its unit i,
-// i + NBUF, ...; the warp refills a buffer as soon as all its lanes have finished reading it.
-// DREG (MT == 1 and K <= 32*KC): each lane keeps the digits of its own blocks in registers for
-// the whole kernel, so the inner loop reads only weights from shared memory.
-template <int TYPE, int MT, int R, int EPI, bool QUIRK, int XMODE, bool DREG>
-__global__ void __launch_bounds__(StreamCfg<TYPE, (EPI == EPI_SWIGLU) ? 2 : 1, R, DREG>::SW * 32, 1)
-gemv_stream_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
-                   const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
-                   const void* __restrict__ xin, const __half* __restrict__ nw, float eps, float* __restrict__ y, int N, int K) {
-    constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
-    using C = StreamCfg<TYPE, NW, R, DREG>;
-    constexpr int QB = C::QB, KC = C::KC, QV = QB / 16, SW = C::SW, NBUF = C::NBUF, NJ = KC / 32;
-    static_assert(!DREG || MT == 1, "register-resident digits are for one row of x");
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nblk = K / 32;
-    const int nch = (nblk + KC - 1) / KC;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                       // [SW][NBUF]
-    uint32_t* xd = reinterpret_cast<uint32_t*>(smem + C::BAR_BYTES);          // [MT][nblk][XW]
-    uint8_t* ring = smem + C::BAR_BYTES + C::digit_bytes(MT, nblk) + (size_t)warp * NBUF * C::BUF_BYTES;
-    const uint32_t bar0 = smem_u32(bars + warp * NBUF);
-    const uint32_t ring0 = smem_u32(ring);
-
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    TRACE_SLOT();
-    TRACE(0);
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < SW * NBUF; i++) mbar_init(smem_u32(bars + i), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    const int groups = (N + R - 1) / R;
-    const int total_warps = gridDim.x * SW;
-    const int gw = warp * gridDim.x + blockIdx.x;
-    const int my_groups = gw < groups ? (groups - gw + total_warps - 1) / total_warps : 0;
-    const int n_it = my_groups * nch;
-    const size_t row_bytes = (size_t)nblk * QB;
-
-    // fill buffer `buf` with unit `it`
-    auto issue = [&](int it, int buf) {
-        const int gi = it / nch, c = it - gi * nch;
-        const int row0 = (gw + gi * total_warps) * R;
-        const int nb = min(KC, nblk - c * KC);
-        const int nrows = min(R, N - row0);
-        const uint32_t bar = bar0 + 8 * buf, dst = ring0 + buf * C::BUF_BYTES;
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(NW * nrows * nb * (QB + 2)));
-        __syncwarp();
-        if (lane < 2 * NW * R) {
-            const int what = lane & 1, ar = lane >> 1, a = ar / R, r = ar - a * R;     // what: 0 quants, 1 scales
-            if (r < nrows) {
-                const int row = row0 + r;
-                if (what == 0)
-                    bulk_g2s(dst + ar * (KC * QB), (a ? qs2 : qs) + (size_t)row * row_bytes + (size_t)c * KC * QB, (uint32_t)(nb * QB), bar);
-                else
-                    bulk_g2s(dst + C::QS_BYTES + ar * (KC * 2), (a ? scales2 : scales) + (size_t)row * nblk + (size_t)c * KC, (uint32_t)(nb * 2), bar);
-            }
-        }
-    };
-
-    // Weights do not depend on the preceding kernel: fill the ring before the dependency wait.
-    for (int i = 0; i < NBUF && i < n_it; i++) issue(i, i);
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE(1);
-
-    if (XMODE != 0) {      // digits of x, 8 lanes per block
-        const float* x = static_cast<const float*>(xin);
-        float inv[MT];
-#pragma unroll
-        for (int m = 0; m < MT; m++) inv[m] = 1.f;
-        if (XMODE == 2) {
-            __shared__ float red[SW][MT];
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                float ss = 0.f;
-                for (int i = threadIdx.x * 4; i < K; i += SW * 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + i);
-                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                if (lane == 0) red[warp][m] = ss;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                float tot = 0.f;
-#pragma unroll
-                for (int w = 0; w < SW; w++) tot += red[w][m];
-                inv[m] = 1.0f / sqrtf(tot / (float)K + eps);
-            }
-        }
-        const int sub = threadIdx.x & 7;
-        const unsigned gmask = 0xffu << (threadIdx.x & 24);
-#pragma unroll
-        for (int m = 0; m < MT; m++)
-            for (int b = threadIdx.x >> 3; b < nblk; b += SW * 4) {
-                const int i = b * 32 + sub * 4;
-                const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + i);
-                float e[4] = {v.x, v.y, v.z, v.w};
-                if (XMODE == 2) {
-                    const uint2 wr = *reinterpret_cast<const uint2*>(nw + i);
-                    const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
-                    const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
-                    e[0] = e[0] * inv[m] * w01.x; e[1] = e[1] * inv[m] * w01.y;
-                    e[2] = e[2] * inv[m] * w23.x; e[3] = e[3] * inv[m] * w23.y;
-                }
-                xq_emit_oct(e, sub, gmask, xd + ((size_t)m * nblk + b) * XW);
-            }
-    } else {
-        const uint4* src = static_cast<const uint4*>(xin);
-        uint4* dst = reinterpret_cast<uint4*>(xd);
-        for (int i = threadIdx.x; i < MT * nblk * (XW / 4); i += SW * 32) dst[i] = src[i];
-    }
-    __syncthreads();
-    TRACE(2);
-
-    uint32_t dg[DREG ? NJ : 1][24];
-    float xsr[DREG ? NJ : 1];
-    if (DREG) {
-#pragma unroll
-        for (int j = 0; j < (DREG ? NJ : 1); j++) {
-            const int b = min(lane + 32 * j, nblk - 1);
-            load_digits(xd + (size_t)b * XW, dg[j]);
-            xsr[j] = __uint_as_float(xd[(size_t)b * XW + 24]);
-        }
-    }
-
-    float acc[NW][R][MT];
-#pragma unroll
-    for (int a = 0; a < NW; a++)
-#pragma unroll
-        for (int r = 0; r < R; r++)
-#pragma unroll
-            for (int m = 0; m < MT; m++) acc[a][r][m] = 0.f;
-
-    int it = 0;
-    bool ok = true;
-    for (; it < n_it; it++) {
-        const int buf = it % NBUF;
-        if (!mbar_wait(bar0 + 8 * buf, (uint32_t)(it / NBUF) & 1u)) { ok = false; break; }
-        const int gi = it / nch, c = it - gi * nch;
-        const uint8_t* bq = ring + (size_t)buf * C::BUF_BYTES;
-        const uint16_t* bs = reinterpret_cast<const uint16_t*>(bq + C::QS_BYTES);
-        const int nb = min(KC, nblk - c * KC);
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            const int b = lane + 32 * j;
-            if (b < nb) {
-                uint4 q[NW * R][QV];
-                uint16_t dh[NW * R];
-#pragma unroll
-                for (int ar = 0; ar < NW * R; ar++) {
-#pragma unroll
-                    for (int v = 0; v < QV; v++) q[ar][v] = *reinterpret_cast<const uint4*>(bq + ar * (KC * QB) + b * QB + 16 * v);
-                    dh[ar] = bs[ar * KC + b];
-                }
-#pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    uint32_t dl[24];
-                    float xsl = 0.f;
-                    if (!DREG) {
-                        const uint32_t* xb = xd + ((size_t)m * nblk + c * KC + b) * XW;
-                        load_digits(xb, dl);
-                        xsl = __uint_as_float(xb[24]);
-                    }
-                    const uint32_t (&dd)[24] = DREG ? dg[DREG ? j : 0] : dl;
-                    const float xs = DREG ? xsr[DREG ? j : 0] : xsl;
-#pragma unroll
-                    for (int a = 0; a < NW; a++)
-#pragma unroll
-                        for (int r = 0; r < R; r++) {
-                            const float t = block_dot<TYPE>(q[a * R + r][0], q[a * R + r][QV - 1], dd);
-                            const float d = QUIRK ? cml_half_to_float(dh[a * R + r]) : __half2float(__ushort_as_half(dh[a * R + r]));
-                            acc[a][r][m] = fmaf(t, d * xs, acc[a][r][m]);
-                        }
-                }
-            }
-        }
-        __syncwarp();                                       // every lane is done with this buffer
-        if (it + NBUF < n_it) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue(it + NBUF, buf);
-        }
-        if (c == nch - 1) {                                 // last chunk of the group: reduce and write
-            const int row0 = (gw + gi * total_warps) * R;
-#pragma unroll
-            for (int a = 0; a < NW; a++)
-#pragma unroll
-                for (int r = 0; r < R; r++)
-#pragma unroll
-                    for (int m = 0; m < MT; m++) {
-                        float v = acc[a][r][m];
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                        acc[a][r][m] = v * kDotUnit<TYPE>;
-                    }
-            if (lane == 0) {
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    if (row0 + r < N) {
-#pragma unroll
-                        for (int m = 0; m < MT; m++) {
-                            float* out = y + (size_t)m * N + row0 + r;
-                            if (EPI == EPI_STORE) *out = acc[0][r][m];
-                            else if (EPI == EPI_ACCUM) *out += acc[0][r][m];
-                            else {
-                                const float g = acc[0][r][m];
-                                *out = (g / (1.0f + expf(-g))) * acc[NW - 1][r][m];
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int a = 0; a < NW; a++)
-#pragma unroll
-                for (int r = 0; r < R; r++)
-#pragma unroll
-                    for (int m = 0; m < MT; m++) acc[a][r][m] = 0.f;
-        }
-    }
-    if (!ok) {
-        // A copy never landed. Record it, then give the copies still addressed to this warp's
-        // buffers one more bounded chance to finish before the CTA's shared memory is released.
-        if (lane == 0) atomicCAS(&g_stream_status, 0, 1 + it % NBUF);
-        for (int k = it; k < n_it && k < it + NBUF; k++) (void)mbar_wait(bar0 + 8 * (k % NBUF), (uint32_t)(k / NBUF) & 1u);
-    }
-#ifdef CMLB200_TRACE
-    __syncthreads();
-    TRACE(3);
-#endif
-}
-
-template <int TYPE, int MT, int EPI, bool QUIRK, int XMODE, bool DREG>
-int launch_stream_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, cudaStream_t st) {
-    constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
-    constexpr int R = (DREG || EPI == EPI_SWIGLU) ? 1 : 2;
-    using C = StreamCfg<TYPE, NW, R, DREG>;
-    const int N = W->rows, K = W->cols, nblk = K / 32;
-    const size_t smem = C::BAR_BYTES + C::digit_bytes(MT, nblk) + (size_t)C::SW * C::NBUF * C::BUF_BYTES;
-    auto kern = gemv_stream_kernel<TYPE, MT, R, EPI, QUIRK, XMODE, DREG>;
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
-    }
-    const int groups = (N + R - 1) / R;
-    const int grid = min(cmlb_num_sms(), (groups + C::SW - 1) / C::SW);
-    return launch_pdl(kern, dim3(grid), dim3(C::SW * 32), smem, st, (const uint8_t*)W->qs, (const uint16_t*)W->scales,
-                      W2 ? (const uint8_t*)W2->qs : (const uint8_t*)nullptr,
-                      W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K);
-}
-
-template <int TYPE, int MT, int EPI, bool QUIRK, int XMODE>
-int launch_stream(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, cudaStream_t st) {
-    if (MT == 1 && W->cols <= 32 * 128) return launch_stream_cfg<TYPE, 1, EPI, QUIRK, XMODE, true>(W, W2, xin, nw, eps, y, st);
-    return launch_stream_cfg<TYPE, MT, EPI, QUIRK, XMODE, false>(W, W2, xin, nw, eps, y, st);
-}
-
-// The streaming kernel needs 16-byte aligned row chunks of the scale plane (K % 256 == 0) and
-// room for the digits of MT rows of x next to the rings.
-inline bool stream_ok(const cmlb200_qmat* W, int MT) {
-    return W->cols % 256 == 0 && (size_t)MT * (W->cols / 32) * XW * 4 <= 80 * 1024 &&
-           ((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)W->scales & 15) == 0;
-}
-
 template <int TYPE, int MT, int EPI, bool QUIRK>
 int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, float* y, int m0, cudaStream_t st) {
     constexpr int R = (EPI == EPI_SWIGLU) ? 2 : 4;
@@ -627,45 +289,20 @@ int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, fl
 int rmsnorm_digits_(const float* x, const __half* w, int rows, int dim, float eps, float* out, uint32_t* xq, cudaStream_t st);
 
 // Rows of x are taken two at a time (one launch streams the weight once for both), then one.
-// x != NULL: fp32 activations, RMS-normalised with nw first when nw != NULL (digits made in the
-// streaming kernel, or in `ws` for the register kernel); else xq holds the digit records.
+// x != NULL: fp32 activations, RMS-normalised with nw first when nw != NULL, turned into digit
+// records in `ws`; else xq holds the digit records.
 template <int TYPE, int EPI, bool QUIRK>
 int run_type(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const __half* nw, float eps, const uint32_t* xq,
              uint32_t* ws, float* y, int M, cudaStream_t st) {
-    const int N = W->rows, K = W->cols, nblk = K / 32;
-    auto digits_to_ws = [&]() -> int {
-        const int rc = nw ? rmsnorm_digits_(x, nw, M, K, eps, nullptr, ws, st) : cmlb200_x_digits_(x, M, K, ws, st);
-        xq = ws;
-        x = nullptr;
-        return rc;
-    };
-    if (x && !stream_ok(W, 1)) {
-        const int rc = digits_to_ws();
+    if (x) {
+        const int rc = nw ? rmsnorm_digits_(x, nw, M, W->cols, eps, nullptr, ws, st) : cmlb200_x_digits_(x, M, W->cols, ws, st);
         if (rc) return rc;
+        xq = ws;
     }
     int m0 = 0, rc = 0;
     while (m0 < M && rc == 0) {
-        const int mt = (M - m0 >= 2) ? 2 : 1;
-        float* ym = y + (size_t)m0 * N;
-        if (stream_ok(W, mt)) {
-            if (x && nw) {
-                const float* xm = x + (size_t)m0 * K;
-                rc = mt == 2 ? launch_stream<TYPE, 2, EPI, QUIRK, 2>(W, W2, xm, nw, eps, ym, st) : launch_stream<TYPE, 1, EPI, QUIRK, 2>(W, W2, xm, nw, eps, ym, st);
-            } else if (x) {
-                const float* xm = x + (size_t)m0 * K;
-                rc = mt == 2 ? launch_stream<TYPE, 2, EPI, QUIRK, 1>(W, W2, xm, nullptr, 0.f, ym, st) : launch_stream<TYPE, 1, EPI, QUIRK, 1>(W, W2, xm, nullptr, 0.f, ym, st);
-            } else {
-                const uint32_t* qm = xq + (size_t)m0 * nblk * XW;
-                rc = mt == 2 ? launch_stream<TYPE, 2, EPI, QUIRK, 0>(W, W2, qm, nullptr, 0.f, ym, st) : launch_stream<TYPE, 1, EPI, QUIRK, 0>(W, W2, qm, nullptr, 0.f, ym, st);
-            }
-        } else {
-            if (!xq) {       // shape fits the streaming kernel for one row but not two: digits on demand
-                rc = digits_to_ws();
-                if (rc) return rc;
-            }
-            rc = mt == 2 ? launch<TYPE, 2, EPI, QUIRK>(W, W2, xq, y, m0, st) : launch<TYPE, 1, EPI, QUIRK>(W, W2, xq, y, m0, st);
-        }
-        m0 += mt;
+        if (M - m0 >= 2) { rc = launch<TYPE, 2, EPI, QUIRK>(W, W2, xq, y, m0, st); m0 += 2; }
+        else { rc = launch<TYPE, 1, EPI, QUIRK>(W, W2, xq, y, m0, st); m0 += 1; }
     }
     return rc;
 }
@@ -699,7 +336,7 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
     if (cmlb200_gemv_mma_ok_(W, epi, M)) return cmlb200_gemv_mma_(W, W2, xq ? nullptr : x, norm_w, eps, xq, y, M, epi, st);
     uint32_t* ws = nullptr;
     if (xq) x = nullptr;
-    else if (!stream_ok(W, 2)) {      // the register kernel may be needed: it reads digits from the library's scratch
+    else {                            // the register kernel reads digits from the library's scratch
         int rc = library_scratch(&ws);
         if (rc) return rc;
         CMLB_REQUIRE(cmlb200_xq_bytes_(M, W->cols) <= kScratchBytes, "cmlb200_gemv: M*K too large for the built-in activation scratch");
@@ -709,18 +346,6 @@ int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
     const bool q8 = W->type == CMLB200_Q8_0;
     if (quirk) return q8 ? run_epi<CMLB200_Q8_0, true>(W, W2, x, nw, eps, xq, ws, y, M, epi, st) : run_epi<CMLB200_Q4_0, true>(W, W2, x, nw, eps, xq, ws, y, M, epi, st);
     return q8 ? run_epi<CMLB200_Q8_0, false>(W, W2, x, nw, eps, xq, ws, y, M, epi, st) : run_epi<CMLB200_Q4_0, false>(W, W2, x, nw, eps, xq, ws, y, M, epi, st);
-}
-
-// Device-side health word of the streaming kernel: 0 while every bounded wait has completed.
-extern "C" int cmlb200_gemv_status(int* status, int reset) {
-    CMLB_REQUIRE(status, "cmlb200_gemv_status: NULL argument");
-    CMLB_CUDA(cudaDeviceSynchronize());
-    CMLB_CUDA(cudaMemcpyFromSymbol(status, g_stream_status, sizeof(int)));
-    if (reset) {
-        const int zero = 0;
-        CMLB_CUDA(cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int)));
-    }
-    return CMLB200_OK;
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------

@@ -137,10 +137,6 @@ int cmlb200_rmsnorm_digits(const float* d_x, const uint16_t* d_w_f16, int rows, 
 int cmlb200_gemv_xq(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* d_xq, float* d_y, int M, int epi, void* stream);
 int cmlb200_gemv_rmsnorm(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* d_x, const uint16_t* d_norm_w_f16, float eps,
                          float* d_y, int M, int epi, void* stream);
-/* The M <= 4 kernels wait for their shared-memory copies with a bounded spin. Synchronises the
- * device and stores 0 in *status if every wait so far completed, else which buffer gave up (the
- * outputs of that launch are then invalid); reset != 0 clears the word. */
-int cmlb200_gemv_status(int* status, int reset);
 
 /* The decode GEMV for callers that cannot allocate device memory at run time (a serving process
  * that gave the whole GPU to its own arena, a real-time loop that must not take the allocator

@@ -128,11 +128,10 @@ def test_gemv_with_subnormal_scales_follows_reference_quirk(pkg, synth, ob, orc,
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
-@pytest.mark.parametrize("K", [512, 1056])                 # streaming kernel (K % 256 == 0) and register kernel
+@pytest.mark.parametrize("K", [512, 1056])                 # tensor-core kernel (K % 256 == 0) and register kernel
 def test_gemv_digit_entry_points_and_fused_rmsnorm(pkg, synth, ob, orc, torch_dev, kind, K):
     """x_digits + gemv_xq, rmsnorm_digits + gemv_xq and gemv_rmsnorm agree with the oracle's
-    rms_norm followed by its linear; the kernels' bounded waits all completed."""
-    import ctypes as C
+    rms_norm followed by its linear."""
     rng = np.random.default_rng(11)
     N, eps = 301, 1e-5
     Wg, Wgf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
@@ -165,9 +164,6 @@ def test_gemv_digit_entry_points_and_fused_rmsnorm(pkg, synth, ob, orc, torch_de
         pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, Wu.q, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 2, stream_ptr()), "gemv_rmsnorm swiglu")
         u = ob.linear_nt(orc, normed, Wuf)
         assert rel_err(d_y.cpu().numpy(), (want / (1.0 + np.exp(-want.astype(np.float64)))).astype(np.float32) * u) <= TOL
-    st = C.c_int(-1)
-    pkg.check(pkg.lib.cmlb200_gemv_status(C.byref(st), 0), "gemv_status")
-    assert st.value == 0
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
