@@ -158,8 +158,47 @@ class QLoRALinear(C.Structure):
                 ("lora_B", C.POINTER(Tensor)), ("enable_double_quant", C.c_bool)]
 
 
+class KVCache(C.Structure):
+    _fields_ = [("key_cache", C.POINTER(Tensor)), ("value_cache", C.POINTER(Tensor)), ("max_seq_len", C.c_int),
+                ("current_len", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int)]
+
+
+class GQAConfig(C.Structure):
+    _fields_ = [("num_heads", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int), ("scale", C.c_float),
+                ("causal", C.c_bool), ("window_size", C.c_int)]
+
+
+class RoPEConfig(C.Structure):
+    _fields_ = [("dim", C.c_int), ("max_seq_len", C.c_int), ("base", C.c_float)]
+
+
+class ParallelLinear(C.Structure):          # CMLColumnParallelLinear and CMLRowParallelLinear share the layout
+    _fields_ = [("weight", C.POINTER(Tensor)), ("bias", C.POINTER(Tensor)), ("in_features", C.c_int), ("out_features", C.c_int),
+                ("tp_size", C.c_int), ("tp_rank", C.c_int)]
+
+
 TP = C.POINTER(Tensor)
 MP = C.POINTER(LlamaModel)
+KP = C.POINTER(KVCache)
+PLP = C.POINTER(ParallelLinear)
+_sig("cml_kv_cache_create", KP, ci, ci, ci)
+_sig("cml_kv_cache_free", None, KP)
+_sig("cml_kv_cache_append", ci, KP, TP, TP)
+_sig("cml_kv_cache_reset", None, KP)
+_sig("cml_kv_cache_get_keys", TP, KP)
+_sig("cml_kv_cache_get_values", TP, KP)
+_sig("cml_gqa_forward", TP, TP, TP, TP, C.POINTER(GQAConfig), TP)
+_sig("cml_gqa_forward_cached", TP, TP, TP, TP, KP, C.POINTER(GQAConfig))
+_sig("cml_rope_forward", TP, TP, ci, C.POINTER(RoPEConfig))
+_sig("cml_column_parallel_create", PLP, TP, TP, ci, ci)
+_sig("cml_column_parallel_free", None, PLP)
+_sig("cml_column_parallel_forward", TP, PLP, TP)
+_sig("cml_row_parallel_create", PLP, TP, TP, ci, ci)
+_sig("cml_row_parallel_free", None, PLP)
+_sig("cml_row_parallel_forward", TP, PLP, TP)
+_sig("cml_tp_all_reduce_sum", TP, C.POINTER(TP), ci)
+_sig("cml_tp_shard_weight", TP, TP, ci, ci, ci)
+_sig("cml_llama_layer_forward", TP, MP, vp, TP, ci)
 _sig("cml_set_log_level", None, ci)
 _sig("tensor_from_data", TP, vp, C.POINTER(ci), ci, C.POINTER(TensorConfig))
 _sig("tensor_zeros", TP, C.POINTER(ci), ci, C.POINTER(TensorConfig))

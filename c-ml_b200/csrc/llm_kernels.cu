@@ -412,14 +412,18 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
         mine[2 + threadIdx.x] = a;
         if (threadIdx.x == 0) { mine[0] = gm; mine[1] = lt; }
     }
-    // ---- the last split of this (row, head) to finish merges all of them
-    __threadfence();
+    // ---- the last split of this (row, head) to finish merges all of them. The barrier orders the
+    // CTA's partial before thread 0's release-acquire increment, which publishes it (cumulativity) and,
+    // in the last CTA, makes the other splits' partials visible to the threads behind the next barrier.
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(&counters[rh], 1u) == (unsigned)nsplit - 1) ? 1u : 0u;
+    if (threadIdx.x == 0) {
+        unsigned int old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(counters + rh) : "memory");
+        s_last = (old == (unsigned)nsplit - 1) ? 1u : 0u;
+        if (s_last) counters[rh] = 0u;                  // ready for the next launch
+    }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
-    if (threadIdx.x == 0) counters[rh] = 0u;            // ready for the next launch
     // Two rounds of loads, each issued as one batch: the splits' (max, sum) pairs by one thread each,
     // then every output element's share of all splits.
     const float* p = partial + rh * nsplit * (HD + 2);

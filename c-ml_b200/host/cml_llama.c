@@ -597,7 +597,7 @@ static int proj_residual_bf16(DevModel* d, const cmlb200_qmat* W, const uint16_t
  * mode 0: one sequence (`seq`), consecutive positions; mode 1: one token for each of `rows`
  * sequences. plan_limit bounds the cache positions the call may touch (sizes the attention
  * splits); logits for all rows land in d->logits. */
-static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_limit) {
+static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan_limit, int only_layer) {
     const CMLLLaMAModel* m = d->key;
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
@@ -605,7 +605,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     const int tiny = rows <= 8;                 /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
     void* st = d->stream;
     DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
-    DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));
+    if (only_layer < 0) DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));
     const int max_limit_raw = quirks ? (mode == 0 ? rows - 1 : 0) : plan_limit;
     const int max_limit = max_limit_raw < c->max_seq_len ? max_limit_raw : c->max_seq_len - 1;
     int splits = 1;
@@ -628,6 +628,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     if (fused_att) DEV(cmlb200_rope_table(d->row_pos, rows, d->hd, c->rope_theta, d->rope_cs, st));
     const size_t esz = kvf32 ? 4 : 2;
     for (int li = 0; li < m->num_layers; li++) {
+        if (only_layer >= 0 && li != only_layer) continue;
         const DevLayer* L = &d->L[li];
         void* kc = (char*)d->kc + (size_t)li * d->kv_layer_elems * esz;
         void* vc = (char*)d->vc + (size_t)li * d->kv_layer_elems * esz;
@@ -682,6 +683,7 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
             if (proj_residual_bf16(d, &L->wd, d->b_c, rows)) return -1;
         }
     }
+    if (only_layer >= 0) return 0;              /* cml_llama_layer_forward: no head, positions stay where they are */
     if (tiny) {
         DEV(cmlb200_gemv_rmsnorm(&d->lm_head, NULL, d->h, (const uint16_t*)d->fnorm, c->rms_norm_eps, d->logits, rows, 0, st));
     } else if (skinny) {
@@ -694,6 +696,10 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     }
     DEV(cmlb200_advance_rows(d->d_cur, rows, mode, seq, st));
     return 0;
+}
+
+static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_limit) {
+    return enqueue_forward_ex(d, rows, mode, seq, plan_limit, -1);
 }
 
 static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows, int mode, int seq, const char* who) {
@@ -876,6 +882,45 @@ void cml_generation_result_free(CMLGenerationResult* result) {
     free(result->token_ids);
     free(result->text);
     free(result);
+}
+
+/* One transformer block on host activations (src/nn/llama.c:454-548): hidden [seq, hidden_size]
+ * fp32 in, a new tensor of the same shape out. The rows take positions start_pos .. start_pos+seq-1
+ * of sequence 0: their keys and values are written into the layer's device cache at those positions
+ * and they attend everything before them. The model's own position counter is left as it was. */
+Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tensor* hidden, int start_pos) {
+    if (!model || !layer || !hidden) return NULL;
+    const char* who = "cml_llama_layer_forward";
+    DevModel* d = dm_find(model);
+    if (!model_ready(model, d)) { LOG_ERROR("%s: weights are not loaded", who); return NULL; }
+    const CMLLLaMAConfig* c = &model->config;
+    int li = -1;
+    for (int i = 0; i < model->num_layers; i++) if (model->layers[i] == layer) li = i;
+    if (li < 0) { LOG_ERROR("%s: the layer does not belong to the model", who); return NULL; }
+    if (hidden->ndim != 2 || hidden->shape[1] != c->hidden_size || !hidden->data) {
+        LOG_ERROR("%s: hidden must be [seq, %d] fp32", who, c->hidden_size);
+        return NULL;
+    }
+    const int rows = hidden->shape[0];
+    if (rows <= 0 || rows > d->max_rows) { LOG_ERROR("%s: seq %d outside 1..%d", who, rows, d->max_rows); return NULL; }
+    if (start_pos < 0 || start_pos + rows > c->max_seq_len) { LOG_ERROR("%s: cache overflow (%d + %d > %d)", who, start_pos, rows, c->max_seq_len); return NULL; }
+    int shape[2] = {rows, c->hidden_size};
+    Tensor* out = cml_tensor_alloc(DTYPE_FLOAT32, shape, 2, false);
+    if (!out) return NULL;
+    const size_t bytes = (size_t)rows * c->hidden_size * sizeof(float);
+    const int saved = d->h_cur[0];
+    int ok = !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->h, hidden->data, bytes, d->stream), who) &&
+             !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &start_pos, sizeof(int), d->stream), who) &&
+             !CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who) &&          /* start_pos is a stack variable */
+             !enqueue_forward_ex(d, rows, 0, 0, start_pos + rows - 1, li) &&
+             !CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->h, bytes, d->stream), who);
+    /* put the model's own position back whatever happened */
+    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &saved, sizeof(int), d->stream), who) || CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) ok = 0;
+    int st = 0;
+    if (cmlb200_gemm_status(&st, 1) == CMLB200_OK && st == 0) cmlb200_gemv_tiles_status(&st, 1);
+    if (st) { LOG_ERROR("%s: a bounded device-side wait expired (code %d)", who, st); ok = 0; }
+    if (!ok) { tensor_free(out); return NULL; }
+    return out;
 }
 
 void cml_llama_reset(CMLLLaMAModel* model) {

@@ -157,15 +157,80 @@ void cml_qlora_linear_invalidate(CMLQLoRALinear* qlora);      /* addition: no C-
 size_t cml_qlora_memory_usage(const CMLQLoRALinear* qlora);
 size_t cml_qlora_full_memory_usage(int in_features, int out_features);
 
-/* ---- include/nn/llm_ops.h:13-32 (the cache object the model structs point at) -------------- */
+/* ---- include/nn/llm_ops.h:13-89: KV cache, grouped-query attention, RoPE ------------------------
+ * Stand-alone operators on host tensors (arithmetic on the device). A cache made by
+ * cml_kv_cache_create holds two dense fp32 host tensors exactly as in C-ML; the caches inside a
+ * CMLLLaMAModel are placeholders (key_cache == NULL): that model's keys and values live on the
+ * device. */
 typedef struct CMLKVCache {
-    Tensor* key_cache;      /* NULL here: keys and values live on the device */
+    Tensor* key_cache;      /* [max_seq_len, num_kv_heads, head_dim] */
     Tensor* value_cache;
     int max_seq_len;
     int current_len;
     int num_kv_heads;
     int head_dim;
 } CMLKVCache;
+CMLKVCache* cml_kv_cache_create(int max_seq_len, int num_kv_heads, int head_dim);
+void cml_kv_cache_free(CMLKVCache* cache);
+/* new_key / new_value: [seq, num_kv_heads, head_dim]; returns the new length, -1 on overflow. */
+int cml_kv_cache_append(CMLKVCache* cache, Tensor* new_key, Tensor* new_value);
+void cml_kv_cache_reset(CMLKVCache* cache);
+Tensor* cml_kv_cache_get_keys(CMLKVCache* cache);       /* new [current_len, kv_heads, head_dim] copy, NULL when empty */
+Tensor* cml_kv_cache_get_values(CMLKVCache* cache);
+
+typedef struct CMLGQAConfig {
+    int num_heads;
+    int num_kv_heads;
+    int head_dim;
+    float scale;            /* <= 0: 1/sqrt(head_dim) */
+    bool causal;            /* key index > query index (both relative to this call) is masked */
+    int window_size;        /* > 0: query index - key index > window_size is masked */
+} CMLGQAConfig;
+/* Q [batch, seq, heads*head_dim], K, V [batch, kv_len, kv_heads*head_dim], mask NULL or
+ * [seq, kv_len] / [batch, seq, kv_len] with 0 = masked; masked scores are -1e9 as in C-ML.
+ * Returns a new [batch, seq, heads*head_dim] tensor. */
+Tensor* cml_gqa_forward(Tensor* Q, Tensor* K, Tensor* V, const CMLGQAConfig* config, Tensor* mask);
+/* Appends K, V (batch 1) to the cache, then attends the whole cached prefix. */
+Tensor* cml_gqa_forward_cached(Tensor* Q, Tensor* K, Tensor* V, CMLKVCache* kv_cache, const CMLGQAConfig* config);
+
+typedef struct CMLRoPEConfig {
+    int dim;
+    int max_seq_len;
+    float base;             /* <= 0: 10000 */
+} CMLRoPEConfig;
+/* In place; returns x. [batch, seq, heads, head_dim], [batch, seq, dim] or [seq, dim]. */
+Tensor* cml_rope_forward(Tensor* x, int start_pos, const CMLRoPEConfig* config);
+
+/* ---- include/distributed/tensor_parallel.h:12-59 (fp32 building blocks) ----------------------- */
+typedef struct CMLColumnParallelLinear {
+    Tensor* weight;         /* [out_features / tp_size, in_features] */
+    Tensor* bias;           /* [out_features / tp_size] or NULL */
+    int in_features;
+    int out_features;
+    int tp_size;
+    int tp_rank;
+} CMLColumnParallelLinear;
+typedef struct CMLRowParallelLinear {
+    Tensor* weight;         /* [out_features, in_features / tp_size] */
+    Tensor* bias;           /* [out_features] on rank 0 only, else NULL */
+    int in_features;
+    int out_features;
+    int tp_size;
+    int tp_rank;
+} CMLRowParallelLinear;
+typedef struct CMLTensorParallelConfig {
+    int tp_size;
+    int tp_rank;
+} CMLTensorParallelConfig;
+CMLColumnParallelLinear* cml_column_parallel_create(Tensor* full_weight, Tensor* full_bias, int tp_size, int tp_rank);
+void cml_column_parallel_free(CMLColumnParallelLinear* cp);
+Tensor* cml_column_parallel_forward(CMLColumnParallelLinear* cp, Tensor* input);
+CMLRowParallelLinear* cml_row_parallel_create(Tensor* full_weight, Tensor* full_bias, int tp_size, int tp_rank);
+void cml_row_parallel_free(CMLRowParallelLinear* rp);
+Tensor* cml_row_parallel_forward(CMLRowParallelLinear* rp, Tensor* input);     /* caller sums the ranks' outputs */
+Tensor* cml_tp_all_reduce_sum(Tensor** partials, int num_parts);
+Tensor* cml_tp_shard_weight(Tensor* weight, int dim, int tp_size, int tp_rank);
+
 typedef struct CMLTokenizer CMLTokenizer;
 
 /* ---- include/nn/llama.h:13-106 -------------------------------------------------------------- */
@@ -242,6 +307,7 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath);
 /* Logits [seq_len, vocab] as a host fp32 tensor the caller frees, one sequence, positions
  * continuing at model->current_seq_len. */
 Tensor* cml_llama_forward(CMLLLaMAModel* model, const int* token_ids, int seq_len);
+Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tensor* hidden, int start_pos);
 CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config);
 void cml_generation_result_free(CMLGenerationResult* result);
 int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config);

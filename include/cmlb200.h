@@ -257,6 +257,20 @@ int cmlb200_event_record(void* event, void* stream);
 int cmlb200_event_elapsed_ms(void* start, void* stop, float* ms);
 int cmlb200_event_destroy(void* event);
 
+/* ---- fp32 operators behind the stand-alone C-ML entry points ------------------------------
+ * cmlb200_gqa_f32: softmax(Q K^T * scale + masks) V with every option of cml_gqa_forward
+ * (src/nn/llm_ops.c:194-372; masked scores are -1e9): q [batch, seq_q, heads*hd], k, v
+ * [batch, kv_len, kv_heads*hd], mask NULL or [seq_q, kv_len] (mask_per_batch 0) /
+ * [batch, seq_q, kv_len] (1) with 0 = masked. kv_len <= 51200.
+ * cmlb200_rope_f32: cml_rope_forward (src/nn/llm_ops.c:702-805) on nvec vectors of last_dim floats,
+ * vector v at position start_pos + (v / inner) % seq_len.
+ * cmlb200_linear_f32: y[M,N] = x[M,K] . w[N,K]^T (+ bias), the forward of C-ML's fp32
+ * column/row-parallel layers (src/distributed/tensor_parallel.c). */
+int cmlb200_gqa_f32(const float* d_q, const float* d_k, const float* d_v, const float* d_mask, int mask_per_batch, int batch, int seq_q,
+                    int kv_len, int heads, int kv_heads, int head_dim, float scale, int causal, int window, float* d_out, void* stream);
+int cmlb200_rope_f32(float* d_x, size_t nvec, int last_dim, int dim, float base, int start_pos, int seq_len, int inner, void* stream);
+int cmlb200_linear_f32(const float* d_x, const float* d_w, const float* d_bias, int M, int N, int K, float* d_y, void* stream);
+
 /* ---- tensor-parallel all-reduce over peer memory -------------------------------------------
  * h[0..n) += sum over ranks of partial[0..n) in one launch per rank, for the decode-sized
  * messages after the row-parallel projections (C-ML: cml_tp_all_reduce_sum,

@@ -166,3 +166,37 @@ def test_error_behaviour_and_reset(pkg, tiny, torch_dev):
     c70 = lib.cml_llama_config_70b()
     assert (c7.hidden_size, c7.intermediate_size, c7.num_layers, c7.num_kv_heads) == (4096, 11008, 32, 32)
     assert (c70.hidden_size, c70.intermediate_size, c70.num_layers, c70.num_heads, c70.num_kv_heads) == (8192, 28672, 80, 64, 8)
+
+
+def test_layer_forward_chain_matches_model_forward(pkg, tiny, torch_dev):
+    """cml_llama_layer_forward block by block (host activations in and out) followed by the oracle's
+    final norm and head reproduces cml_llama_forward's logits; the model's own position is untouched."""
+    path, store = tiny
+    ob = entry.load_oracle_binding()
+    orc = ob.load_orc()
+    tokens = np.random.default_rng(9).integers(0, TINY["vocab"], 6).astype(np.int32)
+    m = device_model(pkg, TINY, path, flags=pkg.KV_FP32)
+    try:
+        want = dev_forward(pkg, m, tokens)
+        assert m.contents.current_seq_len == 6
+        hidden = store["token_embd.weight"].astype(np.float32)[tokens]
+        layers = C.cast(m.contents.layers, C.POINTER(C.c_void_p))
+        for l in range(TINY["layers"]):
+            th = pkg.numpy_to_tensor(hidden)
+            out = pkg.lib.cml_llama_layer_forward(m, layers[l], th, 0)
+            assert out
+            hidden = pkg.tensor_to_numpy(out)
+            pkg.lib.tensor_free(th)
+        assert m.contents.current_seq_len == 6
+        fnorm = np.ascontiguousarray(store["output_norm.weight"].astype(np.float32))
+        normed = np.zeros_like(hidden)
+        orc.orc_rmsnorm(ob.p(np.ascontiguousarray(hidden)), ob.p(fnorm), 6, TINY["hidden"], 1e-5, ob.p(normed))
+        blocks, out_f, in_f = store["output.weight"]
+        head = ob.dequant_blocks(orc, 2, blocks, out_f * in_f).reshape(out_f, in_f)
+        got = ob.linear_nt(orc, normed, head)
+        assert rel_err_inf(got, want) <= 2e-3
+        bad = pkg.numpy_to_tensor(np.zeros((2, TINY["hidden"] + 1), np.float32))
+        assert not pkg.lib.cml_llama_layer_forward(m, layers[0], bad, 0)
+        pkg.lib.tensor_free(bad)
+    finally:
+        pkg.lib.cml_llama_free(m)

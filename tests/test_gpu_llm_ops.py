@@ -1,0 +1,178 @@
+"""The stand-alone KV-cache / GQA / RoPE / tensor-parallel entry points (C-ML include/nn/llm_ops.h:13-89,
+include/distributed/tensor_parallel.h:12-59) against float64 evaluations of C-ML's formulas
+(src/nn/llm_ops.c:194-444, 702-805; src/distributed/tensor_parallel.c) and the oracle's RoPE / GQA."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(pkg, a):
+    t = pkg.numpy_to_tensor(np.ascontiguousarray(a, np.float32))
+    assert t
+    return t
+
+
+def _np(pkg, t):
+    return pkg.tensor_to_numpy(t, free=False)
+
+
+def _gqa_ref(q, k, v, H, KH, D, scale, causal, window, mask):
+    B, SQ, _ = q.shape
+    KV = k.shape[1]
+    out = np.zeros((B, SQ, H * D))
+    for b in range(B):
+        for h in range(H):
+            kh = h // (H // KH)
+            qq = q[b, :, h * D:(h + 1) * D].astype(np.float64)
+            kk = k[b, :, kh * D:(kh + 1) * D].astype(np.float64)
+            vv = v[b, :, kh * D:(kh + 1) * D].astype(np.float64)
+            s = qq @ kk.T * scale
+            i, j = np.arange(SQ)[:, None], np.arange(KV)[None, :]
+            if causal:
+                s[j > i] = -1e9
+            if window > 0:
+                s[(i - j) > window] = -1e9
+            if mask is not None:
+                m = mask if mask.ndim == 2 else mask[b]
+                s[m == 0] = -1e9
+            p = np.exp(s - s.max(1, keepdims=True))
+            p /= p.sum(1, keepdims=True)
+            out[b, :, h * D:(h + 1) * D] = p @ vv
+    return out
+
+
+@pytest.mark.parametrize("H,KH,D", [(8, 2, 64), (4, 4, 32), (6, 3, 128)])
+def test_gqa_forward_options(pkg, torch_dev, H, KH, D):
+    rng = np.random.default_rng(41)
+    B, SQ, KV = 2, 7, 19
+    q = rng.standard_normal((B, SQ, H * D)).astype(np.float32)
+    k = rng.standard_normal((B, KV, KH * D)).astype(np.float32)
+    v = rng.standard_normal((B, KV, KH * D)).astype(np.float32)
+    m2 = (rng.random((SQ, KV)) > 0.3).astype(np.float32)
+    m2[3] = 0.0                                              # a fully masked row: C-ML's -1e9 gives a uniform average
+    m3 = (rng.random((B, SQ, KV)) > 0.3).astype(np.float32)
+    tq, tk, tv = _t(pkg, q), _t(pkg, k), _t(pkg, v)
+    for scale, causal, window, mask in [(0.0, False, 0, None), (0.0, True, 0, None), (0.25, True, 3, None), (0.0, False, 0, m2),
+                                        (0.0, True, 0, m3)]:
+        cfg = pkg.GQAConfig(H, KH, D, scale, causal, window)
+        tm = _t(pkg, mask) if mask is not None else None
+        out = pkg.lib.cml_gqa_forward(tq, tk, tv, C.byref(cfg), tm)
+        assert out
+        got = _np(pkg, out)
+        want = _gqa_ref(q, k, v, H, KH, D, scale if scale > 0 else 1.0 / np.sqrt(D), causal, window, mask)
+        assert got.shape == (B, SQ, H * D)
+        assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+        pkg.lib.tensor_free(out)
+        if tm:
+            pkg.lib.tensor_free(tm)
+    bad = pkg.GQAConfig(5, 2, D, 0.0, False, 0)
+    assert not pkg.lib.cml_gqa_forward(tq, tk, tv, C.byref(bad), None)       # heads not divisible by kv heads
+    for t in (tq, tk, tv):
+        pkg.lib.tensor_free(t)
+
+
+def test_kv_cache_and_cached_attention(pkg, torch_dev):
+    rng = np.random.default_rng(42)
+    H, KH, D, MAXS = 4, 2, 32, 12
+    cache = pkg.lib.cml_kv_cache_create(MAXS, KH, D)
+    assert cache and cache.contents.current_len == 0 and not pkg.lib.cml_kv_cache_get_keys(cache)
+    cfg = pkg.GQAConfig(H, KH, D, 0.0, True, 0)
+    ks, vs = [], []
+    for step, n in enumerate((5, 1, 1)):
+        q = rng.standard_normal((1, n, H * D)).astype(np.float32)
+        k = rng.standard_normal((1, n, KH * D)).astype(np.float32)
+        v = rng.standard_normal((1, n, KH * D)).astype(np.float32)
+        ks.append(k[0]); vs.append(v[0])
+        tq, tk, tv = _t(pkg, q), _t(pkg, k), _t(pkg, v)
+        out = pkg.lib.cml_gqa_forward_cached(tq, tk, tv, cache, C.byref(cfg))
+        assert out
+        K, V = np.concatenate(ks)[None], np.concatenate(vs)[None]
+        assert cache.contents.current_len == K.shape[1]
+        # the causal mask is relative to this call's query index, as in C-ML
+        want = _gqa_ref(q, K, V, H, KH, D, 1.0 / np.sqrt(D), True, 0, None)
+        assert np.abs(_np(pkg, out) - want).max() <= 2e-5
+        for t in (out, tq, tk, tv):
+            pkg.lib.tensor_free(t)
+    tkeys = pkg.lib.cml_kv_cache_get_keys(cache)
+    assert np.array_equal(_np(pkg, tkeys).reshape(7, KH * D), np.concatenate(ks))
+    pkg.lib.tensor_free(tkeys)
+    big = _t(pkg, np.zeros((6, KH, D), np.float32))
+    assert pkg.lib.cml_kv_cache_append(cache, big, big) == -1                  # 7 + 6 > 12
+    pkg.lib.tensor_free(big)
+    pkg.lib.cml_kv_cache_reset(cache)
+    assert cache.contents.current_len == 0
+    pkg.lib.cml_kv_cache_free(cache)
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 3, 16), (2, 5, 24), (6, 16)])
+def test_rope_forward_shapes(pkg, ob, orc, torch_dev, shape):
+    rng = np.random.default_rng(43)
+    x = rng.standard_normal(shape).astype(np.float32)
+    dim, base, start = 16, 10000.0, 9
+    t = _t(pkg, x)
+    cfg = pkg.RoPEConfig(dim, 64, base)
+    r = pkg.lib.cml_rope_forward(t, start, C.byref(cfg))
+    assert r and C.addressof(r.contents) == C.addressof(t.contents)             # in place, same tensor back
+    got = _np(pkg, t)
+    last = shape[-1]
+    half = min(dim, last) // 2
+    want = x.astype(np.float64).copy().reshape(-1, last)
+    if len(shape) == 4:
+        pos = start + (np.arange(want.shape[0]) // shape[2]) % shape[1]
+    elif len(shape) == 3:
+        pos = start + np.arange(want.shape[0]) % shape[1]
+    else:
+        pos = start + np.arange(want.shape[0])
+    i = np.arange(half)
+    th = pos[:, None] * (1.0 / np.power(base, 2.0 * i / dim))[None, :]
+    x0, x1 = want[:, 0:2 * half:2].copy(), want[:, 1:2 * half:2].copy()
+    want[:, 0:2 * half:2] = x0 * np.cos(th) - x1 * np.sin(th)
+    want[:, 1:2 * half:2] = x0 * np.sin(th) + x1 * np.cos(th)
+    assert np.abs(got.reshape(-1, last) - want).max() <= 1e-5
+    pkg.lib.tensor_free(t)
+
+
+def test_tensor_parallel_building_blocks(pkg, torch_dev):
+    """Column-parallel then row-parallel over 4 ranks equals the unsharded two-layer product
+    (C-ML tests/test_tensor_parallel.c:330-430), bias sharded / kept on rank 0, uneven splits refused."""
+    rng = np.random.default_rng(44)
+    tp, B, K, N1, N2 = 4, 3, 24, 32, 20
+    x = rng.standard_normal((B, K)).astype(np.float32)
+    w1 = rng.standard_normal((N1, K)).astype(np.float32); b1 = rng.standard_normal(N1).astype(np.float32)
+    w2 = rng.standard_normal((N2, N1)).astype(np.float32); b2 = rng.standard_normal(N2).astype(np.float32)
+    tx, tw1, tb1, tw2, tb2 = (_t(pkg, a) for a in (x, w1, b1, w2, b2))
+    partials = []
+    for r in range(tp):
+        cp = pkg.lib.cml_column_parallel_create(tw1, tb1, tp, r)
+        rp = pkg.lib.cml_row_parallel_create(tw2, tb2, tp, r)
+        assert cp and rp
+        assert tuple(cp.contents.weight.contents.shape[i] for i in range(2)) == (N1 // tp, K)
+        assert tuple(rp.contents.weight.contents.shape[i] for i in range(2)) == (N2, N1 // tp)
+        assert bool(rp.contents.bias) == (r == 0)
+        h = pkg.lib.cml_column_parallel_forward(cp, tx)
+        assert h
+        hn = _np(pkg, h)
+        assert np.abs(hn - (x.astype(np.float64) @ w1[r * 8:(r + 1) * 8].T + b1[r * 8:(r + 1) * 8])).max() <= 1e-4
+        y = pkg.lib.cml_row_parallel_forward(rp, h)
+        assert y
+        partials.append(y)
+        pkg.lib.tensor_free(h)
+        pkg.lib.cml_column_parallel_free(cp)
+        pkg.lib.cml_row_parallel_free(rp)
+    arr = (pkg.TP * tp)(*partials)
+    total = pkg.lib.cml_tp_all_reduce_sum(arr, tp)
+    assert total
+    want = (x.astype(np.float64) @ w1.T + b1) @ w2.T + b2
+    assert np.abs(_np(pkg, total) - want).max() <= 1e-3 * np.abs(want).max()
+    for t in partials + [total]:
+        pkg.lib.tensor_free(t)
+    assert not pkg.lib.cml_column_parallel_create(tw1, None, 5, 0)             # 32 rows over 5 ranks
+    assert not pkg.lib.cml_tp_shard_weight(tw1, 2, 2, 0)                        # bad dim
+    sh = pkg.lib.cml_tp_shard_weight(tw1, 1, 3, 2)                              # columns 16..23
+    assert np.array_equal(_np(pkg, sh), w1[:, 16:24])
+    pkg.lib.tensor_free(sh)
+    for t in (tx, tw1, tb1, tw2, tb2):
+        pkg.lib.tensor_free(t)
