@@ -59,6 +59,26 @@ for toks in (prompt, np.array([7], np.int32), np.array([11], np.int32)):     # a
     dist.all_gather_object(both, got.tobytes())
     assert both[0] == both[1], "ranks disagree on the logits"
 assert worst < 2e-3, worst
+# one token for each of four sequences in one call (the projection + all-reduce launch takes four rows)
+# against the same calls on an unsharded copy of the model on this GPU
+c1 = pkg.LlamaConfig(cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv_heads"], cfg["max_seq"],
+                     10000.0, 1e-5, 0, 0)
+m1 = pkg.lib.cml_llama_create(C.byref(c1))
+assert m1 and pkg.lib.cml_llama_set_options(m1, pkg.KV_FP32, 4) == 0 and pkg.lib.cml_llama_load_gguf(m1, path.encode()) == 0
+for toks in (prompt, np.array([7], np.int32), np.array([11], np.int32)):
+    assert llama_util.dev_forward(pkg, m1, toks) is not None
+for B in (4, 3, 2):
+    toks = rng.integers(0, cfg["vocab"], B).astype(np.int32)
+    t_tp = pkg.lib.cml_llama_forward_batch(m, pkg.np_ptr(toks), B)
+    t_1 = pkg.lib.cml_llama_forward_batch(m1, pkg.np_ptr(toks), B)
+    assert t_tp and t_1
+    a, b = pkg.tensor_to_numpy(t_tp), pkg.tensor_to_numpy(t_1)
+    err = float(np.abs(a - b).max() / np.abs(b).max())
+    assert err < 2e-3, (B, err)
+    both = [None, None]
+    dist.all_gather_object(both, a.tobytes())
+    assert both[0] == both[1], "ranks disagree on the batched logits"
+pkg.lib.cml_llama_free(m1)
 dist.barrier()
 pkg.lib.cml_llama_free(m)
 dist.destroy_process_group()
