@@ -122,7 +122,7 @@ __device__ __forceinline__ float2 scales_of(uint32_t packed) {
 // y: [MT][N]. K % 256 == 0. BREG: K/256 <= SW, every warp owns at most one unit per item and
 // keeps its B fragments in registers. NW = 2: SwiGLU of two weights (gate, up); NW = 1: epi
 // selects store or accumulate.
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, bool TP>
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, int NPRE, bool TP>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ scales,
                 const uint8_t* __restrict__ qs2, const uint16_t* __restrict__ scales2,
@@ -215,9 +215,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         cp_async_commit();
     };
 
-    // Weights do not depend on the preceding kernel: fill the ring before the dependency wait.
+    // Weights do not depend on the preceding kernel: the first NPRE units are requested before the
+    // dependency wait. The rest of the ring follows right after this warp's loads of x, so that
+    // those loads, which everything else waits for, do not queue behind a ring-full of copies.
 #pragma unroll
-    for (int i = 0; i < NBUF; i++) issue_next(i);
+    for (int i = 0; i < NPRE; i++) issue_next(i);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TRACE(1);
     // tensor-parallel epilogue: sequence number of this all-reduce and the inbox buffer it uses
@@ -226,8 +228,78 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 
     // ---- digits of this warp's units of x into the B table. Lane = (block lane>>3 (+4), elements
     // 4*(lane&7)..+3); a unit is 8 blocks = two such passes, loaded together.
+    const int sub = lane & 7;
+    // values of unit `un` this lane owns: fp32 x (raw; xmode 1, 2) with the norm weights, or rebuilt
+    // from block-scaled digit records (xmode 0)
+    auto load_unit = [&](int un, float (&e)[MT][2][4], uint2 (&wv)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int b = un * KU + (lane >> 3) + 4 * h;
+            const int i = b * 32 + sub * 4;
+            if (xmode == 2) wv[h] = *reinterpret_cast<const uint2*>(nw + i);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                if (xmode == 0) {
+                    const uint32_t* rec = static_cast<const uint32_t*>(xin) + ((size_t)m * nblk + b) * XW;
+                    const uint32_t w0 = rec[sub], w1 = rec[8 + sub], w2 = rec[16 + sub];
+                    const float bs = __uint_as_float(rec[24]);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int X = ((int)(int8_t)(w0 >> (8 * k))) * 65536 + ((int)(int8_t)(w1 >> (8 * k))) * 256 + (int)(int8_t)(w2 >> (8 * k));
+                        e[m][h][k] = (float)X * bs;
+                    }
+                } else {
+                    const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(xin) + (size_t)m * K + i);
+                    e[m][h][0] = v.x; e[m][h][1] = v.y; e[m][h][2] = v.z; e[m][h][3] = v.w;
+                }
+            }
+        }
+    };
+    auto digits_unit = [&](int un, float (&e)[MT][2][4], const uint2 (&wv)[2], const float (&inv)[MT]) {
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            if (xmode == 2) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wv[h].x));
+                    const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wv[h].y));
+                    e[m][h][0] = e[m][h][0] * inv[m] * w01.x; e[m][h][1] = e[m][h][1] * inv[m] * w01.y;
+                    e[m][h][2] = e[m][h][2] * inv[m] * w23.x; e[m][h][3] = e[m][h][3] * inv[m] * w23.y;
+                }
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int k = 0; k < 4; k++) amax = fmaxf(amax, fabsf(e[m][h][k]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float sc = amax > 0.f ? (float)XFULL / amax : 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int b = un * KU + (lane >> 3) + 4 * h;
+                // Z = (X + 0x8080) ^ 0x8080: its bytes 0, 1, 2 are the balanced digits d2, d1, d0 of X
+                uint32_t Z[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) Z[k] = (uint32_t)(__float2int_rn(e[m][h][k] * sc) + 0x8080) ^ 0x8080u;
+                const uint32_t t01 = __byte_perm(Z[0], Z[1], 0x5140), t23 = __byte_perm(Z[2], Z[3], 0x5140);
+                const uint32_t u01 = __byte_perm(Z[0], Z[1], 0x0062), u23 = __byte_perm(Z[2], Z[3], 0x0062);
+                uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (sub & 3) * 2 + (sub >> 2);
+                dst[0] = __byte_perm(u01, u23, 0x5410);
+                dst[8] = __byte_perm(t01, t23, 0x7632);
+                dst[16] = __byte_perm(t01, t23, 0x5410);
+                dst[24] = 0u;
+            }
+            if (lane == 0) xs_all[m * nun + un] = amax / (float)XFULL;
+        }
+    };
+
+    float e0[MT][2][4];
+    uint2 wv0[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+    if (my_nun > 0 && !DBG_SKIP(0)) load_unit(un0, e0, wv0);          // the loads everything waits for go first
+#pragma unroll
+    for (int i = NPRE; i < NBUF; i++) issue_next(i);
     if (!DBG_SKIP(0)) {
-        const int sub = lane & 7;
         float inv[MT];
 #pragma unroll
         for (int m = 0; m < MT; m++) inv[m] = 1.f;
@@ -236,7 +308,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 #pragma unroll
             for (int m = 0; m < MT; m++) {
                 float ss = 0.f;
-                for (int i = lane * 4; i < my_nun * KU * 32; i += 128) {
+                if (my_nun > 0) {
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int k = 0; k < 4; k++) ss = fmaf(e0[m][h][k], e0[m][h][k], ss);
+                }
+                for (int i = KU * 32 + lane * 4; i < my_nun * KU * 32; i += 128) {
                     const float4 v = *reinterpret_cast<const float4*>(x + (size_t)m * K + (size_t)un0 * KU * 32 + i);
                     ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
                 }
@@ -253,61 +331,12 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 inv[m] = 1.0f / sqrtf(tot / (float)K + eps);
             }
         }
-        for (int uo = 0; uo < my_nun; uo++) {
-            const int un = un0 + uo;
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                float e[2][4];
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int b = un * KU + (lane >> 3) + 4 * h;
-                    if (xmode == 0) {                                // rebuild the values from block-scaled records
-                        const uint32_t* rec = static_cast<const uint32_t*>(xin) + ((size_t)m * nblk + b) * XW;
-                        const uint32_t w0 = rec[sub], w1 = rec[8 + sub], w2 = rec[16 + sub];
-                        const float bs = __uint_as_float(rec[24]);
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const int X = ((int)(int8_t)(w0 >> (8 * k))) * 65536 + ((int)(int8_t)(w1 >> (8 * k))) * 256 + (int)(int8_t)(w2 >> (8 * k));
-                            e[h][k] = (float)X * bs;
-                        }
-                    } else {
-                        const int i = b * 32 + sub * 4;
-                        const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(xin) + (size_t)m * K + i);
-                        e[h][0] = v.x; e[h][1] = v.y; e[h][2] = v.z; e[h][3] = v.w;
-                        if (xmode == 2) {
-                            const uint2 wr = *reinterpret_cast<const uint2*>(nw + i);
-                            const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
-                            const float2 w23 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
-                            e[h][0] = e[h][0] * inv[m] * w01.x; e[h][1] = e[h][1] * inv[m] * w01.y;
-                            e[h][2] = e[h][2] * inv[m] * w23.x; e[h][3] = e[h][3] * inv[m] * w23.y;
-                        }
-                    }
-                }
-                float amax = 0.f;
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-#pragma unroll
-                    for (int k = 0; k < 4; k++) amax = fmaxf(amax, fabsf(e[h][k]));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                const float sc = amax > 0.f ? (float)XFULL / amax : 0.f;
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int b = un * KU + (lane >> 3) + 4 * h;
-                    // Z = (X + 0x8080) ^ 0x8080: its bytes 0, 1, 2 are the balanced digits d2, d1, d0 of X
-                    uint32_t Z[4];
-#pragma unroll
-                    for (int k = 0; k < 4; k++) Z[k] = (uint32_t)(__float2int_rn(e[h][k] * sc) + 0x8080) ^ 0x8080u;
-                    const uint32_t t01 = __byte_perm(Z[0], Z[1], 0x5140), t23 = __byte_perm(Z[2], Z[3], 0x5140);
-                    const uint32_t u01 = __byte_perm(Z[0], Z[1], 0x0062), u23 = __byte_perm(Z[2], Z[3], 0x0062);
-                    uint32_t* dst = table + ((size_t)b * NC + m * 4) * 8 + (sub & 3) * 2 + (sub >> 2);
-                    dst[0] = __byte_perm(u01, u23, 0x5410);
-                    dst[8] = __byte_perm(t01, t23, 0x7632);
-                    dst[16] = __byte_perm(t01, t23, 0x5410);
-                    dst[24] = 0u;
-                }
-                if (lane == 0) xs_all[m * nun + un] = amax / (float)XFULL;
-            }
+        if (my_nun > 0) digits_unit(un0, e0, wv0, inv);
+        for (int uo = 1; uo < my_nun; uo++) {
+            float e[MT][2][4];
+            uint2 wv[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+            load_unit(un0 + uo, e, wv);
+            digits_unit(un0 + uo, e, wv, inv);
         }
     }
     __syncwarp();
@@ -530,12 +559,12 @@ size_t smem_bytes(int MT, int nblk, int nbuf) {
            (size_t)SW * nbuf * Cfg<TYPE, NW>::UNIT_BYTES;
 }
 
-template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, bool TP>
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, int NBUF, int NPRE, bool TP>
 int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
                const TpPeers& tpa, cudaStream_t st) {
     const int N = W->rows, K = W->cols;
     const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
-    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF, TP>;
+    auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF, NPRE, TP>;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
         CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -547,20 +576,26 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
                       W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr, xin, nw, eps, y, N, K, xmode, epi, tpa);
 }
 
-// Ring depth. Two buffers per warp measured fastest on the 11008 x 4096 case (6.35 us against
-// 6.68 and 7.17 with three and four): 32 KB of copies per SM are requested before the dependency
-// wait and a deeper ring only lengthens that prologue, which sits on the launch-to-launch path.
-constexpr int kNbuf = 2;
+// Ring depth 2, one unit of it requested before the dependency wait. Measured on the 11008 x 4096
+// case: (2 buffers, 1 before the wait) 6.43 us, (2, 2) 6.52, (3, 1) 6.56, (4, 1) 7.01: more copies in
+// flight do not help a loop that is issue-bound, and they get in the way of the loads of x.
+constexpr int kNbuf = 2, kNpre = 1;
 
 template <int TYPE, int NW>
 bool fits_smem(int MT, int nblk) { return smem_bytes<TYPE, NW>(MT, nblk, kNbuf) <= kSmemLimit; }
+
+template <int TYPE, int MT, int NW, bool QUIRK, bool BREG, bool TP>
+int launch_ring(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
+                const TpPeers& tpa, cudaStream_t st) {
+    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, kNbuf, kNpre, TP>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+}
 
 template <int TYPE, int MT, int NW, bool QUIRK, bool BREG>
 int launch_b(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, const __half* nw, float eps, float* y, int xmode, int epi,
              const TpPeers& tpa, cudaStream_t st) {
     CMLB_REQUIRE((fits_smem<TYPE, NW>(MT, W->cols / 32)), "cmlb200_gemv: K=%d does not fit the tensor-core decode kernel", W->cols);
-    if (NW == 1 && tpa.tp) return launch_cfg<TYPE, MT, 1, QUIRK, BREG, kNbuf, true>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
-    return launch_cfg<TYPE, MT, NW, QUIRK, BREG, kNbuf, false>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    if (NW == 1 && tpa.tp) return launch_ring<TYPE, MT, 1, QUIRK, BREG, true>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
+    return launch_ring<TYPE, MT, NW, QUIRK, BREG, false>(W, W2, xin, nw, eps, y, xmode, epi, tpa, st);
 }
 
 template <int TYPE, int MT, int NW, bool QUIRK>
