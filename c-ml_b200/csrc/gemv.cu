@@ -20,6 +20,11 @@ int cmlb200_gemv_mma_rows_(const cmlb200_qmat* W, int epi);
 int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                       const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
 
+// gemv_mma8.cu: the same for 5 to 8 rows of x per launch (Q4_0)
+bool cmlb200_gemv_mma8_ok_(const cmlb200_qmat* W, int epi);
+int cmlb200_gemv_mma8_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps, float* y, int M,
+                       int epi, cudaStream_t st);
+
 // gemv_tc.cu: tcgen05 integer tensor-core path over the tile-major copy of the weight
 int cmlb200_gemv_tc_(const cmlb200_qmat* W, const float* x, float* y, int M, int accumulate, cudaStream_t st);
 
@@ -256,6 +261,12 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
     const bool tc_ok = W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 && ((uintptr_t)y & 15) == 0;
+    if (W->type == CMLB200_Q4_0 && M > 4 && cmlb200_gemv_mma8_ok_(W, EPI)) {
+        // eight rows of x per launch of the plane-major mma.sync kernel: the weight is streamed once per eight rows
+        for (int m0 = 0; m0 < M && rc == 0; m0 += 8)
+            rc = cmlb200_gemv_mma8_(W, W2, x + (size_t)m0 * W->cols, nullptr, 0.f, y + (size_t)m0 * W->rows, M - m0 < 8 ? M - m0 : 8, EPI, st);
+        return rc;
+    }
     if (W->type != CMLB200_NF4 && M <= kMmaMaxM) {
         // the mma.sync kernel streams the weight once per launch: take it while two launches cover M
         // (or when there is no tile-major copy for the tcgen05 kernel)

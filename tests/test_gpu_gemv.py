@@ -186,3 +186,39 @@ def test_gemv_tensor_core_kernel_edges(pkg, synth, ob, orc, torch_dev, kind, N, 
         with np.errstate(over="ignore"):                  # exp(-g) may overflow to inf for the huge element: silu -> 0
             want = (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u
         assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv_swiglu, Wg, x, N, torch_dev, W2=Wu), want) <= TOL
+
+
+@pytest.mark.parametrize("N,K", [(40, 256), (301, 2816), (48, 4352), (9700, 4096), (333, 11008)])
+def test_gemv_eight_row_kernel(pkg, synth, ob, orc, torch_dev, N, K):
+    """Q4_0 with 5..8 rows of x per launch (plane-major digit columns): a single unit, idle warps in
+    the only phase, a second phase with one unit, more than four items per CTA, three phases; row
+    counts that are not a multiple of 16; all three epilogues, RMSNorm inside the launch, and M
+    above 8 (several launches)."""
+    rng = np.random.default_rng(13)
+    eps = 1e-5
+    Wg, Wgf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    Wu, Wuf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    nw = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    for M in (5, 6, 8, 13, 32):
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        x[0, :32] = 0.0                                   # an all-zero block
+        x[M - 1, 40] = 1e4                                # one huge element in a slice
+        g, u = ob.linear_nt(orc, x, Wgf), ob.linear_nt(orc, x, Wuf)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv, Wg, x, N, torch_dev), g) <= TOL
+        y0 = rng.standard_normal((M, N)).astype(np.float32)
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv_accum, Wg, x, N, torch_dev, y0=y0), y0 + g) <= TOL
+        with np.errstate(over="ignore"):
+            want = (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u
+        assert rel_err(_run(pkg, pkg.lib.cmlb200_gemv_swiglu, Wg, x, N, torch_dev, W2=Wu), want) <= TOL
+        if M > 8:
+            continue
+        x = (3.0 * rng.standard_normal((M, K))).astype(np.float32)
+        normed, nwf = np.zeros_like(x), nw.astype(np.float32)
+        orc.orc_rmsnorm(x.ctypes.data, nwf.ctypes.data, M, K, eps, normed.ctypes.data)
+        d_x, d_nw = to_dev(x, torch_dev), to_dev(nw.view(np.uint16), torch_dev)
+        d_y = torch.zeros((M, N), dtype=torch.float32, device=torch_dev)
+        g, u = ob.linear_nt(orc, normed, Wgf), ob.linear_nt(orc, normed, Wuf)
+        pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, None, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 0, stream_ptr()), "gemv_rmsnorm")
+        assert rel_err(d_y.cpu().numpy(), g) <= TOL
+        pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, Wu.q, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 2, stream_ptr()), "gemv_rmsnorm swiglu")
+        assert rel_err(d_y.cpu().numpy(), (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u) <= TOL
