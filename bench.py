@@ -257,7 +257,8 @@ def main():
     ap.add_argument("--copies", type=int, default=COPIES)
     ap.add_argument("--skip-llama", action="store_true", help="skip the LLaMA-7B decode leg")
     ap.add_argument("--profile-llama", action="store_true",
-                    help="small run for ncu: 4-layer LLaMA-7B-shaped model, 512-token prefill, 6 decode steps, batch 1")
+                    help="small run for ncu: 4-layer LLaMA-7B-shaped model, 512-token prefill, 6 decode steps")
+    ap.add_argument("--profile-batch", type=int, default=1, help="batch size of the --profile-llama run")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
     args = ap.parse_args()
@@ -288,7 +289,7 @@ def main():
 
     if args.profile_llama:
         cfg = dict(LLAMA_7B, layers=4)
-        print(json.dumps({"profile_run": True, **llama_leg(pkg, synth, new_tokens=6, batches=(1,), cfg=cfg, tag="llama7b_4layers")}))
+        print(json.dumps({"profile_run": True, **llama_leg(pkg, synth, new_tokens=6, batches=(args.profile_batch,), cfg=cfg, tag="llama7b_4layers")}))
         return
 
     rng = np.random.default_rng(1234 + rank)

@@ -261,7 +261,7 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
     const bool tc_ok = W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 && ((uintptr_t)y & 15) == 0;
-    if (W->type == CMLB200_Q4_0 && M > 4 && cmlb200_gemv_mma8_ok_(W, EPI)) {
+    if (W->type == CMLB200_Q4_0 && M > 2 && (M > 4 || cmlb200_gemv_mma_rows_(W, EPI) < M) && cmlb200_gemv_mma8_ok_(W, EPI)) {
         // eight rows of x per launch of the plane-major mma.sync kernel: the weight is streamed once per eight rows
         for (int m0 = 0; m0 < M && rc == 0; m0 += 8)
             rc = cmlb200_gemv_mma8_(W, W2, x + (size_t)m0 * W->cols, nullptr, 0.f, y + (size_t)m0 * W->rows, M - m0 < 8 ? M - m0 : 8, EPI, st);

@@ -26,6 +26,7 @@
 int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t st);
 // gemv_mma.cu: the tensor-core kernel for the shapes it takes
 bool cmlb200_gemv_mma_ok_(const cmlb200_qmat* W, int epi, int M);
+int cmlb200_gemv_mma_rows_(const cmlb200_qmat* W, int epi);
 int cmlb200_gemv_mma_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                       const uint32_t* xq, float* y, int M, int epi, cudaStream_t st);
 // gemv_mma8.cu: its sibling for 5 to 8 rows of x in one launch (Q4_0, fp32 x)
@@ -337,7 +338,8 @@ int cmlb200_x_digits_(const float* x, int M, int K, uint32_t* xq, cudaStream_t s
 // norm_w first when that is not NULL.
 int cmlb200_gemv_dp4a_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps,
                        const uint32_t* xq, float* y, int M, int epi, cudaStream_t st) {
-    if (!xq && M > 4 && M <= 8 && cmlb200_gemv_mma8_ok_(W, epi)) return cmlb200_gemv_mma8_(W, W2, x, norm_w, eps, y, M, epi, st);
+    // more rows of x than one launch of the 4-row kernel takes for this shape: the 8-row kernel streams the weight once
+    if (!xq && M > 2 && M <= 8 && (M > 4 || cmlb200_gemv_mma_rows_(W, epi) < M) && cmlb200_gemv_mma8_ok_(W, epi)) return cmlb200_gemv_mma8_(W, W2, x, norm_w, eps, y, M, epi, st);
     if (cmlb200_gemv_mma_ok_(W, epi, M)) return cmlb200_gemv_mma_(W, W2, xq ? nullptr : x, norm_w, eps, xq, y, M, epi, st);
     uint32_t* ws = nullptr;
     if (xq) x = nullptr;
