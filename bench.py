@@ -258,6 +258,7 @@ def main():
     ap.add_argument("--skip-llama", action="store_true", help="skip the LLaMA-7B decode leg")
     ap.add_argument("--profile-llama", action="store_true",
                     help="small run for ncu: 4-layer LLaMA-7B-shaped model, 512-token prefill, 6 decode steps")
+    ap.add_argument("--profile-m", type=int, default=1, choices=[1, 8, 32], help="rows of x of the --profile run")
     ap.add_argument("--profile-batch", type=int, default=1, help="batch size of the --profile-llama run")
     ap.add_argument("--profile", action="store_true",
                     help="small run for ncu: plain launches (no CUDA graph), one sweep per step, headline kernel only")
@@ -308,7 +309,7 @@ def main():
     x_dev = {M: x_host[M].to(dev) for M in x_host}
     y_dev = {M: torch.empty((M, N_ROWS), dtype=torch.float32, device=dev) for M in x_host}
     y_host = {M: torch.empty((M, N_ROWS), dtype=torch.float32).pin_memory() for M in x_host}
-    gemv = pkg.lib.cmlb200_gemv       # M <= 2: CUDA-core integer-dot kernel; M >= 3: tcgen05 kind::i8 kernel
+    gemv = pkg.lib.cmlb200_gemv       # M <= 4: gemv_mma_kernel; above (Q4_0): x_planes_kernel + gemv_mma8_kernel per 8 rows
 
     def sweep(M, sweeps=SWEEPS_PER_STEP):
         xp, yp = x_dev[M].data_ptr(), y_dev[M].data_ptr()
@@ -330,8 +331,8 @@ def main():
         return e0.elapsed_time(e1)
 
     if args.profile:
-        ms = timed_plain(1, args.steps, args.warmup)
-        print(json.dumps({"profile_run": True, "launches": (args.steps + args.warmup) * copies,
+        ms = timed_plain(args.profile_m, args.steps, args.warmup)
+        print(json.dumps({"profile_run": True, "M": args.profile_m, "launches": (args.steps + args.warmup) * copies,
                           "us_per_launch_including_host_overhead": 1e3 * ms / (args.steps * copies)}))
         return
 
