@@ -419,3 +419,7 @@ int cmlb200_gemv_mma8_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const floa
     const bool quirk = (W->flags & CMLB200_QMAT_SUBNORMAL_SCALES) || (W2 && (W2->flags & CMLB200_QMAT_SUBNORMAL_SCALES));
     return quirk ? launch8<true>(W, W2, x, nw, eps, y, M, epi, st) : launch8<false>(W, W2, x, nw, eps, y, M, epi, st);
 }
+
+extern "C" int cmlb200_gemv_batched_from_planes(const cmlb200_qmat* W) {
+    return W && W->qs && W->scales && W->rows > 0 && W->cols > 0 && cmlb200_gemv_mma8_ok_(W, EPI_STORE) && cmlb200_gemv_mma8_ok_(W, EPI_SWIGLU) ? 1 : 0;
+}

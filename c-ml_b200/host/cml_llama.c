@@ -318,7 +318,9 @@ static int upload_qmat(DevModel* d, int type, const uint8_t* blocks, int rows, i
     if (CML_DEV_FAIL(cmlb200_malloc(&out->qs, qb), "upload") || CML_DEV_FAIL(cmlb200_malloc(&out->scales, sb), "upload")) goto done;
     if (CML_DEV_FAIL(cmlb200_memcpy_h2d(out->qs, h_qs, qb, d->stream), "upload") ||
         CML_DEV_FAIL(cmlb200_memcpy_h2d(out->scales, h_sc, sb, d->stream), "upload")) goto done;
-    if (cols % 128 == 0 && d->max_batch > 2) {       /* the tensor-core decode path serves batches of 3..32 */
+    /* the tcgen05 decode path serves batches of 3..32 from a tile-major copy, unless the 8-row
+     * mma.sync kernel takes this weight from the planes (Q4_0, cols % 256 == 0) */
+    if (cols % 128 == 0 && d->max_batch > 2 && !cmlb200_gemv_batched_from_planes(out)) {
         const size_t tb = cmlb200_tiles_bytes(type, rows, cols);
         h_t = malloc(tb);
         if (!h_t) goto done;

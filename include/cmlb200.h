@@ -292,6 +292,12 @@ int cmlb200_tp_ar_status(const void* own_ws, int* status);
 int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x, float* d_h, int M, int tp, int rank, void* const* ws,
                               size_t max_floats, void* stream);
 int cmlb200_gemv_tp_fused_ok(const cmlb200_qmat* W, int M);
+/* 1 when cmlb200_gemv / _accum / _swiglu / _rmsnorm serve 3..32 rows of x for this weight from its
+ * planes layout alone (Q4_0, cols % 256 == 0: the 8-row mma.sync kernel), so that no tile-major
+ * copy (W->tiles) is needed for batched decode (replaces nothing in C-ML: its decode path is the
+ * fp32 matmul of src/ops/ir/execution.c:989-1052 for every batch size). Only type, rows, cols and
+ * the alignment of qs and scales are read. */
+int cmlb200_gemv_batched_from_planes(const cmlb200_qmat* W);
 int cmlb200_ipc_get_handle(void* d_ptr, void* handle64);
 int cmlb200_ipc_open(const void* handle64, void** d_ptr);
 int cmlb200_ipc_close(void* d_ptr);

@@ -45,7 +45,9 @@ assert np.array_equal(W1, F1[rank * (N1 // tp):(rank + 1) * (N1 // tp)])
 assert np.array_equal(W2, F2[:, rank * (N1 // tp):(rank + 1) * (N1 // tp)])
 dist.barrier()
 dist.destroy_process_group()
-print("rank", rank, "ok")
+import sys
+sys.stdout.write("rank %d ok\n" % rank)   # one write: the two ranks share a pipe
+sys.stdout.flush()
 '''
 
 
