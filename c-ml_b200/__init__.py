@@ -77,6 +77,14 @@ _sig("cmlb200_gemv_tiles_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_gemm_bf16", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemm_bf16_splitk", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemm_status", ci, C.POINTER(ci), ci)
+_sig("cmlb200_linear_nf4_general", ci, vp, vp, ci, ci, ci, ci, vp, ci, vp, vp)
+_sig("cmlb200_tp_ar_workspace_bytes", sz, sz)
+_sig("cmlb200_tp_allreduce_add", ci, vp, vp, sz, ci, ci, C.POINTER(vp), sz, vp)
+_sig("cmlb200_gemv_tp_allreduce", ci, C.POINTER(QMat), vp, vp, ci, ci, ci, C.POINTER(vp), sz, vp)
+_sig("cmlb200_gemv_tp_fused_ok", ci, C.POINTER(QMat), ci)
+_sig("cmlb200_tp_ar_status", ci, vp, C.POINTER(ci))
+_sig("cmlb200_tp_ar_status_reset", ci, vp)
+_sig("cmlb200_set_wait_limit", ci, ci)
 
 
 class CmlB200Error(RuntimeError):
@@ -244,6 +252,10 @@ _sig("cml_llama_set_options", ci, MP, ci, ci)
 _sig("cml_tp_shard_qblocks", ci, ci, vp, ci, ci, ci, ci, ci, vp)
 _sig("cml_llama_tp_unique_id", ci, vp)
 _sig("cml_llama_tp_init", ci, MP, vp, ci)
+_sig("cml_init", ci)
+_sig("cml_cleanup", ci)
+_sig("tensor_manual_seed", None, C.c_uint64)
+_sig("tensor_get_seed", C.c_uint64)
 REFERENCE_QUIRKS, KV_FP32, ALL_LOGITS_FP32 = 1, 2, 4
 
 

@@ -1,7 +1,10 @@
 """Builds lib/libcml_b200.so: every csrc/*.cu with nvcc for sm_100a, every csrc/*.c and
 host/*.c with gcc -std=c11, linked into one shared library that exports the cmlb200 C-ABI
-and the C-ML-compatible host API. Incremental (mtime based). No GPU is needed to build."""
+and the C-ML-compatible host API -- exactly the functions and variables the two public headers
+declare (a linker version script generated from include/*.h hides everything else).
+Incremental (mtime based). No GPU is needed to build."""
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -51,6 +54,28 @@ def _compile(src: Path, verbose: bool):
     return obj, (r.stdout + r.stderr)
 
 
+def public_symbols():
+    """Names the public headers declare: every function prototype and every `extern` variable."""
+    names = set()
+    for h in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        text = re.sub(r"//[^\n]*", "", text)
+        for m in re.finditer(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}()]*(?:\([^()]*\)[^;{}()]*)*\)\s*;", text):
+            if m.group(1) not in ("defined", "sizeof", "__attribute__"):
+                names.add(m.group(1))
+        for m in re.finditer(r"\bextern\s+(?!\"C\")[^;()]*?\b([A-Za-z_][A-Za-z0-9_]*)\s*(?:\[[^\]]*\])?\s*;", text):
+            names.add(m.group(1))
+    return sorted(names)
+
+
+def _version_script() -> Path:
+    path = OBJ / "exports.map"
+    body = "{\n  global:\n" + "".join(f"    {n};\n" for n in public_symbols()) + "  local: *;\n};\n"
+    if not path.exists() or path.read_text() != body:
+        path.write_text(body)
+    return path
+
+
 def build(verbose: bool = False) -> Path:
     OBJ.mkdir(parents=True, exist_ok=True)
     srcs = sorted((PKG / "csrc").glob("*.cu")) + sorted((PKG / "csrc").glob("*.c")) + sorted((PKG / "host").glob("*.c"))
@@ -61,8 +86,10 @@ def build(verbose: bool = False) -> Path:
         for _, log in results:
             if log:
                 print(log)
-    if _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-Xlinker", "-Bsymbolic", "-lcudart_static", "-ldl", "-lpthread", "-lrt", "-lm"]
+    vs = _version_script()
+    if _stale(LIB, objs + [vs]):
+        cmd = [_nvcc(), "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-Xlinker", "-Bsymbolic", "-Xlinker", f"--version-script={vs}",
+                                                                             "-lcudart_static", "-ldl", "-lpthread", "-lrt", "-lm"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")

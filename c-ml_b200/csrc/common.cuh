@@ -129,6 +129,7 @@ struct TpPeers {
     float* h;                        // the residual the sum is added to (GEMV epilogue channel)
     size_t max_floats;
     int tp, rank;                    // tp == 0: no all-reduce
+    int spin_limit;                  // polls of a peer's flag or packet before the launch gives up
 };
 __device__ __forceinline__ uint32_t* tpws_seq(uint8_t* ws, int ch) { return reinterpret_cast<uint32_t*>(ws + (ch ? 2048 : 0)); }
 __device__ __forceinline__ uint32_t* tpws_status(uint8_t* ws) { return reinterpret_cast<uint32_t*>(ws + 64); }
@@ -147,6 +148,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 constexpr int kTpSpinLimit = 1 << 22;
+// The limit in force for the next launches (cmlb200_set_wait_limit, or CMLB200_WAIT_LIMIT in the
+// environment, read once; kTpSpinLimit otherwise). Defined in tp_allreduce.cu.
+int cmlb_tp_spin_limit();
 // (value, sequence number) packets: one 8-byte store carries a result and the proof that it
 // belongs to this all-reduce, so the receiver polls the data words themselves and no fence or
 // separate flag is needed between ranks.
@@ -159,13 +163,29 @@ __device__ __forceinline__ uint2 ld_packet_sys(const uint2* p) {
     return v;
 }
 
+constexpr int kMaxDevices = 16;
+// Index of the current device (0 when the query fails); keys every per-device cache below and
+// in the launchers: function attributes, SM counts and scratch buffers belong to one device.
+static inline int cmlb_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return dev;
+}
 static inline int cmlb_num_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
+    static int sms[kMaxDevices] = {};
+    const int dev = cmlb_device_index();
+    if (!sms[dev]) {
+        if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
     }
-    return sms;
+    return sms[dev];
+}
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only: `done`
+// (one array per kernel instantiation, owned by the caller) remembers the largest size set on each.
+template <typename Kern>
+static inline cudaError_t cmlb_ensure_smem(Kern kern, size_t bytes, size_t (&done)[kMaxDevices]) {
+    const int dev = cmlb_device_index();
+    if (bytes <= done[dev]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) done[dev] = bytes;
+    return e;
 }

@@ -3,6 +3,12 @@
 //   Q8_0: y = (float)q * d              (src/core/gguf_quant.c:114-125)
 //   Q4_0: y = (float)(nibble - 8) * d   (src/core/gguf_quant.c:66-82)
 //   NF4 : y = TABLE[idx] * absmax       (src/core/quantization.c:349-366)
+//   Q4_1: y = (float)nibble * d + m                       (src/core/gguf_quant.c:90-112)
+//   Q4_K: y = (float)q4 * (d * sc) - dmin * mn            (src/core/gguf_quant.c:151-196)
+//   Q5_K: y = (float)q5 * (d * sc) - dmin * mn            (src/core/gguf_quant.c:211-270)
+//   Q6_K: y = d * (float)scale8 * (float)(q6 - 32)        (src/core/gguf_quant.c:283-311)
+//   (every product above is exact in fp32 -- at most 24 significant bits -- so contracting a
+//   multiply-add into one instruction cannot change a result bit)
 // fp16 scales widen through cml_half_to_float (common.cuh), which reproduces C-ML's
 // fp16_to_fp32 (src/core/gguf_quant.c:14-58) bit for bit, its subnormal quirk included.
 #include "common.cuh"
@@ -29,6 +35,55 @@ __global__ void dequant_blocks_kernel(const uint8_t* __restrict__ blocks, float*
             const uint8_t byte = p[2 + (j & 15)];
             const int nib = (j < 16) ? (byte & 15) : (byte >> 4);
             dst[e] = (float)(nib - 8) * d;
+        }
+    }
+}
+
+// The other block types C-ML reads (GGUF ids 3, 12, 13, 14), element by element in C-ML's own
+// layout: Q4_K / Q5_K keep each 32-element sub-block in 16 consecutive bytes (low nibble =
+// element k, high nibble = element k + 16 of the sub-block), which is C-ML's definition
+// (src/core/gguf_quant.c:174-187), not ggml's 64-element interleave.
+__device__ __forceinline__ void kquant_scale_min(const uint8_t* sc_raw, int i, int& sc, int& mn) {
+    if (i < 4) { sc = sc_raw[i] & 0x3F; mn = sc_raw[i + 4] & 0x3F; }
+    else {
+        const int j = i - 4;
+        sc = (sc_raw[j + 8] & 0x0F) | ((sc_raw[j] >> 6) << 4);
+        mn = (sc_raw[j + 8] >> 4) | ((sc_raw[j + 4] >> 6) << 4);
+    }
+}
+
+template <int GTYPE>
+__global__ void dequant_other_kernel(const uint8_t* __restrict__ blocks, float* __restrict__ dst, size_t numel) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < numel; e += stride) {
+        if (GTYPE == 3) {                                  // Q4_1: d, m, 16 bytes
+            const uint8_t* p = blocks + (e >> 5) * 20;
+            const int j = (int)(e & 31);
+            const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(p));
+            const float m = half_bits_to_float(*reinterpret_cast<const uint16_t*>(p + 2));
+            const uint8_t byte = p[4 + (j & 15)];
+            dst[e] = (float)((j < 16) ? (byte & 15) : (byte >> 4)) * d + m;
+        } else if (GTYPE == 12 || GTYPE == 13) {           // Q4_K / Q5_K: d, dmin, scales[12], (qh[32],) qs[128]
+            const uint8_t* p = blocks + (e >> 8) * (GTYPE == 12 ? 144 : 176);
+            const int r = (int)(e & 255), i = r >> 5, k = r & 31;
+            const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(p));
+            const float dmin = half_bits_to_float(*reinterpret_cast<const uint16_t*>(p + 2));
+            int sc, mn;
+            kquant_scale_min(p + 4, i, sc, mn);
+            const uint8_t* qs = p + (GTYPE == 12 ? 16 : 48);
+            const uint8_t byte = qs[i * 16 + (k & 15)];
+            int q = (k < 16) ? (byte & 15) : (byte >> 4);
+            if (GTYPE == 13) q |= ((p[16 + (r >> 3)] >> (r & 7)) & 1) << 4;
+            const float scale = d * (float)sc, mnv = dmin * (float)mn;
+            dst[e] = (float)q * scale - mnv;
+        } else {                                           // Q6_K: ql[128], qh[64], scales[16], d
+            const uint8_t* p = blocks + (e >> 8) * 210;
+            const int r = (int)(e & 255);
+            const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(p + 208));
+            const int low4 = (r & 1) ? (p[r >> 1] >> 4) : (p[r >> 1] & 15);
+            const int high2 = (p[128 + (r >> 2)] >> (2 * (r & 3))) & 3;
+            const float sc = (float)(int)(int8_t)p[192 + (r >> 4)];
+            dst[e] = d * sc * (float)((low4 | (high2 << 4)) - 32);
         }
     }
 }
@@ -131,10 +186,18 @@ inline int grid_for(size_t work, int threads) {
 
 extern "C" int cmlb200_gguf_dequantize(int type, const void* d_blocks, float* d_dst, size_t numel, void* stream) {
     CMLB_REQUIRE(d_blocks && d_dst && numel != 0, "cmlb200_gguf_dequantize: NULL pointer or numel == 0");
-    CMLB_REQUIRE(type == CMLB200_Q4_0 || type == CMLB200_Q8_0, "cmlb200_gguf_dequantize: unsupported type %d", type);
-    CMLB_REQUIRE(numel % 32 == 0, "cmlb200_gguf_dequantize: numel must be a multiple of the block size 32");
+    CMLB_REQUIRE(type == CMLB200_Q4_0 || type == CMLB200_Q8_0 || type == 3 || type == 12 || type == 13 || type == 14,
+                 "cmlb200_gguf_dequantize: unsupported type %d", type);
+    const size_t bs = (type == 12 || type == 13 || type == 14) ? 256 : 32;
+    CMLB_REQUIRE(numel % bs == 0, "cmlb200_gguf_dequantize: numel must be a multiple of the block size %zu", bs);
     const int threads = 256;
-    if (type == CMLB200_Q8_0)
+    const dim3 grid = grid_for(numel, threads);
+    cudaStream_t st = as_stream(stream);
+    if (type == 3) dequant_other_kernel<3><<<grid, threads, 0, st>>>((const uint8_t*)d_blocks, d_dst, numel);
+    else if (type == 12) dequant_other_kernel<12><<<grid, threads, 0, st>>>((const uint8_t*)d_blocks, d_dst, numel);
+    else if (type == 13) dequant_other_kernel<13><<<grid, threads, 0, st>>>((const uint8_t*)d_blocks, d_dst, numel);
+    else if (type == 14) dequant_other_kernel<14><<<grid, threads, 0, st>>>((const uint8_t*)d_blocks, d_dst, numel);
+    else if (type == CMLB200_Q8_0)
         dequant_blocks_kernel<CMLB200_Q8_0><<<grid_for(numel, threads), threads, 0, as_stream(stream)>>>(
             (const uint8_t*)d_blocks, d_dst, numel);
     else

@@ -211,7 +211,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * MT;
-    const int total_kb = K / BK;
+    const int total_kb = (K + BK - 1) / BK;          // K % 64 == 32: the last slab's upper half is zero
     const int kb_begin = blockIdx.z * kb_per_split;
     const int kb_end = min(total_kb, kb_begin + kb_per_split);
     const int nkb = kb_end - kb_begin;
@@ -294,10 +294,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         uint32_t* sc_ring = reinterpret_cast<uint32_t*>(smem + SmemLayout::sc_off);
         const float2* lut = reinterpret_cast<const float2*>(smem + SmemLayout::lut_off);
 
+        const int row_blocks = K / 32;
         auto prefetch = [&](int i) {
-            if (i < nkb) {
+            const size_t kblk = (size_t)(kb_begin + i) * 2 + h;       // 32-element block index in the row
+            if (i < nkb && kblk < (size_t)row_blocks) {
                 const int slot = i % RING;
-                const size_t kblk = (size_t)(kb_begin + i) * 2 + h;   // 32-element block index in the row
                 const uint32_t dst = smem_u32(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW);
                 cp_async16(dst, wrow + kblk * RAW);
                 if (RAW == 32) cp_async16(dst + 16, wrow + kblk * RAW + 16);
@@ -306,9 +307,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                     const size_t e = (size_t)n * K + kblk * 32;
                     cp_async4(sdst, reinterpret_cast<const float*>(scales) + e / (size_t)nf4_block);
                 } else {
-                    // two fp16 scales of this K slab share one aligned 32-bit word
-                    const size_t sidx = (size_t)n * (K / 32) + (size_t)(kb_begin + i) * 2;
-                    cp_async4(sdst, reinterpret_cast<const uint16_t*>(scales) + sidx);
+                    // the aligned 32-bit word that holds this block's fp16 scale (rows of an odd
+                    // number of blocks start on odd scale indices)
+                    const size_t sidx = (size_t)n * row_blocks + kblk;
+                    cp_async4(sdst, reinterpret_cast<const uint16_t*>(scales) + (sidx & ~(size_t)1));
                 }
             }
             cp_async_commit();
@@ -321,12 +323,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
             prefetch(i + RING - 1);
             cp_async_wait<RING - 1>();
             const int slot = i % RING;
-            float scale;
-            const uint32_t sw = sc_ring[slot * DQ_THREADS + t];
-            if (TYPE == CMLB200_NF4) scale = __uint_as_float(sw);
-            else scale = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
+            const size_t kblk = (size_t)(kb_begin + i) * 2 + h;
             uint4 out[4];
-            expand32<TYPE>(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW, scale, lut, out);
+            if (kblk < (size_t)row_blocks) {
+                float scale;
+                const uint32_t sw = sc_ring[slot * DQ_THREADS + t];
+                if (TYPE == CMLB200_NF4) scale = __uint_as_float(sw);
+                else scale = cml_half_to_float((uint16_t)((((size_t)n * row_blocks + kblk) & 1) ? (sw >> 16) : (sw & 0xFFFF)));
+                expand32<TYPE>(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW, scale, lut, out);
+            } else {                                          // past the end of the row: zeros meet the zero-filled activations
+#pragma unroll
+                for (int c = 0; c < 4; c++) out[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
 
             const int s = i % STAGES;
             const uint32_t ph = (i / STAGES) & 1;
@@ -430,7 +438,7 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
     CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (x must be 16-byte aligned, K*2 a multiple of 16)", (int)cr);
 
     const int gx = (N + BN - 1) / BN, gy = (M + MT - 1) / MT;
-    const int total_kb = K / BK;
+    const int total_kb = (K + BK - 1) / BK;
     int splits = 1;
     if (splits_forced > 0) splits = splits_forced;
     else {
@@ -461,11 +469,8 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
     }
     auto kern = gemm_kernel<TYPE>;
     const int smem = SmemLayout::total + 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_smem));
     kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, (const uint8_t*)W->qs, W->scales, (__nv_bfloat16*)y, partial,
                                                     M, N, K, MT, W->block, kb_per_split);
     CMLB_LAUNCH_CHECK();
@@ -482,7 +487,7 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
 int gemm_entry(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, float* ws, int splits, void* stream) {
     CMLB_REQUIRE(W && W->qs && W->scales && x && y, "cmlb200_gemm_bf16: NULL argument");
     CMLB_REQUIRE(M >= 1, "cmlb200_gemm_bf16: M=%d must be positive", M);
-    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % BK == 0, "cmlb200_gemm_bf16: cols=%d must be a positive multiple of 64", W->cols);
+    CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "cmlb200_gemm_bf16: cols=%d must be a positive multiple of 32", W->cols);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)W->scales & 3) == 0,
                  "cmlb200_gemm_bf16: x and the weight planes must be 16-byte aligned");
     cudaStream_t st = as_stream(stream);

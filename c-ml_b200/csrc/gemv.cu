@@ -207,11 +207,8 @@ int launch_gemv(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, f
     if ((size_t)kseg * MT > (size_t)kSegMaxFloats) kseg = (kSegMaxFloats / MT) / 64 * 64;
     const size_t smem = (size_t)kseg * MT * sizeof(float);
     auto kern = gemv_kernel<TYPE, MT, R, EPI>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSegMaxFloats * 4));
-        attr_done = true;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)kSegMaxFloats * 4, attr_smem));
     const int ngroups = (N + R - 1) / R;
     int grid = (ngroups + kWarps - 1) / kWarps;
     const int cap = cmlb_num_sms() * 4;
@@ -295,4 +292,41 @@ extern "C" int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float
 extern "C" int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const float* d_x, float* d_y,
                                    int M, void* stream) {
     return gemv_dispatch<EPI_SWIGLU>(Wg, Wu, d_x, d_y, M, stream, "cmlb200_gemv_swiglu");
+}
+
+// ---- NF4 linear for shapes outside the vectorised kernels (any in_features, any block size, blocks
+// that straddle rows): the quantized Linear of src/nn/qlora.c:264-317 element by element, one warp
+// per output value. Element e = n*K + k of the flat [out, in] weight is TABLE[nibble(e)] times
+// scales[min(e / block, num_scales - 1)], even e in the high nibble (src/core/quantization.c:349-366).
+namespace {
+__global__ void __launch_bounds__(256)
+nf4_linear_general_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales, int num_scales, int block,
+                          const float* __restrict__ x, float* __restrict__ y, int M, int N, int K) {
+    const int lane = threadIdx.x & 31;
+    const long long out = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (out >= (long long)M * N) return;
+    const int m = (int)(out / N), n = (int)(out % N);
+    float s = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const size_t e = (size_t)n * K + k;
+        const uint8_t b = packed[e >> 1];
+        const int idx = (e & 1) ? (b & 15) : (b >> 4);
+        size_t bi = e / (size_t)block;
+        if (bi >= (size_t)num_scales) bi = (size_t)num_scales - 1;
+        s = fmaf(x[(size_t)m * K + k], kNF4[idx] * scales[bi], s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) y[out] = s;
+}
+}  // namespace
+
+extern "C" int cmlb200_linear_nf4_general(const uint8_t* d_packed, const float* d_scales, int num_scales, int block, int rows, int cols,
+                                          const float* d_x, int M, float* d_y, void* stream) {
+    CMLB_REQUIRE(d_packed && d_scales && d_x && d_y, "cmlb200_linear_nf4_general: NULL argument");
+    CMLB_REQUIRE(num_scales > 0 && block > 0 && rows > 0 && cols > 0 && M > 0, "cmlb200_linear_nf4_general: bad shape (rows=%d cols=%d M=%d block=%d)", rows, cols, M, block);
+    const long long outs = (long long)M * rows;
+    nf4_linear_general_kernel<<<(unsigned)((outs + 7) / 8), 256, 0, as_stream(stream)>>>(d_packed, d_scales, num_scales, block, d_x, d_y, M, rows, cols);
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
 }

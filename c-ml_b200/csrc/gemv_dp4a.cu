@@ -274,11 +274,8 @@ int launch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const uint32_t* xq, fl
     const size_t smem = (size_t)(K / 32) * MT * XW * sizeof(uint32_t);
     CMLB_REQUIRE(smem <= 200 * 1024, "cmlb200_gemv: K=%d too large for the shared-memory activation digits", K);
     auto kern = gemv_dp4a_kernel<TYPE, MT, R, U, EPI, QUIRK>;
-    static size_t attr_smem = 0;
-    if (smem > 48 * 1024 && smem > attr_smem) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    if (smem > 48 * 1024) CMLB_CUDA(cmlb_ensure_smem(kern, smem, attr_smem));
     // One group of R rows per warp while that keeps the grid within ~8 CTAs per SM; beyond
     // that, more rows per warp (a multiple of R).
     int rows_per_warp = R;

@@ -45,28 +45,6 @@ constexpr int XW = kXqWords;
 __host__ __device__ constexpr int flush_batch(int nw, int mt) { return (void)nw, (void)mt, 4; }
 constexpr int XFULL = kXqFull - 1;     // |X| <= XFULL + 1 after rounding, which still splits into int8 digits
 
-#ifdef CMLB200_TRACE
-// Diagnostic build only: per CTA and launch, global-timer stamps at kernel entry, after the
-// dependency wait, after the digits are in place and at exit.
-__device__ unsigned long long g_trace[16][160][4];
-__device__ unsigned int g_trace_cnt[160];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE_SLOT() unsigned tr_slot = 0; if (threadIdx.x == 0) { tr_slot = atomicAdd(&g_trace_cnt[blockIdx.x], 1u) % 16; }
-#define TRACE(k) if (threadIdx.x == 0) g_trace[tr_slot][blockIdx.x][k] = gtime();
-__device__ int g_dbg_mask;     // parts of the kernel to leave out when counting instructions
-#define DBG_MASK() const int dbg_mask = g_dbg_mask;
-#define DBG_SKIP(b) (dbg_mask & (1 << (b)))
-#else
-#define TRACE_SLOT()
-#define TRACE(k)
-#define DBG_MASK()
-#define DBG_SKIP(b) false
-#endif
-
 // One unit = 16 rows x KU blocks of one weight.
 template <int TYPE, int NW>
 struct Cfg {
@@ -107,9 +85,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
     const uint32_t ring0 = smem_u32(ring);
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    TRACE_SLOT();
-    TRACE(0);
-    DBG_MASK();
 
     // this warp's units of K and this CTA's items
     const int q = nun / SW, rem = nun % SW;
@@ -136,7 +111,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         sptr[a] = (a ? scales2 : scales) + ((size_t)blockIdx.x * 16 + (lane & 15)) * nblk + (size_t)un0 * KU;
     }
     auto issue_next = [&](int buf) {
-        if (iss_it < my_items && my_nun > 0 && !DBG_SKIP(1)) {
+        if (iss_it < my_items && my_nun > 0) {
             const int row0 = ((int)blockIdx.x + iss_it * (int)gridDim.x) * 16;
             const uint32_t dst = ring0 + buf * C::UNIT_BYTES;
             if (row0 + 16 <= N) {
@@ -184,7 +159,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 #pragma unroll
     for (int i = 0; i < NPRE; i++) issue_next(i);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE(1);
     // tensor-parallel epilogue: sequence number of this all-reduce and the inbox buffer it uses
     const uint32_t tp_seq = TP ? tpws_seq(tpa.ws[tpa.rank], 1)[blockIdx.x] + 1 : 0u;
     const int tp_par = (int)(tp_seq & 1u);
@@ -259,10 +233,10 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
 
     float e0[MT][2][4];
     uint2 wv0[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-    if (my_nun > 0 && !DBG_SKIP(0)) load_unit(un0, e0, wv0);          // the loads everything waits for go first
+    if (my_nun > 0) load_unit(un0, e0, wv0);          // the loads everything waits for go first
 #pragma unroll
     for (int i = NPRE; i < NBUF; i++) issue_next(i);
-    if (!DBG_SKIP(0)) {
+    {
         float inv[MT];
 #pragma unroll
         for (int m = 0; m < MT; m++) inv[m] = 1.f;
@@ -303,7 +277,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         }
     }
     __syncwarp();
-    TRACE(2);
 
     // B fragment of block b for MMA j and this thread: column 8j+g (n index), words t and 4+t of the plane
     auto load_b = [&](int b, int j, uint32_t& b0, uint32_t& b1) {
@@ -415,7 +388,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
             float xs[NM];
 #pragma unroll
             for (int j = 0; j < NM; j++) xs[j] = BREG ? xs_reg[j] : xs_all[min(2 * j + xm0, MT - 1) * nun + un0 + o];
-            if (!DBG_SKIP(3)) {
+            {
 #pragma unroll
                 for (int a = 0; a < NW; a++) {
                     float au[NM][2];
@@ -434,7 +407,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         }
 
         // ---- combine the column pairs (t even: d0*256 + d1, t odd: d2*256) and park the item
-        if (DBG_SKIP(2)) continue;
         const int slot = it % FB;
 #pragma unroll
         for (int a = 0; a < NW; a++)
@@ -467,7 +439,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
                 for (int qr = 0; qr < tpa.tp && ok; qr++) {
                     const uint2* src = reinterpret_cast<const uint2*>(tpws_inbox(mine, 1, tp_par, qr, tpa.max_floats)) + at;
                     uint2 pkt = ld_packet_sys(src);
-                    for (int i = 0; pkt.y != tp_seq && i < kTpSpinLimit; i++) pkt = ld_packet_sys(src);
+                    for (int i = 0; pkt.y != tp_seq && i < tpa.spin_limit; i++) pkt = ld_packet_sys(src);
                     if (pkt.y != tp_seq) { ok = false; atomicExch(tpws_status(mine), 1u + qr); }
                     v += __uint_as_float(pkt.x);
                 }
@@ -477,26 +449,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sca
         __syncthreads();
         if (threadIdx.x == 0) tpws_seq(mine, 1)[blockIdx.x] = tp_seq;
     }
-    TRACE(3);
 }
-
-#ifdef CMLB200_TRACE
-}  // namespace
-extern "C" int cmlb200_trace_read_(void* out, int reset) {
-    CMLB_CUDA(cudaDeviceSynchronize());
-    CMLB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
-    if (reset) {
-        static unsigned int zero[160] = {};
-        CMLB_CUDA(cudaMemcpyToSymbol(g_trace_cnt, zero, sizeof(zero)));
-    }
-    return CMLB200_OK;
-}
-extern "C" int cmlb200_dbg_mask_(int mask) {
-    CMLB_CUDA(cudaMemcpyToSymbol(g_dbg_mask, &mask, sizeof(int)));
-    return CMLB200_OK;
-}
-namespace {
-#endif
 
 template <typename Kern, typename... Args>
 int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -528,11 +481,8 @@ int launch_cfg(const cmlb200_qmat* W, const cmlb200_qmat* W2, const void* xin, c
     const int N = W->rows, K = W->cols;
     const size_t smem = smem_bytes<TYPE, NW>(MT, K / 32, NBUF);
     auto kern = gemv_mma_kernel<TYPE, MT, NW, QUIRK, BREG, NBUF, NPRE, TP>;
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    CMLB_CUDA(cmlb_ensure_smem(kern, smem, attr_smem));
     const int grid = min(cmlb_num_sms(), (N + 15) / 16);
     return launch_pdl(kern, dim3(grid), dim3(SW * 32), smem, st, (const uint8_t*)W->qs, (const uint16_t*)W->scales,
                       W2 ? (const uint8_t*)W2->qs : (const uint8_t*)nullptr,
@@ -663,6 +613,7 @@ extern "C" int cmlb200_gemv_tp_allreduce(const cmlb200_qmat* W, const float* d_x
         p.ws[r] = static_cast<uint8_t*>(ws[r]);
     }
     p.tp = tp; p.rank = rank; p.max_floats = max_floats; p.h = d_h;
+    p.spin_limit = cmlb_tp_spin_limit();
     return run_all(W, nullptr, d_x, nullptr, 0.f, nullptr, d_h, M, EPI_STORE, p, as_stream(stream));
 }
 

@@ -51,23 +51,6 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     return v;
 }
 
-#ifdef CMLB200_TRACE
-// Diagnostic build only: per CTA and launch, global-timer stamps at kernel entry, after the
-// dependency wait, after the digits of the first phase and at exit.
-__device__ unsigned long long g_trace8[16][160][4];
-__device__ unsigned int g_trace8_cnt[160];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE_SLOT() unsigned tr_slot = 0; if (threadIdx.x == 0) { tr_slot = atomicAdd(&g_trace8_cnt[blockIdx.x], 1u) % 16; }
-#define TRACE(k) if (threadIdx.x == 0) g_trace8[tr_slot][blockIdx.x][k] = gtime();
-#else
-#define TRACE_SLOT()
-#define TRACE(k)
-#endif
-
 // Digit planes of M <= 8 rows of x for the kernel below. grid = (M, ceil(units / 16)); CTA (m, c)
 // handles units 16c .. 16c+15 of row m, one warp each. planes: [unit][block 8][plane 3][row 8][8 words],
 // word 2t of a (plane, row) = k 4t..4t+3, word 2t+1 = k 16+4t..: thread (g, t) of the MMA reads its B
@@ -160,8 +143,6 @@ gemv_mma8_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sc
     const uint32_t ring0 = smem_u32(ring);
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    TRACE_SLOT();
-    TRACE(0);
 
     const int rgs = (N + 15) / 16;                                   // row groups of 16 weight rows
     const int my_rgs = ((int)blockIdx.x < rgs) ? (rgs - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -211,7 +192,6 @@ gemv_mma8_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sc
 #pragma unroll
     for (int i = 0; i < NPRE; i++) issue_next(i);                    // weights do not depend on the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TRACE(1);
     if (warp < min(nun, SW)) load_b(0);                              // the loads everything waits for go first
 #pragma unroll
     for (int i = NPRE; i < NBUF; i++) issue_next(i);
@@ -286,7 +266,6 @@ gemv_mma8_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sc
     for (int ph = 0; ph < nph; ph++) {
         const bool active = ph * SW + warp < nun;
         if (active && ph > 0) load_b(ph);
-        if (ph == 0) { TRACE(2); }
         for (int li = 0; li < my_items; li++) {
             const int slot = li % FB;
             if (active) {
@@ -308,22 +287,7 @@ gemv_mma8_kernel(const uint8_t* __restrict__ qs, const uint16_t* __restrict__ sc
         }
     }
     cp_async_wait<0>();
-    TRACE(3);
 }
-
-#ifdef CMLB200_TRACE
-}  // namespace
-extern "C" int cmlb200_trace8_read_(void* out, int reset) {
-    CMLB_CUDA(cudaDeviceSynchronize());
-    CMLB_CUDA(cudaMemcpyFromSymbol(out, g_trace8, sizeof(g_trace8)));
-    if (reset) {
-        static unsigned int zero[160] = {};
-        CMLB_CUDA(cudaMemcpyToSymbol(g_trace8_cnt, zero, sizeof(zero)));
-    }
-    return CMLB200_OK;
-}
-namespace {
-#endif
 
 template <typename Kern, typename... Args>
 int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -390,11 +354,8 @@ int launch8(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const
     if (rc) return rc;
     const Plan p = plan_of(W, nwi);
     auto kern = gemv_mma8_kernel<QUIRK>;
-    static size_t attr_smem = 0;
-    if (p.smem > attr_smem) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
-        attr_smem = p.smem;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    CMLB_CUDA(cmlb_ensure_smem(kern, p.smem, attr_smem));
     return launch_pdl(kern, dim3(p.grid), dim3(SW * 32), p.smem, st, (const uint8_t*)W->qs, (const uint16_t*)W->scales,
                       W2 ? (const uint8_t*)W2->qs : (const uint8_t*)nullptr, W2 ? (const uint16_t*)W2->scales : (const uint16_t*)nullptr,
                       (const uint2*)sc->planes, (const float*)sc->xs, y, W->rows, K, M, nwi, epi, p.acc_items);

@@ -38,7 +38,6 @@
 #include "common.cuh"
 
 __device__ int g_tc_status = 0;   // 0 = ok; otherwise the code of the bounded wait that expired
-__device__ int g_tc_where[4] = {0, 0, 0, 0};   // first expiry: code, CTA, stage index, parity waited for
 
 namespace {
 
@@ -83,9 +82,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     *abort_flag = code;
-    if (atomicCAS(&g_tc_status, 0, code) == 0) {
-        g_tc_where[0] = code; g_tc_where[1] = blockIdx.x; g_tc_where[2] = stage; g_tc_where[3] = (int)parity;
-    }
+    (void)stage;
+    atomicCAS(&g_tc_status, 0, code);
     return false;
 }
 // one lane polls, the whole warp learns the verdict
@@ -549,11 +547,8 @@ int run_cfg(const cmlb200_qmat* W, const float* x, float* y, int M, int epi, Scr
     static_assert(MMAX <= 10, "scratch slots hold at most 10 activation rows");
     auto kern = gemv_tc_kernel<TYPE, NCOLS, BC, RS, AS, MMAX, INLINE>;
     const int smem = L::total + 128;
-    static bool attr_done = false;
-    if (!attr_done) {
-        CMLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
-    }
+    static size_t attr_smem[kMaxDevices] = {};
+    CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_smem));
     return launch_pdl(kern, dim3(grid), dim3(L::threads), (size_t)smem, st, (const uint8_t*)W->qs, (const uint8_t*)sc->pay, x, y,
                       sc->slots, sc->flags, W->rows, W->cols, M, total_stages, epi);
 }
@@ -670,13 +665,6 @@ extern "C" int cmlb200_gemv_tiles(const cmlb200_qmat* W, const float* d_x, float
     cudaStream_t st = as_stream(stream);
     if (W->type == CMLB200_Q8_0) return run_type<CMLB200_Q8_0>(W, d_x, d_y, M, accumulate ? EPI_ACCUM : EPI_STORE, st);
     return run_type<CMLB200_Q4_0>(W, d_x, d_y, M, accumulate ? EPI_ACCUM : EPI_STORE, st);
-}
-
-// Where the first bounded wait expired: {code, CTA, stage index, parity}. Diagnostic only.
-extern "C" int cmlb200_gemv_tiles_where_(int* out4) {
-    CMLB_CUDA(cudaDeviceSynchronize());
-    CMLB_CUDA(cudaMemcpyFromSymbol(out4, g_tc_where, 4 * sizeof(int)));
-    return CMLB200_OK;
 }
 
 extern "C" int cmlb200_gemv_tiles_status(int* status, int reset) {

@@ -19,13 +19,14 @@
 //
 // The workspace layout (one per rank, mapped into every other rank through CUDA IPC) is in
 // common.cuh; this file uses channel 0.
+#include <stdlib.h>
+#include <string.h>
 #include "common.cuh"
 
 namespace {
 
 constexpr int CTAS = kTpCtas;
 constexpr int MAX_TP = kTpMaxRanks;
-constexpr int SPIN_LIMIT = kTpSpinLimit;
 
 __global__ void __launch_bounds__(256)
 tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial, int n4, TpPeers peers) {
@@ -59,8 +60,8 @@ tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial
     if ((int)threadIdx.x < tp && (int)threadIdx.x != rank) {
         const uint32_t* f = tpws_flags(mine, 0, threadIdx.x) + c;
         int i = 0;
-        while ((int32_t)(ld_acquire_sys(f) - seq) < 0 && ++i < SPIN_LIMIT) {}
-        if (i >= SPIN_LIMIT) { ok = 0; atomicExch(tpws_status(mine), 1u + threadIdx.x); }
+        while ((int32_t)(ld_acquire_sys(f) - seq) < 0 && ++i < peers.spin_limit) {}
+        if (i >= peers.spin_limit) { ok = 0; atomicExch(tpws_status(mine), 1u + threadIdx.x); }
     }
     __syncthreads();
     if (threadIdx.x == 0) tpws_seq(mine, 0)[c] = seq;
@@ -101,6 +102,7 @@ extern "C" int cmlb200_tp_allreduce_add(float* d_h, const float* d_partial, size
         p.ws[r] = static_cast<uint8_t*>(ws[r]);
     }
     p.tp = tp; p.rank = rank; p.max_floats = max_floats; p.h = d_h;
+    p.spin_limit = cmlb_tp_spin_limit();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(CTAS);
     cfg.blockDim = dim3(256);
@@ -114,12 +116,33 @@ extern "C" int cmlb200_tp_allreduce_add(float* d_h, const float* d_partial, size
     return CMLB200_OK;
 }
 
-// Nonzero once a wait of the kernel above expired on this rank (1 + the peer it waited for).
+// Nonzero once a wait of the kernel above (or of the decode GEMV's all-reduce epilogue) expired
+// on this rank: 1 + the peer it waited for.
 extern "C" int cmlb200_tp_ar_status(const void* own_ws, int* status) {
     CMLB_REQUIRE(own_ws && status, "cmlb200_tp_ar_status: NULL argument");
     uint32_t v = 0;
     CMLB_CUDA(cudaMemcpy(&v, static_cast<const uint8_t*>(own_ws) + 64, sizeof v, cudaMemcpyDeviceToHost));
     *status = (int)v;
+    return CMLB200_OK;
+}
+extern "C" int cmlb200_tp_ar_status_reset(void* own_ws) {
+    CMLB_REQUIRE(own_ws, "cmlb200_tp_ar_status_reset: NULL argument");
+    CMLB_CUDA(cudaMemset(static_cast<uint8_t*>(own_ws) + 64, 0, sizeof(uint32_t)));
+    return CMLB200_OK;
+}
+
+namespace { int g_wait_limit = 0; }      // 0: not set yet
+int cmlb_tp_spin_limit() {
+    if (g_wait_limit <= 0) {
+        const char* e = getenv("CMLB200_WAIT_LIMIT");
+        const long v = e ? strtol(e, nullptr, 10) : 0;
+        g_wait_limit = (v > 0 && v <= kTpSpinLimit) ? (int)v : kTpSpinLimit;
+    }
+    return g_wait_limit;
+}
+extern "C" int cmlb200_set_wait_limit(int polls) {
+    CMLB_REQUIRE(polls >= 0 && polls <= kTpSpinLimit, "cmlb200_set_wait_limit: %d outside 0..%d", polls, kTpSpinLimit);
+    g_wait_limit = polls > 0 ? polls : kTpSpinLimit;
     return CMLB200_OK;
 }
 

@@ -49,11 +49,7 @@ int gguf_dequantize(GGUFTensorType type, const void* src, float* dst, size_t num
     if (!src || !dst || numel == 0) return -1;
     const int bs = gguf_quant_block_size(type);
     if (bs == 0 || numel % (size_t)bs != 0) return -1;
-    if (type != GGUF_TENSOR_Q4_0 && type != GGUF_TENSOR_Q8_0) {
-        LOG_ERROR("gguf_dequantize: block type %d has no device kernel on this path (Q4_0 and Q8_0 only)", (int)type);
-        return -1;
-    }
-    const size_t in_bytes = numel / 32 * gguf_quant_type_size(type);
+    const size_t in_bytes = numel / (size_t)bs * gguf_quant_type_size(type);
     void *d_in = NULL, *d_out = NULL;
     int rc = -1;
     if (CML_DEV_FAIL(cmlb200_malloc(&d_in, in_bytes), "gguf_dequantize")) goto done;

@@ -14,6 +14,7 @@
  * partial outputs of the row-parallel projections are summed with an NCCL all-reduce.
  */
 #include <math.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -61,11 +62,18 @@ typedef struct DevModel {
     int graph_batch, graph_splits;
 } DevModel;
 
+/* Side table of device state, keyed by the public model's address. The list itself is guarded
+ * (threads may create and free different models concurrently); one model is still driven by one
+ * thread at a time, as in C-ML. */
 static DevModel* g_models = NULL;
+static pthread_mutex_t g_models_mu = PTHREAD_MUTEX_INITIALIZER;
 
 static DevModel* dm_find(const CMLLLaMAModel* m) {
-    for (DevModel* d = g_models; d; d = d->next) if (d->key == m) return d;
-    return NULL;
+    pthread_mutex_lock(&g_models_mu);
+    DevModel* d = g_models;
+    while (d && d->key != m) d = d->next;
+    pthread_mutex_unlock(&g_models_mu);
+    return d;
 }
 
 /* ---- configuration presets (src/nn/llama.c:14-69) ------------------------------------------- */
@@ -150,11 +158,12 @@ static void dm_destroy(DevModel* d) {
 
 void cml_llama_free(CMLLLaMAModel* model) {
     if (!model) return;
-    DevModel** pp = &g_models;
-    while (*pp) {
-        if ((*pp)->key == model) { DevModel* d = *pp; *pp = d->next; dm_destroy(d); break; }
-        pp = &(*pp)->next;
-    }
+    DevModel* gone = NULL;
+    pthread_mutex_lock(&g_models_mu);
+    for (DevModel** pp = &g_models; *pp; pp = &(*pp)->next)
+        if ((*pp)->key == model) { gone = *pp; *pp = gone->next; break; }
+    pthread_mutex_unlock(&g_models_mu);
+    dm_destroy(gone);
     if (model->layers) {
         for (int i = 0; i < model->num_layers; i++) {
             CMLLLaMALayer* l = model->layers[i];
@@ -184,8 +193,10 @@ static DevModel* dm_get(CMLLLaMAModel* m) {
     d->tp = m->config.tensor_parallel_size > 1 ? m->config.tensor_parallel_size : 1;
     d->rank = d->tp > 1 ? m->config.tensor_parallel_rank : 0;
     d->device = -1;
+    pthread_mutex_lock(&g_models_mu);
     d->next = g_models;
     g_models = d;
+    pthread_mutex_unlock(&g_models_mu);
     return d;
 }
 
@@ -546,6 +557,27 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
 }
 
 /* ---- forward ------------------------------------------------------------------------------------ */
+/* After the stream has drained: did a bounded device-side wait give up? (tcgen05 pipelines, the
+ * stream-K fix-up, and the peer-memory all-reduce, whose launch then left the residual without the
+ * projection.) Returns -1 and logs; a failed all-reduce also retires the peer path, because the
+ * ranks' sequence counters may no longer agree, and NCCL serves every size from then on. */
+static int dm_check_waits(DevModel* d, const char* who) {
+    int st = 0;
+    if (cmlb200_gemm_status(&st, 1) == CMLB200_OK && st == 0) cmlb200_gemv_tiles_status(&st, 1);
+    if (st) { LOG_ERROR("%s: a bounded device-side wait expired (code %d)", who, st); return -1; }
+    if (d->ar_ok && d->ar_ws[d->rank]) {
+        if (cmlb200_tp_ar_status(d->ar_ws[d->rank], &st) != CMLB200_OK) { LOG_ERROR("%s: %s", who, cmlb200_last_error()); return -1; }
+        if (st) {
+            LOG_ERROR("%s: the all-reduce gave up waiting for rank %d; the result is incomplete (falling back to NCCL)", who, st - 1);
+            cmlb200_tp_ar_status_reset(d->ar_ws[d->rank]);
+            d->ar_ok = 0;
+            if (d->graph) { cmlb200_graph_destroy(d->graph); d->graph = NULL; }
+            return -1;
+        }
+    }
+    return 0;
+}
+
 static int model_ready(const CMLLLaMAModel* m, const DevModel* d) {
     if (!d || !d->embed || !d->fnorm || !d->lm_head.qs) return 0;
     for (int i = 0; i < m->num_layers; i++) {
@@ -735,9 +767,7 @@ static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows,
         tensor_free(out);
         return NULL;
     }
-    int st = 0;
-    if (cmlb200_gemm_status(&st, 1) == CMLB200_OK && st == 0) cmlb200_gemv_tiles_status(&st, 1);
-    if (st) { LOG_ERROR("%s: a bounded device-side wait expired (code %d)", who, st); tensor_free(out); return NULL; }
+    if (dm_check_waits(d, who)) { tensor_free(out); return NULL; }
     if (mode == 0) d->h_cur[seq] += rows;
     else for (int b = 0; b < rows; b++) d->h_cur[b] += 1;
     model->current_seq_len = d->h_cur[0];
@@ -817,9 +847,7 @@ int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int b
     DEV(cmlb200_stream_sync(st));
     cmlb200_event_destroy(e0);
     cmlb200_event_destroy(e1);
-    int stt = 0;
-    if (cmlb200_gemm_status(&stt, 1) == CMLB200_OK && stt == 0) cmlb200_gemv_tiles_status(&stt, 1);
-    if (stt) { LOG_ERROR("cml_llama_decode_greedy: a bounded device-side wait expired (code %d)", stt); return -1; }
+    if (dm_check_waits(d, "cml_llama_decode_greedy")) return -1;
     if (elapsed_ms) *elapsed_ms = ms;
     for (int b = 0; b < batch; b++) d->h_cur[b] += steps;
     model->current_seq_len = d->h_cur[0];
@@ -876,12 +904,67 @@ int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config) {
     return id;
 }
 
+/* C-ML's tokenizer entry points (include/nn/llm_ops.h:147-149): weak references, so they resolve to
+ * the host program's when it links C-ML's src/nn/llm_ops.c and to NULL otherwise. */
+extern int* cml_tokenizer_encode(CMLTokenizer* tok, const char* text, int* num_tokens) __attribute__((weak));
+extern char* cml_tokenizer_decode(CMLTokenizer* tok, const int* tokens, int num_tokens) __attribute__((weak));
+static CMLTokenizerEncodeFn g_tok_encode = NULL;
+static CMLTokenizerDecodeFn g_tok_decode = NULL;
+
+void cml_llama_set_tokenizer_functions(CMLTokenizerEncodeFn encode, CMLTokenizerDecodeFn decode) {
+    g_tok_encode = encode;
+    g_tok_decode = decode;
+}
+
 CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config) {
     if (!model || !prompt || !config) { LOG_ERROR("cml_llama_generate: NULL argument"); return NULL; }
-    /* As in C-ML (src/nn/llama.c:754-762) text generation needs model->tokenizer; the GGUF loader
-     * does not create one. Token-id callers use cml_llama_forward / cml_llama_decode_greedy. */
-    LOG_ERROR("cml_llama_generate: no tokenizer attached to the model");
-    return NULL;
+    if (!model->weights_loaded) { LOG_ERROR("cml_llama_generate: weights not loaded"); return NULL; }
+    const CMLTokenizerEncodeFn enc = g_tok_encode ? g_tok_encode : cml_tokenizer_encode;
+    const CMLTokenizerDecodeFn dec = g_tok_decode ? g_tok_decode : cml_tokenizer_decode;
+    int n_prompt = 0;
+    int* ids = (model->tokenizer && enc) ? enc(model->tokenizer, prompt, &n_prompt) : NULL;
+    if (!ids || n_prompt <= 0) {                     /* no tokenizer: the same failure as src/nn/llama.c:759-763 */
+        LOG_ERROR("cml_llama_generate: tokenization failed or empty prompt");
+        free(ids);
+        return NULL;
+    }
+    const int budget = config->max_new_tokens > 0 ? config->max_new_tokens : 0;
+    CMLGenerationResult* res = (CMLGenerationResult*)calloc(1, sizeof *res);
+    if (res) res->token_ids = (int*)malloc((size_t)(n_prompt + budget) * sizeof(int));
+    if (!res || !res->token_ids) { free(ids); free(res); return NULL; }
+    memcpy(res->token_ids, ids, (size_t)n_prompt * sizeof(int));
+    res->num_tokens = n_prompt;
+
+    cml_llama_reset(model);
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    Tensor* logits = cml_llama_forward(model, ids, n_prompt);       /* prefill; the sampler reads the last row */
+    free(ids);
+    if (!logits) {
+        LOG_ERROR("cml_llama_generate: prefill forward failed");
+        cml_generation_result_free(res);
+        return NULL;
+    }
+    for (int step = 0; step < budget; step++) {
+        int next = cml_llama_sample_token(logits, config);
+        tensor_free(logits);
+        logits = NULL;
+        if (next < 0) { LOG_ERROR("cml_llama_generate: sampling failed at step %d", step); break; }
+        res->token_ids[res->num_tokens++] = next;
+        if (next == config->eos_token_id) break;
+        if (model->current_seq_len >= model->config.max_seq_len) { LOG_WARNING("cml_llama_generate: max sequence length reached"); break; }
+        logits = cml_llama_forward(model, &next, 1);
+        if (!logits) { LOG_ERROR("cml_llama_generate: decode forward failed at step %d", step); break; }
+    }
+    tensor_free(logits);
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double ms = (double)(t1.tv_sec - t0.tv_sec) * 1e3 + (double)(t1.tv_nsec - t0.tv_nsec) / 1e6;
+    res->total_time_ms = (float)ms;
+    const int generated = res->num_tokens - n_prompt;
+    if (ms > 0.0) res->tokens_per_second = (float)(generated * 1e3 / ms);
+    res->text = dec ? dec(model->tokenizer, res->token_ids, res->num_tokens) : NULL;
+    LOG_INFO("Generation complete: %d tokens in %.1f ms (%.1f tok/s)", generated, res->total_time_ms, res->tokens_per_second);
+    return res;
 }
 
 void cml_generation_result_free(CMLGenerationResult* result) {
@@ -923,9 +1006,7 @@ Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tens
              !CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->h, bytes, d->stream), who);
     /* put the model's own position back whatever happened */
     if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &saved, sizeof(int), d->stream), who) || CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) ok = 0;
-    int st = 0;
-    if (cmlb200_gemm_status(&st, 1) == CMLB200_OK && st == 0) cmlb200_gemv_tiles_status(&st, 1);
-    if (st) { LOG_ERROR("%s: a bounded device-side wait expired (code %d)", who, st); ok = 0; }
+    if (dm_check_waits(d, who)) ok = 0;
     if (!ok) { tensor_free(out); return NULL; }
     return out;
 }

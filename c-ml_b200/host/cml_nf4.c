@@ -189,10 +189,8 @@ Tensor* cml_qlora_linear_forward(CMLQLoRALinear* qlora, Tensor* input) {
         LOG_ERROR("cml_qlora_linear_forward: incomplete layer");
         return NULL;
     }
-    if (K % 64 != 0 || w->block_size % 32 != 0 || K % w->block_size != 0) {
-        LOG_ERROR("cml_qlora_linear_forward: the device path needs in_features %% 64 == 0 and a block size that is a multiple of 32 dividing in_features (got %d, block %d)", K, w->block_size);
-        return NULL;
-    }
+    /* shapes the vectorised kernels take; everything else (C-ML accepts any) goes element by element */
+    const int fast = K % 32 == 0 && w->block_size % 32 == 0 && K % w->block_size == 0;
     QloraDev* dev = qdev_find(qlora);
     if (!dev) {
         dev = (QloraDev*)calloc(1, sizeof *dev);
@@ -217,7 +215,10 @@ Tensor* cml_qlora_linear_forward(CMLQLoRALinear* qlora, Tensor* input) {
     ok = ok && !CML_DEV_FAIL(cmlb200_malloc(&d_x, (size_t)M * K * 4), "cml_qlora_linear_forward");
     ok = ok && !CML_DEV_FAIL(cmlb200_malloc(&d_y, (size_t)M * N * 4), "cml_qlora_linear_forward");
     ok = ok && !CML_DEV_FAIL(cmlb200_memcpy_h2d(d_x, input->data, (size_t)M * K * 4, NULL), "cml_qlora_linear_forward");
-    if (ok && M <= 32) {
+    if (ok && !fast) {
+        ok = !CML_DEV_FAIL(cmlb200_linear_nf4_general((const uint8_t*)dev->d_packed, (const float*)dev->d_scales, w->num_scales, w->block_size,
+                                                      N, K, (const float*)d_x, M, (float*)d_y, NULL), "cml_qlora_linear_forward");
+    } else if (ok && M <= 32) {
         ok = !CML_DEV_FAIL(cmlb200_gemv(&W, (const float*)d_x, (float*)d_y, M, NULL), "cml_qlora_linear_forward");
     } else if (ok) {                                   /* prefill-sized batch: bf16 tensor-core path */
         ok = ok && !CML_DEV_FAIL(cmlb200_malloc(&d_xb, (size_t)M * K * 2), "cml_qlora_linear_forward");

@@ -13,6 +13,23 @@
 
 LogLevel g_log_level = LOG_LEVEL_ERROR;
 
+/* ---- library set-up (src/cml.c:376-440) and the tensor seed (include/tensor/tensor.h:143) ------ */
+static int g_init_count = 0;
+static uint64_t g_tensor_seed = 0;
+
+int cml_init(void) {
+    if (g_init_count++ == 0) cml_set_log_level(LOG_LEVEL_ERROR);
+    return 0;
+}
+
+int cml_cleanup(void) {
+    if (g_init_count > 0) g_init_count--;
+    return 0;
+}
+
+void tensor_manual_seed(uint64_t seed) { g_tensor_seed = seed; }
+uint64_t tensor_get_seed(void) { return g_tensor_seed; }
+
 void cml_set_log_level(LogLevel level) { g_log_level = level; }
 
 void cml_log_message(LogLevel level, const char* file, int line, const char* func, const char* format, ...) {

@@ -103,12 +103,15 @@ def make_llama(rng, cfg, quantize, qtype=2, wscale=0.05):
     return tensors, store
 
 
-def write_random_llama_gguf(path, rng, cfg, qtype=2, weight_std=0.02):
+def write_random_llama_gguf(path, rng, cfg, qtype=2, weight_std=0.02, alias_layers=False):
     """A LLaMA-shaped GGUF with random Q4_0/Q8_0 blocks (uniform quants, fp16 scales chosen so
     that the dequantised weights have roughly `weight_std`), fp16 norms near 1 and fp16
     embeddings. Generated tensor by tensor straight into the file, so 7B-sized models need no
-    fp32 staging; every layer reuses the random bytes drawn for layer 0 (the file still holds
-    each layer separately). Returns the number of bytes written."""
+    fp32 staging; every layer reuses the random bytes drawn for layer 0. By default the file
+    still holds each layer separately; with alias_layers the tensor infos of layers 1.. point at
+    layer 0's data (GGUF addresses tensors by offset, so this is a valid file of a fraction of
+    the size; the loader still uploads every layer as its own device copy). Returns the number
+    of bytes written."""
     import struct
     V, H, I, L = cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"]
     hd = H // cfg["heads"]
@@ -128,22 +131,33 @@ def write_random_llama_gguf(path, rng, cfg, qtype=2, weight_std=0.02):
         n = int(np.prod(dims))
         return n * 2 if t == 1 else n // 32 * bb
 
+    def kind_of(name, dims, t):
+        return (name.split(".", 2)[2] if name.startswith("blk.") else name, dims, t)
+
     head = bytearray(struct.pack("<IIQQ", 0x46475547, 3, len(spec), 0))
     off = 0
+    placed = {}         # alias_layers: data offset of the first tensor of each kind
+    stored = []         # the tensors whose bytes go into the file, in order
     for name, dims, t in spec:
         nb = name.encode()
         head += struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(dims))
         for d in dims:
             head += struct.pack("<Q", d)
+        kind = kind_of(name, dims, t)
+        if alias_layers and kind in placed:
+            head += struct.pack("<IQ", t, placed[kind])
+            continue
+        placed[kind] = off
+        stored.append((name, dims, t))
         head += struct.pack("<IQ", t, off)
         off += (nbytes(dims, t) + 31) // 32 * 32
     head += b"\0" * ((-len(head)) % 32)
     cache = {}          # layers share their random bytes: one draw per (tensor kind, shape)
     with open(path, "wb") as f:
         f.write(head)
-        for name, dims, t in spec:
+        for name, dims, t in stored:
             n = int(np.prod(dims))
-            kind = (name.split(".", 2)[2] if name.startswith("blk.") else name, dims, t)
+            kind = kind_of(name, dims, t)
             if kind in cache:
                 raw = cache[kind]
             elif t == 1:

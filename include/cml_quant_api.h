@@ -33,6 +33,17 @@ void cml_log_message(LogLevel level, const char* file, int line, const char* fun
 #define LOG_WARNING(...) cml_log_message(LOG_LEVEL_WARNING, __FILE__, __LINE__, __func__, __VA_ARGS__)
 #define LOG_ERROR(...) cml_log_message(LOG_LEVEL_ERROR, __FILE__, __LINE__, __func__, __VA_ARGS__)
 
+/* ---- include/cml.h:423-424 (src/cml.c:376-440): reference-counted library set-up. Nothing on this
+ * path needs global state beyond the log level (set to LOG_LEVEL_ERROR by the first cml_init, as
+ * C-ML does); both return 0. cml_cleanup without a matching cml_init is a no-op. */
+int cml_init(void);
+int cml_cleanup(void);
+/* include/tensor/tensor.h:143: seed of the tensor random generator. No operator of this path
+ * draws from it (sampling uses rand(), src/nn/llama.c:716); the value is kept and returned by
+ * tensor_get_seed so that callers' set-up code links and behaves the same. */
+void tensor_manual_seed(uint64_t seed);
+uint64_t tensor_get_seed(void);
+
 /* ---- include/backend/device.h:13-21, include/tensor/tensor.h:16-34,40-75,88-93 ----------- */
 typedef enum { DEVICE_CPU, DEVICE_CUDA, DEVICE_METAL, DEVICE_ROCM, DEVICE_OPENCL, DEVICE_SIM_GPU, DEVICE_AUTO } DeviceType;
 
@@ -308,6 +319,13 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath);
  * continuing at model->current_seq_len. */
 Tensor* cml_llama_forward(CMLLLaMAModel* model, const int* token_ids, int seq_len);
 Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tensor* hidden, int start_pos);
+/* src/nn/llama.c:739-851: encode the prompt with model->tokenizer, reset the caches, prefill,
+ * then sample / forward one token at a time until max_new_tokens, the EOS id or the sequence
+ * limit; the result holds prompt + generated ids, the decoded text, the wall time and generated
+ * tokens per second (prefill included, as in C-ML). NULL when the model has no tokenizer (C-ML's
+ * GGUF loader never creates one) or no tokenizer functions are known: they are C-ML's
+ * cml_tokenizer_encode / cml_tokenizer_decode (include/nn/llm_ops.h:147-149), picked up from the
+ * process when it links them, or given with cml_llama_set_tokenizer_functions. */
 CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config);
 void cml_generation_result_free(CMLGenerationResult* result);
 int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config);
@@ -315,6 +333,12 @@ void cml_llama_reset(CMLLLaMAModel* model);
 void cml_llama_print_config(const CMLLLaMAConfig* config);
 
 /* ---- additions (no C-ML counterpart) ---------------------------------------------------------- */
+/* The tokenizer stays C-ML's (src/nn/llm_ops.c:1140-1400 is not part of this library). A caller
+ * whose process does not export cml_tokenizer_encode / cml_tokenizer_decode hands them over here:
+ * encode returns a malloc'd id array and its length, decode a malloc'd string. */
+typedef int* (*CMLTokenizerEncodeFn)(CMLTokenizer* tok, const char* text, int* num_tokens);
+typedef char* (*CMLTokenizerDecodeFn)(CMLTokenizer* tok, const int* tokens, int num_tokens);
+void cml_llama_set_tokenizer_functions(CMLTokenizerEncodeFn encode, CMLTokenizerDecodeFn decode);
 /* Behaviour switches of a model, to be set after cml_llama_create and before the first forward:
  *   CML_B200_REFERENCE_QUIRKS  reproduce two properties of C-ML's forward pass exactly: RoPE
  *       rotates only head 0 (src/nn/llama.c:483-484 passes 2-D tensors to cml_rope_forward) and

@@ -94,7 +94,10 @@ int cmlb200_repack_gguf(int type, const void* h_blocks, int rows, int cols, void
 int cmlb200_unrepack_gguf(int type, const void* h_qs, const void* h_scales, int rows, int cols, void* h_blocks);
 
 /* ---- dequantisation to fp32, bit-exact with C-ML ------------------------- */
-/* gguf_dequantize(type, src, dst, numel) (src/core/gguf_quant.c:351-391) on
+/* All six block types C-ML reads are accepted by their GGUF ids: 2 (Q4_0), 3 (Q4_1), 7 (Q8_0),
+ * 12 (Q4_K), 13 (Q5_K), 14 (Q6_K; src/core/gguf_quant.c:66-311); numel must be a multiple of
+ * the type's block size (32, or 256 for the K types). Only Q4_0 and Q8_0 have matmul kernels.
+ * gguf_dequantize(type, src, dst, numel) (src/core/gguf_quant.c:351-391) on
  * raw GGUF blocks resident on the device. Same argument checks: NULL, numel==0,
  * unknown type or numel % 32 != 0 -> CMLB200_EINVAL. */
 int cmlb200_gguf_dequantize(int type, const void* d_blocks, float* d_dst, size_t numel, void* stream);
@@ -141,7 +144,8 @@ int cmlb200_gemv_rmsnorm(const cmlb200_qmat* W, const cmlb200_qmat* W2, const fl
 /* The decode GEMV for callers that cannot allocate device memory at run time (a serving process
  * that gave the whole GPU to its own arena, a real-time loop that must not take the allocator
  * lock, a sandbox that filters CUDA allocation calls). It has no counterpart in C-ML. Same result
- * as cmlb200_gemv for Q4_0 / Q8_0 weights in the planes layout and M <= 4, but the activation
+ * as cmlb200_gemv within the 2e-3 bound (not bit for bit: the activations are digitised per 32-block
+ * here) for Q4_0 / Q8_0 weights in the planes layout and M <= 4, but the activation
  * scratch is a fixed 512 KiB array inside the library image (resident on every GPU that loads the
  * library until the process exits) and the call performs no cudaMalloc / cudaFree. Limit:
  * M * cols <= 149,796 (e.g. M = 4 with cols = 28672); larger requests fail with CMLB200_EINVAL and
@@ -171,7 +175,7 @@ int cmlb200_gemv_tiles_status(int* status, int reset);
 /* Prefill path, M >= 1 (any M; built for M >= 64): bf16 activations, weights
  * dequantised to bf16 tiles in shared memory, tcgen05 MMAs accumulating fp32
  * in tensor memory, bf16 output. Same reference lines as cmlb200_gemv.
- * cols must be a multiple of 64. */
+ * cols must be a multiple of 32 (a last half slab of 32 is zero-extended). */
 int cmlb200_gemm_bf16(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
                       void* stream);
 /* Same, with the number of K splits chosen by the caller (1 = none). With more than one
@@ -181,6 +185,14 @@ int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, ui
 /* Synchronises the device and reports whether a bounded wait inside the tensor-core kernel
  * expired since the last reset (0 = none). C-ML has no counterpart: its path cannot stall. */
 int cmlb200_gemm_status(int* status, int reset);
+
+/* The quantized Linear of src/nn/qlora.c:264-317 for NF4 weights of ANY shape and block size
+ * (blocks may straddle rows; the block index is clamped as in src/core/quantization.c:359-364):
+ * y[M, rows] = x[M, cols] . dequant(W)^T in fp32, one warp per output value. The vectorised
+ * kernels behind cmlb200_gemv / cmlb200_gemm_bf16 need cols % 32 == 0 and a block size that is a
+ * multiple of 32 dividing cols; this entry point serves everything else. */
+int cmlb200_linear_nf4_general(const uint8_t* d_packed, const float* d_scales, int num_scales, int block, int rows, int cols,
+                               const float* d_x, int M, float* d_y, void* stream);
 
 /* ---- NF4 quantisation on the device: cml_quantize_nf4 (src/core/quantization.c:213-312):
  * per-block absmax floored at 1e-10, x/absmax clamped to [-1,1], nearest code with the first
@@ -284,6 +296,12 @@ int cmlb200_linear_f32(const float* d_x, const float* d_w, const float* d_bias, 
 size_t cmlb200_tp_ar_workspace_bytes(size_t max_floats);
 int cmlb200_tp_allreduce_add(float* d_h, const float* d_partial, size_t n, int tp, int rank, void* const* ws, size_t max_floats, void* stream);
 int cmlb200_tp_ar_status(const void* own_ws, int* status);
+int cmlb200_tp_ar_status_reset(void* own_ws);
+/* How many times a launch polls a peer's flag or packet before it gives up (both all-reduce
+ * forms). 0 restores the default of 2^22 polls (seconds); the environment variable
+ * CMLB200_WAIT_LIMIT sets the initial value. Applies to launches made after the call. C-ML has no
+ * counterpart: src/distributed/nccl_backend.c:397-405 marks work complete immediately. */
+int cmlb200_set_wait_limit(int polls);
 /* The row-parallel projection and its all-reduce in one launch per rank, for M <= 4 and weights
  * the tensor-core decode kernel takes (Q4_0 / Q8_0 planes, cols % 256 == 0):
  * h[M, rows] += sum over ranks of x_rank . dequant(W_rank)^T (src/nn/llama.c:523-530, 538-543 with

@@ -22,10 +22,21 @@ def build_oracle():
     return so
 
 
-def build_ref(reference_root="/root/reference"):
+def reference_root():
+    """Where the C-ML source tree is: $CML_REFERENCE_ROOT, else a `reference` directory beside
+    this repository. None when neither exists (the prebuilt oracle/_ref/ is then used as it is)."""
+    import os
+    for cand in (os.environ.get("CML_REFERENCE_ROOT"), HERE.parent.parent / "reference"):
+        if cand and Path(cand, "src").is_dir() and Path(cand, "include").is_dir():
+            return str(cand)
+    return None
+
+
+def build_ref(root=None):
     """Compile the C-ML reference where its source tree is present; no-op elsewhere."""
-    if Path(reference_root, "src").is_dir():
-        subprocess.run(["make", "-s", "-j8", "-C", str(HERE), "ref", f"REF={reference_root}"], check=True)
+    root = root or reference_root()
+    if root:
+        subprocess.run(["make", "-s", "-j8", "-C", str(HERE), "ref", f"REF={root}"], check=True)
     so = HERE / "_ref" / "libref_driver.so"
     return so if so.exists() else None
 
@@ -105,6 +116,7 @@ def load_ref():
         _sig(lib, "ref_llama_cur_len", ci, vp)
         _sig(lib, "ref_llama_free", None, vp)
         _sig(lib, "ref_sample_greedy", ci, vp, ci, ci)
+        _sig(lib, "ref_sample_token", ci, vp, ci, ci, cf, cf, ci, ci, C.c_uint)
         _sig(lib, "ref_rope_2d", ci, vp, ci, ci, ci, ci, cf)
         _sig(lib, "ref_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, vp)
         _sig(lib, "ref_tp_column_then_row", ci, vp, ci, ci, vp, ci, vp, ci, ci, vp)

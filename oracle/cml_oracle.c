@@ -110,16 +110,90 @@ void orc_dequant_q4_0(const uint8_t* blocks, float* dst, size_t nblocks) {
     }
 }
 
+/* The block types beside Q4_0 / Q8_0 that the reference reads.
+ * Q4_1 (include/core/gguf_quant.h:20-25, src/core/gguf_quant.c:90-112): fp16 d, fp16 m, 16 bytes
+ *   packed like Q4_0; y = (float)nibble * d + m. */
+static float orc_half_at(const uint8_t* p) {
+    uint16_t h;
+    memcpy(&h, p, 2);
+    return orc_fp16_to_fp32(h);
+}
+
+void orc_dequant_q4_1(const uint8_t* blocks, float* dst, size_t nblocks) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t* p = blocks + b * 20;
+        const float d = orc_half_at(p), m = orc_half_at(p + 2);
+        for (int j = 0; j < 16; j++) {
+            dst[b * 32 + j] = (float)(p[4 + j] & 15) * d + m;
+            dst[b * 32 + j + 16] = (float)(p[4 + j] >> 4) * d + m;
+        }
+    }
+}
+
+/* 6-bit scale and min of sub-block i of a Q4_K / Q5_K super-block from its 12 packed bytes
+ * (src/core/gguf_quant.c:162-171): the first four pairs sit in the low 6 bits of bytes i and
+ * i + 4; the last four take a nibble of byte i + 4 and the top two bits of bytes i - 4 and i. */
+static void orc_k_scale_min(const uint8_t* s, int i, int* sc, int* mn) {
+    if (i < 4) { *sc = s[i] & 63; *mn = s[i + 4] & 63; return; }
+    *sc = (s[i + 4] & 15) | ((s[i - 4] >> 6) << 4);
+    *mn = (s[i + 4] >> 4) | ((s[i] >> 6) << 4);
+}
+
+/* Q4_K (gguf_quant.h:34-39, gguf_quant.c:151-196) and Q5_K (gguf_quant.h:41-47,
+ * gguf_quant.c:211-270): 256 elements = 8 sub-blocks of 32; sub-block i keeps its nibbles in
+ * qs[16i .. 16i+15], element k in the low and k + 16 in the high nibble (the reference's own
+ * order); Q5_K adds bit e of the 256-bit field qh as bit 4; y = q * (d * sc) - dmin * mn. */
+static void orc_dequant_q45_k(const uint8_t* blocks, float* dst, size_t nblocks, int five) {
+    const size_t bb = five ? 176 : 144;
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t* p = blocks + b * bb;
+        const float d = orc_half_at(p), dmin = orc_half_at(p + 2);
+        const uint8_t* qh = p + 16;
+        const uint8_t* qs = p + (five ? 48 : 16);
+        for (int e = 0; e < 256; e++) {
+            const int i = e >> 5, k = e & 31;
+            int sc, mn;
+            orc_k_scale_min(p + 4, i, &sc, &mn);
+            const uint8_t byte = qs[i * 16 + (k & 15)];
+            int q = k < 16 ? (byte & 15) : (byte >> 4);
+            if (five) q |= ((qh[e >> 3] >> (e & 7)) & 1) << 4;
+            const float scale = d * (float)sc, minv = dmin * (float)mn;
+            dst[b * 256 + e] = (float)q * scale - minv;
+        }
+    }
+}
+
+/* Q6_K (gguf_quant.h:49-54, gguf_quant.c:283-311): ql[128] low nibbles (even element in the low
+ * half), qh[64] two high bits each, 16 int8 sub-block scales, fp16 d last;
+ * y = d * scale[e / 16] * (q6 - 32). */
+void orc_dequant_q6_k(const uint8_t* blocks, float* dst, size_t nblocks) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t* p = blocks + b * 210;
+        const float d = orc_half_at(p + 208);
+        for (int e = 0; e < 256; e++) {
+            const int low4 = (e & 1) ? (p[e >> 1] >> 4) : (p[e >> 1] & 15);
+            const int high2 = (p[128 + (e >> 2)] >> (2 * (e & 3))) & 3;
+            const float sc = (float)(int8_t)p[192 + (e >> 4)];
+            dst[b * 256 + e] = d * sc * (float)((low4 | (high2 << 4)) - 32);
+        }
+    }
+}
+
 /* Dispatcher with the reference's error contract (src/core/gguf_quant.c:351-391):
  * -1 for NULL pointers, numel == 0, a type without a block size, or numel not
- * a multiple of the block size. Only the two types on the path are restated. */
+ * a multiple of the block size (32; 256 for the K types). */
 int orc_gguf_dequantize(int type, const void* src, float* dst, size_t numel) {
     if (!src || !dst || numel == 0) return -1;
-    if (type != ORC_Q4_0 && type != ORC_Q8_0) return -1;
-    if (numel % 32) return -1;
-    if (type == ORC_Q4_0) orc_dequant_q4_0((const uint8_t*)src, dst, numel / 32);
-    else orc_dequant_q8_0((const uint8_t*)src, dst, numel / 32);
-    return 0;
+    const uint8_t* s = (const uint8_t*)src;
+    switch (type) {
+        case ORC_Q4_0: if (numel % 32) return -1; orc_dequant_q4_0(s, dst, numel / 32); return 0;
+        case ORC_Q8_0: if (numel % 32) return -1; orc_dequant_q8_0(s, dst, numel / 32); return 0;
+        case 3: if (numel % 32) return -1; orc_dequant_q4_1(s, dst, numel / 32); return 0;
+        case 12: if (numel % 256) return -1; orc_dequant_q45_k(s, dst, numel / 256, 0); return 0;
+        case 13: if (numel % 256) return -1; orc_dequant_q45_k(s, dst, numel / 256, 1); return 0;
+        case 14: if (numel % 256) return -1; orc_dequant_q6_k(s, dst, numel / 256); return 0;
+        default: return -1;
+    }
 }
 
 /* Q4_0 / Q8_0 quantisers. C-ML has none (its GGUF writer cannot emit

@@ -241,6 +241,24 @@ int ref_sample_greedy(const float* logits, int rows, int vocab) {
     return id;
 }
 
+/* cml_llama_sample_token (src/nn/llama.c:627-737) with every field of the generation config
+ * given and the C library generator seeded first, so that the draw is reproducible. */
+int ref_sample_token(const float* logits, int rows, int vocab, float temperature, float top_p, int top_k,
+                     int do_sample, unsigned seed) {
+    int sh[2] = {rows, vocab};
+    Tensor* t = t_from(logits, 2, sh);
+    if (!t) return -1;
+    CMLGenerationConfig g = cml_generation_default_config();
+    g.temperature = temperature;
+    g.top_p = top_p;
+    g.top_k = top_k;
+    g.do_sample = do_sample != 0;
+    srand(seed);
+    int id = cml_llama_sample_token(t, &g);
+    tensor_free(t);
+    return id;
+}
+
 /* cml_rope_forward on a 2-D tensor (src/nn/llm_ops.c:702), in place. */
 int ref_rope_2d(float* x, int seq, int width, int head_dim, int start_pos, float base) {
     int sh[2] = {seq, width};

@@ -129,6 +129,47 @@ def main():
         assert ref.ref_tp_column_then_row(p(x), M, K, p(W1), N1, p(W2), N, tp, p(y)) == 0
         out[f"tp_y_{tp}"] = y
 
+    # ---- everything below draws from generators of its own, so that adding a section never changes
+    # the arrays above.
+    # --- the other block types the reference reads (GGUF ids 3, 12, 13, 14): random bytes with sane
+    # fp16 scale fields, plus the special fp16 classes in the first blocks
+    rng2 = np.random.default_rng(20240602)
+    special = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x7BFF, 0x3C00, 0xBC00, 0x0200, 0x8001, 0x1400, 0x2E66], np.uint16)
+    for gid, bb, bs, half_at in ((3, 20, 32, (0, 2)), (12, 144, 256, (0, 2)), (13, 176, 256, (0, 2)), (14, 210, 256, (208,))):
+        nb = 40
+        blocks = rng2.integers(0, 256, (nb, bb), dtype=np.uint8)
+        for off in half_at:
+            h = rng2.uniform(-2e-2, 2e-2, nb).astype(np.float16)
+            blocks[:, off:off + 2] = h.view(np.uint8).reshape(nb, 2)
+            blocks[:len(special), off:off + 2] = np.roll(special, off).view(np.uint8).reshape(-1, 2)
+        blocks = np.ascontiguousarray(blocks.reshape(-1))
+        deq = np.empty(nb * bs, np.float32)
+        assert ref.ref_gguf_dequantize(gid, p(blocks), p(deq), deq.size) == 0
+        out[f"gguf{gid}_blocks"] = blocks
+        out[f"gguf{gid}_dequant_bits"] = deq.view(np.uint32)
+
+    # --- the sampling branch of cml_llama_sample_token: (temperature, top_p, top_k, do_sample, seed) -> id
+    rng3 = np.random.default_rng(20240603)
+    slog = (rng3.standard_normal((2, 200)) * 3).astype(np.float32)
+    slog[1, 17] = slog[1, 40] = slog[1].max() + 1.0          # a tie at the top
+    cases = [(0.8, 0.9, 40, 1, s) for s in range(12)] + [(1.5, 1.0, 0, 1, s) for s in range(6)] + \
+            [(0.3, 0.5, 5, 1, s) for s in range(6)] + [(1.0, 0.0, 3, 1, 7), (0.0, 0.9, 40, 1, 1), (0.8, 0.9, 40, 0, 1), (1.0, 0.95, 1000, 1, 3)]
+    ids = [ref.ref_sample_token(p(slog), 2, 200, t, tp_, tk, ds, sd) for (t, tp_, tk, ds, sd) in cases]
+    out.update(sample_logits=slog, sample_cases=np.array(cases, np.float64), sample_ids=np.array(ids, np.int32))
+
+    # --- quantized Linear on shapes outside the vectorised kernels: the block sizes and sizes the
+    # reference's own tests use (block 16 and 4 on tiny weights) and a block that straddles rows
+    rng4 = np.random.default_rng(20240604)
+    for tag, (n_out2, n_in2, block2, rank2, M2) in (("b16", (8, 16, 16, 2, 3)), ("b4", (4, 8, 4, 2, 2)), ("straddle", (5, 24, 16, 3, 4))):
+        W2 = (rng4.standard_normal((n_out2, n_in2)) * 0.1).astype(np.float32)
+        x2 = rng4.standard_normal((M2, n_in2)).astype(np.float32)
+        A2 = (rng4.standard_normal((rank2, n_in2)) * 0.1).astype(np.float32)
+        B2 = (rng4.standard_normal((n_out2, rank2)) * 0.1).astype(np.float32)
+        y2 = np.empty((M2, n_out2), np.float32)
+        assert ref.ref_qlora_forward(p(x2), M2, n_in2, n_out2, p(W2), None, None, block2, rank2, 4.0, p(A2), p(B2), p(y2)) == 0
+        out.update({f"qlora_{tag}_W": W2, f"qlora_{tag}_x": x2, f"qlora_{tag}_A": A2, f"qlora_{tag}_B": B2, f"qlora_{tag}_y": y2,
+                    f"qlora_{tag}_cfg": np.array([n_out2, n_in2, block2, rank2, M2], np.int32)})
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 

@@ -62,7 +62,8 @@ def test_compute_entry_points_validate_before_launching(pkg):
     fake = 0x1000
     assert lib.cmlb200_gguf_dequantize(7, None, fake, 32, None) == -1
     assert lib.cmlb200_gguf_dequantize(7, fake, fake, 0, None) == -1
-    assert lib.cmlb200_gguf_dequantize(12, fake, fake, 256, None) == -1
+    assert lib.cmlb200_gguf_dequantize(12, fake, fake, 128, None) == -1          # Q4_K blocks hold 256 elements
+    assert lib.cmlb200_gguf_dequantize(6, fake, fake, 256, None) == -1           # not a type C-ML reads
     assert lib.cmlb200_gguf_dequantize(2, fake, fake, 48, None) == -1
     assert lib.cmlb200_dequantize_nf4(fake, fake, 0, 64, 64, fake, None) == -1
     W = pkg.QMat(pkg.Q4_0, 8, 48, 32, fake, fake)            # cols not a multiple of 32
@@ -72,7 +73,7 @@ def test_compute_entry_points_validate_before_launching(pkg):
     assert lib.cmlb200_gemv(W, None, fake, 1, None) == -1
     W = pkg.QMat(pkg.NF4, 8, 64, 48, fake, fake)             # NF4 block must divide cols
     assert lib.cmlb200_gemv(W, fake, fake, 1, None) == -1
-    W = pkg.QMat(pkg.Q4_0, 8, 96, 32, fake, fake)            # tensor-core path wants cols % 64 == 0
+    W = pkg.QMat(pkg.Q4_0, 8, 80, 32, fake, fake)            # cols must be a multiple of 32
     assert lib.cmlb200_gemm_bf16(W, fake, fake, 64, None) == -1
     assert lib.cmlb200_gemm_bf16(pkg.QMat(pkg.Q4_0, 8, 128, 32, fake, fake), fake, fake, 0, None) == -1
 
@@ -90,3 +91,82 @@ def test_tile_major_repack_is_a_bijection(pkg, synth, qtype):
     assert np.array_equal(back, blocks)
     assert pkg.lib.cmlb200_repack_tiles(qtype, pkg.np_ptr(blocks), rows, 48, pkg.np_ptr(tiles)) == -1
     assert pkg.lib.cmlb200_tiles_bytes(100, rows, cols) == 0
+
+
+def test_library_exports_nothing_but_the_declared_symbols(pkg):
+    """The shared library is linked with a version script made from include/*.h: internal helpers
+    (NCCL shim, GGUF internals, kernel launchers) are not part of the ABI."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", str(ROOT / "c-ml_b200" / "lib" / "libcml_b200.so")], capture_output=True, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if line.strip()}
+    declared = set(_declared_functions()) | {"g_log_level", "CML_NF4_TABLE"}
+    assert exported <= declared, sorted(exported - declared)
+
+
+def test_init_cleanup_and_seed_are_reference_counted_no_ops(pkg):
+    """cml_init / cml_cleanup (C-ML src/cml.c:376-440) and tensor_manual_seed
+    (include/tensor/tensor.h:143), which examples/llama_inference.c:79-83 calls before anything else."""
+    import ctypes as C
+    lib = pkg.lib
+    lib.tensor_manual_seed.argtypes = [C.c_uint64]
+    lib.tensor_get_seed.restype = C.c_uint64
+    assert lib.cml_cleanup() == 0                      # without a matching init: nothing happens
+    assert lib.cml_init() == 0 and lib.cml_init() == 0
+    lib.tensor_manual_seed(1234567890123)
+    assert lib.tensor_get_seed() == 1234567890123
+    assert lib.cml_cleanup() == 0 and lib.cml_cleanup() == 0
+
+
+def test_sampling_branch_matches_the_compiled_reference(pkg, ob, ref, golden):
+    """cml_llama_sample_token (src/nn/llama.c:627-737): temperature, descending sort, top-k softmax,
+    top-p cut, renormalisation and one rand() draw. Host code, so it runs without a GPU; the C
+    library generator is seeded exactly as the reference wrapper seeded it."""
+    import ctypes as C
+    libc = C.CDLL(None)
+    logits = np.ascontiguousarray(golden["sample_logits"])
+    t = pkg.numpy_to_tensor(logits)
+    try:
+        for (temp, top_p, top_k, do_sample, seed), want in zip(golden["sample_cases"], golden["sample_ids"]):
+            cfg = pkg.GenerationConfig(float(temp), float(top_p), int(top_k), 16, 2, bool(do_sample))
+            libc.srand(int(seed))
+            got = pkg.lib.cml_llama_sample_token(t, C.byref(cfg))
+            assert got == int(want), (temp, top_p, top_k, do_sample, seed, got, int(want))
+            if ref is not None:
+                assert ref.ref_sample_token(ob.p(logits), 2, logits.shape[1], float(temp), float(top_p), int(top_k), int(do_sample), int(seed)) == got
+        greedy = pkg.GenerationConfig(0.8, 0.9, 40, 16, 2, False)
+        assert pkg.lib.cml_llama_sample_token(t, C.byref(greedy)) == 17          # first of two equal maxima
+        assert pkg.lib.cml_llama_sample_token(None, C.byref(greedy)) == -1
+    finally:
+        pkg.lib.tensor_free(t)
+
+
+def test_generate_needs_loaded_weights_and_a_tokenizer(pkg):
+    import ctypes as C
+    cfg = pkg.LlamaConfig(64, 64, 128, 1, 2, 2, 16, 10000.0, 1e-5, 0, 0)
+    m = pkg.lib.cml_llama_create(C.byref(cfg))
+    assert m
+    pkg.lib.cml_set_log_level(4)
+    gen = pkg.lib.cml_generation_default_config()
+    assert not pkg.lib.cml_llama_generate(m, b"hello", C.byref(gen))            # weights not loaded
+    assert not pkg.lib.cml_llama_generate(None, b"hello", C.byref(gen))
+    pkg.lib.cml_set_log_level(3)
+    pkg.lib.cml_llama_free(m)
+
+
+def test_reference_example_program_links_against_the_library(pkg, ob, tmp_path):
+    """examples/llama_inference.c of the C-ML tree, unmodified, compiles against include/ (through the
+    forwarding cml.h and nn/llama.h) and links against libcml_b200.so alone."""
+    import subprocess
+    root = ob.reference_root()
+    if root is None:
+        pytest.skip("the C-ML source tree is not on this machine")
+    exe = tmp_path / "llama_inference"
+    libdir = ROOT / "c-ml_b200" / "lib"
+    cmd = ["gcc", "-std=c11", "-D_POSIX_C_SOURCE=200809L", f"-I{ROOT / 'include'}", str(Path(root) / "examples" / "llama_inference.c"),
+           "-o", str(exe), f"-L{libdir}", "-lcml_b200", f"-Wl,-rpath,{libdir}", "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe), "-h"], capture_output=True, text=True)
+    assert r.returncode == 0 and "LLaMA inference" in r.stdout
+    r = subprocess.run([str(exe), str(tmp_path / "missing.gguf"), "--greedy"], capture_output=True, text=True)
+    assert r.returncode == 1 and "Failed to load GGUF weights" in r.stderr

@@ -66,3 +66,20 @@ def test_gemm_nf4_config_shape_sampled(pkg, synth, ob, orc, torch_dev, M):
     # whole-output check against an fp64 matmul of the same dequantised weights
     full = xr.reshape(x.shape).astype(np.float64) @ Wf.T.astype(np.float64)
     assert rel_err_inf(got, full) <= TOL
+
+
+@pytest.mark.parametrize("kind,K", [("q4_0", 1376), ("q8_0", 96), ("nf4", 1376), ("q4_0", 32)])
+@pytest.mark.parametrize("M", [40, 300])
+def test_gemm_k_tail_of_half_a_slab(pkg, synth, ob, orc, torch_dev, kind, K, M):
+    """cols % 64 == 32 (LLaMA-7B's FFN width split over 8 ranks is 1376): the last 64-wide slab is
+    half real, half zero; rows of an odd number of blocks start on odd scale indices."""
+    rng = np.random.default_rng(500 + K + M)
+    N = 200
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K, block=32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    _, xr = synth.bf16_round(x)
+    got = _gemm(pkg, synth, W, x, N, torch_dev)
+    assert rel_err_inf(got, ob.linear_nt(orc, xr.reshape(x.shape), Wf)) <= TOL
+    if K >= 256:
+        got2 = _gemm(pkg, synth, W, x, N, torch_dev, splits=3)
+        assert rel_err_inf(got2, ob.linear_nt(orc, xr.reshape(x.shape), Wf)) <= TOL

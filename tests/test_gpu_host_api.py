@@ -19,7 +19,8 @@ def test_gguf_dequantize_host_pointers_bit_exact(pkg, synth, ob, orc, torch_dev)
         assert np.array_equal(out.view(np.uint32), ob.dequant_blocks(orc, qtype, blocks, out.size).view(np.uint32))
         assert pkg.lib.gguf_dequantize(qtype, pkg.np_ptr(blocks), pkg.np_ptr(out), 48) == -1
         assert pkg.lib.gguf_dequantize(qtype, None, pkg.np_ptr(out), 32) == -1
-    assert pkg.lib.gguf_dequantize(12, pkg.np_ptr(blocks), pkg.np_ptr(out), 256) == -1     # Q4_K: no kernel on this path
+    assert pkg.lib.gguf_dequantize(12, pkg.np_ptr(blocks), pkg.np_ptr(out), 128) == -1     # Q4_K blocks hold 256 elements
+    assert pkg.lib.gguf_dequantize(6, pkg.np_ptr(blocks), pkg.np_ptr(out), 256) == -1       # not a type C-ML reads
     assert pkg.lib.gguf_type_is_quantized(2) and pkg.lib.gguf_type_is_quantized(14) and not pkg.lib.gguf_type_is_quantized(0)
     assert pkg.lib.gguf_quant_block_size(7) == 32 and pkg.lib.gguf_quant_block_size(12) == 256 and pkg.lib.gguf_quant_block_size(1) == 0
     assert pkg.lib.gguf_quant_type_size(2) == 18 and pkg.lib.gguf_quant_type_size(7) == 34
@@ -116,3 +117,72 @@ def test_qlora_linear_forward(pkg, ob, orc, torch_dev, M):
     for t in (xt, bad, wt):
         pkg.lib.tensor_free(t)
     pkg.lib.cml_qlora_linear_free(q)
+
+
+@pytest.mark.parametrize("gid,bs,bb", [(3, 32, 20), (12, 256, 144), (13, 256, 176), (14, 256, 210)])
+def test_other_block_types_bit_exact_on_device(pkg, ob, orc, golden, torch_dev, tmp_path, gid, bs, bb):
+    """Q4_1 / Q4_K / Q5_K / Q6_K through gguf_dequantize and gguf_read_tensor: the stored outputs of
+    the compiled reference, then random bytes (any scale pattern) against the oracle."""
+    blocks = np.ascontiguousarray(golden[f"gguf{gid}_blocks"])
+    numel = blocks.size // bb * bs
+    out = np.empty(numel, np.float32)
+    assert pkg.lib.gguf_dequantize(gid, pkg.np_ptr(blocks), pkg.np_ptr(out), numel) == 0
+    assert np.array_equal(out.view(np.uint32), golden[f"gguf{gid}_dequant_bits"])
+    rng = np.random.default_rng(50 + gid)
+    fresh = rng.integers(0, 256, 300 * bb, dtype=np.uint8)
+    out = np.empty(300 * bs, np.float32)
+    assert pkg.lib.gguf_dequantize(gid, pkg.np_ptr(fresh), pkg.np_ptr(out), out.size) == 0
+    want = ob.dequant_blocks(orc, gid, fresh, out.size)
+    both_nan = np.isnan(out) & np.isnan(want)          # NaN scales: a NaN on both sides, payload aside
+    assert np.array_equal(out.view(np.uint32)[~both_nan], want.view(np.uint32)[~both_nan])
+    # a file holding such a tensor can be read now
+    import __graft_entry__ as entry
+    synth = entry.load_synth()
+    path = tmp_path / f"t{gid}.gguf"
+    synth.write_gguf(path, [("w", (bs, 300), gid, fresh.tobytes())])
+    ctx = pkg.lib.gguf_open_read(str(path).encode())
+    assert ctx
+    t = pkg.lib.gguf_read_tensor(ctx, b"w")
+    assert t
+    got = pkg.tensor_to_numpy(t)
+    pkg.lib.gguf_close(ctx)
+    assert np.array_equal(got.reshape(-1).view(np.uint32)[~both_nan], out.view(np.uint32)[~both_nan])
+
+
+@pytest.mark.parametrize("tag", ["b16", "b4", "straddle"])
+def test_qlora_forward_small_blocks_match_reference(pkg, golden, torch_dev, tag):
+    """C-ML's own QLoRA test shapes (tests/test_qlora.c:174,332,453: block 16 and 4 on tiny weights)
+    and a block that straddles rows: stored outputs of the compiled reference's
+    cml_qlora_linear_forward. These shapes run the element-wise NF4 kernel."""
+    n_out, n_in, block, rank, M = (int(v) for v in golden[f"qlora_{tag}_cfg"])
+    W, x, A, B = (np.ascontiguousarray(golden[f"qlora_{tag}_{k}"]) for k in ("W", "x", "A", "B"))
+    wt = pkg.numpy_to_tensor(W)
+    q = pkg.lib.cml_qlora_linear_create(wt, rank, 4.0, block)
+    assert q
+    C.memmove(q.contents.lora_A.contents.data, A.ctypes.data, A.nbytes)
+    C.memmove(q.contents.lora_B.contents.data, B.ctypes.data, B.nbytes)
+    xt = pkg.numpy_to_tensor(x)
+    y = pkg.tensor_to_numpy(pkg.lib.cml_qlora_linear_forward(q, xt))
+    assert y.shape == (M, n_out) and rel_err_inf(y, golden[f"qlora_{tag}_y"]) <= 2e-3
+    pkg.lib.tensor_free(xt)
+    pkg.lib.tensor_free(wt)
+    pkg.lib.cml_qlora_linear_free(q)
+
+
+def test_nf4_tensor_dequantize_direct(pkg, ob, orc, torch_dev):
+    """cml_nf4_tensor_create / cml_nf4_tensor_dequantize (src/nn/qlora.c:10-132): the dequantised
+    tensor has the original shape and the oracle's bits."""
+    rng = np.random.default_rng(35)
+    W = (rng.standard_normal((24, 160)) * 0.07).astype(np.float32)
+    wt = pkg.numpy_to_tensor(W)
+    nf = pkg.lib.cml_nf4_tensor_create(wt, 32)
+    assert nf and nf.contents.block_size == 32 and nf.contents.original_numel == W.size and nf.contents.num_scales == W.size // 32
+    packed = pkg.tensor_to_numpy(nf.contents.packed_data, free=False)
+    scales = np.ctypeslib.as_array(nf.contents.scales, (nf.contents.num_scales,)).copy()
+    got = pkg.tensor_to_numpy(pkg.lib.cml_nf4_tensor_dequantize(nf))
+    assert got.shape == W.shape
+    assert np.array_equal(got.reshape(-1).view(np.uint32), ob.dequant_nf4(orc, packed, scales, 32, W.size).view(np.uint32))
+    assert np.abs(got - W).max() <= 0.2 * np.abs(W).max()
+    assert not pkg.lib.cml_nf4_tensor_dequantize(None)
+    pkg.lib.cml_nf4_tensor_free(nf)
+    pkg.lib.tensor_free(wt)

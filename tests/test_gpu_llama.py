@@ -200,3 +200,117 @@ def test_layer_forward_chain_matches_model_forward(pkg, tiny, torch_dev):
         pkg.lib.tensor_free(bad)
     finally:
         pkg.lib.cml_llama_free(m)
+
+
+SHAPED = {
+    # two layers with LLaMA-7B's layer shapes (C-ML src/nn/llama.c:14-27) and with LLaMA-70B's
+    # (src/nn/llama.c:44-57: 64 query heads over 8 KV heads, FFN 28672); small vocabulary and cache
+    "7b": dict(vocab=512, hidden=4096, inter=11008, layers=2, heads=32, kv_heads=32, max_seq=80),
+    "70b": dict(vocab=512, hidden=8192, inter=28672, layers=2, heads=64, kv_heads=8, max_seq=80),
+}
+
+
+@pytest.mark.parametrize("shape", ["7b", "70b"])
+def test_full_width_layers_match_oracle(pkg, tmp_path, torch_dev, shape):
+    """The kernels as the real models drive them (every warp of the decode GEMV owns K units, K =
+    11008 / 28672 down projections, SwiGLU over 11008 / 28672 rows, head_dim 128 with 32 / 64 heads,
+    GQA 8:1): a 5-token call and two cached single-token calls on the fp32 path, then a batch of 8
+    sequences (the 8-row kernel), then a 40-token prompt on the bf16 tensor-core path."""
+    cfg = SHAPED[shape]
+    rng = np.random.default_rng(77)
+    path = tmp_path / f"shaped_{shape}.gguf"
+    store = build(entry, rng, cfg, path)
+    orc = OracleLlama(entry, cfg, store, rope_all_heads=1, mask_absolute=1)
+    tokens = rng.integers(0, cfg["vocab"], 7).astype(np.int32)
+    m = device_model(pkg, cfg, path, flags=pkg.KV_FP32, max_batch=8)
+    try:
+        for toks in (tokens[:5], tokens[5:6], tokens[6:7]):
+            got, want = dev_forward(pkg, m, toks), orc.forward(toks)
+            assert got is not None and rel_err_inf(got, want) <= 2e-3
+        # eight sequences, one token each: sequence 0 continues, the others start empty
+        nxt = rng.integers(0, cfg["vocab"], 8).astype(np.int32)
+        t = pkg.lib.cml_llama_forward_batch(m, pkg.np_ptr(nxt), 8)
+        assert t
+        got = pkg.tensor_to_numpy(t)
+        assert rel_err_inf(got[0:1], orc.forward(nxt[0:1])) <= 2e-3
+        fresh = OracleLlama(entry, cfg, store, rope_all_heads=1, mask_absolute=1)
+        assert rel_err_inf(got[3:4], fresh.forward(nxt[3:4])) <= 2e-3
+    finally:
+        pkg.lib.cml_llama_free(m)
+    del orc, fresh
+    m = device_model(pkg, cfg, path)
+    try:
+        long = rng.integers(0, cfg["vocab"], 40).astype(np.int32)
+        orc = OracleLlama(entry, cfg, store, rope_all_heads=1, mask_absolute=1)
+        assert rel_err_inf(dev_forward(pkg, m, long), orc.forward(long)) <= 1e-2
+    finally:
+        pkg.lib.cml_llama_free(m)
+
+
+def test_generate_with_a_caller_supplied_tokenizer(pkg, tiny, torch_dev):
+    """cml_llama_generate (src/nn/llama.c:739-851) with tokenizer functions handed over by the
+    caller (a byte-level stand-in here): prompt ids + greedy continuation equal step-by-step
+    forward + cml_llama_sample_token; text, timing and the EOS stop are filled as C-ML fills them."""
+    path, store = tiny
+    lib = pkg.lib
+    libc = C.CDLL(None)
+    libc.malloc.restype = C.c_void_p
+    libc.malloc.argtypes = [C.c_size_t]
+    ENC = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_char_p, C.POINTER(C.c_int))
+    DEC = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int)
+
+    def encode(tok, text, n):
+        ids = list(text)                                   # one id per byte
+        n[0] = len(ids)
+        buf = libc.malloc(4 * max(1, len(ids)))
+        C.memmove(buf, (C.c_int * len(ids))(*ids), 4 * len(ids))
+        return buf
+
+    def decode(tok, ids, n):
+        s = bytes(32 + (ids[i] % 90) for i in range(n)) + b"\0"
+        buf = libc.malloc(len(s))
+        C.memmove(buf, s, len(s))
+        return buf
+
+    enc, dec = ENC(encode), DEC(decode)
+    lib.cml_llama_set_tokenizer_functions.argtypes = [ENC, DEC]
+    lib.cml_llama_set_tokenizer_functions(enc, dec)
+
+    class Result(C.Structure):
+        _fields_ = [("token_ids", C.POINTER(C.c_int)), ("num_tokens", C.c_int), ("text", C.c_char_p),
+                    ("total_time_ms", C.c_float), ("tokens_per_second", C.c_float)]
+
+    m, m2 = device_model(pkg, TINY, path), device_model(pkg, TINY, path)
+    try:
+        gen = lib.cml_generation_default_config()
+        gen.do_sample, gen.max_new_tokens, gen.eos_token_id = False, 6, -1
+        assert not lib.cml_llama_generate(m, b"abc", C.byref(gen))            # model->tokenizer is NULL
+        m.contents.tokenizer = 1                                              # opaque handle passed through to the callbacks
+        prompt = b"hello b200"
+        res = lib.cml_llama_generate(m, prompt, C.byref(gen))
+        assert res
+        r = C.cast(res, C.POINTER(Result)).contents
+        ids = [r.token_ids[i] for i in range(r.num_tokens)]
+        assert ids[:len(prompt)] == list(prompt) and r.num_tokens == len(prompt) + 6
+        want, toks = [], np.array(list(prompt), np.int32)
+        for _ in range(6):
+            t = lib.cml_llama_forward(m2, pkg.np_ptr(toks), len(toks))
+            nxt = lib.cml_llama_sample_token(t, C.byref(gen))
+            lib.tensor_free(t)
+            want.append(nxt)
+            toks = np.array([nxt], np.int32)
+        assert ids[len(prompt):] == want
+        assert r.text == bytes(32 + (i % 90) for i in ids)
+        assert r.total_time_ms > 0 and abs(r.tokens_per_second - 6e3 / r.total_time_ms) < 1e-2 * r.tokens_per_second
+        assert m.contents.current_seq_len == len(prompt) + 6                  # C-ML forwards every appended token, the last included
+        lib.cml_generation_result_free(res)
+        gen.eos_token_id = want[1]                                            # stops right after producing the EOS id
+        res = lib.cml_llama_generate(m, prompt, C.byref(gen))
+        r = C.cast(res, C.POINTER(Result)).contents
+        assert r.num_tokens == len(prompt) + 2 and r.token_ids[r.num_tokens - 1] == want[1]
+        lib.cml_generation_result_free(res)
+        m.contents.tokenizer = None
+    finally:
+        lib.cml_llama_set_tokenizer_functions(ENC(0), DEC(0))
+        lib.cml_llama_free(m)
+        lib.cml_llama_free(m2)

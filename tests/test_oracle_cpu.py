@@ -249,3 +249,36 @@ def test_oracle_equals_compiled_reference_on_fresh_inputs(ob, orc, ref, synth):
     da, db = ob.dequant_nf4(orc, pa, sa, 64, n), np.empty(n, np.float32)
     assert ref.ref_nf4_dequantize(ob.p(pa), ob.p(sa), len(sa), 64, n, ob.p(db)) == 0
     assert np.array_equal(da.view(np.uint32), db.view(np.uint32))
+
+
+@pytest.mark.parametrize("gid,bs,bb", [(3, 32, 20), (12, 256, 144), (13, 256, 176), (14, 256, 210)])
+def test_other_block_types_match_golden_bits(ob, orc, ref, golden, gid, bs, bb):
+    """Q4_1, Q4_K, Q5_K, Q6_K (C-ML src/core/gguf_quant.c:90-311, its own nibble order for the K
+    types) against stored outputs of the compiled reference, and against it directly when built."""
+    blocks = np.ascontiguousarray(golden[f"gguf{gid}_blocks"])
+    numel = blocks.size // bb * bs
+    got = _dq(ob, orc, gid, blocks, numel)
+    assert np.array_equal(got.view(np.uint32), golden[f"gguf{gid}_dequant_bits"])
+    out = np.zeros(numel, np.float32)
+    assert orc.orc_gguf_dequantize(gid, ob.p(blocks), ob.p(out), bs // 2) == -1          # not a whole block
+    if ref is not None:
+        rng = np.random.default_rng(gid)
+        fresh = rng.integers(0, 256, 64 * bb, dtype=np.uint8)
+        a, b = _dq(ob, orc, gid, fresh, 64 * bs), np.empty(64 * bs, np.float32)
+        assert ref.ref_gguf_dequantize(gid, ob.p(fresh), ob.p(b), b.size) == 0
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))                     # any bytes, NaN scales included
+        assert ref.ref_gguf_quant_block_size(gid) == bs and ref.ref_gguf_quant_type_size(gid) == bb
+
+
+@pytest.mark.parametrize("tag", ["b16", "b4", "straddle"])
+def test_qlora_small_block_shapes_match_golden(ob, orc, golden, tag):
+    """The quantized Linear at the block sizes C-ML's own tests use (tests/test_qlora.c:174,332,453:
+    16 and 4) and with a block that straddles two weight rows."""
+    n_out, n_in, block, rank, M = (int(v) for v in golden[f"qlora_{tag}_cfg"])
+    W, x, A, B = (np.ascontiguousarray(golden[f"qlora_{tag}_{k}"]) for k in ("W", "x", "A", "B"))
+    ns = (W.size + block - 1) // block
+    packed, scales = np.zeros((W.size + 1) // 2, np.uint8), np.zeros(ns, np.float32)
+    assert orc.orc_nf4_quantize(ob.p(W), W.size, block, ob.p(packed), ob.p(scales)) == ns
+    y = np.empty((M, n_out), np.float32)
+    assert orc.orc_qlora_forward(ob.p(x), M, n_in, n_out, ob.p(packed), ob.p(scales), ns, block, ob.p(A), ob.p(B), rank, 4.0 / rank, ob.p(y)) == 0
+    assert rel_err_inf(y, golden[f"qlora_{tag}_y"]) < 1e-5

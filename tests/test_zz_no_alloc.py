@@ -13,9 +13,10 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
-def test_noalloc_matches_regular_entry_point_twice(pkg, synth, ob, orc, torch_dev, kind):
+@pytest.mark.parametrize("K", [1024, 1056])               # the tensor-core kernel, and (K % 256 != 0) the dp4a kernel
+def test_noalloc_matches_regular_entry_point_twice(pkg, synth, ob, orc, torch_dev, kind, K):
     rng = np.random.default_rng(4242)
-    N, K = 515, 1024
+    N = 515
     W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
     for call, M in enumerate((2, 1)):                     # two calls in a row, different activations
         x = rng.standard_normal((M, K)).astype(np.float32)
@@ -28,6 +29,26 @@ def test_noalloc_matches_regular_entry_point_twice(pkg, synth, ob, orc, torch_de
         got, want = y_new.cpu().numpy(), y_ref.cpu().numpy()
         assert rel_err(got, want) <= 2e-3, f"call {call}: differs from cmlb200_gemv"
         assert rel_err(got, ob.linear_nt(orc, x, Wf)) <= 2e-3, f"call {call}: differs from the oracle"
+
+
+def test_noalloc_large_accepted_case_allocates_nothing(pkg, synth, ob, orc, torch_dev):
+    """Four rows of 28672 activations (LLaMA-70B's FFN width) use 401 KB of the 512 KiB array. Once
+    the first call on the device has looked the array up, a call leaves the device's free memory
+    exactly as it found it."""
+    rng = np.random.default_rng(4243)
+    N, K, M = 48, 28672, 4
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    d_x = to_dev(x, torch_dev)
+    y = torch.zeros((M, N), dtype=torch.float32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_gemv_noalloc(W.q, d_x.data_ptr(), y.data_ptr(), M, stream_ptr()), "cmlb200_gemv_noalloc")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    y.zero_()
+    pkg.check(pkg.lib.cmlb200_gemv_noalloc(W.q, d_x.data_ptr(), y.data_ptr(), M, stream_ptr()), "cmlb200_gemv_noalloc")
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+    assert rel_err(y.cpu().numpy(), ob.linear_nt(orc, x, Wf)) <= 2e-3
 
 
 def test_noalloc_rejects_what_does_not_fit(pkg, torch_dev):
