@@ -631,7 +631,7 @@ static int proj_residual_bf16(DevModel* d, const cmlb200_qmat* W, const uint16_t
  * mode 0: one sequence (`seq`), consecutive positions; mode 1: one token for each of `rows`
  * sequences. plan_limit bounds the cache positions the call may touch (sizes the attention
  * splits); logits for all rows land in d->logits. */
-static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan_limit, int only_layer) {
+static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan_limit, int only_layer, int with_head) {
     const CMLLLaMAModel* m = d->key;
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
@@ -723,6 +723,10 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
         }
     }
     if (only_layer >= 0) return 0;              /* cml_llama_layer_forward: no head, positions stay where they are */
+    if (!with_head) {                           /* cache fill only (cml_llama_prefill_sequence): nobody reads these logits */
+        DEV(cmlb200_advance_rows(d->d_cur, rows, mode, seq, st));
+        return 0;
+    }
     if (tiny) {
         DEV(cmlb200_gemv_rmsnorm(&d->lm_head, NULL, d->h, (const uint16_t*)d->fnorm, c->rms_norm_eps, d->logits, rows, 0, st));
     } else if (skinny) {
@@ -738,10 +742,12 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
 }
 
 static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_limit) {
-    return enqueue_forward_ex(d, rows, mode, seq, plan_limit, -1);
+    return enqueue_forward_ex(d, rows, mode, seq, plan_limit, -1, 1);
 }
 
-static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows, int mode, int seq, const char* who) {
+/* One forward call. with_logits: the fp32 logits of every row come back as a host tensor (what
+ * C-ML's forward returns); without, the head is skipped and a 1 x 1 placeholder is returned. */
+static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows, int mode, int seq, int with_logits, const char* who) {
     DevModel* d = dm_find(model);
     if (!model_ready(model, d)) { LOG_ERROR("%s: weights are not loaded", who); return NULL; }
     const CMLLLaMAConfig* c = &model->config;
@@ -757,12 +763,12 @@ static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows,
         LOG_ERROR("%s: cache overflow (%d > %d)", who, max_pos, c->max_seq_len);
         return NULL;
     }
-    int shape[2] = {rows, c->vocab_size};
-    Tensor* out = cml_tensor_alloc(DTYPE_FLOAT32, shape, 2, false);
+    int shape[2] = {with_logits ? rows : 1, with_logits ? c->vocab_size : 1};
+    Tensor* out = cml_tensor_alloc(DTYPE_FLOAT32, shape, 2, !with_logits);
     if (!out) return NULL;
     if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_tokens, token_ids, (size_t)rows * 4, d->stream), who) ||
-        enqueue_forward(d, rows, mode, seq, max_pos - 1) ||
-        CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->logits, (size_t)rows * c->vocab_size * 4, d->stream), who) ||
+        enqueue_forward_ex(d, rows, mode, seq, max_pos - 1, -1, with_logits) ||
+        (with_logits && CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->logits, (size_t)rows * c->vocab_size * 4, d->stream), who)) ||
         CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) {
         tensor_free(out);
         return NULL;
@@ -778,17 +784,17 @@ static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows,
 Tensor* cml_llama_forward(CMLLLaMAModel* model, const int* token_ids, int seq_len) {
     if (!model || !token_ids || seq_len <= 0) { LOG_ERROR("cml_llama_forward: invalid arguments"); return NULL; }
     if (!model->embed_tokens) { LOG_ERROR("cml_llama_forward: embed_tokens not loaded"); return NULL; }
-    return run_forward(model, token_ids, seq_len, 0, 0, "cml_llama_forward");
+    return run_forward(model, token_ids, seq_len, 0, 0, 1, "cml_llama_forward");
 }
 
 Tensor* cml_llama_forward_batch(CMLLLaMAModel* model, const int* token_ids, int batch) {
     if (!model || !token_ids || batch <= 0) { LOG_ERROR("cml_llama_forward_batch: invalid arguments"); return NULL; }
-    return run_forward(model, token_ids, batch, 1, 0, "cml_llama_forward_batch");
+    return run_forward(model, token_ids, batch, 1, 0, 1, "cml_llama_forward_batch");
 }
 
 int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_ids, int seq_len) {
     if (!model || !token_ids || seq_len <= 0 || seq < 0) { LOG_ERROR("cml_llama_prefill_sequence: invalid arguments"); return -1; }
-    Tensor* t = run_forward(model, token_ids, seq_len, 0, seq, "cml_llama_prefill_sequence");
+    Tensor* t = run_forward(model, token_ids, seq_len, 0, seq, 0, "cml_llama_prefill_sequence");
     if (!t) return -1;
     tensor_free(t);
     return 0;
@@ -1002,7 +1008,7 @@ Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tens
     int ok = !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->h, hidden->data, bytes, d->stream), who) &&
              !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &start_pos, sizeof(int), d->stream), who) &&
              !CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who) &&          /* start_pos is a stack variable */
-             !enqueue_forward_ex(d, rows, 0, 0, start_pos + rows - 1, li) &&
+             !enqueue_forward_ex(d, rows, 0, 0, start_pos + rows - 1, li, 0) &&
              !CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->h, bytes, d->stream), who);
     /* put the model's own position back whatever happened */
     if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &saved, sizeof(int), d->stream), who) || CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) ok = 0;

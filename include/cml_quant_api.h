@@ -355,7 +355,8 @@ int cml_llama_set_options(CMLLLaMAModel* model, int flags, int max_batch);
 /* One decode step for `batch` independent sequences (each with its own cache and position),
  * one new token each; logits [batch, vocab]. C-ML's forward is single-sequence only. */
 Tensor* cml_llama_forward_batch(CMLLLaMAModel* model, const int* token_ids, int batch);
-/* Prefill sequence `seq` of a batch with its prompt (positions start at 0 for that sequence). */
+/* Prefill sequence `seq` of a batch with its prompt (positions continue where that sequence stands).
+ * Fills the caches only: no logits are produced (the vocabulary projection is skipped). */
 int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_ids, int seq_len);
 /* Greedy decoding kept on the device: feeds each step's arg-max back as the next input for
  * `steps` steps (all `batch` sequences), writes the chosen ids [steps, batch] to out_tokens and
