@@ -69,6 +69,8 @@ _sig("cmlb200_qkv_rope_append", ci, vp, ci, vp, vp, ci, ci, ci, ci, C.c_float, c
 _sig("cmlb200_attention_decode_scratch_bytes", sz, ci, ci, ci, ci)
 _sig("cmlb200_attention_decode", ci, vp, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, vp)
 _sig("cmlb200_rope_table", ci, vp, ci, ci, C.c_float, vp, vp)
+_sig("cmlb200_argmax", ci, vp, ci, ci, vp, vp)
+_sig("cmlb200_embed_f16", ci, vp, vp, ci, ci, ci, vp, vp)
 _sig("cmlb200_tiles_bytes", sz, ci, ci, ci)
 _sig("cmlb200_repack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_unrepack_tiles", ci, ci, vp, ci, ci, vp)

@@ -34,7 +34,18 @@ __global__ void embed_kernel(const __half* __restrict__ table, const int* __rest
     int t = tokens[r];
     if (t < 0 || t >= vocab) t = 0;
     const __half* src = table + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)r * hidden + i] = __half2float(src[i]);
+    float* dst = out + (size_t)r * hidden;
+    if ((hidden & 7) == 0) {                               // 16 bytes of fp16 in, 32 bytes of fp32 out per thread and pass
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < hidden; i += gridDim.y * blockDim.x * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&v.z)), d = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+            *reinterpret_cast<float4*>(dst + i) = make_float4(a.x, a.y, b.x, b.y);
+            *reinterpret_cast<float4*>(dst + i + 4) = make_float4(c.x, c.y, d.x, d.y);
+        }
+    } else {
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) dst[i] = __half2float(src[i]);
+    }
 }
 
 // ---- RMSNorm: x * (1 / sqrt(mean(x^2) + eps)) * w, fp16 weight, fp32 or bf16 output
@@ -459,39 +470,99 @@ attention_decode_kernel(const float* __restrict__ qkv, int stride, KV* __restric
 }
 
 // ---- greedy pick: first index holding the strict maximum of each row
-__global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
+__device__ __forceinline__ void argmax_take(float& bv, int& bi, float v, int i) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }          // first index of the strict maximum; NaN never wins
+}
+__device__ __forceinline__ void argmax_warp(float& bv, int& bi) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        argmax_take(bv, bi, ov, oi);
     }
+}
+// One cluster of ARGMAX_CTAS CTAs per row: every CTA scans a contiguous slice of the row with
+// 16-byte loads, the slice winners meet in the shared memory of the cluster's first CTA
+// (distributed shared memory), which picks the row's winner. No global scratch, fixed order.
+constexpr int ARGMAX_CTAS = 8, ARGMAX_THREADS = 256;
+__global__ void __cluster_dims__(ARGMAX_CTAS, 1, 1) __launch_bounds__(ARGMAX_THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out, float2* __restrict__ out_pair, int index_offset) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float sv[ARGMAX_THREADS / 32];
+    __shared__ int si[ARGMAX_THREADS / 32];
+    __shared__ float cv[ARGMAX_CTAS];
+    __shared__ int ci[ARGMAX_CTAS];
+    const int part = blockIdx.x % ARGMAX_CTAS, r = blockIdx.x / ARGMAX_CTAS;
+    const float* row = logits + (size_t)r * vocab;
+    const int per = ((vocab + ARGMAX_CTAS - 1) / ARGMAX_CTAS + 3) & ~3;
+    const int lo = min(vocab, part * per), hi = min(vocab, lo + per);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if ((vocab & 3) == 0 && ((uintptr_t)row & 15) == 0) {
+        for (int i = lo + threadIdx.x * 4; i < hi; i += ARGMAX_THREADS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            argmax_take(bv, bi, v.x, i); argmax_take(bv, bi, v.y, i + 1);
+            argmax_take(bv, bi, v.z, i + 2); argmax_take(bv, bi, v.w, i + 3);
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) argmax_take(bv, bi, row[i], i);
+    }
+    argmax_warp(bv, bi);
     if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
     if (threadIdx.x < 32) {
-        const int nw = blockDim.x >> 5;
-        bv = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
-        bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        bv = threadIdx.x < ARGMAX_THREADS / 32 ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < ARGMAX_THREADS / 32 ? si[threadIdx.x] : 0x7fffffff;
+        argmax_warp(bv, bi);
+        if (threadIdx.x == 0) {                            // this slice's winner into slot `part` of CTA 0's arrays
+            uint32_t dv, di;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dv) : "r"((uint32_t)__cvta_generic_to_shared(&cv[part])), "r"(0));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(di) : "r"((uint32_t)__cvta_generic_to_shared(&ci[part])), "r"(0));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dv), "f"(bv) : "memory");
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(di), "r"(bi) : "memory");
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (part == 0 && threadIdx.x < 32) {
+        bv = threadIdx.x < ARGMAX_CTAS ? cv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < ARGMAX_CTAS ? ci[threadIdx.x] : 0x7fffffff;
+        argmax_warp(bv, bi);
+        if (threadIdx.x == 0) {
+            if (out) out[r] = (bi == 0x7fffffff) ? 0 : bi;
+            // (value, global index) of this slice of a vocabulary split over ranks; an empty result keeps -inf
+            if (out_pair) out_pair[r] = make_float2(bv, __int_as_float(bi == 0x7fffffff ? 0x7fffffff : bi + index_offset));
+        }
     }
 }
+
+// Winner per row among `parts` (value, index) candidates laid out [part][row]: greatest value, lowest
+// index among equals (the candidates come from consecutive slices of one row, so this is the row's
+// first strict maximum).
+__global__ void argmax_merge_kernel(const float2* __restrict__ pairs, int parts, int rows, int* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int q = 0; q < parts; q++) {
+        const float2 c = pairs[(size_t)q * rows + r];
+        argmax_take(bv, bi, c.x, __float_as_int(c.y));
+    }
+    out[r] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// dst[row][part * w + j] = src[part][row][j]: the slices of a row gathered from all ranks, side by side.
+__global__ void gather_columns_kernel(const float* __restrict__ src, int parts, int rows, int w, float* __restrict__ dst) {
+    const size_t total = (size_t)parts * rows * w, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int j = (int)(i % w), row = (int)((i / w) % rows), part = (int)(i / ((size_t)w * rows));
+        dst[((size_t)row * parts + part) * w + j] = src[i];
+    }
+}
+
 
 // ---- row bookkeeping kept on the device so that a decode step can be replayed as a CUDA graph
 // mode 0: sequence `seq`, `rows` consecutive positions starting at cur_len[seq] (prefill / single decode)
@@ -591,7 +662,8 @@ inline int ew_grid(size_t n) {
 extern "C" int cmlb200_embed_f16(const uint16_t* d_table_f16, const int* d_tokens, int rows, int hidden, int vocab,
                                  float* d_out, void* stream) {
     CMLB_REQUIRE(d_table_f16 && d_tokens && d_out && rows > 0 && hidden > 0 && vocab > 0, "cmlb200_embed_f16: bad argument");
-    CMLB_CUDA(launch_dep(embed_kernel, dim3(rows), dim3(256), as_stream(stream), (const __half*)d_table_f16, d_tokens, hidden, vocab, d_out));
+    const int slices = hidden >= 4096 ? 2 : 1;             // two CTAs per row once a row is 8 KB of fp16
+    CMLB_CUDA(launch_dep(embed_kernel, dim3(rows, slices), dim3(256), as_stream(stream), (const __half*)d_table_f16, d_tokens, hidden, vocab, d_out));
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
@@ -766,7 +838,30 @@ extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* 
 
 extern "C" int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream) {
     CMLB_REQUIRE(d_logits && d_out && rows > 0 && vocab > 0, "cmlb200_argmax: bad argument");
-    CMLB_CUDA(launch_dep(argmax_kernel, dim3(rows), dim3(1024), as_stream(stream), d_logits, vocab, d_out));
+    CMLB_CUDA(launch_dep(argmax_kernel, dim3(rows * ARGMAX_CTAS), dim3(ARGMAX_THREADS), as_stream(stream), d_logits, vocab, d_out, (float2*)nullptr, 0));
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_argmax_slice(const float* d_logits, int rows, int width, int index_offset, float* d_pairs, void* stream) {
+    CMLB_REQUIRE(d_logits && d_pairs && rows > 0 && width > 0 && index_offset >= 0, "cmlb200_argmax_slice: bad argument");
+    CMLB_CUDA(launch_dep(argmax_kernel, dim3(rows * ARGMAX_CTAS), dim3(ARGMAX_THREADS), as_stream(stream), d_logits, width, (int*)nullptr,
+                         reinterpret_cast<float2*>(d_pairs), index_offset));
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_argmax_merge(const float* d_pairs, int parts, int rows, int* d_out, void* stream) {
+    CMLB_REQUIRE(d_pairs && d_out && parts > 0 && rows > 0, "cmlb200_argmax_merge: bad argument");
+    CMLB_CUDA(launch_dep(argmax_merge_kernel, dim3((rows + 63) / 64), dim3(64), as_stream(stream), reinterpret_cast<const float2*>(d_pairs), parts, rows, d_out));
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
+extern "C" int cmlb200_gather_columns(const float* d_src, int parts, int rows, int width, float* d_dst, void* stream) {
+    CMLB_REQUIRE(d_src && d_dst && parts > 0 && rows > 0 && width > 0, "cmlb200_gather_columns: bad argument");
+    const size_t total = (size_t)parts * rows * width;
+    gather_columns_kernel<<<(unsigned)min((size_t)2368, (total + 255) / 256), 256, 0, as_stream(stream)>>>(d_src, parts, rows, width, d_dst);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }

@@ -54,6 +54,10 @@ typedef struct DevModel {
     void* stream;
     int qkv_w;                             /* qw_l + 2 * kvw_l */
     float *h, *nrm, *qkv, *att, *ffn, *g, *u, *tmp, *logits, *att_scratch, *rope_cs;
+    /* vocabulary projection split by rows over the ranks (vocab % tp == 0): this rank's slice of
+     * the logits, the slices of all ranks as gathered, and the (value, index) pairs of the greedy pick */
+    int vocab_l;
+    float *logits_l, *logits_g, *pairs;
     uint16_t *b_a, *b_b, *b_c, *b_d;       /* bf16 staging of the prefill path */
     int *d_tokens, *d_cur, *row_seq, *row_pos, *row_limit, *d_hist;
     int* h_cur;
@@ -142,7 +146,7 @@ static void dm_destroy(DevModel* d) {
     }
     qmat_free(&d->lm_head);
     void* bufs[] = {d->embed, d->fnorm, d->kc, d->vc, d->h, d->nrm, d->qkv, d->att, d->ffn, d->g, d->u, d->tmp,
-                    d->logits, d->att_scratch, d->rope_cs, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
+                    d->logits, d->logits_l, d->logits_g, d->pairs, d->att_scratch, d->rope_cs, d->b_a, d->b_b, d->b_c, d->b_d, d->d_tokens, d->d_cur, d->row_seq,
                     d->row_pos, d->row_limit, d->d_hist};
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
@@ -290,6 +294,12 @@ static int dm_alloc_buffers(DevModel* d) {
     DEV(cmlb200_malloc((void**)&d->u, (size_t)SKINNY_ROWS * d->inter_l * 4));
     DEV(cmlb200_malloc((void**)&d->tmp, R * H * 4));
     DEV(cmlb200_malloc((void**)&d->logits, R * c->vocab_size * 4));
+    d->vocab_l = (d->tp > 1 && c->vocab_size % d->tp == 0) ? c->vocab_size / d->tp : c->vocab_size;
+    if (d->vocab_l != c->vocab_size) {
+        DEV(cmlb200_malloc((void**)&d->logits_l, R * d->vocab_l * 4));
+        DEV(cmlb200_malloc((void**)&d->logits_g, R * c->vocab_size * 4));
+        DEV(cmlb200_malloc((void**)&d->pairs, (size_t)(d->tp + 1) * SKINNY_ROWS * 8));
+    }
     DEV(cmlb200_malloc((void**)&d->b_a, R * (wide > (size_t)H ? wide : (size_t)H) * 2));
     DEV(cmlb200_malloc((void**)&d->b_b, R * (wide > (size_t)c->vocab_size ? wide : (size_t)c->vocab_size) * 2));
     DEV(cmlb200_malloc((void**)&d->b_c, R * wide * 2));
@@ -497,7 +507,8 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
                 case SLOT_G: out_f = I; in_f = H; dst = &d->L[layer].wg; pub = &model->layers[layer]->gate_proj; break;
                 case SLOT_U: out_f = I; in_f = H; dst = &d->L[layer].wu; pub = &model->layers[layer]->up_proj; break;
                 case SLOT_D: out_f = H; in_f = I; by_rows = 0; dst = &d->L[layer].wd; pub = &model->layers[layer]->down_proj; break;
-                default: out_f = c->vocab_size; in_f = H; by_rows = -1; dst = &d->lm_head; pub = &model->lm_head; break;   /* replicated */
+                default:                                        /* split by rows when the vocabulary divides, else replicated */
+                    out_f = c->vocab_size; in_f = H; by_rows = d->vocab_l != c->vocab_size ? 1 : -1; dst = &d->lm_head; pub = &model->lm_head; break;
             }
             if (info->type != GGUF_TENSOR_Q4_0 && info->type != GGUF_TENSOR_Q8_0)
                 LOG_ERROR("cml_llama_load_gguf: tensor '%s' has GGUF type %d; projections must be Q4_0 or Q8_0", name, (int)info->type);
@@ -727,15 +738,21 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
         DEV(cmlb200_advance_rows(d->d_cur, rows, mode, seq, st));
         return 0;
     }
+    const int split_head = d->vocab_l != c->vocab_size;
+    float* lg = split_head ? d->logits_l : d->logits;          /* [rows, vocab_l] */
     if (tiny) {
-        DEV(cmlb200_gemv_rmsnorm(&d->lm_head, NULL, d->h, (const uint16_t*)d->fnorm, c->rms_norm_eps, d->logits, rows, 0, st));
+        DEV(cmlb200_gemv_rmsnorm(&d->lm_head, NULL, d->h, (const uint16_t*)d->fnorm, c->rms_norm_eps, lg, rows, 0, st));
     } else if (skinny) {
         DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, d->nrm, NULL, st));
-        if (lin_f32(d, &d->lm_head, d->nrm, d->logits, rows, 0)) return -1;
+        if (lin_f32(d, &d->lm_head, d->nrm, lg, rows, 0)) return -1;
     } else {
         DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
         DEV(cmlb200_gemm_bf16(&d->lm_head, d->b_a, d->b_b, rows, st));
-        DEV(cmlb200_bf16_to_f32(d->b_b, d->logits, (size_t)rows * c->vocab_size, st));
+        DEV(cmlb200_bf16_to_f32(d->b_b, lg, (size_t)rows * d->vocab_l, st));
+    }
+    if (split_head && with_head == 1) {                        /* full logits wanted: all-gather the slices, put them side by side */
+        if (cml_nccl_allgather_bytes(d->comm, d->logits_l, d->logits_g, (size_t)rows * d->vocab_l * 4, st)) return -1;
+        DEV(cmlb200_gather_columns(d->logits_g, d->tp, rows, d->vocab_l, d->logits, st));
     }
     DEV(cmlb200_advance_rows(d->d_cur, rows, mode, seq, st));
     return 0;
@@ -800,6 +817,24 @@ int cml_llama_prefill_sequence(CMLLLaMAModel* model, int seq, const int* token_i
     return 0;
 }
 
+/* One decode step and its greedy pick, enqueued: the next token of every sequence into d->d_tokens.
+ * With a split vocabulary projection no logits travel: every rank reduces its slice to one
+ * (value, index) pair per row, the pairs are all-gathered (8 bytes per row and rank) and merged. */
+static int enqueue_greedy_step(DevModel* d, int batch, int plan_limit) {
+    const CMLLLaMAConfig* c = &d->key->config;
+    void* st = d->stream;
+    if (d->vocab_l == c->vocab_size) {
+        if (enqueue_forward(d, batch, 1, 0, plan_limit)) return -1;
+        DEV(cmlb200_argmax(d->logits, batch, c->vocab_size, d->d_tokens, st));
+        return 0;
+    }
+    if (enqueue_forward_ex(d, batch, 1, 0, plan_limit, -1, 2)) return -1;
+    DEV(cmlb200_argmax_slice(d->logits_l, batch, d->vocab_l, d->rank * d->vocab_l, d->pairs, st));
+    if (cml_nccl_allgather_bytes(d->comm, d->pairs, d->pairs + 2 * SKINNY_ROWS, (size_t)batch * 8, st)) return -1;
+    DEV(cmlb200_argmax_merge(d->pairs + 2 * SKINNY_ROWS, d->tp, batch, d->d_tokens, st));
+    return 0;
+}
+
 int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int batch, int steps, int* out_tokens, float* elapsed_ms) {
     if (!model || !first_tokens || !out_tokens || batch <= 0 || steps <= 0) { LOG_ERROR("cml_llama_decode_greedy: invalid arguments"); return -1; }
     DevModel* d = dm_find(model);
@@ -826,15 +861,13 @@ int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int b
         if (d->graph) { cmlb200_graph_destroy(d->graph); d->graph = NULL; }
         /* The first step runs eagerly: first-use initialisation inside the kernels' launchers
          * (function attributes, scratch allocation) must not happen during stream capture. */
-        if (enqueue_forward(d, batch, 1, 0, plan_limit)) return -1;
-        DEV(cmlb200_argmax(d->logits, batch, c->vocab_size, d->d_tokens, st));
+        if (enqueue_greedy_step(d, batch, plan_limit)) return -1;
         DEV(cmlb200_memcpy_d2d(d->d_hist, d->d_tokens, (size_t)batch * 4, st));
         DEV(cmlb200_stream_sync(st));
         s0 = 1;
         if (steps > 1) {
             DEV(cmlb200_graph_begin(st));
-            int rc = enqueue_forward(d, batch, 1, 0, plan_limit);
-            if (!rc && CML_DEV_FAIL(cmlb200_argmax(d->logits, batch, c->vocab_size, d->d_tokens, st), "cml_llama_decode_greedy")) rc = -1;
+            int rc = enqueue_greedy_step(d, batch, plan_limit);
             void* g = NULL;
             if (CML_DEV_FAIL(cmlb200_graph_end(st, &g), "cml_llama_decode_greedy") || rc) { if (g) cmlb200_graph_destroy(g); return -1; }
             d->graph = g;

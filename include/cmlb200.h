@@ -241,6 +241,15 @@ int cmlb200_attention_decode(const float* d_qkv, int row_stride, void* d_kcache,
 int cmlb200_rope_table(const int* d_row_pos, int rows, int head_dim, float base, float* d_cs, void* stream);
 /* Greedy branch of cml_llama_sample_token (src/nn/llama.c:650-660): first index of the maximum. */
 int cmlb200_argmax(const float* d_logits, int rows, int vocab, int* d_out, void* stream);
+/* The same choice when the vocabulary projection is split over tensor-parallel ranks (C-ML has no
+ * counterpart: its lm_head is one matmul, src/nn/llama.c:598-606): every rank reduces its slice
+ * [rows, width] to one (value, index + index_offset) pair per row (8 bytes each, fp32 value and
+ * int32 index bits); the pairs of all ranks, laid out [rank][row], are merged to the row's first
+ * strict maximum. cmlb200_gather_columns puts gathered logit slices [rank][row][width] side by side
+ * as [row][ranks * width]. */
+int cmlb200_argmax_slice(const float* d_logits, int rows, int width, int index_offset, float* d_pairs, void* stream);
+int cmlb200_argmax_merge(const float* d_pairs, int parts, int rows, int* d_out, void* stream);
+int cmlb200_gather_columns(const float* d_src, int parts, int rows, int width, float* d_dst, void* stream);
 /* Row bookkeeping kept on the device so that a decode step replays as a CUDA graph.
  * mode 0: sequence `seq`, rows consecutive positions from cur_len[seq]; mode 1: rows sequences,
  * one token each at cur_len[b]. relative_mask reproduces C-ML's call-relative causal mask. */

@@ -7,7 +7,7 @@ import numpy as np
 TINY = dict(vocab=256, hidden=256, inter=512, layers=2, heads=4, kv_heads=2, max_seq=96)
 
 
-def build(entry, rng, cfg, path, qtype=2):
+def build(entry, rng, cfg, path, qtype=2, wscale=0.05):
     synth, ob = entry.load_synth(), entry.load_oracle_binding()
     orc = ob.load_orc()
 
@@ -17,7 +17,7 @@ def build(entry, rng, cfg, path, qtype=2):
         (orc.orc_quantize_q4_0 if qtype == 2 else orc.orc_quantize_q8_0)(ob.p(np.ascontiguousarray(w)), ob.p(blocks), nb)
         return blocks
 
-    tensors, store = synth.make_llama(rng, cfg, quantize, qtype)
+    tensors, store = synth.make_llama(rng, cfg, quantize, qtype, wscale)
     synth.write_gguf(path, tensors)
     return store
 

@@ -176,3 +176,43 @@ def test_tensor_parallel_building_blocks(pkg, torch_dev):
     pkg.lib.tensor_free(sh)
     for t in (tx, tw1, tb1, tw2, tb2):
         pkg.lib.tensor_free(t)
+
+
+@pytest.mark.parametrize("vocab", [32000, 1001, 7])
+def test_argmax_first_strict_maximum(pkg, ob, orc, torch_dev, vocab):
+    """Greedy branch of cml_llama_sample_token (src/nn/llama.c:650-660): the first index of the
+    strictly greatest logit; ties go to the lowest index, NaN never wins, rows are independent."""
+    import torch
+    rng = np.random.default_rng(vocab)
+    rows = 5
+    lg = rng.standard_normal((rows, vocab)).astype(np.float32)
+    lg[1, [vocab - 1, vocab // 2, 3 % vocab]] = 9.0                # a three-way tie
+    lg[2, :] = -np.inf                                             # nothing beats the first element
+    lg[3, 0] = np.nan
+    lg[3, vocab - 1] = 50.0
+    lg[4, vocab - 1] = 77.0                                        # the winner in the last slice
+    d = torch.from_numpy(lg).to(torch_dev)
+    out = torch.full((rows,), -1, dtype=torch.int32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_argmax(d.data_ptr(), rows, vocab, out.data_ptr(), None), "cmlb200_argmax")
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = [orc.orc_argmax_first(ob.p(np.ascontiguousarray(lg[r])), vocab) for r in (0, 1, 2, 4)]
+    assert [int(got[r]) for r in (0, 1, 2, 4)] == want
+    assert int(got[1]) == min(vocab - 1, vocab // 2, 3 % vocab) and int(got[2]) == 0 and int(got[3]) == vocab - 1
+
+
+@pytest.mark.parametrize("hidden", [4096, 8192, 100])
+def test_embedding_gather(pkg, torch_dev, hidden):
+    """embed_tokens_lookup (src/nn/llama.c:421-452): fp16 rows widened to fp32, out-of-range ids read row 0."""
+    import torch
+    rng = np.random.default_rng(hidden)
+    vocab = 50
+    table = rng.standard_normal((vocab, hidden)).astype(np.float16)
+    toks = np.array([3, 49, 0, -1, 50, 7], np.int32)
+    d_t, d_k = torch.from_numpy(table).to(torch_dev), torch.from_numpy(toks).to(torch_dev)
+    out = torch.zeros((len(toks), hidden), dtype=torch.float32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_embed_f16(d_t.data_ptr(), d_k.data_ptr(), len(toks), hidden, vocab, out.data_ptr(), None), "cmlb200_embed_f16")
+    torch.cuda.synchronize()
+    idx = np.where((toks < 0) | (toks >= vocab), 0, toks)
+    assert np.array_equal(out.cpu().numpy(), table[idx].astype(np.float32))
+

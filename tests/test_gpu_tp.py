@@ -37,7 +37,9 @@ torch.cuda.set_device(rank)
 # all-reduce launch more than one item, and 8 KV heads leave one per rank.
 cfg = llama_util.TINY if case == "tiny" else dict(vocab=256, hidden=4096, inter=11008, layers=2, heads=32, kv_heads=8, max_seq=96)
 path = os.path.join(work, "tp_model.gguf")
-store = llama_util.build(entry, np.random.default_rng(5), cfg, path if rank == 0 else os.path.join(work, f"scratch{rank}.gguf"))
+# weights of std 1/sqrt(hidden) keep the activations of the wide model of order one
+store = llama_util.build(entry, np.random.default_rng(5), cfg, path if rank == 0 else os.path.join(work, f"scratch{rank}.gguf"),
+                         wscale=0.05 if case == "tiny" else 1.0 / np.sqrt(cfg["hidden"]))
 dist.barrier()
 ident = torch.zeros(128, dtype=torch.uint8)
 if rank == 0:
