@@ -345,7 +345,7 @@ def llama_leg(pkg, synth, torch, dist, dev, rank, world, cfg, tag, prompt_len, n
             step_ms = dec_ms / new_tokens
             # bytes one decode step must read per GPU: this rank's weight shard, the head, the caches
             kv_bytes = 2 * cfg["layers"] * B * (prompt_len + new_tokens / 2) * cfg["kv_heads"] * hd * 2
-            step_bytes = wbytes / world + head_bytes + kv_bytes / world
+            step_bytes = wbytes / world + (head_bytes / world if cfg["vocab"] % world == 0 else head_bytes) + kv_bytes / world
             out[f"decode_tok_s_b{B}"] = B * new_tokens / (dec_ms * 1e-3)
             out[f"decode_ms_per_step_b{B}"] = step_ms
             out[f"decode_roofline_b{B}"] = {"bound": "hbm", "achieved": step_bytes / (step_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -380,6 +380,7 @@ def main():
                     help="small run for ncu: plain launches (no CUDA graph) of one kernel family only")
     ap.add_argument("--profile-m", type=int, default=1, help="rows of x of the --profile run")
     ap.add_argument("--profile-batch", type=int, default=1, help="batch size of --profile llama")
+    ap.add_argument("--only-gemm", action="store_true", help="run the NF4 prefill-GEMM leg alone")
     ap.add_argument("--cpu-leg", default=None, choices=["gemv", "llama"], help=argparse.SUPPRESS)
     ap.add_argument("--calls", type=int, default=3, help=argparse.SUPPRESS)
     ap.add_argument("--llama-steps", type=int, default=4, help=argparse.SUPPRESS)
@@ -544,6 +545,9 @@ def main():
             out[f"M{M}"] = {"us_per_call": per * 1e6, "tflops": tf, "roofline": rl}
         return out
 
+    if args.only_gemm:
+        print(json.dumps({"only_gemm": True, "nf4_gemm_4096x4096_bf16": nf4_gemm_leg((64, 512, 2048), max(2, args.steps // 8), 3)}))
+        return
     if args.profile == "gemm":
         nf4_gemm_leg((args.profile_m,), args.steps, args.warmup, ncopies=4, plain=True)
         print(json.dumps({"profile_run": True, "M": args.profile_m, "launches": (args.steps + args.warmup) * 4}))

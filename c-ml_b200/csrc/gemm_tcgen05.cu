@@ -9,12 +9,23 @@
 // activation rows (the MMA "N" side, operand B) and walks K in slabs of 64:
 //   warp 0      one lane issues TMA tensor loads of the bf16 activation slab (128B swizzle)
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x MT x 16, kind::f16)
-//   warps 2..9  stream the packed weights with cp.async into a private ring, expand them to
-//               bf16 (one fp32 multiply, one rounding) and store them in the canonical
+//   warps 2..9  expand the packed weights of a slab to bf16 and store them in the canonical
 //               K-major 128B-swizzled layout the MMA reads; afterwards they are the epilogue:
-//               tcgen05.ld the fp32 accumulators, round to bf16 and write Y.
-// No cluster multicast is used. Every wait on an mbarrier is bounded; on expiry the CTA
-// raises a status flag (readable with cmlb200_gemm_status) and drains instead of hanging.
+//               tcgen05.ld the fp32 accumulators, round to bf16 and write Y
+//   warp 10     one lane issues TMA tensor loads of the PACKED weights (a [128 rows x 32 or 64
+//               byte] box per slab, into a ring) and of their scales (a [128 rows x 8 slabs]
+//               box per 8 slabs), so that no warp gathers 128 different cache lines per slab
+// Expansion cost decides this kernel (a slab of 8192 weights per 128 x 256 x 64 MMA group):
+//   Q4_0  no table: a byte permute drops two nibbles into the mantissas of two bf16 halves
+//         (0x43nn = 128 + n), one packed subtract gives n - 8 exactly, one packed multiply
+//         applies the block scale: 15 instructions per 8 weights, nothing read from shared memory
+//   NF4   one 4-byte table entry per packed BYTE (both code values as bf16), the table kept in
+//         8 copies so that lanes rarely meet in a bank, one packed multiply by the block scale
+//   Q8_0  convert, multiply in fp32, round once
+// Q4_0 and NF4 therefore round twice (scale or code value to bf16, then the product); the path's
+// tolerance is 1e-2 of the largest output. No cluster multicast is used. Every wait on an
+// mbarrier is bounded; on expiry the CTA raises a status flag (cmlb200_gemm_status), waits for
+// its copies in flight, frees its tensor memory and returns.
 #include <cuda.h>
 #include "common.cuh"
 
@@ -22,30 +33,33 @@ namespace {
 
 constexpr int BN = 128;             // weight rows per CTA (MMA M)
 constexpr int BK = 64;              // K slab: 64 bf16 = one 128-byte swizzle row
-constexpr int STAGES = 4;
 constexpr int DQ_WARPS = 8;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
-constexpr int THREADS = 64 + DQ_THREADS;
+constexpr int THREADS = 64 + DQ_THREADS + 32;
 constexpr int A_BYTES = BN * BK * 2;            // 16 KB
 constexpr int B_BYTES_MAX = 256 * BK * 2;       // 32 KB
-// cp.async prefetch depth of the packed weights; 32-byte slots (Q8_0) get a shorter ring so
-// that every format fits the same 227 KB shared-memory budget
-template <int TYPE> struct Ring { static constexpr int depth = (TYPE == CMLB200_Q8_0) ? 2 : 4;
-                                  static constexpr int slot = (TYPE == CMLB200_Q8_0) ? 32 : 16; };
+constexpr int SC_SLABS = 8;                     // slabs per scale box (4 bytes per row and slab)
+constexpr int SC_BYTES = BN * SC_SLABS * 4;     // 4 KB
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-__device__ int g_gemm_status = 0;   // 0 = ok; otherwise a code identifying the wait that expired
-
-struct SmemLayout {
+template <int TYPE> struct Cfg {
+    static constexpr int RAWB = (TYPE == CMLB200_Q8_0) ? 64 : 32;       // packed bytes per row and slab
+    static constexpr int STAGES = (TYPE == CMLB200_Q8_0) ? 3 : 4;       // A/B stages
+    static constexpr int RSTAGES = 4;                                   // packed-weight ring
+    static constexpr int RAW_STAGE = BN * RAWB;
+    static constexpr int LUT_BYTES = (TYPE == CMLB200_NF4) ? 8 * 256 * 4 : 0;
     // offsets from the 1024-byte aligned base
-    static constexpr int a_off = 0;                                   // STAGES * A_BYTES
-    static constexpr int b_off = STAGES * A_BYTES;                    // STAGES * B_BYTES_MAX
-    static constexpr int raw_off = b_off + STAGES * B_BYTES_MAX;      // depth * DQ_THREADS * slot = 16 KB
-    static constexpr int sc_off = raw_off + 16384;                    // depth * DQ_THREADS * 4 <= 4 KB
-    static constexpr int lut_off = sc_off + 4096;                     // 256 * 8
-    static constexpr int bar_off = lut_off + 256 * 8;                 // barriers + tmem slot + abort flag
-    static constexpr int total = bar_off + 256;
+    static constexpr int a_off = 0;
+    static constexpr int b_off = STAGES * A_BYTES;
+    static constexpr int raw_off = b_off + STAGES * B_BYTES_MAX;
+    static constexpr int sc_off = raw_off + RSTAGES * RAW_STAGE;
+    static constexpr int lut_off = sc_off + 2 * SC_BYTES;
+    static constexpr int bar_off = lut_off + LUT_BYTES;
+    static constexpr int nbars = 3 * STAGES + 1 + 2 * RSTAGES + 4;
+    static constexpr int total = bar_off + 8 * nbars + 32;
 };
+
+__device__ int g_gemm_status = 0;   // 0 = ok; otherwise a code identifying the wait that expired
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -70,14 +84,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
     for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
         if (mbar_try(bar, parity)) return true;
-        if (it > 64) {
+        if (it > 1024) {
             if (*abort_flag) return false;
-            __nanosleep(128);
+            __nanosleep(32);
         }
     }
     *abort_flag = code;
     atomicCAS(&g_gemm_status, 0, code);
     return false;
+}
+// one lane polls; the verdict is made warp-uniform so that no lane is left behind at a __syncwarp
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, bool ok) {
+    int okl = ok ? 1 : 0;
+    if (ok && (threadIdx.x & 31) == 0) okl = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, okl, 0) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -119,29 +139,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ uint32_t bf162_mul(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf162_sub(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
 
 // Expand the 32 weights this thread owns (row n, K offset k0 + 32*h) into four 16-byte
-// chunks of bf16, in element order. `raw` points at this thread's slot of the packed ring.
+// chunks of bf16, in element order. `raw`: the thread's packed bytes (16, or 32 for Q8_0).
 template <int TYPE>
-__device__ __forceinline__ void expand32(const uint8_t* raw, float scale, const float2* lut, uint4 (&out)[4]) {
+__device__ __forceinline__ void expand32(const uint4 (&raw)[2], float scale, const uint32_t* lut, int lane, uint4 (&out)[4]) {
     if (TYPE == CMLB200_Q8_0) {
-        const uint4 v0 = *reinterpret_cast<const uint4*>(raw);
-        const uint4 v1 = *reinterpret_cast<const uint4*>(raw + 16);
-        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             uint32_t o[4];
@@ -155,59 +171,65 @@ __device__ __forceinline__ void expand32(const uint8_t* raw, float scale, const 
             }
             out[c] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-    } else {
-        const uint4 v = *reinterpret_cast<const uint4*>(raw);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        if (TYPE == CMLB200_NF4) {
-            // word i = bytes 4i..4i+3 = elements 8i..8i+7; lut[byte] = (high-nibble value, low-nibble value)
+    } else if (TYPE == CMLB200_NF4) {
+        // word i = bytes 4i..4i+3 = elements 8i..8i+7; lut[byte] = (bf16 of the high-nibble code, of the low-nibble code)
+        const uint32_t w[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+        const uint32_t s2 = pack_bf16(scale, scale);
+        const uint32_t* tab = lut + (lane & 7);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t o[4];
+        for (int c = 0; c < 4; c++) {
+            uint32_t o[4];
 #pragma unroll
-                for (int p = 0; p < 4; p++) {
-                    const float2 t = lut[(w[c] >> (8 * p)) & 0xFF];
-                    o[p] = pack_bf16(t.x * scale, t.y * scale);
-                }
-                out[c] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-        } else {
-            // Q4_0: byte j -> element j (low nibble) and j+16 (high nibble); lut[byte] = (low-8, high-8)
-            float lo[16], hi[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const float2 t = lut[(w[j >> 2] >> (8 * (j & 3))) & 0xFF];
-                lo[j] = t.x * scale;
-                hi[j] = t.y * scale;
-            }
-#pragma unroll
-            for (int c = 0; c < 2; c++) {
-                out[c] = make_uint4(pack_bf16(lo[8 * c], lo[8 * c + 1]), pack_bf16(lo[8 * c + 2], lo[8 * c + 3]),
-                                    pack_bf16(lo[8 * c + 4], lo[8 * c + 5]), pack_bf16(lo[8 * c + 6], lo[8 * c + 7]));
-                out[c + 2] = make_uint4(pack_bf16(hi[8 * c], hi[8 * c + 1]), pack_bf16(hi[8 * c + 2], hi[8 * c + 3]),
-                                        pack_bf16(hi[8 * c + 4], hi[8 * c + 5]), pack_bf16(hi[8 * c + 6], hi[8 * c + 7]));
-            }
+            for (int p = 0; p < 4; p++) o[p] = bf162_mul(tab[((w[c] >> (8 * p)) & 0xFF) << 3], s2);
+            out[c] = make_uint4(o[0], o[1], o[2], o[3]);
         }
+    } else {
+        // Q4_0: byte j -> element j (low nibble) and j+16 (high nibble). 0x43nn as bf16 is 128 + n.
+        const uint32_t w[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+        const uint32_t s2 = pack_bf16(scale, scale);
+        const uint32_t bias = 0x43084308u;                 // (136, 136): 128 + n - 136 = n - 8
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t l4 = w[i] & 0x0F0F0F0Fu, h4 = (w[i] >> 4) & 0x0F0F0F0Fu;
+            lo[2 * i] = bf162_mul(bf162_sub(__byte_perm(l4, 0x43434343u, 0x4140), bias), s2);
+            lo[2 * i + 1] = bf162_mul(bf162_sub(__byte_perm(l4, 0x43434343u, 0x4342), bias), s2);
+            hi[2 * i] = bf162_mul(bf162_sub(__byte_perm(h4, 0x43434343u, 0x4140), bias), s2);
+            hi[2 * i + 1] = bf162_mul(bf162_sub(__byte_perm(h4, 0x43434343u, 0x4342), bias), s2);
+        }
+        out[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        out[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        out[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        out[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
     }
 }
 
 // grid = (ceil(N/128), ceil(M/MT), splits). With splits > 1 each z-slice covers a K range and
 // writes fp32 partial sums [split][M][N] to `partial`; a second kernel reduces them.
-template <int TYPE>
+// SCTMA: the scales come as 4 bytes per row and slab (two fp16 of Q4_0 / Q8_0, or one fp32 of NF4
+// with block 64) through the tensor map `smap`; otherwise every expansion thread loads its own.
+template <int TYPE, bool SCTMA>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ qs,
-            const void* __restrict__ scales, __nv_bfloat16* __restrict__ y, float* __restrict__ partial,
-            int M, int N, int K, int MT, int nf4_block, int kb_per_split) {
+gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+            const __grid_constant__ CUtensorMap smap, const void* __restrict__ scales, __nv_bfloat16* __restrict__ y,
+            float* __restrict__ partial, int M, int N, int K, int MT, int nf4_block, int kb_per_split) {
+    using C = Cfg<TYPE>;
+    constexpr int STAGES = C::STAGES, RS = C::RSTAGES, RAWB = C::RAWB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bars = sbase + SmemLayout::bar_off;
-    // barrier slots (8 B each): full_a[S], full_b[S], empty[S], accum
+    const uint32_t bars = sbase + C::bar_off;
+    // barrier slots (8 B each)
     auto full_a = [&](int s) { return bars + 8 * s; };
     auto full_b = [&](int s) { return bars + 8 * (STAGES + s); };
     auto empty = [&](int s) { return bars + 8 * (2 * STAGES + s); };
     const uint32_t accum_bar = bars + 8 * (3 * STAGES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SmemLayout::bar_off + 8 * (3 * STAGES + 1));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::bar_off + 8 * (3 * STAGES + 1) + 8);
+    auto raw_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + s); };
+    auto raw_empty = [&](int s) { return bars + 8 * (3 * STAGES + 1 + RS + s); };
+    auto sc_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + 2 * RS + s); };
+    auto sc_empty = [&](int s) { return bars + 8 * (3 * STAGES + 1 + 2 * RS + 2 + s); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::bar_off + 8 * C::nbars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::bar_off + 8 * C::nbars + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * MT;
@@ -225,6 +247,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
             mbar_init(empty(s), 1);
         }
         mbar_init(accum_bar, 1);
+        for (int s = 0; s < RS; s++) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
+        for (int s = 0; s < 2; s++) { mbar_init(sc_full(s), 1); mbar_init(sc_empty(s), DQ_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -233,12 +257,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                      ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp >= 2) {
-        // byte -> (first, second) value table for the 4-bit formats
-        float2* lut = reinterpret_cast<float2*>(smem + SmemLayout::lut_off);
+    if (TYPE == CMLB200_NF4 && warp >= 2 && warp < 2 + DQ_WARPS) {
+        // byte -> (high-nibble code, low-nibble code) as two bf16, eight copies interleaved
+        uint32_t* lut = reinterpret_cast<uint32_t*>(smem + C::lut_off);
         const int b = threadIdx.x - 64;
-        if (TYPE == CMLB200_NF4) lut[b] = make_float2(kNF4[b >> 4], kNF4[b & 15]);
-        else lut[b] = make_float2((float)((b & 15) - 8), (float)((b >> 4) - 8));
+        const uint32_t e = pack_bf16(kNF4[b >> 4], kNF4[b & 15]);
+#pragma unroll
+        for (int c = 0; c < 8; c++) lut[b * 8 + c] = e;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -254,7 +279,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 const uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(empty(s), ph ^ 1, abort_flag, 1)) break;
                 mbar_expect_tx(full_b(s), (uint32_t)MT * BK * 2);
-                tma_load_2d(sbase + SmemLayout::b_off + s * B_BYTES_MAX, &xmap, (kb_begin + i) * BK, m0, full_b(s));
+                tma_load_2d(sbase + C::b_off + s * B_BYTES_MAX, &xmap, (kb_begin + i) * BK, m0, full_b(s));
                 issued = i + 1;
             }
             // never leave a bulk copy in flight behind an exiting CTA
@@ -272,8 +297,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 ok = mbar_wait(full_a(s), ph, abort_flag, 3) && mbar_wait(full_b(s), ph, abort_flag, 4);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = make_desc_sw128(sbase + SmemLayout::a_off + s * A_BYTES);
-                const uint64_t bdesc = make_desc_sw128(sbase + SmemLayout::b_off + s * B_BYTES_MAX);
+                const uint64_t adesc = make_desc_sw128(sbase + C::a_off + s * A_BYTES);
+                const uint64_t bdesc = make_desc_sw128(sbase + C::b_off + s * B_BYTES_MAX);
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; kk++)   // advance 32 bytes inside the swizzle row per K=16 step
                     umma_f16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (i | kk) ? 1u : 0u);
@@ -281,86 +306,87 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
             }
             umma_commit(accum_bar);   // arrives once every MMA issued so far has retired
         }
+    } else if (warp == 2 + DQ_WARPS) {
+        // ---------------- TMA producer: packed weights and their scales ----------------
+        if (lane == 0) {
+            int issued = 0, sc_issued = 0;
+            const int c_first = kb_begin / SC_SLABS;
+            for (int i = 0; i < nkb; i++) {
+                if (SCTMA && (i == 0 || (kb_begin + i) % SC_SLABS == 0)) {
+                    const int cs = sc_issued & 1;
+                    if (!mbar_wait(sc_empty(cs), ((sc_issued >> 1) & 1) ^ 1, abort_flag, 7)) break;
+                    mbar_expect_tx(sc_full(cs), SC_BYTES);
+                    tma_load_2d(sbase + C::sc_off + cs * SC_BYTES, &smap, (c_first + sc_issued) * (SC_SLABS * 4), n0, sc_full(cs));
+                    sc_issued++;
+                }
+                const int rs = i % RS;
+                if (!mbar_wait(raw_empty(rs), ((i / RS) & 1) ^ 1, abort_flag, 8)) break;
+                mbar_expect_tx(raw_full(rs), C::RAW_STAGE);
+                tma_load_2d(sbase + C::raw_off + rs * C::RAW_STAGE, &wmap, (kb_begin + i) * RAWB, n0, raw_full(rs));
+                issued = i + 1;
+            }
+            for (int i = max(0, issued - RS); i < issued; i++) mbar_wait(raw_full(i % RS), (i / RS) & 1, abort_flag, 9);
+            for (int c = max(0, sc_issued - 2); c < sc_issued; c++) mbar_wait(sc_full(c & 1), (c >> 1) & 1, abort_flag, 10);
+        }
     } else {
         // ---------------- weight expansion (operand A), then epilogue ----------------
         const int t = threadIdx.x - 64;
         const int r = t >> 1, h = t & 1;
-        const int n = min(n0 + r, N - 1);     // rows past N repeat the last row; never stored
-        constexpr int RAW = Ring<TYPE>::slot;
-        constexpr int RING = Ring<TYPE>::depth;
-        static_assert(RING * DQ_THREADS * RAW <= 16384, "packed-weight ring overflows its shared-memory region");
-        const uint8_t* wrow = qs + (size_t)n * ((size_t)K * RAW / 32);
-        uint8_t* raw_ring = smem + SmemLayout::raw_off;
-        uint32_t* sc_ring = reinterpret_cast<uint32_t*>(smem + SmemLayout::sc_off);
-        const float2* lut = reinterpret_cast<const float2*>(smem + SmemLayout::lut_off);
-
+        const int n = min(n0 + r, N - 1);     // rows past N hold zeros from the tensor load; never stored
         const int row_blocks = K / 32;
-        auto prefetch = [&](int i) {
-            const size_t kblk = (size_t)(kb_begin + i) * 2 + h;       // 32-element block index in the row
-            if (i < nkb && kblk < (size_t)row_blocks) {
-                const int slot = i % RING;
-                const uint32_t dst = smem_u32(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW);
-                cp_async16(dst, wrow + kblk * RAW);
-                if (RAW == 32) cp_async16(dst + 16, wrow + kblk * RAW + 16);
-                const uint32_t sdst = smem_u32(sc_ring + slot * DQ_THREADS + t);
-                if (TYPE == CMLB200_NF4) {
-                    const size_t e = (size_t)n * K + kblk * 32;
-                    cp_async4(sdst, reinterpret_cast<const float*>(scales) + e / (size_t)nf4_block);
-                } else {
-                    // the aligned 32-bit word that holds this block's fp16 scale (rows of an odd
-                    // number of blocks start on odd scale indices)
-                    const size_t sidx = (size_t)n * row_blocks + kblk;
-                    cp_async4(sdst, reinterpret_cast<const uint16_t*>(scales) + (sidx & ~(size_t)1));
-                }
-            }
-            cp_async_commit();
-        };
-#pragma unroll
-        for (int i = 0; i < RING - 1; i++) prefetch(i);
+        const uint32_t* lut = reinterpret_cast<const uint32_t*>(smem + C::lut_off);
+        const uint8_t* my_raw = smem + C::raw_off + r * RAWB + h * (RAWB / 2);
+        const int c_first = kb_begin / SC_SLABS;
 
         bool ok = true;
         for (int i = 0; i < nkb; i++) {
-            prefetch(i + RING - 1);
-            cp_async_wait<RING - 1>();
-            const int slot = i % RING;
-            const size_t kblk = (size_t)(kb_begin + i) * 2 + h;
-            uint4 out[4];
-            if (kblk < (size_t)row_blocks) {
-                float scale;
-                const uint32_t sw = sc_ring[slot * DQ_THREADS + t];
+            const int kb = kb_begin + i;
+            const size_t kblk = (size_t)kb * 2 + h;               // 32-element block index in the row
+            const bool in_row = kblk < (size_t)row_blocks;
+            // scales that do not come by tensor load are fetched before the waits, which hide part of the latency
+            float scale = 0.f;
+            if (!SCTMA && in_row) {
+                if (TYPE == CMLB200_NF4) scale = reinterpret_cast<const float*>(scales)[((size_t)n * K + kblk * 32) / (size_t)nf4_block];
+                else scale = cml_half_to_float(reinterpret_cast<const uint16_t*>(scales)[(size_t)n * row_blocks + kblk]);
+            }
+            const int rs = i % RS;
+            ok = warp_wait(raw_full(rs), (i / RS) & 1, abort_flag, 11, ok);
+            const int cl = kb / SC_SLABS - c_first, cs = cl & 1;
+            if (SCTMA && (i == 0 || kb % SC_SLABS == 0)) ok = warp_wait(sc_full(cs), (cl >> 1) & 1, abort_flag, 12, ok);
+            if (!ok) break;
+            uint4 raw[2];
+            raw[0] = *reinterpret_cast<const uint4*>(my_raw + rs * C::RAW_STAGE);
+            if (RAWB == 64) raw[1] = *reinterpret_cast<const uint4*>(my_raw + rs * C::RAW_STAGE + 16);
+            if (SCTMA) {
+                const uint32_t sw = *reinterpret_cast<const uint32_t*>(smem + C::sc_off + cs * SC_BYTES + r * (SC_SLABS * 4) + (kb % SC_SLABS) * 4);
                 if (TYPE == CMLB200_NF4) scale = __uint_as_float(sw);
-                else scale = cml_half_to_float((uint16_t)((((size_t)n * row_blocks + kblk) & 1) ? (sw >> 16) : (sw & 0xFFFF)));
-                expand32<TYPE>(raw_ring + ((size_t)slot * DQ_THREADS + t) * RAW, scale, lut, out);
-            } else {                                          // past the end of the row: zeros meet the zero-filled activations
+                else scale = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(raw_empty(rs));
+                if (SCTMA && (kb % SC_SLABS == SC_SLABS - 1 || i == nkb - 1)) mbar_arrive(sc_empty(cs));
+            }
+            uint4 out[4];
+            if (in_row) expand32<TYPE>(raw, scale, lut, lane, out);
+            else {                                            // past the end of the row: zeros meet the zero-filled activations
 #pragma unroll
                 for (int c = 0; c < 4; c++) out[c] = make_uint4(0u, 0u, 0u, 0u);
             }
-
             const int s = i % STAGES;
-            const uint32_t ph = (i / STAGES) & 1;
-            // one lane polls; the verdict is made warp-uniform so that no lane can be left
-            // behind at the __syncwarp below
-            int okl = ok ? 1 : 0;
-            if (ok && lane == 0) okl = mbar_wait(empty(s), ph ^ 1, abort_flag, 5) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-            if (ok) {
-                uint8_t* arow = smem + SmemLayout::a_off + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+            ok = warp_wait(empty(s), ((i / STAGES) & 1) ^ 1, abort_flag, 5, ok);
+            if (!ok) break;
+            uint8_t* arow = smem + C::a_off + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-                for (int c = 0; c < 4; c++)
-                    *reinterpret_cast<uint4*>(arow + (((4 * h + c) ^ (r & 7)) << 4)) = out[c];
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_a(s));
-            }
+            for (int c = 0; c < 4; c++)
+                *reinterpret_cast<uint4*>(arow + (((4 * h + c) ^ (r & 7)) << 4)) = out[c];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_a(s));
         }
-        cp_async_wait<0>();
 
         // ---- epilogue: D[n][m] (lane = weight row, column = activation row) -> Y[m][n]
-        {
-            int okl = ok ? 1 : 0;
-            if (ok && lane == 0) okl = mbar_wait(accum_bar, 0, abort_flag, 6) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-        }
+        ok = warp_wait(accum_bar, 0, abort_flag, 6, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int q = warp & 3;                 // the TMEM lane quadrant this warp may read
@@ -436,6 +462,28 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (x must be 16-byte aligned, K*2 a multiple of 16)", (int)cr);
+    // the packed weights as bytes [N][row_bytes], a box of 128 rows by one slab's bytes
+    using C = Cfg<TYPE>;
+    CUtensorMap wmap, smap;
+    const cuuint64_t row_bytes = (cuuint64_t)K * C::RAWB / BK;
+    const cuuint64_t wdims[2] = {row_bytes, (cuuint64_t)N};
+    const cuuint64_t wstr[1] = {row_bytes};
+    const cuuint32_t wbox[2] = {(cuuint32_t)C::RAWB, (cuuint32_t)BN};
+    cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W->qs, wdims, wstr, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled (weights) failed with %d", (int)cr);
+    // scales as bytes [N][4 per slab] when every row and slab has exactly four of them on a 16-byte row pitch:
+    // the two fp16 of Q4_0 / Q8_0, or the fp32 of NF4 with block 64; K % 256 == 0
+    const bool sctma = K % 256 == 0 && ((uintptr_t)W->scales & 15) == 0 && (TYPE != CMLB200_NF4 || W->block == 64);
+    smap = wmap;
+    if (sctma) {
+        const cuuint64_t sdims[2] = {(cuuint64_t)K / 16, (cuuint64_t)N};
+        const cuuint64_t sstr[1] = {(cuuint64_t)K / 16};
+        const cuuint32_t sbox[2] = {(cuuint32_t)(SC_SLABS * 4), (cuuint32_t)BN};
+        cr = enc(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, W->scales, sdims, sstr, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled (scales) failed with %d", (int)cr);
+    }
 
     const int gx = (N + BN - 1) / BN, gy = (M + MT - 1) / MT;
     const int total_kb = (K + BK - 1) / BK;
@@ -467,12 +515,18 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
             partial = g_ws[dev].ptr;
         }
     }
-    auto kern = gemm_kernel<TYPE>;
-    const int smem = SmemLayout::total + 1024;
-    static size_t attr_smem[kMaxDevices] = {};
-    CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_smem));
-    kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, (const uint8_t*)W->qs, W->scales, (__nv_bfloat16*)y, partial,
-                                                    M, N, K, MT, W->block, kb_per_split);
+    const int smem = C::total + 1024;
+    static_assert(C::total + 1024 <= 227 * 1024, "the stages do not fit shared memory");
+    static size_t attr_a[kMaxDevices] = {}, attr_b[kMaxDevices] = {};
+    if (sctma) {
+        auto kern = gemm_kernel<TYPE, true>;
+        CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_a));
+        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, (__nv_bfloat16*)y, partial, M, N, K, MT, W->block, kb_per_split);
+    } else {
+        auto kern = gemm_kernel<TYPE, false>;
+        CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_b));
+        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, (__nv_bfloat16*)y, partial, M, N, K, MT, W->block, kb_per_split);
+    }
     CMLB_LAUNCH_CHECK();
     if (splits > 1) {
         const size_t mn = (size_t)M * N;
