@@ -9,10 +9,14 @@
 // activation rows (the MMA "N" side, operand B) and walks K in slabs of 64:
 //   warp 0      one lane issues TMA tensor loads of the bf16 activation slab (128B swizzle)
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x MT x 16, kind::f16)
-//   warps 2..9  expand the packed weights of a slab to bf16 and store them in the canonical
-//               K-major 128B-swizzled layout the MMA reads; afterwards they are the epilogue:
-//               tcgen05.ld the fp32 accumulators, round to bf16 and write Y
-//   warp 10     one lane issues TMA tensor loads of the PACKED weights (a [128 rows x 32 or 64
+//   warps 2..17 expand the packed weights to bf16 and store them in the canonical K-major
+//               128B-swizzled layout the MMA reads. Expanding a slab is a chain of dependent
+//               steps (wait, load, convert, store, fence, signal) of about a microsecond whatever
+//               the number of threads sharing it, so the sixteen warps form four groups and
+//               group g takes slabs g, g+4, g+8, ...: four slabs are in flight at once.
+//               Afterwards the same warps are the epilogue: tcgen05.ld the fp32 accumulators,
+//               round to bf16 and write Y
+//   warp 18     one lane issues TMA tensor loads of the PACKED weights (a [128 rows x 32 or 64
 //               byte] box per slab, into a ring) and of their scales (a [128 rows x 8 slabs]
 //               box per 8 slabs), so that no warp gathers 128 different cache lines per slab
 // Expansion cost decides this kernel (a slab of 8192 weights per 128 x 256 x 64 MMA group):
@@ -33,7 +37,9 @@ namespace {
 
 constexpr int BN = 128;             // weight rows per CTA (MMA M)
 constexpr int BK = 64;              // K slab: 64 bf16 = one 128-byte swizzle row
-constexpr int DQ_WARPS = 8;
+constexpr int DQ_WARPS = 16;
+constexpr int DQ_GROUPS = 4;                    // slabs being expanded at once
+constexpr int GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
 constexpr int THREADS = 64 + DQ_THREADS + 32;
 constexpr int A_BYTES = BN * BK * 2;            // 16 KB
@@ -55,7 +61,7 @@ template <int TYPE> struct Cfg {
     static constexpr int sc_off = raw_off + RSTAGES * RAW_STAGE;
     static constexpr int lut_off = sc_off + 2 * SC_BYTES;
     static constexpr int bar_off = lut_off + LUT_BYTES;
-    static constexpr int nbars = 3 * STAGES + 1 + 2 * RSTAGES + 4;
+    static constexpr int nbars = 3 * STAGES + 1 + 2 * RSTAGES + 2;
     static constexpr int total = bar_off + 8 * nbars + 32;
 };
 
@@ -93,11 +99,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicCAS(&g_gemm_status, 0, code);
     return false;
 }
-// one lane polls; the verdict is made warp-uniform so that no lane is left behind at a __syncwarp
+// Every lane waits on the barrier itself (each reader of bytes that a tensor load wrote has to
+// observe the barrier's phase on its own); the verdict is then made warp-uniform so that no lane
+// is left behind at a __syncwarp.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, bool ok) {
-    int okl = ok ? 1 : 0;
-    if (ok && (threadIdx.x & 31) == 0) okl = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, okl, 0) != 0;
+    bool mine = ok;
+    if (ok) {
+        mine = false;
+        for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+            if (mbar_try(bar, parity)) { mine = true; break; }
+            if (it > 1024) {
+                if (*abort_flag) break;
+                __nanosleep(32);
+            }
+        }
+        if (!mine && !*abort_flag) { *abort_flag = code; atomicCAS(&g_gemm_status, 0, code); }
+    }
+    return __all_sync(0xffffffffu, mine);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -227,7 +245,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
     auto raw_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + s); };
     auto raw_empty = [&](int s) { return bars + 8 * (3 * STAGES + 1 + RS + s); };
     auto sc_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + 2 * RS + s); };
-    auto sc_empty = [&](int s) { return bars + 8 * (3 * STAGES + 1 + 2 * RS + 2 + s); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::bar_off + 8 * C::nbars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::bar_off + 8 * C::nbars + 8);
 
@@ -242,13 +259,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_a(s), DQ_WARPS);
+            mbar_init(full_a(s), GROUP_WARPS);
             mbar_init(full_b(s), 1);
             mbar_init(empty(s), 1);
         }
         mbar_init(accum_bar, 1);
-        for (int s = 0; s < RS; s++) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DQ_WARPS); }
-        for (int s = 0; s < 2; s++) { mbar_init(sc_full(s), 1); mbar_init(sc_empty(s), DQ_WARPS); }
+        for (int s = 0; s < RS; s++) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), GROUP_WARPS); }
+        for (int s = 0; s < 2; s++) mbar_init(sc_full(s), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -257,7 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
                      ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (TYPE == CMLB200_NF4 && warp >= 2 && warp < 2 + DQ_WARPS) {
+    if (TYPE == CMLB200_NF4 && threadIdx.x >= 64 && threadIdx.x < 64 + 256) {
         // byte -> (high-nibble code, low-nibble code) as two bf16, eight copies interleaved
         uint32_t* lut = reinterpret_cast<uint32_t*>(smem + C::lut_off);
         const int b = threadIdx.x - 64;
@@ -312,15 +329,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
             int issued = 0, sc_issued = 0;
             const int c_first = kb_begin / SC_SLABS;
             for (int i = 0; i < nkb; i++) {
+                // Slot of slab i - RS free: its group has read that slab's bytes AND its scales. Waits
+                // happen in slab order, so by now every slab up to i - RS is done with the scale box
+                // that the box loaded below replaces (it ended at least RS + 1 slabs ago).
+                const int rs = i % RS;
+                if (!mbar_wait(raw_empty(rs), ((i / RS) & 1) ^ 1, abort_flag, 8)) break;
                 if (SCTMA && (i == 0 || (kb_begin + i) % SC_SLABS == 0)) {
                     const int cs = sc_issued & 1;
-                    if (!mbar_wait(sc_empty(cs), ((sc_issued >> 1) & 1) ^ 1, abort_flag, 7)) break;
                     mbar_expect_tx(sc_full(cs), SC_BYTES);
                     tma_load_2d(sbase + C::sc_off + cs * SC_BYTES, &smap, (c_first + sc_issued) * (SC_SLABS * 4), n0, sc_full(cs));
                     sc_issued++;
                 }
-                const int rs = i % RS;
-                if (!mbar_wait(raw_empty(rs), ((i / RS) & 1) ^ 1, abort_flag, 8)) break;
                 mbar_expect_tx(raw_full(rs), C::RAW_STAGE);
                 tma_load_2d(sbase + C::raw_off + rs * C::RAW_STAGE, &wmap, (kb_begin + i) * RAWB, n0, raw_full(rs));
                 issued = i + 1;
@@ -330,56 +349,69 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
         }
     } else {
         // ---------------- weight expansion (operand A), then epilogue ----------------
-        const int t = threadIdx.x - 64;
-        const int r = t >> 1, h = t & 1;
-        const int n = min(n0 + r, N - 1);     // rows past N hold zeros from the tensor load; never stored
+        // group = which slabs (i % 4), tg = thread within the group; a thread expands two (row, half)
+        // items of its group's slab: rows tg/2 and 64 + tg/2, half tg & 1
+        const int dqw = warp - 2, grp = dqw % DQ_GROUPS, tg = (dqw / DQ_GROUPS) * 32 + lane;
+        const int h = tg & 1;
         const int row_blocks = K / 32;
         const uint32_t* lut = reinterpret_cast<const uint32_t*>(smem + C::lut_off);
-        const uint8_t* my_raw = smem + C::raw_off + r * RAWB + h * (RAWB / 2);
         const int c_first = kb_begin / SC_SLABS;
+        int chunk_seen = -1;
 
         bool ok = true;
-        for (int i = 0; i < nkb; i++) {
+        for (int i = grp; i < nkb; i += DQ_GROUPS) {
             const int kb = kb_begin + i;
             const size_t kblk = (size_t)kb * 2 + h;               // 32-element block index in the row
             const bool in_row = kblk < (size_t)row_blocks;
             // scales that do not come by tensor load are fetched before the waits, which hide part of the latency
-            float scale = 0.f;
+            float scale[2] = {0.f, 0.f};
             if (!SCTMA && in_row) {
-                if (TYPE == CMLB200_NF4) scale = reinterpret_cast<const float*>(scales)[((size_t)n * K + kblk * 32) / (size_t)nf4_block];
-                else scale = cml_half_to_float(reinterpret_cast<const uint16_t*>(scales)[(size_t)n * row_blocks + kblk]);
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int n = min(n0 + 64 * e + (tg >> 1), N - 1);
+                    if (TYPE == CMLB200_NF4) scale[e] = reinterpret_cast<const float*>(scales)[((size_t)n * K + kblk * 32) / (size_t)nf4_block];
+                    else scale[e] = cml_half_to_float(reinterpret_cast<const uint16_t*>(scales)[(size_t)n * row_blocks + kblk]);
+                }
             }
             const int rs = i % RS;
             ok = warp_wait(raw_full(rs), (i / RS) & 1, abort_flag, 11, ok);
             const int cl = kb / SC_SLABS - c_first, cs = cl & 1;
-            if (SCTMA && (i == 0 || kb % SC_SLABS == 0)) ok = warp_wait(sc_full(cs), (cl >> 1) & 1, abort_flag, 12, ok);
+            if (SCTMA && cl != chunk_seen) { ok = warp_wait(sc_full(cs), (cl >> 1) & 1, abort_flag, 12, ok); chunk_seen = cl; }
             if (!ok) break;
-            uint4 raw[2];
-            raw[0] = *reinterpret_cast<const uint4*>(my_raw + rs * C::RAW_STAGE);
-            if (RAWB == 64) raw[1] = *reinterpret_cast<const uint4*>(my_raw + rs * C::RAW_STAGE + 16);
-            if (SCTMA) {
-                const uint32_t sw = *reinterpret_cast<const uint32_t*>(smem + C::sc_off + cs * SC_BYTES + r * (SC_SLABS * 4) + (kb % SC_SLABS) * 4);
-                if (TYPE == CMLB200_NF4) scale = __uint_as_float(sw);
-                else scale = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
+            uint4 raw[2][2];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const uint8_t* src = smem + C::raw_off + rs * C::RAW_STAGE + (64 * e + (tg >> 1)) * RAWB + h * (RAWB / 2);
+                raw[e][0] = *reinterpret_cast<const uint4*>(src);
+                if (RAWB == 64) raw[e][1] = *reinterpret_cast<const uint4*>(src + 16);
+                if (SCTMA) {
+                    const uint32_t sw = *reinterpret_cast<const uint32_t*>(smem + C::sc_off + cs * SC_BYTES + (64 * e + (tg >> 1)) * (SC_SLABS * 4) + (kb % SC_SLABS) * 4);
+                    if (TYPE == CMLB200_NF4) scale[e] = __uint_as_float(sw);
+                    else scale[e] = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
+                }
             }
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(raw_empty(rs));
-                if (SCTMA && (kb % SC_SLABS == SC_SLABS - 1 || i == nkb - 1)) mbar_arrive(sc_empty(cs));
-            }
-            uint4 out[4];
-            if (in_row) expand32<TYPE>(raw, scale, lut, lane, out);
-            else {                                            // past the end of the row: zeros meet the zero-filled activations
+            if (lane == 0) mbar_arrive(raw_empty(rs));            // bytes and scales of this slab are in registers
+            uint4 out[2][4];
 #pragma unroll
-                for (int c = 0; c < 4; c++) out[c] = make_uint4(0u, 0u, 0u, 0u);
+            for (int e = 0; e < 2; e++) {
+                if (in_row) expand32<TYPE>(raw[e], scale[e], lut, lane, out[e]);
+                else {                                            // past the end of the row: zeros meet the zero-filled activations
+#pragma unroll
+                    for (int c = 0; c < 4; c++) out[e][c] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             const int s = i % STAGES;
             ok = warp_wait(empty(s), ((i / STAGES) & 1) ^ 1, abort_flag, 5, ok);
             if (!ok) break;
-            uint8_t* arow = smem + C::a_off + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-            for (int c = 0; c < 4; c++)
-                *reinterpret_cast<uint4*>(arow + (((4 * h + c) ^ (r & 7)) << 4)) = out[c];
+            for (int e = 0; e < 2; e++) {
+                const int r = 64 * e + (tg >> 1);
+                uint8_t* arow = smem + C::a_off + s * A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4*>(arow + (((4 * h + c) ^ (r & 7)) << 4)) = out[e][c];
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a(s));
@@ -390,9 +422,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int q = warp & 3;                 // the TMEM lane quadrant this warp may read
-            const int half = (warp - 2) >> 2;       // two warps share a quadrant and split the columns
+            const int part = (warp - 2) >> 2;       // four warps share a quadrant and split the columns
             const int nrow = n0 + q * 32 + lane;
-            for (int c0 = half * 32; c0 < MT; c0 += 64) {
+            for (int c0 = part * 32; c0 < MT; c0 += 32 * GROUP_WARPS) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 if (nrow < N) {

@@ -86,11 +86,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicCAS(&g_tc_status, 0, code);
     return false;
 }
-// one lane polls, the whole warp learns the verdict
+// Every lane waits on the barrier itself (each reader of bytes that a bulk copy wrote has to observe
+// the barrier's phase on its own); the verdict is then made warp-uniform.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, bool ok, int stage = -1) {
-    int okl = ok ? 1 : 0;
-    if (ok && (threadIdx.x & 31) == 0) okl = mbar_wait(bar, parity, abort_flag, code, stage) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, okl, 0) != 0;
+    bool mine = ok;
+    if (ok) {
+        mine = false;
+        for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+            if (mbar_try(bar, parity)) { mine = true; break; }
+            if (it > 4096) {
+                if (*abort_flag) break;
+                __nanosleep(32);
+            }
+        }
+        if (!mine && !*abort_flag) { *abort_flag = code; atomicCAS(&g_tc_status, 0, code); }
+    }
+    (void)stage;
+    return __all_sync(0xffffffffu, mine);
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
