@@ -69,6 +69,7 @@ _sig("cmlb200_qkv_rope_append", ci, vp, ci, vp, vp, ci, ci, ci, ci, C.c_float, c
 _sig("cmlb200_attention_decode_scratch_bytes", sz, ci, ci, ci, ci)
 _sig("cmlb200_attention_decode", ci, vp, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, vp)
 _sig("cmlb200_rope_table", ci, vp, ci, ci, C.c_float, vp, vp)
+_sig("cmlb200_attention_prefill", ci, vp, ci, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp, vp, vp)
 _sig("cmlb200_argmax", ci, vp, ci, ci, vp, vp)
 _sig("cmlb200_embed_f16", ci, vp, vp, ci, ci, ci, vp, vp)
 _sig("cmlb200_tiles_bytes", sz, ci, ci, ci)
@@ -78,6 +79,7 @@ _sig("cmlb200_gemv_tiles", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
 _sig("cmlb200_gemv_tiles_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_gemm_bf16", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemm_bf16_splitk", ci, C.POINTER(QMat), vp, vp, ci, ci, vp)
+_sig("cmlb200_gemm_bf16_ex", ci, C.POINTER(QMat), vp, ci, ci, vp, vp, vp)
 _sig("cmlb200_gemm_status", ci, C.POINTER(ci), ci)
 _sig("cmlb200_linear_nf4_general", ci, vp, vp, ci, ci, ci, ci, vp, ci, vp, vp)
 _sig("cmlb200_tp_ar_workspace_bytes", sz, sz)

@@ -222,6 +222,24 @@ __device__ __forceinline__ void expand32(const uint4 (&raw)[2], float scale, con
     }
 }
 
+// What happens to a finished output value (the sum over all of K) at flat index i of [M, N]:
+//   GEMM_OUT_BF16    stored as bf16                         (the plain product)
+//   GEMM_OUT_F32     stored as fp32                         (Q/K/V: RoPE and attention read fp32)
+//   GEMM_ACC_F32     added to an fp32 array                 (attention-out and FFN-down onto the residual,
+//                                                            src/nn/llama.c:523-530, 538-543)
+//   GEMM_SWIGLU_BF16 silu(gate[i]) * value stored as bf16   (the up projection finishing SwiGLU,
+//                                                            src/nn/llama.c:126-155; gate may be the output array)
+enum { GEMM_OUT_BF16 = 0, GEMM_OUT_F32 = 1, GEMM_ACC_F32 = 2, GEMM_SWIGLU_BF16 = 3 };
+__device__ __forceinline__ void epilogue_store(void* out, const __nv_bfloat16* gate, int mode, size_t i, float v) {
+    if (mode == GEMM_OUT_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else if (mode == GEMM_OUT_F32) static_cast<float*>(out)[i] = v;
+    else if (mode == GEMM_ACC_F32) static_cast<float*>(out)[i] += v;
+    else {
+        const float g = __bfloat162float(gate[i]);
+        static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * v);
+    }
+}
+
 // grid = (ceil(N/128), ceil(M/MT), splits). With splits > 1 each z-slice covers a K range and
 // writes fp32 partial sums [split][M][N] to `partial`; a second kernel reduces them.
 // SCTMA: the scales come as 4 bytes per row and slab (two fp16 of Q4_0 / Q8_0, or one fp32 of NF4
@@ -229,8 +247,9 @@ __device__ __forceinline__ void expand32(const uint4 (&raw)[2], float scale, con
 template <int TYPE, bool SCTMA>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-            const __grid_constant__ CUtensorMap smap, const void* __restrict__ scales, __nv_bfloat16* __restrict__ y,
-            float* __restrict__ partial, int M, int N, int K, int MT, int nf4_block, int kb_per_split) {
+            const __grid_constant__ CUtensorMap smap, const void* __restrict__ scales, void* __restrict__ out,
+            const __nv_bfloat16* __restrict__ gate, int mode, float* __restrict__ partial, int M, int N, int K, int MT,
+            int nf4_block, int kb_per_split) {
     using C = Cfg<TYPE>;
     constexpr int STAGES = C::STAGES, RS = C::RSTAGES, RAWB = C::RAWB;
     extern __shared__ uint8_t smem_raw[];
@@ -433,7 +452,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
                         const int m = m0 + c0 + j;
                         if (m < M && c0 + j < MT) {
                             if (partial) partial[((size_t)blockIdx.z * M + m) * N + nrow] = __uint_as_float(v[j]);
-                            else y[(size_t)m * N + nrow] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            else epilogue_store(out, gate, mode, (size_t)m * N + nrow, __uint_as_float(v[j]));
                         }
                     }
                 }
@@ -448,12 +467,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
     }
 }
 
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, size_t mn, int splits) {
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, const __nv_bfloat16* __restrict__ gate,
+                                     int mode, size_t mn, int splits) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += stride) {
         float s = 0.f;
         for (int z = 0; z < splits; z++) s += partial[(size_t)z * mn + i];
-        y[i] = __float2bfloat16_rn(s);
+        epilogue_store(out, gate, mode, i, s);
     }
 }
 
@@ -479,7 +499,8 @@ struct Workspace { float* ptr; size_t bytes; };
 Workspace g_ws[16] = {};
 
 template <int TYPE>
-int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, float* ws, int splits_forced, cudaStream_t st) {
+int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, void* y, const uint16_t* gate, int mode, int M, float* ws, int splits_forced,
+                cudaStream_t st) {
     const int N = W->rows, K = W->cols;
     int MT = M >= 256 ? 256 : ((M + 15) / 16) * 16;
     EncodeTiledFn enc;
@@ -553,37 +574,40 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, fl
     if (sctma) {
         auto kern = gemm_kernel<TYPE, true>;
         CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_a));
-        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, (__nv_bfloat16*)y, partial, M, N, K, MT, W->block, kb_per_split);
+        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, y, (const __nv_bfloat16*)gate, mode, partial, M, N, K, MT,
+                                                          W->block, kb_per_split);
     } else {
         auto kern = gemm_kernel<TYPE, false>;
         CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_b));
-        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, (__nv_bfloat16*)y, partial, M, N, K, MT, W->block, kb_per_split);
+        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, y, (const __nv_bfloat16*)gate, mode, partial, M, N, K, MT,
+                                                          W->block, kb_per_split);
     }
     CMLB_LAUNCH_CHECK();
     if (splits > 1) {
         const size_t mn = (size_t)M * N;
         int grid = (int)((mn + 255) / 256);
         if (grid > cmlb_num_sms() * 8) grid = cmlb_num_sms() * 8;
-        splitk_reduce_kernel<<<grid, 256, 0, st>>>(partial, (__nv_bfloat16*)y, mn, splits);
+        splitk_reduce_kernel<<<grid, 256, 0, st>>>(partial, y, (const __nv_bfloat16*)gate, mode, mn, splits);
         CMLB_LAUNCH_CHECK();
     }
     return CMLB200_OK;
 }
 
-int gemm_entry(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, float* ws, int splits, void* stream) {
+int gemm_entry(const cmlb200_qmat* W, const uint16_t* x, void* y, const uint16_t* gate, int mode, int M, float* ws, int splits, void* stream) {
     CMLB_REQUIRE(W && W->qs && W->scales && x && y, "cmlb200_gemm_bf16: NULL argument");
+    CMLB_REQUIRE(mode >= GEMM_OUT_BF16 && mode <= GEMM_SWIGLU_BF16 && (mode != GEMM_SWIGLU_BF16 || gate), "cmlb200_gemm_bf16_ex: bad output mode %d", mode);
     CMLB_REQUIRE(M >= 1, "cmlb200_gemm_bf16: M=%d must be positive", M);
     CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "cmlb200_gemm_bf16: cols=%d must be a positive multiple of 32", W->cols);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)W->qs & 15) == 0 && ((uintptr_t)W->scales & 3) == 0,
                  "cmlb200_gemm_bf16: x and the weight planes must be 16-byte aligned");
     cudaStream_t st = as_stream(stream);
     switch (W->type) {
-        case CMLB200_Q8_0: return launch_gemm<CMLB200_Q8_0>(W, x, y, M, ws, splits, st);
-        case CMLB200_Q4_0: return launch_gemm<CMLB200_Q4_0>(W, x, y, M, ws, splits, st);
+        case CMLB200_Q8_0: return launch_gemm<CMLB200_Q8_0>(W, x, y, gate, mode, M, ws, splits, st);
+        case CMLB200_Q4_0: return launch_gemm<CMLB200_Q4_0>(W, x, y, gate, mode, M, ws, splits, st);
         case CMLB200_NF4:
             CMLB_REQUIRE(W->block >= 32 && W->block % 32 == 0 && W->cols % W->block == 0,
                          "cmlb200_gemm_bf16: NF4 block size %d must be a multiple of 32 that divides cols", W->block);
-            return launch_gemm<CMLB200_NF4>(W, x, y, M, ws, splits, st);
+            return launch_gemm<CMLB200_NF4>(W, x, y, gate, mode, M, ws, splits, st);
         default: CMLB_REQUIRE(false, "cmlb200_gemm_bf16: unsupported weight type %d", W->type);
     }
     return CMLB200_EINVAL;
@@ -592,13 +616,18 @@ int gemm_entry(const cmlb200_qmat* W, const uint16_t* x, uint16_t* y, int M, flo
 }  // namespace
 
 extern "C" int cmlb200_gemm_bf16(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M, void* stream) {
-    return gemm_entry(W, d_x_bf16, d_y_bf16, M, nullptr, 0, stream);
+    return gemm_entry(W, d_x_bf16, d_y_bf16, nullptr, GEMM_OUT_BF16, M, nullptr, 0, stream);
+}
+
+extern "C" int cmlb200_gemm_bf16_ex(const cmlb200_qmat* W, const uint16_t* d_x_bf16, int M, int mode, void* d_out, const uint16_t* d_gate_bf16,
+                                    void* stream) {
+    return gemm_entry(W, d_x_bf16, d_out, d_gate_bf16, mode, M, nullptr, 0, stream);
 }
 
 extern "C" int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
                                         int splits, void* stream) {
     CMLB_REQUIRE(splits >= 1, "cmlb200_gemm_bf16_splitk: splits must be >= 1");
-    return gemm_entry(W, d_x_bf16, d_y_bf16, M, nullptr, splits, stream);
+    return gemm_entry(W, d_x_bf16, d_y_bf16, nullptr, GEMM_OUT_BF16, M, nullptr, splits, stream);
 }
 
 extern "C" int cmlb200_gemm_status(int* status, int reset) {

@@ -629,10 +629,10 @@ static int proj_residual_f32(DevModel* d, const cmlb200_qmat* W, const float* x,
 }
 
 static int proj_residual_bf16(DevModel* d, const cmlb200_qmat* W, const uint16_t* x, int rows) {
-    DEV(cmlb200_gemm_bf16(W, x, d->b_b, rows, d->stream));
     const size_t n = (size_t)rows * W->rows;
-    if (d->tp == 1) { DEV(cmlb200_add_bf16(d->h, d->b_b, n, d->stream)); return 0; }
-    DEV(cmlb200_bf16_to_f32(d->b_b, d->tmp, n, d->stream));
+    /* one GPU: the GEMM adds onto the fp32 residual in its epilogue; several: fp32 partial sums, all-reduce, add */
+    if (d->tp == 1) { DEV(cmlb200_gemm_bf16_ex(W, x, rows, CMLB200_GEMM_ACC_F32, d->h, NULL, d->stream)); return 0; }
+    DEV(cmlb200_gemm_bf16_ex(W, x, rows, CMLB200_GEMM_OUT_F32, d->tmp, NULL, d->stream));
     if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, n, d->stream)) return -1;
     DEV(cmlb200_add_f32(d->h, d->tmp, n, d->stream));
     return 0;
@@ -690,10 +690,17 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
             if (lin_f32(d, &L->wqkv, d->nrm, d->qkv, rows, 0)) return -1;
         } else {
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n1, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
-            DEV(cmlb200_gemm_bf16(&L->wqkv, d->b_a, d->b_b, rows, st));
-            DEV(cmlb200_bf16_to_f32(d->b_b, d->qkv, (size_t)rows * d->qkv_w, st));
+            DEV(cmlb200_gemm_bf16_ex(&L->wqkv, d->b_a, rows, CMLB200_GEMM_OUT_F32, d->qkv, NULL, st));
         }
-        if (fused_att) {
+        /* prompt-sized call on the bf16 path with an fp16 cache: tiled tensor-core attention, bf16 output
+         * straight into the attention-out GEMM's operand buffer */
+        const int tiled_att = !skinny && !kvf32 && mode == 0 && (d->hd == 64 || d->hd == 128);
+        if (tiled_att) {
+            DEV(cmlb200_qkv_rope_append(d->qkv, d->qkv_w, d->row_seq, d->row_pos, rows, d->heads_l, d->kvh_l, d->hd, c->rope_theta,
+                                        rotate, kc, vc, c->max_seq_len, kvf32, st));
+            DEV(cmlb200_attention_prefill(d->qkv, d->qkv_w, kc, vc, seq, d->row_limit, rows, d->heads_l, d->kvh_l, d->hd, c->max_seq_len,
+                                          NULL, d->b_a, st));
+        } else if (fused_att) {
             DEV(cmlb200_attention_decode(d->qkv, d->qkv_w, kc, vc, d->row_seq, d->row_pos, d->row_limit, rows, d->heads_l, d->kvh_l,
                                          d->hd, c->max_seq_len, max_limit, kvf32, d->rope_cs, d->att, d->att_scratch, splits, st));
         } else {
@@ -724,12 +731,11 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
                 }
             }
         } else {
-            DEV(cmlb200_f32_to_bf16(d->att, d->b_a, (size_t)rows * d->qw_l, st));
+            if (!tiled_att) DEV(cmlb200_f32_to_bf16(d->att, d->b_a, (size_t)rows * d->qw_l, st));
             if (proj_residual_bf16(d, &L->wo, d->b_a, rows)) return -1;
             DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)L->n2, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
             DEV(cmlb200_gemm_bf16(&L->wg, d->b_a, d->b_c, rows, st));
-            DEV(cmlb200_gemm_bf16(&L->wu, d->b_a, d->b_d, rows, st));
-            DEV(cmlb200_swiglu_bf16(d->b_c, d->b_d, d->b_c, (size_t)rows * d->inter_l, st));
+            DEV(cmlb200_gemm_bf16_ex(&L->wu, d->b_a, rows, CMLB200_GEMM_SWIGLU_BF16, d->b_c, d->b_c, st));   /* silu(gate) * up, in place */
             if (proj_residual_bf16(d, &L->wd, d->b_c, rows)) return -1;
         }
     }
@@ -747,8 +753,7 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
         if (lin_f32(d, &d->lm_head, d->nrm, lg, rows, 0)) return -1;
     } else {
         DEV(cmlb200_rmsnorm(d->h, (const uint16_t*)d->fnorm, rows, H, c->rms_norm_eps, NULL, d->b_a, st));
-        DEV(cmlb200_gemm_bf16(&d->lm_head, d->b_a, d->b_b, rows, st));
-        DEV(cmlb200_bf16_to_f32(d->b_b, lg, (size_t)rows * d->vocab_l, st));
+        DEV(cmlb200_gemm_bf16_ex(&d->lm_head, d->b_a, rows, CMLB200_GEMM_OUT_F32, lg, NULL, st));
     }
     if (split_head && with_head == 1) {                        /* full logits wanted: all-gather the slices, put them side by side */
         if (cml_nccl_allgather_bytes(d->comm, d->logits_l, d->logits_g, (size_t)rows * d->vocab_l * 4, st)) return -1;

@@ -178,6 +178,18 @@ int cmlb200_gemv_tiles_status(int* status, int reset);
  * cols must be a multiple of 32 (a last half slab of 32 is zero-extended). */
 int cmlb200_gemm_bf16(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
                       void* stream);
+/* The same product with what happens to the finished values chosen by `mode`:
+ *   CMLB200_GEMM_OUT_BF16     d_out bf16 [M, rows] (as cmlb200_gemm_bf16)
+ *   CMLB200_GEMM_OUT_F32      d_out fp32 [M, rows]
+ *   CMLB200_GEMM_ACC_F32      d_out fp32 [M, rows] += product (the residual adds of src/nn/llama.c:523-530, 538-543)
+ *   CMLB200_GEMM_SWIGLU_BF16  d_out bf16 = silu(d_gate_bf16) * product (src/nn/llama.c:126-155 with W the
+ *                             up projection and d_gate_bf16 the gate projection's output; may alias d_out) */
+#define CMLB200_GEMM_OUT_BF16 0
+#define CMLB200_GEMM_OUT_F32 1
+#define CMLB200_GEMM_ACC_F32 2
+#define CMLB200_GEMM_SWIGLU_BF16 3
+int cmlb200_gemm_bf16_ex(const cmlb200_qmat* W, const uint16_t* d_x_bf16, int M, int mode, void* d_out, const uint16_t* d_gate_bf16,
+                         void* stream);
 /* Same, with the number of K splits chosen by the caller (1 = none). With more than one
  * split the partial sums pass through an fp32 scratch buffer owned by the library. */
 int cmlb200_gemm_bf16_splitk(const cmlb200_qmat* W, const uint16_t* d_x_bf16, uint16_t* d_y_bf16, int M,
@@ -218,6 +230,14 @@ int cmlb200_kv_append(const float* d_k, const float* d_v, void* d_kcache, void* 
  * cmlb200_attention_scratch_floats(rows, heads, head_dim, splits) floats. */
 size_t cmlb200_attention_scratch_floats(int rows, int heads, int head_dim, int splits);
 int cmlb200_attention(const float* d_q, const void* d_kcache, const void* d_vcache, const int* d_row_seq, const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq, int max_limit, int kv_is_f32, float* d_out, float* d_scratch, int splits, void* stream);
+/* The same attention for prompt-sized calls: `rows` query rows of ONE sequence (`seq`) against that
+ * sequence's fp16 cache, tiled over 64 rows x 64 keys on the tensor cores (fp16 operands, fp32
+ * accumulation) so that keys and values are read once per 64 rows. Row r attends cache slots
+ * 0..d_row_limit[r]. head_dim 64 or 128. Writes fp32 and / or bf16 [rows, heads*head_dim]; either
+ * output pointer may be NULL. Part of the bf16 prefill pipeline (tolerance 1e-2). */
+int cmlb200_attention_prefill(const float* d_q, int q_stride, const void* d_kcache_f16, const void* d_vcache_f16, int seq,
+                              const int* d_row_limit, int rows, int heads, int kv_heads, int head_dim, int max_seq,
+                              float* d_out_f32, uint16_t* d_out_bf16, void* stream);
 /* Fused variants used by the decode step: Q rows `q_stride` floats apart (Q inside a fused q|k|v
  * buffer), attention output optionally also written as activation digits (d_xq, may be NULL); and
  * RoPE on the Q and K parts of such a buffer followed by the K/V cache append in one launch.

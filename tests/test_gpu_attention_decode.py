@@ -82,3 +82,42 @@ def test_attention_decode_matches_unfused_path_and_formulas(pkg, torch_dev, kv_f
     # same cache contents (the rotation may contract its multiply-adds differently in the two kernels)
     assert torch.equal(d_vc, e_vc)
     assert torch.allclose(d_kc.float(), e_kc.float(), rtol=0, atol=2e-6 if kv_f32 else 0)
+
+
+@pytest.mark.parametrize("heads,kvh,hd", [(8, 2, 128), (4, 4, 64)])
+@pytest.mark.parametrize("start", [0, 37])
+def test_attention_prefill_tiles_match_formulas(pkg, torch_dev, heads, kvh, hd, start):
+    """The tiled tensor-core attention of prompt-sized calls (64 query rows x 64 keys per step, fp16
+    operands) against a float64 softmax(Q K^T / sqrt(d)) V over the same fp16 cache: 150 rows (a
+    ragged last tile) at absolute positions start .. start+149 of sequence 1, every row limited to
+    its own position; fp32 and bf16 outputs. Tolerance: the bf16 prefill pipeline's 1e-2."""
+    rng = np.random.default_rng(41 + start)
+    rows, nseq, max_seq, seq = 150, 3, 256, 1
+    qw, kvw = heads * hd, kvh * hd
+    stride = qw + 2 * kvw                                      # Q sits inside a q|k|v row, as the projection leaves it
+    kc = rng.standard_normal((nseq, max_seq, kvw)).astype(np.float16)
+    vc = rng.standard_normal((nseq, max_seq, kvw)).astype(np.float16)
+    qkv = rng.standard_normal((rows, stride)).astype(np.float32)
+    limit = (start + np.arange(rows)).astype(np.int32)
+    want = np.zeros((rows, qw))
+    for r in range(rows):
+        K = kc[seq, :limit[r] + 1].astype(np.float64).reshape(-1, kvh, hd)
+        V = vc[seq, :limit[r] + 1].astype(np.float64).reshape(-1, kvh, hd)
+        for h in range(heads):
+            kh = h // (heads // kvh)
+            sc = K[:, kh] @ qkv[r, h * hd:(h + 1) * hd].astype(np.float64) / np.sqrt(hd)
+            pr = np.exp(sc - sc.max()); pr /= pr.sum()
+            want[r, h * hd:(h + 1) * hd] = pr @ V[:, kh]
+    d_q, d_kc, d_vc, d_lim = to_dev(qkv, torch_dev), to_dev(kc, torch_dev), to_dev(vc, torch_dev), to_dev(limit, torch_dev)
+    o32 = torch.zeros((rows, qw), dtype=torch.float32, device=torch_dev)
+    o16 = torch.zeros((rows, qw), dtype=torch.uint16, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_attention_prefill(d_q.data_ptr(), stride, d_kc.data_ptr(), d_vc.data_ptr(), seq, d_lim.data_ptr(), rows, heads, kvh, hd,
+                                                max_seq, o32.data_ptr(), o16.data_ptr(), stream_ptr()), "attention_prefill")
+    torch.cuda.synchronize()
+    got = o32.cpu().numpy()
+    assert np.abs(got - want).max() / np.abs(want).max() <= 1e-2
+    got16 = (o16.cpu().numpy().astype(np.uint32) << 16).view(np.float32)
+    assert np.abs(got16 - want).max() / np.abs(want).max() <= 1e-2
+    assert pkg.lib.cmlb200_attention_prefill(d_q.data_ptr(), stride, d_kc.data_ptr(), d_vc.data_ptr(), seq, d_lim.data_ptr(), rows, heads, kvh, 32,
+                                             max_seq, o32.data_ptr(), None, stream_ptr()) == -1          # head_dim 32 stays on the general kernel
+

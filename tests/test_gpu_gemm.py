@@ -83,3 +83,38 @@ def test_gemm_k_tail_of_half_a_slab(pkg, synth, ob, orc, torch_dev, kind, K, M):
     if K >= 256:
         got2 = _gemm(pkg, synth, W, x, N, torch_dev, splits=3)
         assert rel_err_inf(got2, ob.linear_nt(orc, xr.reshape(x.shape), Wf)) <= TOL
+
+
+@pytest.mark.parametrize("M", [48, 300])
+def test_gemm_output_modes(pkg, synth, ob, orc, torch_dev, M):
+    """The epilogues the LLaMA prefill uses: fp32 output, accumulation onto an fp32 residual, and
+    SwiGLU of an earlier gate output (in place), with and without the split-K reduction (M = 48
+    takes it on this shape)."""
+    rng = np.random.default_rng(700 + M)
+    N, K = 384, 1024
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, "q4_0", N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    xb, xr = synth.bf16_round(x)
+    want = ob.linear_nt(orc, xr.reshape(x.shape), Wf)
+    d_x = to_dev(xb.reshape(x.shape), torch_dev)
+    out32 = torch.zeros((M, N), dtype=torch.float32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_gemm_bf16_ex(W.q, d_x.data_ptr(), M, 1, out32.data_ptr(), None, stream_ptr()), "out_f32")
+    torch.cuda.synchronize()
+    assert rel_err_inf(out32.cpu().numpy(), want) <= TOL
+    h0 = rng.standard_normal((M, N)).astype(np.float32)
+    h = to_dev(h0, torch_dev)
+    pkg.check(pkg.lib.cmlb200_gemm_bf16_ex(W.q, d_x.data_ptr(), M, 2, h.data_ptr(), None, stream_ptr()), "acc_f32")
+    torch.cuda.synchronize()
+    assert np.abs(h.cpu().numpy() - (h0 + want)).max() <= TOL * np.abs(want).max()
+    gate = rng.standard_normal((M, N)).astype(np.float32)
+    gb, gr = synth.bf16_round(gate)
+    gr = gr.reshape(gate.shape)
+    buf = to_dev(gb.reshape(gate.shape), torch_dev)
+    pkg.check(pkg.lib.cmlb200_gemm_bf16_ex(W.q, d_x.data_ptr(), M, 3, buf.data_ptr(), buf.data_ptr(), stream_ptr()), "swiglu")
+    torch.cuda.synchronize()
+    ref = (gr / (1.0 + np.exp(-gr.astype(np.float64)))) * want
+    assert np.abs(synth.bf16_to_f32(buf.cpu().numpy()) - ref).max() <= TOL * np.abs(ref).max()
+    assert gemm_status(pkg) == 0
+    assert pkg.lib.cmlb200_gemm_bf16_ex(W.q, d_x.data_ptr(), M, 3, buf.data_ptr(), None, stream_ptr()) == -1      # SwiGLU needs the gate
+    assert pkg.lib.cmlb200_gemm_bf16_ex(W.q, d_x.data_ptr(), M, 7, buf.data_ptr(), None, stream_ptr()) == -1
+
