@@ -247,33 +247,41 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ qkv, int stride, cons
                                        int rotate_all, int rotate_any, KV* __restrict__ kc, KV* __restrict__ vc, int max_seq) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // grid = (rows, heads + 2*kv_heads): one CTA per Q head, K head or V head; thread i owns pair i
-    const int r = blockIdx.x, hh = blockIdx.y, i = threadIdx.x;
-    const int qw = heads * hd, kvw = kv_heads * hd;
+    // grid = (rows, groups of 32 heads), block = (hd/2 pairs, 4): thread (i, y) owns pair i of heads
+    // y, y+4, ... of its group (Q heads, then K heads, then V heads) and computes the rotation of
+    // its pair once for all of them
+    const int r = blockIdx.x, i = threadIdx.x;
+    const int qw = heads * hd, kvw = kv_heads * hd, total = heads + 2 * kv_heads;
     float* row = qkv + (size_t)r * stride;
-    const size_t dst = ((size_t)row_seq[r] * max_seq + row_pos[r]) * kvw;
-    if (hh >= heads + kv_heads) {                                   // V head: straight copy into the cache
-        const int h = hh - heads - kv_heads;
-        const float* v = row + qw + kvw + (size_t)h * hd + 2 * i;
-        vc[dst + (size_t)h * hd + 2 * i] = (KV)v[0];
-        vc[dst + (size_t)h * hd + 2 * i + 1] = (KV)v[1];
-        return;
-    }
-    const bool is_k = hh >= heads;
-    const int h = is_k ? hh - heads : hh;
-    float* v = row + (is_k ? qw : 0) + (size_t)h * hd + 2 * i;
-    float a = v[0], b = v[1];
-    if (rotate_any && (rotate_all || h == 0)) {
+    const int pos = row_pos[r];
+    const size_t dst = ((size_t)row_seq[r] * max_seq + pos) * kvw;
+    float c = 1.f, sn = 0.f;
+    if (rotate_any) {
         const float freq = 1.0f / powf(base, (float)(2 * i) / (float)hd);
-        const float th = (float)row_pos[r] * freq;
-        const float c = cosf(th), sn = sinf(th);
-        const float na = a * c - b * sn, nb = a * sn + b * c;
-        a = na; b = nb;
-        v[0] = a; v[1] = b;
+        const float th = (float)pos * freq;
+        c = cosf(th); sn = sinf(th);
     }
-    if (is_k) {
-        kc[dst + (size_t)h * hd + 2 * i] = (KV)a;
-        kc[dst + (size_t)h * hd + 2 * i + 1] = (KV)b;
+    for (int hh = blockIdx.y * 32 + threadIdx.y; hh < min(total, (int)blockIdx.y * 32 + 32); hh += 4) {
+        if (hh >= heads + kv_heads) {                               // V head: straight copy into the cache
+            const int h = hh - heads - kv_heads;
+            const float* v = row + qw + kvw + (size_t)h * hd + 2 * i;
+            vc[dst + (size_t)h * hd + 2 * i] = (KV)v[0];
+            vc[dst + (size_t)h * hd + 2 * i + 1] = (KV)v[1];
+            continue;
+        }
+        const bool is_k = hh >= heads;
+        const int h = is_k ? hh - heads : hh;
+        float* v = row + (is_k ? qw : 0) + (size_t)h * hd + 2 * i;
+        float a = v[0], b = v[1];
+        if (rotate_any && (rotate_all || h == 0)) {
+            const float na = a * c - b * sn, nb = a * sn + b * c;
+            a = na; b = nb;
+            v[0] = a; v[1] = b;
+        }
+        if (is_k) {
+            kc[dst + (size_t)h * hd + 2 * i] = (KV)a;
+            kc[dst + (size_t)h * hd + 2 * i + 1] = (KV)b;
+        }
     }
 }
 
@@ -818,8 +826,9 @@ extern "C" int cmlb200_qkv_rope_append(float* d_qkv, int row_stride, const int* 
                  "cmlb200_qkv_rope_append: bad shape");
     if (base <= 0.f) base = 10000.0f;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rows, heads + 2 * kv_heads);
-    cfg.blockDim = dim3(head_dim / 2);
+    CMLB_REQUIRE(head_dim <= 512, "cmlb200_qkv_rope_append: head_dim %d above 512", head_dim);
+    cfg.gridDim = dim3(rows, (heads + 2 * kv_heads + 31) / 32);
+    cfg.blockDim = dim3(head_dim / 2, 4);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
