@@ -25,6 +25,10 @@ bool cmlb200_gemv_mma8_ok_(const cmlb200_qmat* W, int epi);
 int cmlb200_gemv_mma8_(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, const uint16_t* norm_w, float eps, float* y, int M,
                        int epi, cudaStream_t st);
 
+// gemv_kquant.cu: Q4_1 / Q4_K / Q5_K / Q6_K weights straight from the GGUF block stream
+bool cmlb200_is_kquant_type_(int type);
+int cmlb200_gemv_kquant_(const cmlb200_qmat* W, const float* x, float* y, int M, int accumulate, cudaStream_t st);
+
 // gemv_tc.cu: tcgen05 integer tensor-core path over the tile-major copy of the weight
 int cmlb200_gemv_tc_(const cmlb200_qmat* W, const float* x, float* y, int M, int accumulate, cudaStream_t st);
 
@@ -232,8 +236,9 @@ int gemv_type(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x, flo
 }
 
 int check_qmat(const cmlb200_qmat* W, const char* who) {
-    CMLB_REQUIRE(W && W->qs && W->scales, "%s: NULL weight", who);
+    CMLB_REQUIRE(W && W->qs && (W->scales || cmlb200_is_kquant_type_(W->type)), "%s: NULL weight", who);
     CMLB_REQUIRE(W->rows > 0 && W->cols > 0 && W->cols % 32 == 0, "%s: weight shape %dx%d (cols must be a multiple of 32)", who, W->rows, W->cols);
+    if (cmlb200_is_kquant_type_(W->type)) return CMLB200_OK;     // the block-stream kernel checks the rest
     CMLB_REQUIRE(W->type == CMLB200_Q4_0 || W->type == CMLB200_Q8_0 || W->type == CMLB200_NF4, "%s: unsupported weight type %d", who, W->type);
     if (W->type == CMLB200_NF4)
         CMLB_REQUIRE(W->block >= 32 && W->block % 32 == 0 && W->cols % W->block == 0,
@@ -257,6 +262,10 @@ int gemv_dispatch(const cmlb200_qmat* W, const cmlb200_qmat* W2, const float* x,
     CMLB_REQUIRE(M >= 1 && M <= 32, "%s: M=%d outside the decode range 1..32", who, M);
     CMLB_REQUIRE(((uintptr_t)x & 15) == 0, "%s: x must be 16-byte aligned", who);
     cudaStream_t st = as_stream(stream);
+    if (cmlb200_is_kquant_type_(W->type)) {
+        CMLB_REQUIRE(EPI != EPI_SWIGLU, "%s: GGUF type %d has no fused SwiGLU kernel; use cmlb200_gemv twice and cmlb200_swiglu_f32", who, W->type);
+        return cmlb200_gemv_kquant_(W, x, y, M, EPI == EPI_ACCUM, st);
+    }
     const bool tc_ok = W->type != CMLB200_NF4 && M > kDp4aMaxM && W->tiles && EPI != EPI_SWIGLU && W->cols % 128 == 0 && ((uintptr_t)y & 15) == 0;
     if (W->type == CMLB200_Q4_0 && M > 2 && (M > 4 || cmlb200_gemv_mma_rows_(W, EPI) < M) && cmlb200_gemv_mma8_ok_(W, EPI)) {
         // eight rows of x per launch of the plane-major mma.sync kernel: the weight is streamed once per eight rows

@@ -45,6 +45,7 @@ typedef struct DevModel {
     void* ar_ws[8];
     size_t ar_max_floats;
     int ar_ok;
+    int generic_w;                         /* some projection is Q4_1 / Q4_K / Q5_K / Q6_K: fp32 row-block path for every call */
     int hd, heads_l, kvh_l, qw_l, kvw_l, inter_l;
     DevLayer* L;
     void *embed, *fnorm;
@@ -330,6 +331,17 @@ static int upload_qmat(DevModel* d, int type, const uint8_t* blocks, int rows, i
     out->rows = rows;
     out->cols = cols;
     out->block = 32;
+    if (type != GGUF_TENSOR_Q4_0 && type != GGUF_TENSOR_Q8_0) {
+        /* Q4_1 / Q4_K / Q5_K / Q6_K: the block stream goes to the device as it is; the model then runs
+         * every call on the fp32 row-block path (no fused or tensor-core kernels for these types) */
+        const size_t bs = gguf_quant_block_size((GGUFTensorType)type), bytes = (size_t)rows * ((size_t)cols / bs) * gguf_quant_type_size((GGUFTensorType)type);
+        out->block = (int)bs;
+        if (CML_DEV_FAIL(cmlb200_malloc(&out->qs, bytes), "upload") || CML_DEV_FAIL(cmlb200_memcpy_h2d(out->qs, blocks, bytes, d->stream), "upload") ||
+            CML_DEV_FAIL(cmlb200_stream_sync(d->stream), "upload"))
+            return -1;
+        d->generic_w = 1;
+        return 0;
+    }
     const size_t qb = cmlb200_qs_bytes(type, rows, cols, 32), sb = cmlb200_scale_bytes(type, rows, cols, 32);
     void *h_qs = malloc(qb), *h_sc = malloc(sb), *h_t = NULL;
     int rc = -1;
@@ -428,11 +440,12 @@ static int classify(const char* name, int* layer) {
 int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int dim, int tp_size, int tp_rank, void* out) {
     const size_t bb = gguf_quant_type_size((GGUFTensorType)type);
     if (!blocks || !out) { LOG_ERROR("cml_tp_shard_qblocks: NULL argument"); return -1; }
-    if (!bb || gguf_quant_block_size((GGUFTensorType)type) != 32) { LOG_ERROR("cml_tp_shard_qblocks: type %d is not a 32-element block type", type); return -1; }
+    const int bs = (int)gguf_quant_block_size((GGUFTensorType)type);
+    if (!bb || bs <= 1) { LOG_ERROR("cml_tp_shard_qblocks: type %d is not a block-quantized type", type); return -1; }
     if (dim != 0 && dim != 1) { LOG_ERROR("cml_tp_shard_qblocks: dim must be 0 or 1, got %d", dim); return -1; }
     if (tp_size <= 0 || tp_rank < 0 || tp_rank >= tp_size) { LOG_ERROR("cml_tp_shard_qblocks: invalid tp_size=%d or tp_rank=%d", tp_size, tp_rank); return -1; }
-    if (rows <= 0 || cols <= 0 || cols % 32) { LOG_ERROR("cml_tp_shard_qblocks: bad shape %dx%d", rows, cols); return -1; }
-    const int nblk = cols / 32;
+    if (rows <= 0 || cols <= 0 || cols % bs) { LOG_ERROR("cml_tp_shard_qblocks: bad shape %dx%d for %d-element blocks", rows, cols, bs); return -1; }
+    const int nblk = cols / bs;
     const uint8_t* full = (const uint8_t*)blocks;
     uint8_t* dst = (uint8_t*)out;
     if (dim == 0) {
@@ -440,7 +453,7 @@ int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int d
         const size_t n = (size_t)(rows / tp_size) * nblk * bb;
         memcpy(dst, full + (size_t)tp_rank * n, n);
     } else {
-        if (cols % tp_size || (cols / tp_size) % 32) { LOG_ERROR("cml_tp_shard_qblocks: cols (%d) must split into %d multiples of 32", cols, tp_size); return -1; }
+        if (cols % tp_size || (cols / tp_size) % bs) { LOG_ERROR("cml_tp_shard_qblocks: cols (%d) must split into %d multiples of %d", cols, tp_size, bs); return -1; }
         const int lb = nblk / tp_size;
         for (int r = 0; r < rows; r++) memcpy(dst + (size_t)r * lb * bb, full + ((size_t)r * nblk + (size_t)tp_rank * lb) * bb, (size_t)lb * bb);
     }
@@ -450,7 +463,9 @@ int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int d
 static uint8_t* shard_blocks(const uint8_t* full, int type, int rows, int cols, int tp, int rank, int by_rows, int* orow, int* ocol) {
     *orow = by_rows ? rows / tp : rows;
     *ocol = by_rows ? cols : cols / tp;
-    uint8_t* out = (uint8_t*)malloc((size_t)*orow * (*ocol / 32) * gguf_quant_type_size((GGUFTensorType)type));
+    const size_t bs = gguf_quant_block_size((GGUFTensorType)type);
+    if (bs <= 1 || *ocol % (int)bs) { LOG_ERROR("a shard of %d columns is not a whole number of %zu-element blocks", *ocol, bs); return NULL; }
+    uint8_t* out = (uint8_t*)malloc((size_t)*orow * ((size_t)*ocol / bs) * gguf_quant_type_size((GGUFTensorType)type));
     if (out && cml_tp_shard_qblocks(type, full, rows, cols, by_rows ? 0 : 1, tp, rank, out)) { free(out); out = NULL; }
     return out;
 }
@@ -510,8 +525,11 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
                 default:                                        /* split by rows when the vocabulary divides, else replicated */
                     out_f = c->vocab_size; in_f = H; by_rows = d->vocab_l != c->vocab_size ? 1 : -1; dst = &d->lm_head; pub = &model->lm_head; break;
             }
-            if (info->type != GGUF_TENSOR_Q4_0 && info->type != GGUF_TENSOR_Q8_0)
-                LOG_ERROR("cml_llama_load_gguf: tensor '%s' has GGUF type %d; projections must be Q4_0 or Q8_0", name, (int)info->type);
+            if (info->type != GGUF_TENSOR_Q4_0 && info->type != GGUF_TENSOR_Q8_0 && info->type != GGUF_TENSOR_Q4_1 &&
+                info->type != GGUF_TENSOR_Q4_K && info->type != GGUF_TENSOR_Q5_K && info->type != GGUF_TENSOR_Q6_K)
+                LOG_ERROR("cml_llama_load_gguf: tensor '%s' has GGUF type %d; projections must be Q4_0, Q8_0, Q4_1, Q4_K, Q5_K or Q6_K", name, (int)info->type);
+            else if (in_f % (int)gguf_quant_block_size(info->type))
+                LOG_ERROR("cml_llama_load_gguf: tensor '%s': in_features %d is not a whole number of %zu-element blocks", name, in_f, gguf_quant_block_size(info->type));
             else if (info->ndim != 2 || info->shape[0] != in_f || info->shape[1] != out_f)
                 LOG_ERROR("cml_llama_load_gguf: tensor '%s' has dims (%lld, %lld), expected (in=%d, out=%d)", name,
                           (long long)info->shape[0], (long long)(info->ndim > 1 ? info->shape[1] : 0), in_f, out_f);
@@ -531,7 +549,7 @@ int cml_llama_load_gguf(CMLLLaMAModel* model, const char* filepath) {
                     L->pend_type = (int)info->type;
                     rc = 0;
                     if (L->pend[0] && L->pend[1] && L->pend[2]) {
-                        const size_t bb = gguf_quant_type_size(info->type), rowb = (size_t)(H / 32) * bb;
+                        const size_t bb = gguf_quant_type_size(info->type), rowb = ((size_t)H / gguf_quant_block_size(info->type)) * bb;
                         const size_t qb = (size_t)d->qw_l * rowb, kb = (size_t)d->kvw_l * rowb;
                         uint8_t* all = (uint8_t*)malloc(qb + 2 * kb);
                         if (all) {
@@ -646,8 +664,8 @@ static int enqueue_forward_ex(DevModel* d, int rows, int mode, int seq, int plan
     const CMLLLaMAModel* m = d->key;
     const CMLLLaMAConfig* c = &m->config;
     const int H = c->hidden_size, quirks = (d->flags & CML_B200_REFERENCE_QUIRKS) != 0, kvf32 = (d->flags & CML_B200_KV_FP32) != 0;
-    const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32);
-    const int tiny = rows <= 8;                 /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
+    const int skinny = rows <= SKINNY_ROWS || (d->flags & CML_B200_ALL_LOGITS_FP32) || d->generic_w;
+    const int tiny = rows <= 8 && !d->generic_w;   /* tensor-core decode GEMV with RMSNorm applied inside the projection launch */
     void* st = d->stream;
     DEV(cmlb200_prepare_rows(d->d_cur, rows, mode, quirks, seq, d->row_seq, d->row_pos, d->row_limit, st));
     if (only_layer < 0) DEV(cmlb200_embed_f16((const uint16_t*)d->embed, d->d_tokens, rows, H, c->vocab_size, d->h, st));

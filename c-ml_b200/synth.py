@@ -21,6 +21,41 @@ def q4_0_blocks(rng, rows, cols, d_lo=1e-3, d_hi=2e-2):
     return blk.reshape(-1)
 
 
+GGUF_BLOCK = {2: (32, 18), 3: (32, 20), 7: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}   # type -> (elements, bytes)
+
+
+def gguf_blocks(rng, gtype, rows, cols, std=0.02):
+    """Random GGUF blocks of type Q4_1 (3), Q4_K (12), Q5_K (13) or Q6_K (14) in C-ML's layouts
+    (src/core/gguf_quant.c:90-311) whose dequantised weights have mean about 0 and roughly `std`:
+    uniform quants, small integer sub-block scales, fp16 d / dmin / m chosen to centre the values."""
+    if gtype == 2: return q4_0_blocks(rng, rows, cols, std / 6, std / 3)
+    if gtype == 7: return q8_0_blocks(rng, rows, cols, std / 100, std / 50)
+    be, bb = GGUF_BLOCK[gtype]
+    nb = rows * cols // be
+    blk = rng.integers(0, 256, (nb, bb), dtype=np.uint8)
+    f16 = lambda a: np.asarray(a, np.float16).view(np.uint8).reshape(nb, 2)
+    if gtype == 3:                                   # w = q * d + m, q uniform 0..15
+        d = rng.uniform(0.5, 1.0, nb) * std / 4.6
+        blk[:, 0:2] = f16(d)
+        blk[:, 2:4] = f16(-7.5 * d * rng.uniform(0.9, 1.1, nb))
+    elif gtype in (12, 13):                          # w = q * (d * sc) - dmin * mn, q uniform 0..15 (0..31)
+        qmax = 15 if gtype == 12 else 31
+        sc = rng.integers(2, 8 if gtype == 12 else 4, (nb, 8))
+        mn = np.clip(np.rint(qmax / 2 * sc + rng.integers(-2, 3, (nb, 8))), 0, 63).astype(np.int64)
+        s = np.zeros((nb, 12), np.int64)             # get_scale_min_k4's packing
+        s[:, 0:4] = sc[:, 0:4] | ((sc[:, 4:8] >> 4) << 6)
+        s[:, 4:8] = mn[:, 0:4] | ((mn[:, 4:8] >> 4) << 6)
+        s[:, 8:12] = (sc[:, 4:8] & 15) | ((mn[:, 4:8] & 15) << 4)
+        d = rng.uniform(0.5, 1.0, nb) * std / (5.0 * (qmax + 1) / 3.46)
+        blk[:, 0:2] = f16(d)
+        blk[:, 2:4] = f16(d)
+        blk[:, 4:16] = s.astype(np.uint8)
+    else:                                            # w = d * scale8 * (q - 32), q uniform 0..63
+        blk[:, 192:208] = rng.integers(-24, 25, (nb, 16)).astype(np.int8).view(np.uint8)
+        blk[:, 208:210] = f16(rng.uniform(0.5, 1.0, nb) * std / (14.0 * 18.5))
+    return blk.reshape(-1)
+
+
 def nf4_weight(rng, rows, cols, block=64, s_lo=0.01, s_hi=0.1):
     """NF4 packed bytes (indices uniform 0..15) and fp32 absmax per block of the flat index."""
     packed = rng.integers(0, 256, rows * cols // 2, dtype=np.uint8)

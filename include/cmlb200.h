@@ -32,6 +32,15 @@ extern "C" {
 #define CMLB200_Q4_0 2
 #define CMLB200_Q8_0 7
 #define CMLB200_NF4 100
+/* The other block types C-ML reads (src/core/gguf_quant.c:90-311), by GGUF id. A weight of one of
+ * these types is the tensor's block stream unchanged: `qs` = rows * (cols / B) blocks, row-major,
+ * 16-byte aligned, B = 32 (Q4_1, 20-byte blocks) or 256 (Q4_K 144, Q5_K 176, Q6_K 210 bytes);
+ * `scales` = NULL, `block` = B. cmlb200_gemv / cmlb200_gemv_accum take them (M <= 32);
+ * cmlb200_gguf_dequantize expands them bit-exactly. */
+#define CMLB200_Q4_1 3
+#define CMLB200_Q4_K 12
+#define CMLB200_Q5_K 13
+#define CMLB200_Q6_K 14
 
 /* A quantized [rows, cols] weight (rows = out features N, cols = in features
  * K; y = x . W^T as in src/nn/qlora.c:309-317) in the repacked device layout:

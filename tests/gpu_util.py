@@ -39,6 +39,19 @@ class DevQMat:
         return cls(pkg, dev, pkg.NF4, rows, cols, packed, scales, block)
 
 
+class DevBlockStream:
+    """A Q4_1 / Q4_K / Q5_K / Q6_K weight: the GGUF block stream uploaded unchanged."""
+
+    def __init__(self, pkg, dev, gtype, rows, cols, blocks):
+        self.qs = to_dev(blocks, dev)
+        self.q = pkg.QMat(gtype, rows, cols, 32 if gtype == 3 else 256, self.qs.data_ptr(), None, 0, None)
+
+
+def make_block_stream(pkg, synth, ob, orc, dev, rng, gtype, N, K, std=0.02):
+    blocks = synth.gguf_blocks(rng, gtype, N, K, std)
+    return DevBlockStream(pkg, dev, gtype, N, K, blocks), ob.dequant_blocks(orc, gtype, blocks, N * K).reshape(N, K)
+
+
 def make_weight(pkg, synth, ob, orc, dev, rng, kind, N, K, block=64):
     """Returns (DevQMat, dequantised fp32 [N,K] from the oracle)."""
     if kind == "nf4":

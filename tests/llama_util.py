@@ -12,6 +12,8 @@ def build(entry, rng, cfg, path, qtype=2, wscale=0.05):
     orc = ob.load_orc()
 
     def quantize(w):
+        if qtype not in (2, 7):                            # Q4_1 / K types: random blocks of the same spread (no quantiser for them)
+            return synth.gguf_blocks(rng, qtype, w.shape[0], w.shape[1], wscale)
         nb = w.size // 32
         blocks = np.zeros(nb * (18 if qtype == 2 else 34), np.uint8)
         (orc.orc_quantize_q4_0 if qtype == 2 else orc.orc_quantize_q8_0)(ob.p(np.ascontiguousarray(w)), ob.p(blocks), nb)

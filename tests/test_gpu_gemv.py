@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from conftest import rel_err, rel_err_inf
-from gpu_util import make_weight, stream_ptr, to_dev
+from gpu_util import make_block_stream, make_weight, stream_ptr, to_dev
 
 pytestmark = pytest.mark.gpu
 # M <= 4 rounds x to 24 bits relative to each 32-block maximum: as good as fp32 accumulation
@@ -222,3 +222,41 @@ def test_gemv_eight_row_kernel(pkg, synth, ob, orc, torch_dev, N, K):
         assert rel_err(d_y.cpu().numpy(), g) <= TOL
         pkg.check(pkg.lib.cmlb200_gemv_rmsnorm(Wg.q, Wu.q, d_x.data_ptr(), d_nw.data_ptr(), eps, d_y.data_ptr(), M, 2, stream_ptr()), "gemv_rmsnorm swiglu")
         assert rel_err(d_y.cpu().numpy(), (g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u) <= TOL
+
+
+@pytest.mark.parametrize("gtype", [3, 12, 13, 14])
+@pytest.mark.parametrize("M", [1, 3, 8, 13])
+def test_gemv_other_gguf_block_types(pkg, synth, ob, orc, torch_dev, gtype, M):
+    """Q4_1, Q4_K, Q5_K, Q6_K weights straight from the block stream (C-ML's own nibble order for
+    the K types), against the oracle's dequantise-then-multiply."""
+    rng = np.random.default_rng(500 + 10 * gtype + M)
+    N, K = 301, 1536 if gtype != 3 else 1504          # ragged N; Q4_1: K a multiple of 32 only
+    W, Wf = make_block_stream(pkg, synth, ob, orc, torch_dev, rng, gtype, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    got = _run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev)
+    want = ob.linear_nt(orc, x, Wf)
+    assert rel_err(got, want) <= TOL
+    y0 = rng.standard_normal((M, N)).astype(np.float32)
+    acc = _run(pkg, pkg.lib.cmlb200_gemv_accum, W, x, N, torch_dev, y0=y0)
+    assert rel_err(acc, y0 + want) <= TOL
+
+
+@pytest.mark.parametrize("gtype,N,K", [(12, 4096, 4096), (14, 4096, 11008)])
+def test_gemv_other_block_types_long_k_sampled_rows(pkg, synth, ob, orc, torch_dev, gtype, N, K):
+    """LLaMA-7B widths: K longer than one staged segment of x at M = 8."""
+    rng = np.random.default_rng(40 + gtype)
+    W, Wf = make_block_stream(pkg, synth, ob, orc, torch_dev, rng, gtype, N, K)
+    x = rng.standard_normal((8, K)).astype(np.float32)
+    got = _run(pkg, pkg.lib.cmlb200_gemv, W, x, N, torch_dev)
+    rows = rng.choice(N, 64, replace=False)
+    assert rel_err(got[:, rows], ob.linear_nt(orc, x, Wf[rows])) <= TOL
+
+
+def test_gemv_other_block_types_reject_swiglu_and_partial_blocks(pkg, synth, ob, orc, torch_dev):
+    rng = np.random.default_rng(3)
+    W, _ = make_block_stream(pkg, synth, ob, orc, torch_dev, rng, 12, 16, 512)
+    x = to_dev(rng.standard_normal((1, 512)).astype(np.float32), torch_dev)
+    y = torch.zeros((1, 16), dtype=torch.float32, device=torch_dev)
+    assert pkg.lib.cmlb200_gemv_swiglu(W.q, W.q, x.data_ptr(), y.data_ptr(), 1, stream_ptr()) != 0
+    bad = pkg.QMat(12, 16, 384, 256, W.qs.data_ptr(), None, 0, None)       # 384 is not a whole number of 256-blocks
+    assert pkg.lib.cmlb200_gemv(bad, x.data_ptr(), y.data_ptr(), 1, stream_ptr()) != 0

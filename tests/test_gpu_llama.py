@@ -319,3 +319,34 @@ def test_generate_with_a_caller_supplied_tokenizer(pkg, tiny, torch_dev):
         lib.cml_llama_set_tokenizer_functions(ENC(0), DEC(0))
         lib.cml_llama_free(m)
         lib.cml_llama_free(m2)
+
+
+@pytest.mark.parametrize("gtype", [3, 12, 13, 14])
+def test_models_with_other_block_types_match_oracle(pkg, tmp_path, torch_dev, gtype):
+    """Projections stored as Q4_1 / Q4_K / Q5_K / Q6_K: the loader keeps the block stream and every
+    call runs on the fp32 path. Prefill, single-token steps, batched decode and the greedy loop."""
+    rng = np.random.default_rng(900 + gtype)
+    path = tmp_path / f"tiny_type{gtype}.gguf"
+    store = build(entry, rng, TINY, path, qtype=gtype, wscale=0.06)
+    orc = OracleLlama(entry, TINY, store, qtype=gtype, rope_all_heads=1, mask_absolute=1)
+    tokens = rng.integers(0, TINY["vocab"], 40).astype(np.int32)
+    m = device_model(pkg, TINY, path, max_batch=2)
+    try:
+        assert rel_err_inf(dev_forward(pkg, m, tokens[:36]), orc.forward(tokens[:36])) <= 2e-3     # more rows than one skinny pass
+        for i in range(36, 40):
+            got, want = dev_forward(pkg, m, tokens[i:i + 1]), orc.forward(tokens[i:i + 1])
+            assert rel_err_inf(got, want) <= 2e-3 and int(got[0].argmax()) == int(want[0].argmax())
+        greedy = pkg.lib.cml_generation_default_config()
+        greedy.do_sample = False
+        first = int(got[0].argmax())
+        want_toks, tok = [], first
+        for _ in range(5):
+            lg = orc.forward(np.array([tok], np.int32))
+            tok = int(lg[0].argmax())
+            want_toks.append(tok)
+        out = np.zeros(5, np.int32)
+        ms = C.c_float(0)
+        assert pkg.lib.cml_llama_decode_greedy(m, pkg.np_ptr(np.array([first], np.int32)), 1, 5, pkg.np_ptr(out), C.byref(ms)) == 0
+        assert out.tolist() == want_toks
+    finally:
+        pkg.lib.cml_llama_free(m)
