@@ -50,10 +50,10 @@ LLAMA_7B = dict(vocab=32000, hidden=4096, inter=11008, layers=32, heads=32, kv_h
 LLAMA_70B = dict(vocab=32000, hidden=8192, inter=28672, layers=80, heads=64, kv_heads=8, max_seq=1280)
 
 
-def alg_bytes(M, rows=N_ROWS, cols=K_COLS, block_bytes=18):
+def alg_bytes(M, rows=N_ROWS, cols=K_COLS, block_bytes=18, block_elems=32):
     """Algorithmic bytes of one GEMV launch: packed weight (18 B per 32 Q4_0 weights, 34 B per 32
-    Q8_0 weights) + x + y."""
-    return rows * cols // 32 * block_bytes + M * cols * 4 + M * rows * 4
+    Q8_0 weights, 144 / 210 B per 256 Q4_K / Q6_K weights) + x + y."""
+    return rows * cols // block_elems * block_bytes + M * cols * 4 + M * rows * 4
 
 
 def measured_peaks():
@@ -468,7 +468,7 @@ def main():
 
     gemv = pkg.lib.cmlb200_gemv
 
-    def gemv_leg(weights, rows, cols, M, steps, warmup, block_bytes, rng):
+    def gemv_leg(weights, rows, cols, M, steps, warmup, block_bytes, rng, block_elems=32):
         x = torch.from_numpy(rng.standard_normal((M, cols)).astype(np.float32)).to(dev)
         y = torch.empty((M, rows), dtype=torch.float32, device=dev)
 
@@ -477,7 +477,7 @@ def main():
                 pkg.check(gemv(W, x.data_ptr(), y.data_ptr(), M, sp), "cmlb200_gemv")
         ms = timed_graph(sweep, steps, warmup)
         per_launch_s = ms * 1e-3 / (steps * len(weights) * SWEEPS_PER_STEP)
-        ab = alg_bytes(M, rows, cols, block_bytes)
+        ab = alg_bytes(M, rows, cols, block_bytes, block_elems)
         gbs = ab / per_launch_s / 1e9
         return {"us_per_call": per_launch_s * 1e6, "value": gbs, "unit": "GB/s", "pct_of_8TBps": 100.0 * gbs / 8000.0,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
@@ -607,6 +607,17 @@ def main():
         legs["q8_0_4096x4096_M1"], _ = gemv_leg(w8, 4096, 4096, 1, few, 3, 34, rng)
         del w8, keep8
         torch.cuda.empty_cache()
+        # ---- the other GGUF block types, straight from the block stream (CUDA-core kernel)
+        for gtype, tag in ((12, "q4_k"), (14, "q6_k")):
+            be, bb = synth.GGUF_BLOCK[gtype]
+            wk, keepk = [], []
+            for _ in range(24):
+                d_b = torch.from_numpy(synth.gguf_blocks(rng, gtype, 4096, 4096)).to(dev)
+                keepk.append(d_b)
+                wk.append(pkg.QMat(gtype, 4096, 4096, be, d_b.data_ptr(), None, 0, None))
+            legs[f"{tag}_4096x4096_M1"], _ = gemv_leg(wk, 4096, 4096, 1, few, 3, bb, rng, block_elems=be)
+            del wk, keepk
+            torch.cuda.empty_cache()
         legs["nf4_gemm_4096x4096_bf16"] = nf4_gemm_leg((64, 512, 2048), few, 3)
         torch.cuda.empty_cache()
     if not args.skip_llama:

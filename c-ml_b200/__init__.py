@@ -180,6 +180,22 @@ class GQAConfig(C.Structure):
                 ("causal", C.c_bool), ("window_size", C.c_int)]
 
 
+class PageBlock(C.Structure):
+    _fields_ = [("key_data", C.POINTER(C.c_float)), ("value_data", C.POINTER(C.c_float)), ("num_tokens", C.c_int),
+                ("block_id", C.c_int), ("in_use", C.c_bool)]
+
+
+class BlockTable(C.Structure):
+    _fields_ = [("block_ids", C.POINTER(C.c_int)), ("num_blocks", C.c_int), ("capacity", C.c_int), ("seq_len", C.c_int)]
+
+
+class PagedKVCache(C.Structure):
+    _fields_ = [("blocks", C.POINTER(PageBlock)), ("num_blocks", C.c_int), ("max_blocks", C.c_int),
+                ("free_list", C.POINTER(C.c_int)), ("free_count", C.c_int), ("sequences", C.POINTER(BlockTable)),
+                ("num_sequences", C.c_int), ("max_sequences", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int),
+                ("block_size", C.c_int), ("total_allocated", C.c_size_t), ("total_freed", C.c_size_t)]
+
+
 class RoPEConfig(C.Structure):
     _fields_ = [("dim", C.c_int), ("max_seq_len", C.c_int), ("base", C.c_float)]
 
@@ -202,6 +218,53 @@ _sig("cml_kv_cache_get_values", TP, KP)
 _sig("cml_gqa_forward", TP, TP, TP, TP, C.POINTER(GQAConfig), TP)
 _sig("cml_gqa_forward_cached", TP, TP, TP, TP, KP, C.POINTER(GQAConfig))
 _sig("cml_rope_forward", TP, TP, ci, C.POINTER(RoPEConfig))
+PKP = C.POINTER(PagedKVCache)
+_sig("cml_paged_kv_cache_create", PKP, ci, ci, ci, ci)
+_sig("cml_paged_kv_cache_free", None, PKP)
+_sig("cml_paged_cache_alloc_block", ci, PKP)
+_sig("cml_paged_cache_free_block", None, PKP, ci)
+_sig("cml_paged_cache_init_sequence", ci, PKP)
+_sig("cml_paged_cache_free_sequence", None, PKP, ci)
+_sig("cml_paged_cache_append", ci, PKP, ci, vp, vp)
+_sig("cml_paged_gqa_forward", TP, PKP, ci, TP, C.POINTER(GQAConfig))
+class SpeculativeConfig(C.Structure):
+    _fields_ = [("num_draft_tokens", C.c_int), ("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int), ("do_sample", C.c_bool)]
+
+
+class SpeculativeResult(C.Structure):
+    _fields_ = [("accepted_tokens", C.POINTER(C.c_int)), ("num_accepted", C.c_int), ("num_drafted", C.c_int), ("num_verified", C.c_int),
+                ("acceptance_rate", C.c_float), ("draft_time_ms", C.c_double), ("verify_time_ms", C.c_double), ("total_time_ms", C.c_double)]
+
+
+ModelForwardFn = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.c_int)
+SampleTokenFn = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_float)
+
+
+class SpeculativeDecoder(C.Structure):
+    _fields_ = [("config", SpeculativeConfig), ("draft_model_ctx", C.c_void_p), ("draft_forward", ModelForwardFn), ("draft_sample", SampleTokenFn),
+                ("target_model_ctx", C.c_void_p), ("target_forward", ModelForwardFn), ("target_sample", SampleTokenFn), ("vocab_size", C.c_int),
+                ("total_drafted", C.c_size_t), ("total_accepted", C.c_size_t), ("total_steps", C.c_size_t)]
+
+
+class SpeculativeLlama(C.Structure):
+    _fields_ = [("model", MP), ("cached_tokens", C.POINTER(C.c_int)), ("cached_len", C.c_int), ("capacity", C.c_int), ("min_rows", C.c_int),
+                ("rows_computed", C.c_size_t), ("calls", C.c_size_t)]
+
+
+SDP, SRP, SLP = C.POINTER(SpeculativeDecoder), C.POINTER(SpeculativeResult), C.POINTER(SpeculativeLlama)
+_sig("cml_speculative_default_config", SpeculativeConfig)
+_sig("cml_speculative_create", SDP, C.POINTER(SpeculativeConfig), ci)
+_sig("cml_speculative_free", None, SDP)
+_sig("cml_speculative_set_draft_model", None, SDP, vp, vp, vp)
+_sig("cml_speculative_set_target_model", None, SDP, vp, vp, vp)
+_sig("cml_speculative_decode_step", SRP, SDP, vp, ci)
+_sig("cml_speculative_result_free", None, SRP)
+_sig("cml_speculative_acceptance_rate", C.c_float, SDP)
+_sig("cml_speculative_llama_create", SLP, MP, C.c_bool)
+_sig("cml_speculative_llama_free", None, SLP)
+_sig("cml_speculative_llama_forward", TP, vp, vp, ci)
+_sig("cml_speculative_llama_sample", ci, vp, TP, C.c_float)
+_sig("cml_llama_truncate", ci, MP, ci, ci)
 _sig("cml_column_parallel_create", PLP, TP, TP, ci, ci)
 _sig("cml_column_parallel_free", None, PLP)
 _sig("cml_column_parallel_forward", TP, PLP, TP)

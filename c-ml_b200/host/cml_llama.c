@@ -1086,6 +1086,32 @@ void cml_llama_reset(CMLLLaMAModel* model) {
     model->current_seq_len = 0;
 }
 
+/* Rolls sequence `seq` back to new_len tokens: the cache entries below new_len stay valid, the
+ * next call continues at position new_len (speculative decoding drops rejected drafts this way).
+ * A model without device state (weights not loaded yet) only accepts new_len == 0. */
+int cml_llama_truncate(CMLLLaMAModel* model, int seq, int new_len) {
+    if (!model || seq < 0 || new_len < 0) { LOG_ERROR("cml_llama_truncate: invalid arguments"); return -1; }
+    DevModel* d = dm_find(model);
+    if (!d || !d->d_cur) {
+        if (new_len == 0 && seq == 0) return 0;
+        LOG_ERROR("cml_llama_truncate: the model holds no device state");
+        return -1;
+    }
+    if (seq >= d->max_batch) { LOG_ERROR("cml_llama_truncate: sequence %d outside the configured batch of %d", seq, d->max_batch); return -1; }
+    if (new_len > d->h_cur[seq]) { LOG_ERROR("cml_llama_truncate: new length %d exceeds the %d cached tokens", new_len, d->h_cur[seq]); return -1; }
+    if (new_len == d->h_cur[seq]) return 0;
+    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur + seq, &new_len, sizeof(int), d->stream), "cml_llama_truncate") ||
+        CML_DEV_FAIL(cmlb200_stream_sync(d->stream), "cml_llama_truncate"))
+        return -1;
+    d->h_cur[seq] = new_len;
+    if (seq == 0) {
+        model->current_seq_len = new_len;
+        for (int i = 0; i < model->num_layers; i++)
+            if (model->layers[i] && model->layers[i]->kv_cache) model->layers[i]->kv_cache->current_len = new_len;
+    }
+    return 0;
+}
+
 void cml_llama_print_config(const CMLLLaMAConfig* config) {
     if (!config) return;
     const int hd = config->hidden_size / config->num_heads;

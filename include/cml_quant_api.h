@@ -204,6 +204,55 @@ Tensor* cml_gqa_forward(Tensor* Q, Tensor* K, Tensor* V, const CMLGQAConfig* con
 /* Appends K, V (batch 1) to the cache, then attends the whole cached prefix. */
 Tensor* cml_gqa_forward_cached(Tensor* Q, Tensor* K, Tensor* V, CMLKVCache* kv_cache, const CMLGQAConfig* config);
 
+/* ---- include/nn/paged_attention.h:14-80 --------------------------------------------------------
+ * Paged KV cache: a pool of 16-token blocks shared by up to max_sequences sequences, a stack free
+ * list, one block table per sequence. Same structs and return values as C-ML. A block's key_data /
+ * value_data are host memory ([block_size, num_kv_heads, head_dim], readable by the caller); the
+ * attention runs on a device copy of the pool that cml_paged_gqa_forward brings up to date, so
+ * tokens must be written with cml_paged_cache_append. */
+#define CML_PAGE_BLOCK_SIZE 16
+#define CML_MAX_BLOCKS 4096
+#define CML_MAX_SEQUENCES 256
+typedef struct CMLPageBlock {
+    float* key_data;
+    float* value_data;
+    int num_tokens;
+    int block_id;
+    bool in_use;
+} CMLPageBlock;
+typedef struct CMLBlockTable {
+    int* block_ids;
+    int num_blocks;
+    int capacity;
+    int seq_len;
+} CMLBlockTable;
+typedef struct CMLPagedKVCache {
+    CMLPageBlock* blocks;
+    int num_blocks;
+    int max_blocks;
+    int* free_list;
+    int free_count;
+    CMLBlockTable* sequences;
+    int num_sequences;
+    int max_sequences;
+    int num_kv_heads;
+    int head_dim;
+    int block_size;
+    size_t total_allocated;
+    size_t total_freed;
+} CMLPagedKVCache;
+CMLPagedKVCache* cml_paged_kv_cache_create(int max_blocks, int max_sequences, int num_kv_heads, int head_dim);
+void cml_paged_kv_cache_free(CMLPagedKVCache* cache);
+int cml_paged_cache_alloc_block(CMLPagedKVCache* cache);              /* block id, -1 when the pool is exhausted */
+void cml_paged_cache_free_block(CMLPagedKVCache* cache, int block_id);
+int cml_paged_cache_init_sequence(CMLPagedKVCache* cache);            /* sequence id, -1 when all slots are taken */
+void cml_paged_cache_free_sequence(CMLPagedKVCache* cache, int seq_id);
+/* key, value: [num_kv_heads * head_dim] of one token; a new block is taken when the tail block is full */
+int cml_paged_cache_append(CMLPagedKVCache* cache, int seq_id, const float* key, const float* value);
+/* Q [1, seq_q, num_heads*head_dim]; query row i sits at position seq_len - seq_q + i of the
+ * sequence. Returns a new [1, seq_q, num_heads*head_dim] tensor, NULL on error. */
+Tensor* cml_paged_gqa_forward(CMLPagedKVCache* cache, int seq_id, Tensor* Q, const CMLGQAConfig* config);
+
 typedef struct CMLRoPEConfig {
     int dim;
     int max_seq_len;
@@ -372,6 +421,74 @@ int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int d
  * ranks by any means, then every rank calls cml_llama_tp_init before loading weights. */
 int cml_llama_tp_unique_id(void* id128);
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device);
+
+/* ---- include/nn/speculative.h:15-90 ------------------------------------------------------------
+ * Draft K tokens with one model, verify them with one call of another, keep the longest run that
+ * matches the target's arg-max plus one more token. Same structs, callbacks and return values as
+ * C-ML; the decoder is host code. */
+#define CML_SPEC_MAX_DRAFT_TOKENS 16
+typedef struct CMLSpeculativeConfig {
+    int num_draft_tokens;       /* K, 1..CML_SPEC_MAX_DRAFT_TOKENS (default 5) */
+    float temperature;
+    float top_p;
+    int top_k;
+    bool do_sample;
+} CMLSpeculativeConfig;
+typedef struct CMLSpeculativeResult {
+    int* accepted_tokens;       /* accepted drafts, then the target's correction or bonus token */
+    int num_accepted;           /* entries of accepted_tokens */
+    int num_drafted;
+    int num_verified;
+    float acceptance_rate;      /* accepted drafts / drafted */
+    double draft_time_ms;
+    double verify_time_ms;
+    double total_time_ms;
+} CMLSpeculativeResult;
+/* logits [seq_len, vocab_size] of the whole sequence; the decoder frees the tensor */
+typedef Tensor* (*CMLModelForwardFn)(void* model_ctx, const int* token_ids, int seq_len);
+typedef int (*CMLSampleTokenFn)(void* model_ctx, Tensor* logits, float temperature);
+typedef struct CMLSpeculativeDecoder {
+    CMLSpeculativeConfig config;
+    void* draft_model_ctx;
+    CMLModelForwardFn draft_forward;
+    CMLSampleTokenFn draft_sample;
+    void* target_model_ctx;
+    CMLModelForwardFn target_forward;
+    CMLSampleTokenFn target_sample;
+    int vocab_size;
+    size_t total_drafted;
+    size_t total_accepted;
+    size_t total_steps;
+} CMLSpeculativeDecoder;
+CMLSpeculativeConfig cml_speculative_default_config(void);
+CMLSpeculativeDecoder* cml_speculative_create(const CMLSpeculativeConfig* config, int vocab_size);
+void cml_speculative_free(CMLSpeculativeDecoder* decoder);
+void cml_speculative_set_draft_model(CMLSpeculativeDecoder* dec, void* ctx, CMLModelForwardFn forward_fn, CMLSampleTokenFn sample_fn);
+void cml_speculative_set_target_model(CMLSpeculativeDecoder* dec, void* ctx, CMLModelForwardFn forward_fn, CMLSampleTokenFn sample_fn);
+CMLSpeculativeResult* cml_speculative_decode_step(CMLSpeculativeDecoder* dec, const int* prefix_tokens, int prefix_len);
+void cml_speculative_result_free(CMLSpeculativeResult* result);
+float cml_speculative_acceptance_rate(const CMLSpeculativeDecoder* dec);
+
+/* Callbacks that drive a device-resident CMLLLaMAModel (no counterpart in C-ML, whose callers wrap
+ * cml_llama_forward themselves and re-run the whole sequence on every call). The context tracks
+ * the tokens held by the model's KV cache: a call rolls the cache back to the longest common
+ * prefix and forwards only the remaining rows, at least 1 for a draft model and
+ * CML_SPEC_MAX_DRAFT_TOKENS + 1 for a target model; rows of the reused prefix come back as zeros.
+ * cml_llama_truncate sets the position of sequence `seq` back to new_len (0 <= new_len <= current). */
+typedef struct CMLSpeculativeLlama {
+    CMLLLaMAModel* model;
+    int* cached_tokens;
+    int cached_len;
+    int capacity;
+    int min_rows;
+    size_t rows_computed;       /* statistics: rows forwarded / calls */
+    size_t calls;
+} CMLSpeculativeLlama;
+CMLSpeculativeLlama* cml_speculative_llama_create(CMLLLaMAModel* model, bool is_target);
+void cml_speculative_llama_free(CMLSpeculativeLlama* ctx);
+Tensor* cml_speculative_llama_forward(void* model_ctx, const int* token_ids, int seq_len);
+int cml_speculative_llama_sample(void* model_ctx, Tensor* logits, float temperature);
+int cml_llama_truncate(CMLLLaMAModel* model, int seq, int new_len);
 
 #ifdef __cplusplus
 }

@@ -307,6 +307,12 @@ int cmlb200_event_record(void* event, void* stream);
 int cmlb200_event_elapsed_ms(void* start, void* stop, float* ms);
 int cmlb200_event_destroy(void* event);
 
+/* Attention of one sequence over a paged KV pool (src/nn/paged_attention.c:332-480). d_q, d_out:
+ * [seq_q, heads*head_dim] fp32; d_kpool, d_vpool: [blocks][block_size][kv_heads*head_dim] fp32;
+ * d_block_ids: the sequence's block table. Query row i sits at position kv_len - seq_q + i. */
+int cmlb200_paged_gqa_f32(const float* d_q, const float* d_kpool, const float* d_vpool, const int* d_block_ids, int block_size,
+                          int seq_q, int kv_len, int heads, int kv_heads, int head_dim, float scale, int causal, float* d_out,
+                          void* stream);
 /* ---- fp32 operators behind the stand-alone C-ML entry points ------------------------------
  * cmlb200_gqa_f32: softmax(Q K^T * scale + masks) V with every option of cml_gqa_forward
  * (src/nn/llm_ops.c:194-372; masked scores are -1e9): q [batch, seq_q, heads*hd], k, v

@@ -79,6 +79,7 @@ def load_orc():
     _sig(lib, "orc_rmsnorm", None, vp, vp, ci, ci, cf, vp)
     _sig(lib, "orc_rope", None, vp, ci, ci, ci, ci, cf, ci)
     _sig(lib, "orc_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp)
+    _sig(lib, "orc_paged_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp)
     _sig(lib, "orc_llama_forward", ci, C.POINTER(OrcLlamaStruct), vp, ci, vp)
     _sig(lib, "orc_argmax_first", ci, vp, ci)
     _sig(lib, "orc_tp_shard", ci, vp, ci, ci, ci, ci, ci, vp)
@@ -119,6 +120,8 @@ def load_ref():
         _sig(lib, "ref_sample_token", ci, vp, ci, ci, cf, cf, ci, ci, C.c_uint)
         _sig(lib, "ref_rope_2d", ci, vp, ci, ci, ci, ci, cf)
         _sig(lib, "ref_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, vp)
+        _sig(lib, "ref_paged_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ci, ci, vp)
+        _sig(lib, "ref_speculative_step", ci, vp, vp, ci, ci, vp, ci, ci, vp, vp, vp)
         _sig(lib, "ref_tp_column_then_row", ci, vp, ci, ci, vp, ci, vp, ci, ci, vp)
         lib.ref_init()
     _ref_cache.append(lib)

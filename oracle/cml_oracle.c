@@ -429,6 +429,48 @@ int orc_gqa(const float* q, const float* k, const float* v, int seq, int kv_len,
     return 0;
 }
 
+/* Paged attention of one sequence (src/nn/paged_attention.c:332-480): the keys and values of the
+ * sequence's blocks, walked in block-table order, are its tokens 0..kv_len-1 (here already
+ * gathered: K/V [kv_len, kv_heads*hd]); query row sq sits at absolute position
+ * kv_len - seq_q + sq (:425-433); score = dot * scale, masked ones become -1e9 (:418-436), softmax
+ * with max subtraction (:9-29), out += p * v in token order (:441-460). scale <= 0 means
+ * 1/sqrt(hd) (:381-384). */
+int orc_paged_gqa(const float* q, const float* k, const float* v, int seq_q, int kv_len, int heads,
+                  int kv_heads, int hd, float scale, int causal, float* out) {
+    if (heads <= 0 || kv_heads <= 0 || hd <= 0 || heads % kv_heads || kv_len <= 0 || seq_q <= 0) return -1;
+    int groups = heads / kv_heads;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)hd);
+    float* sc = (float*)malloc((size_t)kv_len * sizeof(float));
+    if (!sc) return -1;
+    for (int h = 0; h < heads; h++) {
+        int kh = h / groups;
+        for (int sq = 0; sq < seq_q; sq++) {
+            const float* qv = q + ((size_t)sq * heads + h) * hd;
+            int abs_pos = kv_len - seq_q + sq;
+            for (int sk = 0; sk < kv_len; sk++) {
+                const float* kv = k + ((size_t)sk * kv_heads + kh) * hd;
+                float d = 0.f;
+                for (int i = 0; i < hd; i++) d += qv[i] * kv[i];
+                sc[sk] = (causal && sk > abs_pos) ? -1e9f : d * scale;
+            }
+            float mx = sc[0];
+            for (int sk = 1; sk < kv_len; sk++) if (sc[sk] > mx) mx = sc[sk];
+            float sum = 0.f;
+            for (int sk = 0; sk < kv_len; sk++) { sc[sk] = expf(sc[sk] - mx); sum += sc[sk]; }
+            if (sum > 0.f) {
+                float inv = 1.0f / sum;
+                for (int sk = 0; sk < kv_len; sk++) sc[sk] *= inv;
+            }
+            float* o = out + ((size_t)sq * heads + h) * hd;
+            for (int i = 0; i < hd; i++) o[i] = 0.f;
+            for (int sk = 0; sk < kv_len; sk++)
+                for (int i = 0; i < hd; i++) o[i] += sc[sk] * v[((size_t)sk * kv_heads + kh) * hd + i];
+        }
+    }
+    free(sc);
+    return 0;
+}
+
 static float orc_silu(float g) { return g / (1.0f + expf(-g)); } /* src/ops/ir/execution.c:2980-2987 */
 
 /* A LLaMA model as flat fp32 arrays, in the reference's orientation: every

@@ -19,7 +19,9 @@
 #include "distributed/tensor_parallel.h"
 #include "nn/llama.h"
 #include "nn/llm_ops.h"
+#include "nn/paged_attention.h"
 #include "nn/qlora.h"
+#include "nn/speculative.h"
 #include "ops/uops.h"
 #include "tensor/tensor.h"
 
@@ -289,6 +291,96 @@ int ref_gqa(const float* q, const float* k, const float* v, int seq, int kv_len,
     if (tq) tensor_free(tq);
     if (tk) tensor_free(tk);
     if (tv) tensor_free(tv);
+    return rc;
+}
+
+/* The paged KV cache and cml_paged_gqa_forward (src/nn/paged_attention.c): a pool of max_blocks
+ * blocks, one sequence, kv_len appended tokens (`spoil` tokens of another sequence appended and
+ * freed first, so that the block table is not the identity), then one forward call. Returns the
+ * number of blocks the sequence holds, or -1. */
+int ref_paged_gqa(const float* q, const float* k, const float* v, int seq_q, int kv_len, int heads, int kv_heads,
+                  int hd, float scale, int causal, int max_blocks, int spoil, float* out) {
+    CMLPagedKVCache* c = cml_paged_kv_cache_create(max_blocks, 4, kv_heads, hd);
+    if (!c) return -1;
+    const size_t kvw = (size_t)kv_heads * hd;
+    int rc = -1, other = -1;
+    if (spoil > 0) {
+        other = cml_paged_cache_init_sequence(c);
+        for (int i = 0; i < spoil && other >= 0; i++) if (cml_paged_cache_append(c, other, k, v)) other = -2;
+    }
+    int s = cml_paged_cache_init_sequence(c);
+    if (s >= 0 && other != -2) {
+        int ok = 1;
+        for (int t = 0; t < kv_len && ok; t++) {
+            if (other >= 0 && t == kv_len / 2) { cml_paged_cache_free_sequence(c, other); other = -1; }   /* its blocks come back mid-way */
+            ok = cml_paged_cache_append(c, s, k + (size_t)t * kvw, v + (size_t)t * kvw) == 0;
+        }
+        int qs[3] = {1, seq_q, heads * hd};
+        Tensor* tq = ok ? t_from(q, 3, qs) : NULL;
+        CMLGQAConfig g = {.num_heads = heads, .num_kv_heads = kv_heads, .head_dim = hd, .scale = scale,
+                          .causal = causal != 0, .window_size = 0};
+        Tensor* o = tq ? cml_paged_gqa_forward(c, s, tq, &g) : NULL;
+        if (o) {
+            memcpy(out, tensor_data_ptr(o), (size_t)seq_q * heads * hd * sizeof(float));
+            tensor_free(o);
+            rc = c->sequences[s].num_blocks;
+        }
+        if (tq) tensor_free(tq);
+    }
+    cml_paged_kv_cache_free(c);
+    return rc;
+}
+
+/* cml_speculative_decode_step (src/nn/speculative.c:88-250) over two table-driven stand-in models:
+ * after token t a model predicts next[t] (logit 1.0, and the same value again at index next[t] + 1
+ * when t is odd, which pins the first-maximum rule). The draft model returns NULL for sequences of
+ * draft_fail_len tokens or more (0: never). out_tokens takes K + 1 entries; meta = {num_accepted,
+ * num_drafted, num_verified, total_drafted, total_accepted, total_steps}. */
+typedef struct { const int* next; int vocab; int fail_len; } TableLM;
+static Tensor* table_forward(void* ctx, const int* toks, int n) {
+    const TableLM* m = (const TableLM*)ctx;
+    if (m->fail_len > 0 && n >= m->fail_len) return NULL;
+    float* lg = (float*)calloc((size_t)n * m->vocab, sizeof(float));
+    if (!lg) return NULL;
+    for (int r = 0; r < n; r++) {
+        const int nx = m->next[toks[r]];
+        lg[(size_t)r * m->vocab + nx] = 1.0f;
+        if ((toks[r] & 1) && nx + 1 < m->vocab) lg[(size_t)r * m->vocab + nx + 1] = 1.0f;
+    }
+    int sh[2] = {n, m->vocab};
+    Tensor* t = t_from(lg, 2, sh);
+    free(lg);
+    return t;
+}
+static int table_sample(void* ctx, Tensor* lg, float temperature) {
+    (void)temperature;
+    const TableLM* m = (const TableLM*)ctx;
+    const float* p = (const float*)tensor_data_ptr(lg) + (size_t)(lg->shape[0] - 1) * m->vocab;
+    int best = 0;
+    for (int i = 1; i < m->vocab; i++) if (p[i] > p[best]) best = i;
+    return best;
+}
+int ref_speculative_step(const int* draft_next, const int* target_next, int vocab, int draft_fail_len, const int* prefix,
+                         int prefix_len, int K, int* out_tokens, int* meta, float* rates) {
+    CMLSpeculativeConfig cfg = cml_speculative_default_config();
+    cfg.num_draft_tokens = K;
+    CMLSpeculativeDecoder* dec = cml_speculative_create(&cfg, vocab);
+    if (!dec) return -1;
+    TableLM dm = {draft_next, vocab, draft_fail_len}, tm = {target_next, vocab, 0};
+    cml_speculative_set_draft_model(dec, &dm, table_forward, table_sample);
+    cml_speculative_set_target_model(dec, &tm, table_forward, table_sample);
+    CMLSpeculativeResult* r = cml_speculative_decode_step(dec, prefix, prefix_len);
+    int rc = -1;
+    if (r) {
+        for (int i = 0; i < r->num_accepted; i++) out_tokens[i] = r->accepted_tokens[i];
+        meta[0] = r->num_accepted; meta[1] = r->num_drafted; meta[2] = r->num_verified;
+        meta[3] = (int)dec->total_drafted; meta[4] = (int)dec->total_accepted; meta[5] = (int)dec->total_steps;
+        rates[0] = r->acceptance_rate;
+        rates[1] = cml_speculative_acceptance_rate(dec);
+        cml_speculative_result_free(r);
+        rc = 0;
+    }
+    cml_speculative_free(dec);
     return rc;
 }
 

@@ -170,6 +170,44 @@ def main():
         out.update({f"qlora_{tag}_W": W2, f"qlora_{tag}_x": x2, f"qlora_{tag}_A": A2, f"qlora_{tag}_B": B2, f"qlora_{tag}_y": y2,
                     f"qlora_{tag}_cfg": np.array([n_out2, n_in2, block2, rank2, M2], np.int32)})
 
+    # --- paged KV cache + cml_paged_gqa_forward: (seq_q, kv_len, heads, kv_heads, hd, scale, causal, spoil)
+    rng5 = np.random.default_rng(20240605)
+    pcases = [(1, 37, 4, 2, 16, 0.0, 1, 20), (5, 21, 4, 4, 8, 0.0, 1, 0), (3, 16, 6, 2, 32, 0.25, 0, 5), (4, 4, 2, 1, 16, 0.0, 1, 0)]
+    for i, (sq, kvl, hh, kh, hd2, sc2, cz, spoil) in enumerate(pcases):
+        pq = rng5.standard_normal((sq, hh * hd2)).astype(np.float32)
+        pk = rng5.standard_normal((kvl, kh * hd2)).astype(np.float32)
+        pv = rng5.standard_normal((kvl, kh * hd2)).astype(np.float32)
+        po = np.empty((sq, hh * hd2), np.float32)
+        nb = ref.ref_paged_gqa(p(pq), p(pk), p(pv), sq, kvl, hh, kh, hd2, sc2, cz, 8, spoil, p(po))
+        assert nb == (kvl + 15) // 16, nb
+        out.update({f"paged{i}_q": pq, f"paged{i}_k": pk, f"paged{i}_v": pv, f"paged{i}_out": po,
+                    f"paged{i}_cfg": np.array([sq, kvl, hh, kh, hd2, cz, spoil], np.int32), f"paged{i}_scale": np.array([sc2], np.float32)})
+
+    # --- cml_speculative_decode_step over table-driven stand-in models (see oracle/ref_driver.c):
+    # all drafts accepted, first draft rejected, a miss in the middle, a draft model that gives up
+    rng6 = np.random.default_rng(20240606)
+    vocab6 = 23
+    tgt = rng6.permutation(vocab6).astype(np.int32)
+    scases = []
+    for name, K6, nmiss, fail in (("all", 5, 0, 0), ("first", 4, 1, 0), ("mid", 6, 1, 0), ("giveup", 5, 0, 9), ("k1", 1, 0, 0), ("k16", 16, 3, 0)):
+        drf = tgt.copy()
+        prefix6 = rng6.integers(0, vocab6, 7).astype(np.int32)
+        # walk the target chain from the prefix's last token and break the draft table along it
+        chain = [int(prefix6[-1])]
+        for _ in range(K6 + 1):
+            chain.append(int(tgt[chain[-1]]))
+        if nmiss:
+            at = {"first": 0, "mid": 3, "k16": 9}[name]
+            drf[chain[at]] = (tgt[chain[at]] + 2) % vocab6
+        toks = np.full(K6 + 1, -1, np.int32)
+        meta = np.zeros(6, np.int32)
+        rates = np.zeros(2, np.float32)
+        assert ref.ref_speculative_step(p(drf), p(tgt), vocab6, fail, p(prefix6), len(prefix6), K6, p(toks), p(meta), p(rates)) == 0
+        out.update({f"spec_{name}_draft": drf, f"spec_{name}_prefix": prefix6, f"spec_{name}_tokens": toks, f"spec_{name}_meta": meta,
+                    f"spec_{name}_rates": rates, f"spec_{name}_cfg": np.array([K6, fail], np.int32)})
+        scases.append(name)
+    out["spec_target"] = tgt
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 

@@ -1,6 +1,7 @@
 """CPU-side checks of the drop-in boundary: the C-ABI library loads, exports every symbol the
 public headers declare, rejects bad arguments without touching a GPU, and the host repack is
 a byte-exact bijection."""
+import ctypes as C
 import re
 from pathlib import Path
 
@@ -170,3 +171,115 @@ def test_reference_example_program_links_against_the_library(pkg, ob, tmp_path):
     assert r.returncode == 0 and "LLaMA inference" in r.stdout
     r = subprocess.run([str(exe), str(tmp_path / "missing.gguf"), "--greedy"], capture_output=True, text=True)
     assert r.returncode == 1 and "Failed to load GGUF weights" in r.stderr
+
+
+def test_reference_paged_attention_test_program_runs_against_the_library(pkg, ob, tmp_path):
+    """tests/test_paged_attention.c of the C-ML tree, unmodified, builds against include/ and
+    libcml_b200.so; every case that needs no device passes here (the three that call
+    cml_paged_gqa_forward with valid arguments need a GPU and are covered by the GPU tests)."""
+    import subprocess
+    root = ob.reference_root()
+    if root is None:
+        pytest.skip("the C-ML source tree is not on this machine")
+    exe = tmp_path / "test_paged_attention"
+    libdir = ROOT / "c-ml_b200" / "lib"
+    cmd = ["gcc", "-std=c11", "-D_POSIX_C_SOURCE=200809L", f"-I{ROOT / 'include'}", str(Path(root) / "tests" / "test_paged_attention.c"),
+           "-o", str(exe), f"-L{libdir}", "-lcml_b200", f"-Wl,-rpath,{libdir}", "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    text = r.stdout + r.stderr
+    verdicts = re.findall(r"^\s{2}(\w+)\s.*?\[(PASS|FAIL)\]", text, flags=re.M | re.S)
+    failed = {name for name, v in verdicts if v == "FAIL"}
+    assert len(verdicts) == 20, text[-2000:]
+    assert failed <= {"paged_gqa_output_shape", "paged_gqa_multi_query_tokens", "paged_gqa_output_nonzero"}, failed
+
+
+def _table_models(pkg, next_draft, next_target, vocab, fail_len):
+    """ctypes callbacks of the stand-in models the golden vectors were made with (oracle/ref_driver.c:
+    after token t the model predicts next[t], with an equal logit at next[t] + 1 when t is odd)."""
+    keep = []
+
+    def forward(table, fail):
+        def fn(_ctx, toks, n):
+            if fail and n >= fail:
+                return None
+            lg = np.zeros((n, vocab), np.float32)
+            for r in range(n):
+                nx = int(table[toks[r]])
+                lg[r, nx] = 1.0
+                if toks[r] & 1 and nx + 1 < vocab:
+                    lg[r, nx + 1] = 1.0
+            return C.cast(pkg.numpy_to_tensor(lg), C.c_void_p).value
+        return pkg.ModelForwardFn(fn)
+
+    def sample(_ctx, logits, _temperature):
+        a = pkg.tensor_to_numpy(C.cast(logits, pkg.TP), free=False)
+        return int(np.argmax(a[-1]))
+    keep += [forward(next_draft, fail_len), forward(next_target, 0), pkg.SampleTokenFn(sample)]
+    return keep
+
+
+def test_speculative_decode_step_matches_the_compiled_reference(pkg, golden):
+    tgt = golden["spec_target"]
+    vocab = len(tgt)
+    for name in ("all", "first", "mid", "giveup", "k1", "k16"):
+        K, fail = (int(x) for x in golden[f"spec_{name}_cfg"])
+        cfg = pkg.lib.cml_speculative_default_config()
+        assert (cfg.num_draft_tokens, cfg.top_k, cfg.do_sample) == (5, 40, True) and abs(cfg.temperature - 0.8) < 1e-7
+        cfg.num_draft_tokens = K
+        dec = pkg.lib.cml_speculative_create(C.byref(cfg), vocab)
+        assert dec
+        fd, ft, fs = _table_models(pkg, golden[f"spec_{name}_draft"], tgt, vocab, fail)
+        pkg.lib.cml_speculative_set_draft_model(dec, None, C.cast(fd, C.c_void_p), C.cast(fs, C.c_void_p))
+        pkg.lib.cml_speculative_set_target_model(dec, None, C.cast(ft, C.c_void_p), C.cast(fs, C.c_void_p))
+        prefix = np.ascontiguousarray(golden[f"spec_{name}_prefix"], np.int32)
+        pkg.lib.cml_set_log_level(5)
+        res = pkg.lib.cml_speculative_decode_step(dec, pkg.np_ptr(prefix), len(prefix))
+        pkg.lib.cml_set_log_level(3)
+        assert res
+        r, want_meta, want_rates = res.contents, golden[f"spec_{name}_meta"], golden[f"spec_{name}_rates"]
+        got = [r.accepted_tokens[i] for i in range(r.num_accepted)]
+        assert got == golden[f"spec_{name}_tokens"][:r.num_accepted].tolist(), name
+        d = dec.contents
+        assert [r.num_accepted, r.num_drafted, r.num_verified, d.total_drafted, d.total_accepted, d.total_steps] == want_meta.tolist(), name
+        assert r.acceptance_rate == want_rates[0] and pkg.lib.cml_speculative_acceptance_rate(dec) == want_rates[1]
+        assert r.total_time_ms >= r.draft_time_ms >= 0 and r.verify_time_ms >= 0
+        pkg.lib.cml_speculative_result_free(res)
+        pkg.lib.cml_speculative_free(dec)
+
+
+def test_speculative_argument_checks(pkg):
+    pkg.lib.cml_set_log_level(5)
+    cfg = pkg.lib.cml_speculative_default_config()
+    assert not pkg.lib.cml_speculative_create(None, 10)
+    assert not pkg.lib.cml_speculative_create(C.byref(cfg), 0)
+    cfg.num_draft_tokens = 17
+    assert not pkg.lib.cml_speculative_create(C.byref(cfg), 10)
+    cfg.num_draft_tokens = 3
+    dec = pkg.lib.cml_speculative_create(C.byref(cfg), 10)
+    one = np.array([1], np.int32)
+    assert not pkg.lib.cml_speculative_decode_step(dec, pkg.np_ptr(one), 1)          # callbacks not set
+    assert not pkg.lib.cml_speculative_decode_step(None, pkg.np_ptr(one), 1)
+    assert pkg.lib.cml_speculative_acceptance_rate(dec) == 0.0 and pkg.lib.cml_speculative_acceptance_rate(None) == 0.0
+    pkg.lib.cml_speculative_free(dec)
+    pkg.lib.cml_speculative_free(None)
+    pkg.lib.cml_speculative_result_free(None)
+    assert not pkg.lib.cml_speculative_llama_create(None, False)
+    pkg.lib.cml_set_log_level(3)
+
+
+def test_reference_speculative_test_program_passes_against_the_library(pkg, ob, tmp_path):
+    """tests/test_speculative.c of the C-ML tree, unmodified (mock models, no device needed): 18 of 18."""
+    import subprocess
+    root = ob.reference_root()
+    if root is None:
+        pytest.skip("the C-ML source tree is not on this machine")
+    exe = tmp_path / "test_speculative"
+    libdir = ROOT / "c-ml_b200" / "lib"
+    cmd = ["gcc", "-std=c11", "-D_POSIX_C_SOURCE=200809L", f"-I{ROOT / 'include'}", str(Path(root) / "tests" / "test_speculative.c"),
+           "-o", str(exe), f"-L{libdir}", "-lcml_b200", f"-Wl,-rpath,{libdir}", "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "18/18 passed" in r.stdout, (r.stdout + r.stderr)[-1500:]

@@ -350,3 +350,86 @@ def test_models_with_other_block_types_match_oracle(pkg, tmp_path, torch_dev, gt
         assert out.tolist() == want_toks
     finally:
         pkg.lib.cml_llama_free(m)
+
+
+def _greedy_reference_tokens(pkg, path, prompt, n):
+    """n greedy tokens of the model at `path` after `prompt`, one cml_llama_forward per token."""
+    m = device_model(pkg, TINY, path)
+    try:
+        lg = dev_forward(pkg, m, prompt)
+        out = [int(lg[-1].argmax())]
+        while len(out) < n:
+            out.append(int(dev_forward(pkg, m, np.array(out[-1:], np.int32))[0].argmax()))
+        return out
+    finally:
+        pkg.lib.cml_llama_free(m)
+
+
+@pytest.mark.parametrize("same_draft", [True, False])
+def test_speculative_decoding_reproduces_the_target_models_greedy_tokens(pkg, tiny, tmp_path, torch_dev, same_draft):
+    """cml_speculative_decode_step over two device-resident models through the cache-keeping
+    callbacks: the accepted tokens are exactly the target's greedy continuation, whatever the draft
+    model proposes; with the target as its own draft every draft is accepted; the callbacks forward
+    only the rows past the cached prefix."""
+    path, _ = tiny
+    dpath = path
+    if not same_draft:
+        dpath = tmp_path / "draft.gguf"
+        build(entry, np.random.default_rng(77), TINY, dpath)
+    prompt = np.random.default_rng(31).integers(0, TINY["vocab"], 9).astype(np.int32)
+    want = _greedy_reference_tokens(pkg, path, prompt, 24)
+    target, draft = device_model(pkg, TINY, path), device_model(pkg, TINY, dpath)
+    tctx, dctx = pkg.lib.cml_speculative_llama_create(target, True), pkg.lib.cml_speculative_llama_create(draft, False)
+    cfg = pkg.lib.cml_speculative_default_config()
+    cfg.num_draft_tokens, cfg.temperature = 4, 0.0
+    dec = pkg.lib.cml_speculative_create(C.byref(cfg), TINY["vocab"])
+    fwd = C.cast(pkg.lib.cml_speculative_llama_forward, C.c_void_p)
+    smp = C.cast(pkg.lib.cml_speculative_llama_sample, C.c_void_p)
+    pkg.lib.cml_speculative_set_draft_model(dec, C.cast(dctx, C.c_void_p), fwd, smp)
+    pkg.lib.cml_speculative_set_target_model(dec, C.cast(tctx, C.c_void_p), fwd, smp)
+    try:
+        seq, got, steps = prompt.tolist(), [], 0
+        while len(got) < 20:
+            arr = np.array(seq, np.int32)
+            res = pkg.lib.cml_speculative_decode_step(dec, pkg.np_ptr(arr), len(arr))
+            assert res
+            r = res.contents
+            new = [r.accepted_tokens[i] for i in range(r.num_accepted)]
+            assert 1 <= len(new) <= 5 and r.num_drafted == 4
+            pkg.lib.cml_speculative_result_free(res)
+            seq += new
+            got += new
+            steps += 1
+        assert got == want[:len(got)]
+        rate = pkg.lib.cml_speculative_acceptance_rate(dec)
+        if same_draft:
+            assert rate == 1.0 and steps == 4
+        else:
+            assert rate < 1.0
+        # the target saw the prompt once and then at most 17 rows per step; the draft at most prompt + (rows past its cache)
+        t, d = tctx.contents, dctx.contents
+        assert t.calls == steps and t.rows_computed <= len(prompt) + 4 + 17 * (steps - 1)
+        assert d.calls == 4 * steps and d.rows_computed <= len(prompt) + 4 * steps + 6 * steps
+        assert target.contents.current_seq_len == t.cached_len
+    finally:
+        pkg.lib.cml_speculative_free(dec)
+        pkg.lib.cml_speculative_llama_free(tctx)
+        pkg.lib.cml_speculative_llama_free(dctx)
+        pkg.lib.cml_llama_free(target)
+        pkg.lib.cml_llama_free(draft)
+
+
+def test_truncate_rolls_the_cache_back(pkg, tiny, torch_dev):
+    path, _ = tiny
+    toks = np.random.default_rng(8).integers(0, TINY["vocab"], 14).astype(np.int32)
+    m = device_model(pkg, TINY, path)
+    try:
+        full = dev_forward(pkg, m, toks)
+        assert pkg.lib.cml_llama_truncate(m, 0, 9) == 0 and m.contents.current_seq_len == 9
+        again = dev_forward(pkg, m, toks[9:])
+        assert rel_err_inf(again, full[9:]) <= 2e-3
+        pkg.lib.cml_set_log_level(5)
+        assert pkg.lib.cml_llama_truncate(m, 0, 15) == -1 and pkg.lib.cml_llama_truncate(m, 3, 0) == -1 and pkg.lib.cml_llama_truncate(m, 0, -1) == -1
+        pkg.lib.cml_set_log_level(3)
+    finally:
+        pkg.lib.cml_llama_free(m)

@@ -282,3 +282,27 @@ def test_qlora_small_block_shapes_match_golden(ob, orc, golden, tag):
     y = np.empty((M, n_out), np.float32)
     assert orc.orc_qlora_forward(ob.p(x), M, n_in, n_out, ob.p(packed), ob.p(scales), ns, block, ob.p(A), ob.p(B), rank, 4.0 / rank, ob.p(y)) == 0
     assert rel_err_inf(y, golden[f"qlora_{tag}_y"]) < 1e-5
+
+
+def test_paged_attention_matches_golden_and_reference(ob, orc, golden):
+    """cml_paged_gqa_forward: causal mask anchored at the end of the cached sequence, explicit and
+    default scale, block tables that are not the identity (src/nn/paged_attention.c:332-480)."""
+    ref = ob.load_ref()
+    for i in range(4):
+        sq, kvl, hh, kh, hd, cz, spoil = (int(x) for x in golden[f"paged{i}_cfg"])
+        sc = float(golden[f"paged{i}_scale"][0])
+        q, k, v = golden[f"paged{i}_q"], golden[f"paged{i}_k"], golden[f"paged{i}_v"]
+        out = np.empty_like(golden[f"paged{i}_out"])
+        assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), sq, kvl, hh, kh, hd, sc, cz, ob.p(out)) == 0
+        assert np.abs(out - golden[f"paged{i}_out"]).max() < 1e-5
+        if ref is not None:
+            live = np.empty_like(out)
+            assert ref.ref_paged_gqa(ob.p(q), ob.p(k), ob.p(v), sq, kvl, hh, kh, hd, sc, cz, 8, spoil, ob.p(live)) == (kvl + 15) // 16
+            assert np.array_equal(live, golden[f"paged{i}_out"])
+    # causal with the query anchored at the end: one query row over kv_len keys sees all of them
+    q, k, v = golden["paged0_q"], golden["paged0_k"], golden["paged0_v"]
+    a, b = np.empty_like(q), np.empty_like(q)
+    assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), 1, 37, 4, 2, 16, 0.0, 1, ob.p(a)) == 0
+    assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), 1, 37, 4, 2, 16, 0.0, 0, ob.p(b)) == 0
+    assert np.array_equal(a, b)
+    assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), 1, 37, 3, 2, 16, 0.0, 1, ob.p(a)) == -1
