@@ -72,6 +72,7 @@ _sig("cmlb200_rope_table", ci, vp, ci, ci, C.c_float, vp, vp)
 _sig("cmlb200_attention_prefill", ci, vp, ci, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp, vp, vp)
 _sig("cmlb200_argmax", ci, vp, ci, ci, vp, vp)
 _sig("cmlb200_embed_f16", ci, vp, vp, ci, ci, ci, vp, vp)
+_sig("cmlb200_rmsnorm", ci, vp, vp, ci, ci, C.c_float, vp, vp, vp)
 _sig("cmlb200_tiles_bytes", sz, ci, ci, ci)
 _sig("cmlb200_repack_tiles", ci, ci, vp, ci, ci, vp)
 _sig("cmlb200_unrepack_tiles", ci, ci, vp, ci, ci, vp)

@@ -73,6 +73,47 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const __half* __rest
     }
 }
 
+// The same for rows of up to 8192 elements with dim % 4 == 0 (every LLaMA width): the row is read
+// once with 16-byte loads and stays in registers between the sum of squares and the scaling; bf16
+// results leave as 8-byte stores.
+template <bool BF16_OUT>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const float* __restrict__ x, const __half* __restrict__ w, int dim, float eps, void* out) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, nv = dim >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * dim);
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < nv ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) tot += red[k];
+    const float inv = 1.0f / sqrtf(tot / (float)dim + eps);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < nv) {
+            const uint2 wv = reinterpret_cast<const uint2*>(w)[i];
+            const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&wv.x)), w23 = __half22float2(*reinterpret_cast<const __half2*>(&wv.y));
+            const float a = v[j].x * inv * w01.x, b = v[j].y * inv * w01.y, c = v[j].z * inv * w23.x, d = v[j].w * inv * w23.y;
+            if (BF16_OUT) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                reinterpret_cast<uint2*>(out)[(size_t)r * nv + i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            } else {
+                reinterpret_cast<float4*>(out)[(size_t)r * nv + i] = make_float4(a, b, c, d);
+            }
+        }
+    }
+}
+
 // ---- RoPE, interleaved pairs (2i, 2i+1), freq = 1 / powf(base, 2i / head_dim), in place.
 // heads_to_rotate = 1 reproduces C-ML's behaviour on the 2-D [seq, heads*head_dim] tensors
 // llama.c passes (only the first head_dim columns rotate); = heads rotates every head.
@@ -679,7 +720,11 @@ extern "C" int cmlb200_embed_f16(const uint16_t* d_table_f16, const int* d_token
 extern "C" int cmlb200_rmsnorm(const float* d_x, const uint16_t* d_w_f16, int rows, int dim, float eps, float* d_out_f32,
                                uint16_t* d_out_bf16, void* stream) {
     CMLB_REQUIRE(d_x && d_w_f16 && (d_out_f32 || d_out_bf16) && rows > 0 && dim > 0, "cmlb200_rmsnorm: bad argument");
-    if (d_out_bf16) rmsnorm_kernel<true><<<rows, 256, 0, as_stream(stream)>>>(d_x, (const __half*)d_w_f16, dim, eps, d_out_bf16);
+    const bool vec = dim % 4 == 0 && dim <= 8192 && ((uintptr_t)d_x & 15) == 0 && ((uintptr_t)d_w_f16 & 7) == 0 &&
+                     (d_out_bf16 ? ((uintptr_t)d_out_bf16 & 7) == 0 : ((uintptr_t)d_out_f32 & 15) == 0);
+    if (vec && d_out_bf16) rmsnorm_vec_kernel<true><<<rows, 256, 0, as_stream(stream)>>>(d_x, (const __half*)d_w_f16, dim, eps, d_out_bf16);
+    else if (vec) rmsnorm_vec_kernel<false><<<rows, 256, 0, as_stream(stream)>>>(d_x, (const __half*)d_w_f16, dim, eps, d_out_f32);
+    else if (d_out_bf16) rmsnorm_kernel<true><<<rows, 256, 0, as_stream(stream)>>>(d_x, (const __half*)d_w_f16, dim, eps, d_out_bf16);
     else rmsnorm_kernel<false><<<rows, 256, 0, as_stream(stream)>>>(d_x, (const __half*)d_w_f16, dim, eps, d_out_f32);
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;

@@ -216,3 +216,26 @@ def test_embedding_gather(pkg, torch_dev, hidden):
     idx = np.where((toks < 0) | (toks >= vocab), 0, toks)
     assert np.array_equal(out.cpu().numpy(), table[idx].astype(np.float32))
 
+
+
+@pytest.mark.parametrize("dim", [4096, 8192, 1376, 100, 8200])
+def test_rmsnorm_fp32_and_bf16_outputs(pkg, ob, orc, synth, torch_dev, dim):
+    """RMSNorm (src/nn/llama.c:71-124) with an fp16 weight: the vectorised single-pass kernel (dim % 4 == 0,
+    up to 8192) and the general one, fp32 output against the oracle and bf16 output as its rounding."""
+    import torch
+    rng = np.random.default_rng(dim)
+    rows = 5
+    x = (rng.standard_normal((rows, dim)) * rng.uniform(0.1, 4.0, (rows, 1))).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float16)
+    want = np.empty_like(x)
+    orc.orc_rmsnorm(ob.p(x), ob.p(w.astype(np.float32)), rows, dim, 1e-5, ob.p(want))
+    d_x, d_w = torch.from_numpy(x).to(torch_dev), torch.from_numpy(w).to(torch_dev)
+    o32 = torch.zeros((rows, dim), dtype=torch.float32, device=torch_dev)
+    o16 = torch.zeros((rows, dim), dtype=torch.bfloat16, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_rmsnorm(d_x.data_ptr(), d_w.data_ptr(), rows, dim, 1e-5, o32.data_ptr(), None, None), "cmlb200_rmsnorm")
+    pkg.check(pkg.lib.cmlb200_rmsnorm(d_x.data_ptr(), d_w.data_ptr(), rows, dim, 1e-5, None, o16.data_ptr(), None), "cmlb200_rmsnorm")
+    torch.cuda.synchronize()
+    got = o32.cpu().numpy()
+    assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
+    _, rounded = synth.bf16_round(got)
+    assert np.array_equal(o16.float().cpu().numpy(), rounded)
