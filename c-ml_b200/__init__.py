@@ -266,6 +266,35 @@ _sig("cml_speculative_llama_free", None, SLP)
 _sig("cml_speculative_llama_forward", TP, vp, vp, ci)
 _sig("cml_speculative_llama_sample", ci, vp, TP, C.c_float)
 _sig("cml_llama_truncate", ci, MP, ci, ci)
+class SequenceRequest(C.Structure):
+    _fields_ = [("request_id", C.c_int), ("prompt_tokens", C.POINTER(C.c_int)), ("num_prompt_tokens", C.c_int), ("max_new_tokens", C.c_int),
+                ("temperature", C.c_float), ("top_p", C.c_float), ("status", C.c_int), ("paged_seq_id", C.c_int),
+                ("generated_tokens", C.POINTER(C.c_int)), ("num_generated", C.c_int), ("gen_capacity", C.c_int), ("current_pos", C.c_int),
+                ("submit_time_ms", C.c_double), ("first_token_time_ms", C.c_double), ("finish_time_ms", C.c_double)]
+
+
+class ServingStats(C.Structure):
+    _fields_ = [("total_requests", C.c_size_t), ("completed_requests", C.c_size_t), ("active_sequences", C.c_size_t),
+                ("total_tokens_generated", C.c_size_t), ("avg_time_to_first_token_ms", C.c_double), ("avg_tokens_per_second", C.c_double),
+                ("total_time_ms", C.c_double)]
+
+
+class ServingConfig(C.Structure):
+    _fields_ = [("max_batch_size", C.c_int), ("max_queue_size", C.c_int), ("max_seq_len", C.c_int), ("max_new_tokens_default", C.c_int),
+                ("temperature_default", C.c_float), ("top_p_default", C.c_float)]
+
+
+FinishFn = C.CFUNCTYPE(None, C.POINTER(SequenceRequest), C.c_void_p)
+_sig("cml_serving_default_config", ServingConfig)
+_sig("cml_serving_create", vp, C.POINTER(ServingConfig))
+_sig("cml_serving_free", None, vp)
+_sig("cml_serving_submit", ci, vp, vp, ci, ci)
+_sig("cml_serving_step", ci, vp)
+_sig("cml_serving_get_status", ci, vp, ci)
+_sig("cml_serving_get_tokens", C.POINTER(C.c_int), vp, ci, C.POINTER(C.c_int))
+_sig("cml_serving_finish_request", ci, vp, ci)
+_sig("cml_serving_get_stats", ServingStats, vp)
+_sig("cml_serving_run_llama", ci, vp, MP, ci, ci, vp, vp)
 _sig("cml_column_parallel_create", PLP, TP, TP, ci, ci)
 _sig("cml_column_parallel_free", None, PLP)
 _sig("cml_column_parallel_forward", TP, PLP, TP)

@@ -422,6 +422,84 @@ int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int d
 int cml_llama_tp_unique_id(void* id128);
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device);
 
+/* ---- include/nn/serving.h:18-110 ---------------------------------------------------------------
+ * Continuous-batching scheduler: request queue, active batch, status and timing bookkeeping, same
+ * structs and return values as C-ML. This layer never runs the model itself (as in C-ML). */
+#define CML_SERVING_MAX_BATCH 64
+#define CML_SERVING_MAX_QUEUE 1024
+typedef enum {
+    CML_SEQ_STATUS_QUEUED = 0,
+    CML_SEQ_STATUS_PREFILL,
+    CML_SEQ_STATUS_DECODING,
+    CML_SEQ_STATUS_FINISHED,
+    CML_SEQ_STATUS_ERROR,
+} CMLSequenceStatus;
+typedef struct CMLSequenceRequest {
+    int request_id;
+    int* prompt_tokens;
+    int num_prompt_tokens;
+    int max_new_tokens;
+    float temperature;
+    float top_p;
+    CMLSequenceStatus status;
+    int paged_seq_id;           /* id in the paged KV cache; cml_serving_run_llama keeps the model's batch slot here */
+    int* generated_tokens;
+    int num_generated;
+    int gen_capacity;
+    int current_pos;
+    double submit_time_ms;
+    double first_token_time_ms;
+    double finish_time_ms;
+} CMLSequenceRequest;
+typedef struct CMLServingStats {
+    size_t total_requests;
+    size_t completed_requests;
+    size_t active_sequences;
+    size_t total_tokens_generated;
+    double avg_time_to_first_token_ms;
+    double avg_tokens_per_second;
+    double total_time_ms;
+} CMLServingStats;
+typedef struct CMLServingConfig {
+    int max_batch_size;
+    int max_queue_size;
+    int max_seq_len;
+    int max_new_tokens_default;
+    float temperature_default;
+    float top_p_default;
+} CMLServingConfig;
+typedef struct CMLServingContext {
+    CMLServingConfig config;
+    CMLSequenceRequest** queue;         /* circular */
+    int queue_head;
+    int queue_tail;
+    int queue_count;
+    int queue_capacity;
+    CMLSequenceRequest** active_batch;
+    int batch_size;
+    CMLPagedKVCache* kv_cache;          /* not owned */
+    CMLServingStats stats;
+    int next_request_id;
+} CMLServingContext;
+CMLServingConfig cml_serving_default_config(void);
+CMLServingContext* cml_serving_create(const CMLServingConfig* config);
+void cml_serving_free(CMLServingContext* ctx);
+void cml_serving_set_kv_cache(CMLServingContext* ctx, CMLPagedKVCache* cache);
+/* request id (> 0), -1 when the queue is full; the prompt is copied; max_new_tokens 0 = the default */
+int cml_serving_submit(CMLServingContext* ctx, const int* prompt_tokens, int num_tokens, int max_new_tokens);
+int cml_serving_step(CMLServingContext* ctx);                    /* admits queued requests; returns the active count */
+CMLSequenceStatus cml_serving_get_status(CMLServingContext* ctx, int request_id);
+const int* cml_serving_get_tokens(CMLServingContext* ctx, int request_id, int* out_count);
+int cml_serving_finish_request(CMLServingContext* ctx, int request_id);
+CMLServingStats cml_serving_get_stats(const CMLServingContext* ctx);
+/* Runs the scheduler over a device-resident LLaMA (no C-ML counterpart): admitted requests are
+ * prefilled into free batch slots of the model and all slots take one greedy decode step per
+ * iteration through cml_llama_forward_batch, until queue and batch are empty or max_steps (> 0)
+ * steps were taken. on_finish (optional) sees each request before it is freed. Returns the number
+ * of batched decode steps, -1 on error. The model needs max_batch >= the context's max_batch_size. */
+int cml_serving_run_llama(CMLServingContext* ctx, CMLLLaMAModel* model, int eos_token, int max_steps,
+                          void (*on_finish)(const CMLSequenceRequest* request, void* user), void* user);
+
 /* ---- include/nn/speculative.h:15-90 ------------------------------------------------------------
  * Draft K tokens with one model, verify them with one call of another, keep the longest run that
  * matches the target's arg-max plus one more token. Same structs, callbacks and return values as

@@ -283,3 +283,19 @@ def test_reference_speculative_test_program_passes_against_the_library(pkg, ob, 
     assert r.returncode == 0, r.stderr
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and "18/18 passed" in r.stdout, (r.stdout + r.stderr)[-1500:]
+
+
+def test_reference_serving_test_program_passes_against_the_library(pkg, ob, tmp_path):
+    """tests/test_serving.c of the C-ML tree, unmodified (scheduler bookkeeping only): 25 of 25."""
+    import subprocess
+    root = ob.reference_root()
+    if root is None:
+        pytest.skip("the C-ML source tree is not on this machine")
+    exe = tmp_path / "test_serving"
+    libdir = ROOT / "c-ml_b200" / "lib"
+    cmd = ["gcc", "-std=c11", "-D_POSIX_C_SOURCE=200809L", f"-I{ROOT / 'include'}", str(Path(root) / "tests" / "test_serving.c"),
+           "-o", str(exe), f"-L{libdir}", "-lcml_b200", f"-Wl,-rpath,{libdir}", "-lm"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "25/25 passed" in r.stdout, (r.stdout + r.stderr)[-1500:]

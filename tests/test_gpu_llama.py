@@ -433,3 +433,43 @@ def test_truncate_rolls_the_cache_back(pkg, tiny, torch_dev):
         pkg.lib.cml_set_log_level(3)
     finally:
         pkg.lib.cml_llama_free(m)
+
+
+def test_continuous_batching_runner_matches_per_request_greedy_decoding(pkg, tiny, torch_dev):
+    """cml_serving_run_llama: five requests of different prompt and output lengths through three
+    batch slots; every request's tokens equal a stand-alone greedy run of the same prompt, slots are
+    reused as requests finish, the scheduler's statistics add up."""
+    path, _ = tiny
+    rng = np.random.default_rng(55)
+    reqs = [(rng.integers(0, TINY["vocab"], n).astype(np.int32), k) for n, k in ((9, 6), (3, 11), (14, 4), (1, 7), (6, 9))]
+    want = [_greedy_reference_tokens(pkg, path, p, k) for p, k in reqs]
+    cfg = pkg.lib.cml_serving_default_config()
+    cfg.max_batch_size = 3
+    ctx = pkg.lib.cml_serving_create(C.byref(cfg))
+    m = device_model(pkg, TINY, path, max_batch=3)
+    got = {}
+
+    def finished(req, _user):
+        r = req.contents
+        got[r.request_id] = [r.generated_tokens[i] for i in range(r.num_generated)]
+    cb = pkg.FinishFn(finished)
+    try:
+        ids = [pkg.lib.cml_serving_submit(ctx, pkg.np_ptr(p), len(p), k) for p, k in reqs]
+        assert ids == [1, 2, 3, 4, 5]
+        steps = pkg.lib.cml_serving_run_llama(ctx, m, -1, 0, C.cast(cb, C.c_void_p), None)
+        assert steps > 0
+        for rid, w in zip(ids, want):
+            assert got[rid] == w, rid
+        st = pkg.lib.cml_serving_get_stats(ctx)
+        assert st.total_requests == 5 and st.completed_requests == 5 and st.active_sequences == 0
+        assert st.total_tokens_generated == sum(k for _, k in reqs)
+        # three slots for 37 tokens: fewer batched steps than tokens, more than the longest request
+        assert 11 <= steps < 37
+        # an end-of-sequence token stops a request early
+        eos = want[0][2]
+        rid = pkg.lib.cml_serving_submit(ctx, pkg.np_ptr(reqs[0][0]), len(reqs[0][0]), 6)
+        assert pkg.lib.cml_serving_run_llama(ctx, m, int(eos), 0, C.cast(cb, C.c_void_p), None) > 0
+        assert got[rid] == want[0][:want[0].index(eos) + 1]
+    finally:
+        pkg.lib.cml_serving_free(ctx)
+        pkg.lib.cml_llama_free(m)
