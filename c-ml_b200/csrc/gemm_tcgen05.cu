@@ -5,7 +5,9 @@
 // triple loop" (src/nn/qlora.c:264-317) and its dequantize-at-load + fp32 matmul
 // (src/core/gguf.c:271-295, src/ops/ir/execution.c:989-1052).
 //
-// One CTA owns a tile of 128 weight rows (the MMA "M" side, operand A) by MT <= 256
+// One CTA owns a tile of 128 weight rows (the MMA "M" side, operand A) by MT <= 256 (or 512: two MMAs
+// per K step into two accumulators, so that a weight slab is expanded once for 512 activation rows;
+// chosen where a cost model says it saves CTA waves)
 // activation rows (the MMA "N" side, operand B) and walks K in slabs of 64:
 //   warp 0      one lane issues TMA tensor loads of the bf16 activation slab (128B swizzle)
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x MT x 16, kind::f16)
@@ -43,25 +45,37 @@ constexpr int GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
 constexpr int THREADS = 64 + DQ_THREADS + 32;
 constexpr int A_BYTES = BN * BK * 2;            // 16 KB
-constexpr int B_BYTES_MAX = 256 * BK * 2;       // 32 KB
+constexpr int B_HALF = 256 * BK * 2;            // 32 KB: 256 activation rows, what one MMA instruction takes
 constexpr int SC_SLABS = 8;                     // slabs per scale box (4 bytes per row and slab)
 constexpr int SC_BYTES = BN * SC_SLABS * 4;     // 4 KB
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-template <int TYPE> struct Cfg {
+// WIDE: tiles of up to 512 activation rows (two MMA instructions per K step on the same expanded
+// weight slab, accumulators side by side in all 512 columns of tensor memory): the expansion, which
+// decides this kernel, is paid once per 512 instead of once per 256 activation rows. The activation
+// ring then holds two 64 KB stages; the narrow form keeps as many activation as weight stages.
+template <int TYPE, bool WIDE> struct Cfg {
     static constexpr int RAWB = (TYPE == CMLB200_Q8_0) ? 64 : 32;       // packed bytes per row and slab
-    static constexpr int STAGES = (TYPE == CMLB200_Q8_0) ? 3 : 4;       // A/B stages
-    static constexpr int RSTAGES = 4;                                   // packed-weight ring
+    // The expanded-weight (A) stages and the packed-weight ring have exactly one slot per expansion
+    // group: group g then only ever reuses slot g, whose previous user was its own previous slab, so a
+    // parity wait can never be two phases away from the barrier (with fewer slots than groups a fast
+    // group could see "phase complete" for a phase that has not begun: a first Q8_0 configuration
+    // with three stages had that flaw).
+    static constexpr int STAGES = DQ_GROUPS;
+    static constexpr int RSTAGES = DQ_GROUPS;
+    // activation (B) stages: producer and consumer are one thread each and move in lockstep
+    static constexpr int BSTAGES = WIDE ? 2 : (TYPE == CMLB200_Q8_0 ? 3 : 4);
+    static constexpr int B_STAGE = WIDE ? 2 * B_HALF : B_HALF;
     static constexpr int RAW_STAGE = BN * RAWB;
     static constexpr int LUT_BYTES = (TYPE == CMLB200_NF4) ? 8 * 256 * 4 : 0;
     // offsets from the 1024-byte aligned base
     static constexpr int a_off = 0;
     static constexpr int b_off = STAGES * A_BYTES;
-    static constexpr int raw_off = b_off + STAGES * B_BYTES_MAX;
+    static constexpr int raw_off = b_off + BSTAGES * B_STAGE;
     static constexpr int sc_off = raw_off + RSTAGES * RAW_STAGE;
     static constexpr int lut_off = sc_off + 2 * SC_BYTES;
     static constexpr int bar_off = lut_off + LUT_BYTES;
-    static constexpr int nbars = 3 * STAGES + 1 + 2 * RSTAGES + 2;
+    static constexpr int nbars = 2 * STAGES + 2 * BSTAGES + 1 + 2 * RSTAGES + 2;
     static constexpr int total = bar_off + 8 * nbars + 32;
 };
 
@@ -240,30 +254,32 @@ __device__ __forceinline__ void epilogue_store(void* out, const __nv_bfloat16* g
     }
 }
 
-// grid = (ceil(N/128), ceil(M/MT), splits). With splits > 1 each z-slice covers a K range and
+// grid = (ceil(N/128), ceil(M/MT), splits); MT <= 256, or 512 in the WIDE form. With splits > 1 each z-slice covers a K range and
 // writes fp32 partial sums [split][M][N] to `partial`; a second kernel reduces them.
 // SCTMA: the scales come as 4 bytes per row and slab (two fp16 of Q4_0 / Q8_0, or one fp32 of NF4
 // with block 64) through the tensor map `smap`; otherwise every expansion thread loads its own.
-template <int TYPE, bool SCTMA>
+template <int TYPE, bool SCTMA, bool WIDE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
             const __grid_constant__ CUtensorMap smap, const void* __restrict__ scales, void* __restrict__ out,
             const __nv_bfloat16* __restrict__ gate, int mode, float* __restrict__ partial, int M, int N, int K, int MT,
             int nf4_block, int kb_per_split) {
-    using C = Cfg<TYPE>;
-    constexpr int STAGES = C::STAGES, RS = C::RSTAGES, RAWB = C::RAWB;
+    using C = Cfg<TYPE, WIDE>;
+    constexpr int STAGES = C::STAGES, BST = C::BSTAGES, RS = C::RSTAGES, RAWB = C::RAWB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + C::bar_off;
     // barrier slots (8 B each)
+    constexpr int NB0 = 2 * STAGES + 2 * BST;
     auto full_a = [&](int s) { return bars + 8 * s; };
-    auto full_b = [&](int s) { return bars + 8 * (STAGES + s); };
-    auto empty = [&](int s) { return bars + 8 * (2 * STAGES + s); };
-    const uint32_t accum_bar = bars + 8 * (3 * STAGES);
-    auto raw_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + s); };
-    auto raw_empty = [&](int s) { return bars + 8 * (3 * STAGES + 1 + RS + s); };
-    auto sc_full = [&](int s) { return bars + 8 * (3 * STAGES + 1 + 2 * RS + s); };
+    auto empty = [&](int s) { return bars + 8 * (STAGES + s); };
+    auto full_b = [&](int s) { return bars + 8 * (2 * STAGES + s); };
+    // (slots 2 * STAGES + BST .. 2 * STAGES + 2 * BST - 1 of the barrier area are spare)
+    const uint32_t accum_bar = bars + 8 * NB0;
+    auto raw_full = [&](int s) { return bars + 8 * (NB0 + 1 + s); };
+    auto raw_empty = [&](int s) { return bars + 8 * (NB0 + 1 + RS + s); };
+    auto sc_full = [&](int s) { return bars + 8 * (NB0 + 1 + 2 * RS + s); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::bar_off + 8 * C::nbars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::bar_off + 8 * C::nbars + 8);
 
@@ -277,11 +293,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
     while ((int)tmem_cols < MT) tmem_cols <<= 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_a(s), GROUP_WARPS);
-            mbar_init(full_b(s), 1);
-            mbar_init(empty(s), 1);
-        }
+        for (int s = 0; s < STAGES; s++) { mbar_init(full_a(s), GROUP_WARPS); mbar_init(empty(s), 1); }
+        for (int s = 0; s < BST; s++) mbar_init(full_b(s), 1);
         mbar_init(accum_bar, 1);
         for (int s = 0; s < RS; s++) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), GROUP_WARPS); }
         for (int s = 0; s < 2; s++) mbar_init(sc_full(s), 1);
@@ -311,33 +324,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
         if (lane == 0) {
             int issued = 0;
             for (int i = 0; i < nkb; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait(empty(s), ph ^ 1, abort_flag, 1)) break;
+                const int s = i % BST;
+                // stage s was last read by the MMAs of slab i - BST, whose completion the issuer signals
+                // on that slab's weight-stage barrier (one commit per slab serves both rings)
+                if (i >= BST && !mbar_wait(empty((i - BST) % STAGES), ((i - BST) / STAGES) & 1, abort_flag, 1)) break;
                 mbar_expect_tx(full_b(s), (uint32_t)MT * BK * 2);
-                tma_load_2d(sbase + C::b_off + s * B_BYTES_MAX, &xmap, (kb_begin + i) * BK, m0, full_b(s));
+                tma_load_2d(sbase + C::b_off + s * C::B_STAGE, &xmap, (kb_begin + i) * BK, m0, full_b(s));
+                if (WIDE && MT > 256)                              // rows 256.. of the tile: the second MMA's operand
+                    tma_load_2d(sbase + C::b_off + s * C::B_STAGE + B_HALF, &xmap, (kb_begin + i) * BK, m0 + 256, full_b(s));
                 issued = i + 1;
             }
             // never leave a bulk copy in flight behind an exiting CTA
-            for (int i = max(0, issued - STAGES); i < issued; i++)
-                mbar_wait(full_b(i % STAGES), (i / STAGES) & 1, abort_flag, 2);
+            for (int i = max(0, issued - BST); i < issued; i++)
+                mbar_wait(full_b(i % BST), (i / BST) & 1, abort_flag, 2);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+            const int n_lo = MT < 256 ? MT : 256, n_hi = MT - n_lo;       // activation rows of the first / second MMA
+            const uint32_t ibase = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 4) << 24);
+            const uint32_t idesc = ibase | ((uint32_t)(n_lo >> 3) << 17), idesc_hi = ibase | ((uint32_t)(n_hi >> 3) << 17);
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                ok = mbar_wait(full_a(s), ph, abort_flag, 3) && mbar_wait(full_b(s), ph, abort_flag, 4);
+                const int s = i % STAGES, sb = i % BST;
+                ok = mbar_wait(full_a(s), (i / STAGES) & 1, abort_flag, 3) && mbar_wait(full_b(sb), (i / BST) & 1, abort_flag, 4);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t adesc = make_desc_sw128(sbase + C::a_off + s * A_BYTES);
-                const uint64_t bdesc = make_desc_sw128(sbase + C::b_off + s * B_BYTES_MAX);
+                const uint64_t bdesc = make_desc_sw128(sbase + C::b_off + sb * C::B_STAGE);
+                const uint64_t bdesc_hi = make_desc_sw128(sbase + C::b_off + sb * C::B_STAGE + B_HALF);
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; kk++)   // advance 32 bytes inside the swizzle row per K=16 step
+                for (int kk = 0; kk < BK / 16; kk++) {  // advance 32 bytes inside the swizzle row per K=16 step
                     umma_f16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (i | kk) ? 1u : 0u);
+                    if (WIDE && n_hi > 0)
+                        umma_f16(tmem_base + 256u, adesc + (uint64_t)(2 * kk), bdesc_hi + (uint64_t)(2 * kk), idesc_hi, (i | kk) ? 1u : 0u);
+                }
                 umma_commit(empty(s));
             }
             umma_commit(accum_bar);   // arrives once every MMA issued so far has retired
@@ -409,8 +430,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
                     else scale[e] = cml_half_to_float((uint16_t)(h ? (sw >> 16) : (sw & 0xFFFF)));
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(raw_empty(rs));            // bytes and scales of this slab are in registers
             uint4 out[2][4];
 #pragma unroll
             for (int e = 0; e < 2; e++) {
@@ -420,6 +439,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CU
                     for (int c = 0; c < 4; c++) out[e][c] = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
+            // The slot is handed back only now, after the arithmetic above has consumed every loaded
+            // register. Signalling right behind the load instructions is not enough: the arrival can
+            // overtake loads that are still queued in a busy shared-memory pipe, the producer then
+            // refills the slot, and those loads return the bytes of a later slab (seen as whole 16-row
+            // bands carrying the weights of slab i + ring depth, more often with the NF4 table traffic).
+            __syncwarp();
+            if (lane == 0) mbar_arrive(raw_empty(rs));
             const int s = i % STAGES;
             ok = warp_wait(empty(s), ((i / STAGES) & 1) ^ 1, abort_flag, 5, ok);
             if (!ok) break;
@@ -498,25 +524,49 @@ int get_encoder(EncodeTiledFn* out) {
 struct Workspace { float* ptr; size_t bytes; };
 Workspace g_ws[16] = {};
 
+// K splits for a grid of gx x gy tiles: few tiles are split so that every SM gets a CTA, with at
+// least 8 slabs per CTA.
+inline int auto_splits(int gx, int gy, int total_kb, int sms) {
+    int splits = 1;
+    while (gx * gy * splits * 2 <= sms && total_kb / (splits * 2) >= 8) splits *= 2;
+    return splits;
+}
+
+// Estimated time (us) of one launch with tiles of mt activation rows: per 64-wide K slab a 256-row
+// tile takes SLAB_N us (bound by the weight expansion), a 512-row tile SLAB_W (bound by the 64 KB of
+// activations it pulls from L2), plus 8 us per wave of CTAs for pipeline fill and epilogue, plus
+// the split-K partial sums going out and back in at about 5 TB/s.
+constexpr double SLAB_N = 0.6, SLAB_W = 0.95;     // fitted to 4096x4096, 11008x4096, 4096x11008 at M = 512 .. 4096
+inline double tile_cost_us(int M, int N, int K, int mt, int sms) {
+    const int gx = (N + BN - 1) / BN, gy = (M + mt - 1) / mt, total_kb = (K + BK - 1) / BK;
+    const int splits = auto_splits(gx, gy, total_kb, sms);
+    const int waves = (gx * gy * splits + sms - 1) / sms;
+    return waves * ((double)((total_kb + splits - 1) / splits) * (mt > 256 ? SLAB_W : SLAB_N) + 8.0) +
+           (splits > 1 ? (double)splits * M * N * 8.0 / 5e6 : 0.0);
+}
+
 template <int TYPE>
 int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, void* y, const uint16_t* gate, int mode, int M, float* ws, int splits_forced,
                 cudaStream_t st) {
     const int N = W->rows, K = W->cols;
-    int MT = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+    // more than 256 activation rows: 512-row tiles (the weight slab is expanded once for both halves)
+    const bool wide = M > 256 && splits_forced <= 0 && Cfg<TYPE, true>::total + 1024 <= 227 * 1024 &&
+                      tile_cost_us(M, N, K, 512, cmlb_num_sms()) < tile_cost_us(M, N, K, 256, cmlb_num_sms());    // (Q8_0's 8 KB packed slabs leave no room for it)
+    const int MT = wide ? 512 : (M >= 256 ? 256 : ((M + 15) / 16) * 16);
     EncodeTiledFn enc;
     int rc = get_encoder(&enc);
     if (rc) return rc;
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)MT};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)(MT > 256 ? 256 : MT)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CMLB_REQUIRE(cr == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (x must be 16-byte aligned, K*2 a multiple of 16)", (int)cr);
     // the packed weights as bytes [N][row_bytes], a box of 128 rows by one slab's bytes
-    using C = Cfg<TYPE>;
+    using C = Cfg<TYPE, false>;
     CUtensorMap wmap, smap;
     const cuuint64_t row_bytes = (cuuint64_t)K * C::RAWB / BK;
     const cuuint64_t wdims[2] = {row_bytes, (cuuint64_t)N};
@@ -543,9 +593,7 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, void* y, const uint16_
     int splits = 1;
     if (splits_forced > 0) splits = splits_forced;
     else {
-        // few tiles: split K so that every SM gets a CTA, but keep at least 8 slabs per CTA
-        const int sms = cmlb_num_sms();
-        while (gx * gy * splits * 2 <= sms && total_kb / (splits * 2) >= 8) splits *= 2;
+        splits = auto_splits(gx, gy, total_kb, cmlb_num_sms());
     }
     if (splits > total_kb) splits = total_kb;
     const int kb_per_split = (total_kb + splits - 1) / splits;
@@ -568,20 +616,22 @@ int launch_gemm(const cmlb200_qmat* W, const uint16_t* x, void* y, const uint16_
             partial = g_ws[dev].ptr;
         }
     }
-    const int smem = C::total + 1024;
-    static_assert(C::total + 1024 <= 227 * 1024, "the stages do not fit shared memory");
-    static size_t attr_a[kMaxDevices] = {}, attr_b[kMaxDevices] = {};
-    if (sctma) {
-        auto kern = gemm_kernel<TYPE, true>;
-        CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_a));
-        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, y, (const __nv_bfloat16*)gate, mode, partial, M, N, K, MT,
-                                                          W->block, kb_per_split);
-    } else {
-        auto kern = gemm_kernel<TYPE, false>;
-        CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr_b));
-        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, y, (const __nv_bfloat16*)gate, mode, partial, M, N, K, MT,
-                                                          W->block, kb_per_split);
-    }
+    static_assert(Cfg<TYPE, false>::total + 1024 <= 227 * 1024, "the stages do not fit shared memory");
+    static size_t attr[4][kMaxDevices] = {};
+#define GEMM_LAUNCH(SC, WD, slot)                                                                                                     \
+    do {                                                                                                                             \
+        auto kern = gemm_kernel<TYPE, SC, WD>;                                                                                       \
+        const int smem = Cfg<TYPE, WD>::total + 1024;                                                                                \
+        CMLB_CUDA(cmlb_ensure_smem(kern, (size_t)smem, attr[slot]));                                                                 \
+        kern<<<dim3(gx, gy, splits), THREADS, smem, st>>>(xmap, wmap, smap, W->scales, y, (const __nv_bfloat16*)gate, mode, partial, M, N, \
+                                                          K, MT, W->block, kb_per_split);                                           \
+    } while (0)
+    constexpr bool kWideFits = Cfg<TYPE, true>::total + 1024 <= 227 * 1024;
+    if (sctma && wide) GEMM_LAUNCH(true, kWideFits, 0);
+    else if (sctma) GEMM_LAUNCH(true, false, 1);
+    else if (wide) GEMM_LAUNCH(false, kWideFits, 2);
+    else GEMM_LAUNCH(false, false, 3);
+#undef GEMM_LAUNCH
     CMLB_LAUNCH_CHECK();
     if (splits > 1) {
         const size_t mn = (size_t)M * N;

@@ -26,7 +26,7 @@ def _gemm(pkg, synth, W, x, N, dev, splits=0):
 
 
 @pytest.mark.parametrize("kind", ["nf4", "q4_0", "q8_0"])
-@pytest.mark.parametrize("M", [1, 16, 64, 100, 300])
+@pytest.mark.parametrize("M", [1, 16, 64, 100, 256, 300, 513, 1000])
 def test_gemm_matches_oracle(pkg, synth, ob, orc, torch_dev, kind, M):
     rng = np.random.default_rng(200 + M)
     N, K = 200, 512                                    # ragged N (tile is 128 rows)
@@ -66,6 +66,20 @@ def test_gemm_nf4_config_shape_sampled(pkg, synth, ob, orc, torch_dev, M):
     # whole-output check against an fp64 matmul of the same dequantised weights
     full = xr.reshape(x.shape).astype(np.float64) @ Wf.T.astype(np.float64)
     assert rel_err_inf(got, full) <= TOL
+
+
+@pytest.mark.parametrize("kind,N,K,M", [("q4_0", 11008, 4096, 512), ("nf4", 4096, 4096, 2000), ("q4_0", 4096, 11008, 2048), ("nf4", 4096, 4096, 4096)])
+def test_gemm_large_shapes_repeated(pkg, synth, ob, orc, torch_dev, kind, N, K, M):
+    """LLaMA-sized weights with 512 to 4096 activation rows, incl. a ragged last tile; every output
+    against an fp64 product, three launches in a row (cold and warm caches: a pipeline race would show
+    as whole output columns off by a K slab's worth)."""
+    rng = np.random.default_rng(900 + M)
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    _, xr = synth.bf16_round(x)
+    full = xr.reshape(x.shape).astype(np.float64) @ Wf.T.astype(np.float64)
+    for _ in range(3):
+        assert rel_err_inf(_gemm(pkg, synth, W, x, N, torch_dev), full) <= TOL
 
 
 @pytest.mark.parametrize("kind,K", [("q4_0", 1376), ("q8_0", 96), ("nf4", 1376), ("q4_0", 32)])
