@@ -311,6 +311,10 @@ def llama_leg(pkg, synth, torch, dist, dev, rank, world, cfg, tag, prompt_len, n
         assert m and pkg.lib.cml_llama_set_options(m, 0, max(batches)) == 0
         if world > 1:
             assert pkg.lib.cml_llama_tp_init(m, idb, dev.index) == 0, "cml_llama_tp_init failed"
+            nf, pm, nm = C.c_size_t(0), C.c_float(0), C.c_float(0)
+            which = pkg.lib.cml_llama_tp_prompt_allreduce(m, C.byref(nf), C.byref(pm), C.byref(nm))
+            out["prompt_allreduce"] = {"used": "peer_memory" if which == 1 else "nccl", "probe_bytes": nf.value * 4,
+                                       "peer_memory_ms": pm.value, "nccl_plus_add_ms": nm.value}
         t0 = time.perf_counter()
         assert pkg.lib.cml_llama_load_gguf(m, path.encode()) == 0, "cml_llama_load_gguf failed"
         out["load_s"] = time.perf_counter() - t0
@@ -659,7 +663,7 @@ def main():
         if world > 1:
             for tag in ("llama70b_q4_0", "llama7b_q4_0"):
                 if tag in legs and "error" not in legs[tag]:
-                    line["tp"] = {"model": tag, "n_gpus": world, **{k: v for k, v in legs[tag].items() if k.startswith(("decode_tok_s", "prefill_tok_s", "decode_ms"))}}
+                    line["tp"] = {"model": tag, "n_gpus": world, **{k: v for k, v in legs[tag].items() if k.startswith(("decode_tok_s", "prefill_tok_s", "decode_ms", "prompt_allreduce"))}}
                     break
         print(json.dumps(line))
     if world > 1:

@@ -88,6 +88,9 @@ _sig("cmlb200_tp_allreduce_add", ci, vp, vp, sz, ci, ci, C.POINTER(vp), sz, vp)
 _sig("cmlb200_gemv_tp_allreduce", ci, C.POINTER(QMat), vp, vp, ci, ci, ci, C.POINTER(vp), sz, vp)
 _sig("cmlb200_gemv_tp_fused_ok", ci, C.POINTER(QMat), ci)
 _sig("cmlb200_tp_ar_status", ci, vp, C.POINTER(ci))
+_sig("cmlb200_tp_ar_bulk_workspace_bytes", sz, sz, ci)
+_sig("cmlb200_tp_allreduce_bulk_add", ci, vp, vp, sz, ci, ci, C.POINTER(vp), sz, vp)
+_sig("cmlb200_tp_allreduce_bulk_emulate", ci, C.POINTER(vp), C.POINTER(vp), sz, ci, C.POINTER(vp), sz, vp)
 _sig("cmlb200_tp_ar_status_reset", ci, vp)
 _sig("cmlb200_set_wait_limit", ci, ci)
 
@@ -349,6 +352,7 @@ _sig("cml_llama_set_options", ci, MP, ci, ci)
 _sig("cml_tp_shard_qblocks", ci, ci, vp, ci, ci, ci, ci, ci, vp)
 _sig("cml_llama_tp_unique_id", ci, vp)
 _sig("cml_llama_tp_init", ci, MP, vp, ci)
+_sig("cml_llama_tp_prompt_allreduce", ci, MP, C.POINTER(sz), C.POINTER(C.c_float), C.POINTER(C.c_float))
 _sig("cml_init", ci)
 _sig("cml_cleanup", ci)
 _sig("tensor_manual_seed", None, C.c_uint64)

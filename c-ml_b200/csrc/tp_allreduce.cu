@@ -81,7 +81,191 @@ tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial
     }
 }
 
+
+// ---- prompt-sized messages -------------------------------------------------------------------
+// The kernel above sends every rank's whole partial to every peer, which is right for the 16-512 KB
+// of a decode step. A prompt's row-parallel projection leaves 16-64 MB per rank; for that size the
+// sum is split by rank ("reduce-scatter, then all-gather", all inside one launch per rank):
+//   1. every CTA pushes, for each peer q, its share of slice q of the local partial into the inbox A
+//      that q keeps for this rank, fences, and raises flag A;
+//   2. it waits for flag A of all peers, sums its share of this rank's own slice in rank order
+//      (the local partial and the inboxes), adds the sum onto h and pushes it into the inbox B of
+//      every peer, fences, and raises flag B;
+//   3. it waits for flag B of all peers and adds their summed slices onto h.
+// Each slice is summed by one rank, in rank order, so all ranks end with bit-identical h. A rank
+// sends 2 (tp - 1) / tp of the message over NVLink instead of tp - 1 times the message.
+// Element i of a slice belongs to CTA (i / 256) % kBulkCtas on every rank, so CTA c only ever
+// depends on CTA c of its peers; the inboxes alternate with the parity of the sequence number as
+// above. The workspace is a second allocation with its own header:
+//   +64 u32 status   +1024 u32 seq[64]   +4096 u32 flagA[8][64]   +8192 u32 flagB[8][64]
+//   +16384 float4 inbox[A|B][parity][from < tp][region4]
+// With EMU the ranks are blockIdx.y of ONE cooperative launch over buffers of one GPU: the way to
+// exercise the protocol where only one device is at hand (launches that wait on one another must
+// not be separate launches on the same GPU).
+constexpr int kBulkCtas = 64;
+constexpr int kBulkThreads = 256;
+struct BulkArgs {
+    uint8_t* ws[MAX_TP];
+    float* h[MAX_TP];               // [0] only, unless emulating
+    const float* partial[MAX_TP];
+    size_t region4;                 // float4 per (inbox, parity, from) region
+    int n4, tp, rank, spin_limit;
+};
+__device__ __forceinline__ uint32_t* bulk_seq(uint8_t* ws) { return reinterpret_cast<uint32_t*>(ws + 1024); }
+__device__ __forceinline__ uint32_t* bulk_flag(uint8_t* ws, int which, int from) {
+    return reinterpret_cast<uint32_t*>(ws + 4096 + 4096 * which) + from * kBulkCtas;
+}
+__device__ __forceinline__ float4* bulk_inbox(uint8_t* ws, int which, int parity, int from, int tp, size_t region4) {
+    return reinterpret_cast<float4*>(ws + kTpHeaderBytes) + (((size_t)which * 2 + parity) * tp + from) * region4;
+}
+__device__ __forceinline__ void add4(float4& a, const float4 b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+
+// All peers' flag words for CTA c reach seq, or the launch records which peer it gave up on.
+__device__ __forceinline__ bool bulk_wait(uint8_t* mine, int which, int tp, int rank, int c, uint32_t seq, int spin_limit, int* ok) {
+    if ((int)threadIdx.x < tp && (int)threadIdx.x != rank) {
+        const uint32_t* f = bulk_flag(mine, which, threadIdx.x) + c;
+        int i = 0;
+        while ((int32_t)(ld_acquire_sys(f) - seq) < 0 && ++i < spin_limit) {}
+        if (i >= spin_limit) { *ok = 0; atomicExch(tpws_status(mine), 1u + threadIdx.x); }
+    }
+    __syncthreads();
+    return *ok != 0;
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(kBulkThreads)
+tp_allreduce_bulk_kernel(BulkArgs a) {
+    if (!EMU) asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int tp = a.tp, rank = EMU ? (int)blockIdx.y : a.rank;
+    uint8_t* mine = a.ws[rank];
+    const int c = blockIdx.x, t = threadIdx.x;
+    const uint32_t seq = bulk_seq(mine)[c] + 1;
+    const int parity = (int)(seq & 1u);
+    const int per = (a.n4 + tp - 1) / tp;                      // float4 per slice
+    const float4* src = reinterpret_cast<const float4*>(a.partial[EMU ? rank : 0]);
+    float4* h4 = reinterpret_cast<float4*>(a.h[EMU ? rank : 0]);
+    constexpr int STEP = kBulkCtas * kBulkThreads;
+    __shared__ int ok;
+    if (t == 0) ok = 1;
+
+    // 1. slice q of the local partial -> rank q
+    for (int d = 1; d < tp; d++) {
+        const int q = (rank + d) % tp;
+        const int lo = min(a.n4, q * per), len = min(a.n4, lo + per) - lo;
+        float4* dst = bulk_inbox(a.ws[q], 0, parity, rank, tp, a.region4);
+        for (int i = c * kBulkThreads + t; i < len; i += STEP) dst[i] = src[lo + i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (t < tp && t != rank) st_release_sys(bulk_flag(a.ws[t], 0, rank) + c, seq);
+
+    // 2. this rank's slice: sum in rank order, add onto h, hand the sum to every peer
+    const bool got_a = bulk_wait(mine, 0, tp, rank, c, seq, a.spin_limit, &ok);
+    if (got_a) {
+        const int lo = min(a.n4, rank * per), len = min(a.n4, lo + per) - lo;
+        for (int i = c * kBulkThreads + t; i < len; i += STEP) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < tp; q++) add4(acc, q == rank ? src[lo + i] : __ldcg(bulk_inbox(mine, 0, parity, q, tp, a.region4) + i));
+            for (int d = 1; d < tp; d++) bulk_inbox(a.ws[(rank + d) % tp], 1, parity, rank, tp, a.region4)[i] = acc;
+            float4 o = h4[lo + i];
+            add4(o, acc);
+            h4[lo + i] = o;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // after an expired wait no flag B goes out: the peers' own waits expire and set their status words
+    if (got_a && t < tp && t != rank) st_release_sys(bulk_flag(a.ws[t], 1, rank) + c, seq);
+
+    // 3. the other ranks' summed slices
+    const bool got_b = got_a && bulk_wait(mine, 1, tp, rank, c, seq, a.spin_limit, &ok);
+    if (got_b) {
+        for (int d = 1; d < tp; d++) {
+            const int q = (rank + d) % tp;
+            const int lo = min(a.n4, q * per), len = min(a.n4, lo + per) - lo;
+            const float4* in = bulk_inbox(mine, 1, parity, q, tp, a.region4);
+            for (int i = c * kBulkThreads + t; i < len; i += STEP) {
+                float4 o = h4[lo + i];
+                add4(o, __ldcg(in + i));
+                h4[lo + i] = o;
+            }
+        }
+    }
+    if (t == 0) bulk_seq(mine)[c] = seq;
+}
+
+int bulk_args(BulkArgs* a, size_t n, int tp, void* const* ws, size_t max_floats, const char* who) {
+    CMLB_REQUIRE(ws, "%s: NULL argument", who);
+    CMLB_REQUIRE(tp >= 2 && tp <= MAX_TP, "%s: tp=%d (must be 2..8)", who, tp);
+    CMLB_REQUIRE(max_floats > 0 && max_floats % 4 == 0, "%s: max_floats=%zu must be a positive multiple of 4", who, max_floats);
+    CMLB_REQUIRE(n > 0 && n % 4 == 0 && n <= max_floats && n / 4 <= 0x7fffffff, "%s: n=%zu must be a multiple of 4 and at most %zu", who, n, max_floats);
+    for (int r = 0; r < tp; r++) {
+        CMLB_REQUIRE(ws[r], "%s: workspace of rank %d missing", who, r);
+        a->ws[r] = static_cast<uint8_t*>(ws[r]);
+    }
+    a->region4 = (max_floats / 4 + tp - 1) / tp;
+    a->n4 = (int)(n / 4);
+    a->tp = tp;
+    a->spin_limit = cmlb_tp_spin_limit();
+    return CMLB200_OK;
+}
+
 }  // namespace
+
+// Workspace of the prompt-sized all-reduce for messages of up to max_floats values over tp ranks.
+extern "C" size_t cmlb200_tp_ar_bulk_workspace_bytes(size_t max_floats, int tp) {
+    if (tp < 2 || tp > MAX_TP) return 0;
+    const size_t region4 = (max_floats / 4 + tp - 1) / tp;
+    return kTpHeaderBytes + 2 * 2 * (size_t)tp * region4 * sizeof(float4);
+}
+
+// h[0..n) += sum over ranks of partial[0..n), for n of prompt size. ws[r] = rank r's bulk workspace
+// as mapped in this process (zero-filled once before the first call on any rank; tp and max_floats
+// fixed for the life of the workspace). Every rank must make the same sequence of calls.
+extern "C" int cmlb200_tp_allreduce_bulk_add(float* d_h, const float* d_partial, size_t n, int tp, int rank, void* const* ws,
+                                             size_t max_floats, void* stream) {
+    CMLB_REQUIRE(d_h && d_partial, "cmlb200_tp_allreduce_bulk_add: NULL argument");
+    CMLB_REQUIRE(rank >= 0 && rank < tp, "cmlb200_tp_allreduce_bulk_add: rank %d outside 0..%d", rank, tp - 1);
+    CMLB_REQUIRE(((uintptr_t)d_h & 15) == 0 && ((uintptr_t)d_partial & 15) == 0, "cmlb200_tp_allreduce_bulk_add: buffers must be 16-byte aligned");
+    BulkArgs a = {};
+    if (int rc = bulk_args(&a, n, tp, ws, max_floats, "cmlb200_tp_allreduce_bulk_add")) return rc;
+    a.rank = rank;
+    a.h[0] = d_h;
+    a.partial[0] = d_partial;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kBulkCtas);
+    cfg.blockDim = dim3(kBulkThreads);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CMLB_CUDA(cudaLaunchKernelEx(&cfg, tp_allreduce_bulk_kernel<false>, a));
+    return CMLB200_OK;
+}
+
+// The same exchange with all tp ranks on ONE device, as one cooperative launch (every CTA of every
+// rank resident at once): d_h[r], d_partial[r], ws[r] are rank r's buffers on the current device.
+// For checking the protocol on a single GPU; a real job runs one process per GPU and the call above.
+extern "C" int cmlb200_tp_allreduce_bulk_emulate(float* const* d_h, const float* const* d_partial, size_t n, int tp, void* const* ws,
+                                                 size_t max_floats, void* stream) {
+    CMLB_REQUIRE(d_h && d_partial, "cmlb200_tp_allreduce_bulk_emulate: NULL argument");
+    BulkArgs a = {};
+    if (int rc = bulk_args(&a, n, tp, ws, max_floats, "cmlb200_tp_allreduce_bulk_emulate")) return rc;
+    for (int r = 0; r < tp; r++) {
+        CMLB_REQUIRE(d_h[r] && d_partial[r] && ((uintptr_t)d_h[r] & 15) == 0 && ((uintptr_t)d_partial[r] & 15) == 0,
+                     "cmlb200_tp_allreduce_bulk_emulate: buffers of rank %d missing or not 16-byte aligned", r);
+        a.h[r] = d_h[r];
+        a.partial[r] = d_partial[r];
+    }
+    int per_sm = 0;
+    CMLB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_allreduce_bulk_kernel<true>, kBulkThreads, 0));
+    CMLB_REQUIRE(per_sm * cmlb_num_sms() >= kBulkCtas * tp, "cmlb200_tp_allreduce_bulk_emulate: %d CTAs do not fit on the device at once", kBulkCtas * tp);
+    void* args[] = {&a};
+    CMLB_CUDA(cudaLaunchCooperativeKernel((const void*)tp_allreduce_bulk_kernel<true>, dim3(kBulkCtas, tp), dim3(kBulkThreads), args, 0, as_stream(stream)));
+    return CMLB200_OK;
+}
 
 extern "C" size_t cmlb200_tp_ar_workspace_bytes(size_t max_floats) {
     return kTpHeaderBytes + 2 * 2 * (size_t)MAX_TP * max_floats * sizeof(float);

@@ -45,6 +45,13 @@ typedef struct DevModel {
     void* ar_ws[8];
     size_t ar_max_floats;
     int ar_ok;
+    /* the same for prompt-sized messages (second workspace, slices summed by rank); arb_ok only when
+     * its start-up check passed on every rank and it was faster there than ncclAllReduce */
+    void* arb_ws[8];
+    size_t arb_max_floats;
+    int arb_ok;
+    float arb_ms[2];                       /* start-up timing of one sum: peer memory, ncclAllReduce + add */
+    size_t arb_probe_floats;
     int generic_w;                         /* some projection is Q4_1 / Q4_K / Q5_K / Q6_K: fp32 row-block path for every call */
     int hd, heads_l, kvh_l, qw_l, kvw_l, inter_l;
     DevLayer* L;
@@ -152,6 +159,7 @@ static void dm_destroy(DevModel* d) {
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) cmlb200_free(bufs[i]);
     free(d->h_cur);
     for (int r = 0; r < 8; r++) {
+        if (d->arb_ws[r]) { if (r == d->rank) cmlb200_free(d->arb_ws[r]); else cmlb200_ipc_close(d->arb_ws[r]); }
         if (!d->ar_ws[r]) continue;
         if (r == d->rank) cmlb200_free(d->ar_ws[r]);
         else cmlb200_ipc_close(d->ar_ws[r]);
@@ -217,31 +225,128 @@ int cml_llama_set_options(CMLLLaMAModel* model, int flags, int max_batch) {
 
 int cml_llama_tp_unique_id(void* id128) { return cml_nccl_unique_id(id128); }
 
-/* Maps every rank's all-reduce workspace into this process: own allocation, CUDA IPC handles
- * exchanged with one ncclAllGather. Ranks must be separate processes on GPUs with peer access;
- * anything else leaves ar_ok = 0 and the NCCL path in charge. */
-static int tp_peer_setup(DevModel* d) {
-    const int H = d->key->config.hidden_size;
+/* Every rank contributes one 64-byte record; all[r] receives rank r's. The collective is always
+ * entered, so ranks that hit a local error before it still meet the others. */
+static int tp_gather64(DevModel* d, const unsigned char mine[64], unsigned char all[8 * 64]) {
     void *d_mine = NULL, *d_all = NULL;
-    unsigned char mine[64], all[8 * 64];
     int rc = -1;
-    if (d->tp > 8) return -1;
-    d->ar_max_floats = (size_t)SKINNY_ROWS * H;
-    const size_t bytes = cmlb200_tp_ar_workspace_bytes(d->ar_max_floats);
-    if (cmlb200_malloc(&d->ar_ws[d->rank], bytes) || cmlb200_memset(d->ar_ws[d->rank], 0, bytes, NULL) || cmlb200_device_sync()) goto done;
-    if (cmlb200_ipc_get_handle(d->ar_ws[d->rank], mine)) goto done;
     if (cmlb200_malloc(&d_mine, 64) || cmlb200_malloc(&d_all, 64 * (size_t)d->tp)) goto done;
     if (cmlb200_memcpy_h2d(d_mine, mine, 64, NULL) || cmlb200_device_sync()) goto done;
     if (cml_nccl_allgather_bytes(d->comm, d_mine, d_all, 64, NULL) || cmlb200_device_sync()) goto done;
     if (cmlb200_memcpy_d2h(all, d_all, 64 * (size_t)d->tp, NULL) || cmlb200_device_sync()) goto done;
     rc = 0;
-    for (int r = 0; r < d->tp && rc == 0; r++)
-        if (r != d->rank && cmlb200_ipc_open(all + 64 * r, &d->ar_ws[r])) rc = -1;
 done:
     cmlb200_free(d_mine);
     cmlb200_free(d_all);
+    return rc;
+}
+
+/* 1 when `local_ok` holds on every rank. */
+static int tp_all_agree(DevModel* d, int local_ok) {
+    unsigned char mine[64] = {0}, all[8 * 64];
+    mine[0] = local_ok ? 1 : 0;
+    if (tp_gather64(d, mine, all)) return 0;
+    for (int r = 0; r < d->tp; r++)
+        if (!all[64 * r]) return 0;
+    return 1;
+}
+
+/* Allocates this rank's workspace of `bytes` (zero-filled) and maps every other rank's into this
+ * process through CUDA IPC handles. ws[rank] = own allocation. 0 only when it worked on all ranks. */
+static int tp_map_workspaces(DevModel* d, size_t bytes, void** ws) {
+    unsigned char mine[64] = {0}, all[8 * 64], zero[64] = {0};
+    int ok = !cmlb200_malloc(&ws[d->rank], bytes) && !cmlb200_memset(ws[d->rank], 0, bytes, NULL) && !cmlb200_device_sync() &&
+             !cmlb200_ipc_get_handle(ws[d->rank], mine);
+    if (!ok) memset(mine, 0, 64);                    /* an all-zero handle tells the others */
+    if (tp_gather64(d, mine, all)) ok = 0;
+    for (int r = 0; ok && r < d->tp; r++)
+        if (!memcmp(all + 64 * r, zero, 64)) ok = 0;
+    for (int r = 0; ok && r < d->tp; r++)
+        if (r != d->rank && cmlb200_ipc_open(all + 64 * r, &ws[r])) ok = 0;
+    return tp_all_agree(d, ok) ? 0 : -1;
+}
+
+/* Peer-memory all-reduce for decode-sized rows. Ranks must be separate processes on GPUs with peer
+ * access; anything else leaves ar_ok = 0 and the NCCL path in charge. */
+static int tp_peer_setup(DevModel* d) {
+    const int H = d->key->config.hidden_size;
+    if (d->tp > 8) return -1;
+    d->ar_max_floats = (size_t)SKINNY_ROWS * H;
+    const int rc = tp_map_workspaces(d, cmlb200_tp_ar_workspace_bytes(d->ar_max_floats), d->ar_ws);
     d->ar_ok = rc == 0;
     return rc;
+}
+
+static double now_ms(void) {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+}
+
+/* The prompt-sized all-reduce over peer memory is used when (a) its workspaces map on every rank,
+ * (b) one sum of a known pattern comes out exact on every rank and (c) it is faster than
+ * ncclAllReduce + add on the same message by the slowest rank's clock. CML_B200_TP_BULK=1 skips
+ * (c), =0 keeps NCCL. Every rank enters the same collectives and takes the same decision. */
+static void tp_bulk_setup(DevModel* d) {
+    const char* env = getenv("CML_B200_TP_BULK");
+    const int H = d->key->config.hidden_size;
+    if (d->tp > 8 || (env && env[0] == '0')) return;
+    int rows = d->key->config.max_seq_len;
+    if (rows < SKINNY_ROWS) rows = SKINNY_ROWS;
+    if (rows > 2048) rows = 2048;
+    d->arb_max_floats = ((size_t)rows * H + 3) & ~(size_t)3;
+    if (tp_map_workspaces(d, cmlb200_tp_ar_bulk_workspace_bytes(d->arb_max_floats, d->tp), d->arb_ws)) return;
+    const size_t n = d->arb_max_floats < ((size_t)4 << 20) ? d->arb_max_floats : ((size_t)4 << 20);
+    float *hp = malloc(n * 4), *dh = NULL, *dp = NULL;
+    int good = hp && !cmlb200_malloc((void**)&dh, n * 4) && !cmlb200_malloc((void**)&dp, n * 4);
+    if (!tp_all_agree(d, good)) goto done;
+    /* (b) exactness: partial = (i mod 251) * (rank + 1) on zeros -> (i mod 251) * tp (tp + 1) / 2 */
+    int st = 0;
+    for (size_t i = 0; i < n; i++) hp[i] = (float)((i % 251) * (size_t)(d->rank + 1));
+    good = !cmlb200_memcpy_h2d(dp, hp, n * 4, NULL) && !cmlb200_memset(dh, 0, n * 4, NULL) && !cmlb200_device_sync() &&
+           !cmlb200_tp_allreduce_bulk_add(dh, dp, n, d->tp, d->rank, d->arb_ws, d->arb_max_floats, NULL) && !cmlb200_device_sync() &&
+           !cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) && st == 0 && !cmlb200_memcpy_d2h(hp, dh, n * 4, NULL) && !cmlb200_device_sync();
+    const float tri = (float)(d->tp * (d->tp + 1) / 2);
+    for (size_t i = 0; good && i < n; i++) good = hp[i] == (float)(i % 251) * tri;
+    if (!tp_all_agree(d, good)) {
+        LOG_WARNING("cml_llama_tp_init: the peer-memory all-reduce for prompts failed its start-up check%s; NCCL serves prompts", good ? " on another rank" : "");
+        goto done;
+    }
+    /* (c) the clock: 4 sums of n values each way */
+    float ms_bulk, ms_nccl;
+    double t0 = now_ms();
+    for (int k = 0; k < 4; k++) cmlb200_tp_allreduce_bulk_add(dh, dp, n, d->tp, d->rank, d->arb_ws, d->arb_max_floats, NULL);
+    cmlb200_device_sync();
+    ms_bulk = (float)(now_ms() - t0);
+    cml_nccl_allreduce_sum_f32(d->comm, dp, n, NULL);
+    cmlb200_device_sync();
+    t0 = now_ms();
+    for (int k = 0; k < 4; k++) { cml_nccl_allreduce_sum_f32(d->comm, dp, n, NULL); cmlb200_add_f32(dh, dp, n, NULL); }
+    cmlb200_device_sync();
+    ms_nccl = (float)(now_ms() - t0);
+    unsigned char mine[64] = {0}, all[8 * 64];
+    memcpy(mine, &ms_bulk, 4);
+    memcpy(mine + 4, &ms_nccl, 4);
+    st = 0;
+    if (tp_gather64(d, mine, all) || cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) || st) goto done;
+    float worst_bulk = 0.f, worst_nccl = 0.f;
+    for (int r = 0; r < d->tp; r++) {
+        float b, c;
+        memcpy(&b, all + 64 * r, 4);
+        memcpy(&c, all + 64 * r + 4, 4);
+        if (b > worst_bulk) worst_bulk = b;
+        if (c > worst_nccl) worst_nccl = c;
+    }
+    d->arb_ok = (env && env[0] == '1') || worst_bulk < worst_nccl;
+    d->arb_ms[0] = worst_bulk / 4;
+    d->arb_ms[1] = worst_nccl / 4;
+    d->arb_probe_floats = n;
+    LOG_INFO("cml_llama_tp_init: all-reduce of %zu floats over %d ranks: peer memory %.3f ms, NCCL + add %.3f ms -> %s for prompts",
+             n, d->tp, worst_bulk / 4, worst_nccl / 4, d->arb_ok ? "peer memory" : "NCCL");
+done:
+    free(hp);
+    cmlb200_free(dh);
+    cmlb200_free(dp);
 }
 
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
@@ -254,8 +359,19 @@ int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     d->device = device;
     if (cml_nccl_init(&d->comm, d->tp, d->rank, id128)) return -1;
     const char* only = getenv("CML_B200_TP_NCCL_ONLY");
-    if (!(only && only[0] == '1') && tp_peer_setup(d)) LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size");
+    if (only && only[0] == '1') return 0;
+    if (tp_peer_setup(d)) { LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size"); return 0; }
+    tp_bulk_setup(d);
     return 0;
+}
+
+int cml_llama_tp_prompt_allreduce(CMLLLaMAModel* model, size_t* probe_floats, float* peer_ms, float* nccl_ms) {
+    DevModel* d = model ? dm_get(model) : NULL;
+    if (!d) return -1;
+    if (probe_floats) *probe_floats = d->arb_probe_floats;
+    if (peer_ms) *peer_ms = d->arb_ms[0];
+    if (nccl_ms) *nccl_ms = d->arb_ms[1];
+    return d->arb_ok;
 }
 
 static int dm_alloc_buffers(DevModel* d) {
@@ -604,6 +720,15 @@ static int dm_check_waits(DevModel* d, const char* who) {
             return -1;
         }
     }
+    if (d->arb_ok && d->arb_ws[d->rank]) {
+        if (cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) != CMLB200_OK) { LOG_ERROR("%s: %s", who, cmlb200_last_error()); return -1; }
+        if (st) {
+            LOG_ERROR("%s: the prompt-sized all-reduce gave up waiting for rank %d; the result is incomplete (falling back to NCCL)", who, st - 1);
+            cmlb200_tp_ar_status_reset(d->arb_ws[d->rank]);
+            d->arb_ok = 0;
+            return -1;
+        }
+    }
     return 0;
 }
 
@@ -651,6 +776,13 @@ static int proj_residual_bf16(DevModel* d, const cmlb200_qmat* W, const uint16_t
     /* one GPU: the GEMM adds onto the fp32 residual in its epilogue; several: fp32 partial sums, all-reduce, add */
     if (d->tp == 1) { DEV(cmlb200_gemm_bf16_ex(W, x, rows, CMLB200_GEMM_ACC_F32, d->h, NULL, d->stream)); return 0; }
     DEV(cmlb200_gemm_bf16_ex(W, x, rows, CMLB200_GEMM_OUT_F32, d->tmp, NULL, d->stream));
+    if (d->arb_ok && n % 4 == 0) {               /* slices summed by rank over peer memory, added onto h in the same launch */
+        for (size_t o = 0; o < n; o += d->arb_max_floats) {
+            const size_t len = n - o < d->arb_max_floats ? n - o : d->arb_max_floats;
+            DEV(cmlb200_tp_allreduce_bulk_add(d->h + o, d->tmp + o, len, d->tp, d->rank, d->arb_ws, d->arb_max_floats, d->stream));
+        }
+        return 0;
+    }
     if (cml_nccl_allreduce_sum_f32(d->comm, d->tmp, n, d->stream)) return -1;
     DEV(cmlb200_add_f32(d->h, d->tmp, n, d->stream));
     return 0;

@@ -421,6 +421,13 @@ int cml_tp_shard_qblocks(int type, const void* blocks, int rows, int cols, int d
  * ranks by any means, then every rank calls cml_llama_tp_init before loading weights. */
 int cml_llama_tp_unique_id(void* id128);
 int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device);
+/* Which all-reduce serves prompt-sized row-parallel projections after cml_llama_tp_init: 1 = the
+ * peer-memory form (slices summed by rank inside one launch), 0 = ncclAllReduce, -1 = no such model.
+ * The init call times one sum of *probe_floats values each way on every rank (*peer_ms, *nccl_ms:
+ * the slowest rank's; zero when the peer form was unavailable or failed its exactness check) and
+ * keeps the faster; CML_B200_TP_BULK=1 / =0 in the environment forces the choice. No C-ML
+ * counterpart (its all-reduce is always ncclAllReduce, src/distributed/tensor_parallel.c:195-260). */
+int cml_llama_tp_prompt_allreduce(CMLLLaMAModel* model, size_t* probe_floats, float* peer_ms, float* nccl_ms);
 
 /* ---- include/nn/serving.h:18-110 ---------------------------------------------------------------
  * Continuous-batching scheduler: request queue, active batch, status and timing bookkeeping, same

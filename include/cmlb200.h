@@ -341,6 +341,23 @@ size_t cmlb200_tp_ar_workspace_bytes(size_t max_floats);
 int cmlb200_tp_allreduce_add(float* d_h, const float* d_partial, size_t n, int tp, int rank, void* const* ws, size_t max_floats, void* stream);
 int cmlb200_tp_ar_status(const void* own_ws, int* status);
 int cmlb200_tp_ar_status_reset(void* own_ws);
+/* The same sum for prompt-sized messages (tens of MB): one launch per rank in which every rank sums
+ * one slice of the message (in rank order) and hands the summed slice to the others, so a rank
+ * sends 2 (tp - 1) / tp of the message instead of tp - 1 times the message. Replaces the
+ * ncclAllReduce C-ML issues after a row-parallel projection of a whole prompt
+ * (src/distributed/tensor_parallel.c:195-260). A second workspace per rank, of
+ * cmlb200_tp_ar_bulk_workspace_bytes(max_floats, tp) bytes, zero-filled once and mapped like the
+ * first; tp and max_floats are fixed for its life. n % 4 == 0, n <= max_floats. cmlb200_tp_ar_status
+ * on the bulk workspace reports an expired wait; h may then be partly updated and the caller must
+ * discard the forward. */
+size_t cmlb200_tp_ar_bulk_workspace_bytes(size_t max_floats, int tp);
+int cmlb200_tp_allreduce_bulk_add(float* d_h, const float* d_partial, size_t n, int tp, int rank, void* const* ws, size_t max_floats,
+                                  void* stream);
+/* All tp ranks of that exchange on ONE device as one cooperative launch (d_h[r], d_partial[r],
+ * ws[r]: rank r's buffers on the current device): checks the protocol where a single GPU is at
+ * hand. Launches that wait on one another must never be separate launches on one GPU. */
+int cmlb200_tp_allreduce_bulk_emulate(float* const* d_h, const float* const* d_partial, size_t n, int tp, void* const* ws, size_t max_floats,
+                                      void* stream);
 /* How many times a launch polls a peer's flag or packet before it gives up (both all-reduce
  * forms). 0 restores the default of 2^22 polls (seconds); the environment variable
  * CMLB200_WAIT_LIMIT sets the initial value. Applies to launches made after the call. C-ML has no

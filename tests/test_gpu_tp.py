@@ -4,8 +4,10 @@ over all ranks (C-ML src/distributed/tensor_parallel.c:25-101, 195-260;
 tests/test_tensor_parallel.c:330-430). Every rank must produce the oracle's logits, and all ranks
 the same bits. Cases that need more GPUs than the box has are skipped.
 
-Also here, on ONE GPU: the bounded waits of the two peer-memory all-reduce forms are made to run
-out (a peer workspace that nobody writes) and must leave a status word behind, not a hang."""
+Also here, on ONE GPU: the bounded waits of the peer-memory all-reduce forms are made to run
+out (a peer workspace that nobody writes) and must leave a status word behind, not a hang; and the
+prompt-sized all-reduce runs with all its ranks inside one cooperative launch against the sum in
+rank order."""
 import os
 import subprocess
 import sys
@@ -97,7 +99,8 @@ assert pkg.lib.cml_llama_decode_greedy(m, pkg.np_ptr(first), 1, 6, pkg.np_ptr(o_
 assert pkg.lib.cml_llama_decode_greedy(m1, pkg.np_ptr(first), 1, 6, pkg.np_ptr(o_1), C.byref(ms)) == 0
 assert o_tp.tolist() == o_1.tolist(), (o_tp, o_1)
 same_on_all_ranks(o_tp, "the greedy tokens")
-# a 40-token prompt: the bf16 tensor-core path with an NCCL all-reduce per row-parallel projection
+# a 40-token prompt: the bf16 tensor-core path, the row-parallel projections summed over peer memory by slices
+# (CML_B200_TP_BULK=1) or by ncclAllReduce (CML_B200_TP_NCCL_ONLY=1)
 pkg.lib.cml_llama_reset(m)
 long = rng.integers(0, cfg["vocab"], 40).astype(np.int32)
 got = llama_util.dev_forward(pkg, m, long)
@@ -118,13 +121,14 @@ print(f"rank {rank} ok {worst:.2e}")
 @pytest.mark.parametrize("case,ranks,nccl_only", [("tiny", 2, "0"), ("tiny", 2, "1"), ("wide", 2, "0"), ("wide", 4, "0"), ("wide", 8, "0"), ("wide", 8, "1")])
 def test_tensor_parallel_matches_oracle(tmp_path, case, ranks, nccl_only):
     """nccl_only "0": decode-sized rows go through the peer-memory all-reduce (inside the GEMV launch
-    where the weight allows), "1": NCCL for every size."""
+    where the weight allows) and prompts through its sliced form (forced on: left alone, the start-up
+    timing picks between it and NCCL), "1": NCCL for every size."""
     import torch
     if torch.cuda.device_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", CML_B200_TP_NCCL_ONLY=nccl_only)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", CML_B200_TP_NCCL_ONLY=nccl_only, CML_B200_TP_BULK="1")
     port = 29500 + ranks * 10 + int(nccl_only) + (5 if case == "wide" else 0)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr", "127.0.0.1",
            "--master-port", str(port), str(script), str(ROOT), str(tmp_path), case]
@@ -222,3 +226,58 @@ def test_fused_projection_allreduce_wait_expires_with_a_status(pkg, synth, ob, o
         assert np.abs(h[1].cpu().numpy() - want).max() <= 2e-3 * np.abs(want).max() * 1e-2
     finally:
         pkg.check(lib.cmlb200_set_wait_limit(0))
+
+
+def test_bulk_allreduce_wait_expires_with_a_status(pkg, torch_dev):
+    """The prompt-sized form, rank 0 of 2 launched alone: its wait for the peer's slice runs out, the
+    launch returns, the status names the peer and h is as it was."""
+    import ctypes as C
+    import torch
+    lib = pkg.lib
+    n, max_floats = 1 << 16, 1 << 17
+    nbytes = lib.cmlb200_tp_ar_bulk_workspace_bytes(max_floats, 2)
+    ws = [torch.zeros(nbytes, dtype=torch.uint8, device=torch_dev) for _ in range(2)]
+    arr = (C.c_void_p * 2)(ws[0].data_ptr(), ws[1].data_ptr())
+    part = torch.ones(n, dtype=torch.float32, device=torch_dev)
+    h = torch.full((n,), 3.0, dtype=torch.float32, device=torch_dev)
+    pkg.check(lib.cmlb200_set_wait_limit(2000))
+    try:
+        pkg.check(lib.cmlb200_tp_allreduce_bulk_add(h.data_ptr(), part.data_ptr(), n, 2, 0, arr, max_floats, None))
+        torch.cuda.synchronize()
+        assert _status(pkg, ws[0]) == 2
+        assert torch.equal(h, torch.full_like(h, 3.0))
+    finally:
+        pkg.check(lib.cmlb200_set_wait_limit(0))
+    assert lib.cmlb200_tp_allreduce_bulk_add(h.data_ptr(), part.data_ptr(), n + 2, 2, 0, arr, max_floats, None) == -1   # n % 4
+    assert lib.cmlb200_tp_allreduce_bulk_add(h.data_ptr(), part.data_ptr(), 2 * max_floats, 2, 0, arr, max_floats, None) == -1
+
+
+@pytest.mark.parametrize("tp", [2, 3, 4, 8])
+def test_bulk_allreduce_all_ranks_in_one_launch(pkg, torch_dev, tp):
+    """All ranks of the prompt-sized all-reduce as one cooperative launch on this GPU: after every call
+    each rank's h is h + (((p0 + p1) + p2) + ...) bit for bit, for message sizes that split evenly,
+    raggedly, into less than one float4 per rank, and up to the workspace limit; consecutive calls
+    alternate the inboxes."""
+    import ctypes as C
+    import torch
+    lib = pkg.lib
+    max_floats = 3 << 20
+    nbytes = lib.cmlb200_tp_ar_bulk_workspace_bytes(max_floats, tp)
+    ws = [torch.zeros(nbytes, dtype=torch.uint8, device=torch_dev) for _ in range(tp)]
+    arr = (C.c_void_p * tp)(*[w.data_ptr() for w in ws])
+    rng = np.random.default_rng(40 + tp)
+    for n in (4, 8, 4 * 1001, 1 << 20, max_floats - 4, max_floats, 4 * 77):
+        parts = [rng.standard_normal(n).astype(np.float32) for _ in range(tp)]
+        h0 = [rng.standard_normal(n).astype(np.float32) for _ in range(tp)]
+        d_p = [torch.from_numpy(a).to(torch_dev) for a in parts]
+        d_h = [torch.from_numpy(a).to(torch_dev) for a in h0]
+        pa = (C.c_void_p * tp)(*[a.data_ptr() for a in d_p])
+        ha = (C.c_void_p * tp)(*[a.data_ptr() for a in d_h])
+        pkg.check(lib.cmlb200_tp_allreduce_bulk_emulate(ha, pa, n, tp, arr, max_floats, None))
+        torch.cuda.synchronize()
+        total = np.zeros(n, np.float32)
+        for a in parts:
+            total = total + a
+        for r in range(tp):
+            assert _status(pkg, ws[r]) == 0
+            assert np.array_equal(d_h[r].cpu().numpy(), h0[r] + total), (n, r)
