@@ -57,6 +57,7 @@ _sig("cmlb200_dequantize_nf4", ci, vp, vp, ci, ci, sz, vp, vp)
 _sig("cmlb200_gemv", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_noalloc", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_accum", ci, C.POINTER(QMat), vp, vp, ci, vp)
+_sig("cmlb200_gemv_host", ci, C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_gemv_swiglu", ci, C.POINTER(QMat), C.POINTER(QMat), vp, vp, ci, vp)
 _sig("cmlb200_xq_bytes", sz, ci, ci)
 _sig("cmlb200_x_digits", ci, vp, ci, ci, vp, vp)

@@ -303,6 +303,79 @@ extern "C" int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* W
     return gemv_dispatch<EPI_SWIGLU>(Wg, Wu, d_x, d_y, M, stream, "cmlb200_gemv_swiglu");
 }
 
+// ---- host activations in, host result out ----------------------------------------------------
+// C-ML's quantized Linear takes and returns host tensors (src/nn/qlora.c:264-317; the GGUF path
+// dequantises to a host tensor and multiplies there, src/core/gguf.c:271-295). For a decode-sized call
+// the two DMA copies and their bookkeeping cost several times the GEMV, so with page-locked host
+// buffers the copies become two small kernels in the same programmatic-launch chain as the GEMV:
+// one reads x from host memory over the bus into a device staging row (and lets the GEMV start
+// prefetching weights meanwhile), one writes y from the device straight into the host buffer with
+// 16-byte stores. Pageable buffers go through cudaMemcpyAsync. The call returns when y is in h_y.
+namespace {
+template <bool VEC>
+__global__ void __launch_bounds__(256) host_stage_kernel(const float* __restrict__ src, float* __restrict__ dst, size_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        if (i < n / 4) reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+    } else if (i < n) {
+        dst[i] = src[i];
+    }
+}
+int host_stage(const float* src, float* dst, size_t n, cudaStream_t st) {
+    const bool vec = n % 4 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0;
+    const size_t items = vec ? n / 4 : n;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((items + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (vec) CMLB_CUDA(cudaLaunchKernelEx(&cfg, host_stage_kernel<true>, src, dst, n));
+    else CMLB_CUDA(cudaLaunchKernelEx(&cfg, host_stage_kernel<false>, src, dst, n));
+    return CMLB200_OK;
+}
+struct HostStage { float* x; size_t xcap; float* y; size_t ycap; };
+HostStage g_host_stage[kMaxDevices] = {};
+int stage_reserve(float** buf, size_t* cap, size_t n) {
+    if (n <= *cap) return CMLB200_OK;
+    if (*buf) { CMLB_CUDA(cudaDeviceSynchronize()); CMLB_CUDA(cudaFree(*buf)); *buf = nullptr; *cap = 0; }
+    CMLB_CUDA(cudaMalloc(reinterpret_cast<void**>(buf), n * sizeof(float)));
+    *cap = n;
+    return CMLB200_OK;
+}
+// The address a kernel can use for a page-locked host pointer, nullptr for pageable memory.
+const float* device_view(const float* h) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, h) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return a.type == cudaMemoryTypeHost ? static_cast<const float*>(a.devicePointer) : nullptr;
+}
+}  // namespace
+
+extern "C" int cmlb200_gemv_host(const cmlb200_qmat* W, const float* h_x, float* h_y, int M, void* stream) {
+    int rc = check_qmat(W, "cmlb200_gemv_host");
+    if (rc) return rc;
+    CMLB_REQUIRE(h_x && h_y, "cmlb200_gemv_host: NULL activation pointer");
+    CMLB_REQUIRE(M >= 1 && M <= 32, "cmlb200_gemv_host: M=%d outside the decode range 1..32", M);
+    HostStage& s = g_host_stage[cmlb_device_index()];
+    const size_t nx = (size_t)M * W->cols, ny = (size_t)M * W->rows;
+    if ((rc = stage_reserve(&s.x, &s.xcap, nx)) || (rc = stage_reserve(&s.y, &s.ycap, ny))) return rc;
+    cudaStream_t st = as_stream(stream);
+    const float* vx = device_view(h_x);
+    float* vy = const_cast<float*>(device_view(h_y));
+    if (vx) { if ((rc = host_stage(vx, s.x, nx, st))) return rc; }
+    else CMLB_CUDA(cudaMemcpyAsync(s.x, h_x, nx * sizeof(float), cudaMemcpyHostToDevice, st));
+    if ((rc = gemv_dispatch<EPI_STORE>(W, nullptr, s.x, s.y, M, stream, "cmlb200_gemv_host"))) return rc;
+    if (vy) { if ((rc = host_stage(s.y, vy, ny, st))) return rc; }
+    else CMLB_CUDA(cudaMemcpyAsync(h_y, s.y, ny * sizeof(float), cudaMemcpyDeviceToHost, st));
+    CMLB_CUDA(cudaStreamSynchronize(st));
+    return CMLB200_OK;
+}
+
 // ---- NF4 linear for shapes outside the vectorised kernels (any in_features, any block size, blocks
 // that straddle rows): the quantized Linear of src/nn/qlora.c:264-317 element by element, one warp
 // per output value. Element e = n*K + k of the flat [out, in] weight is TABLE[nibble(e)] times

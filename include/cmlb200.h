@@ -131,6 +131,13 @@ int cmlb200_gemv_swiglu(const cmlb200_qmat* Wg, const cmlb200_qmat* Wu, const fl
                         int M, void* stream);
 /* y += x . W^T (residual add fused; src/nn/llama.c:523-530 and :538-543). */
 int cmlb200_gemv_accum(const cmlb200_qmat* W, const float* d_x, float* d_y, int M, void* stream);
+/* One quantized Linear on HOST activations, host result out (what C-ML's Linear forward does with
+ * host tensors: src/nn/qlora.c:264-317, src/core/gguf.c:271-295 + the fp32 matmul). h_x [M, cols],
+ * h_y [M, rows], M <= 32. With page-locked buffers (cmlb200_host_alloc_pinned, cudaHostAlloc,
+ * cudaHostRegister) x is read and y is written over the bus by two small kernels chained to the GEMV,
+ * no DMA copy; pageable buffers are copied with cudaMemcpyAsync. Synchronises `stream`: y is in h_y on
+ * return. Keeps two staging rows per device, grown on demand (the first call allocates). */
+int cmlb200_gemv_host(const cmlb200_qmat* W, const float* h_x, float* h_y, int M, void* stream);
 
 /* The same kernels with the activation "digits" (the block-fixed-point form of x the integer-dot
  * GEMV consumes) made explicit, so that one set of digits serves several projections of the same

@@ -260,3 +260,37 @@ def test_gemv_other_block_types_reject_swiglu_and_partial_blocks(pkg, synth, ob,
     assert pkg.lib.cmlb200_gemv_swiglu(W.q, W.q, x.data_ptr(), y.data_ptr(), 1, stream_ptr()) != 0
     bad = pkg.QMat(12, 16, 384, 256, W.qs.data_ptr(), None, 0, None)       # 384 is not a whole number of 256-blocks
     assert pkg.lib.cmlb200_gemv(bad, x.data_ptr(), y.data_ptr(), 1, stream_ptr()) != 0
+
+
+@pytest.mark.parametrize("kind,N,K", [("q4_0", 11008, 4096), ("q8_0", 1000, 1056), ("nf4", 384, 1024), ("q4_0", 200, 512)])
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_gemv_host_buffers(pkg, synth, ob, orc, torch_dev, kind, N, K, M):
+    """cmlb200_gemv_host: host activations in, host result out, with page-locked buffers (read and
+    written by kernels over the bus) and with pageable ones (DMA copies). Both must give the bits
+    of cmlb200_gemv on device buffers, and those match the oracle within the fp32 bound."""
+    import torch
+    rng = np.random.default_rng(1200 + M + K)
+    W, Wf = make_weight(pkg, synth, ob, orc, torch_dev, rng, kind, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    d_x = to_dev(x, torch_dev)
+    d_y = torch.zeros((M, N), dtype=torch.float32, device=torch_dev)
+    pkg.check(pkg.lib.cmlb200_gemv(W.q, d_x.data_ptr(), d_y.data_ptr(), M, stream_ptr()), "gemv")
+    torch.cuda.synchronize()
+    dev_result = d_y.cpu().numpy()
+    assert rel_err(dev_result, ob.linear_nt(orc, x, Wf)) <= TOL
+    xp = torch.from_numpy(x).pin_memory()
+    yp = torch.zeros((M, N), dtype=torch.float32).pin_memory()
+    for _ in range(2):                                   # the second call reuses the staging rows
+        yp.zero_()
+        pkg.check(pkg.lib.cmlb200_gemv_host(W.q, xp.data_ptr(), yp.data_ptr(), M, stream_ptr()), "gemv_host pinned")
+        assert np.array_equal(yp.numpy(), dev_result)
+    y_pageable = np.zeros((M, N), np.float32)
+    pkg.check(pkg.lib.cmlb200_gemv_host(W.q, x.ctypes.data, y_pageable.ctypes.data, M, stream_ptr()), "gemv_host pageable")
+    assert np.array_equal(y_pageable, dev_result)
+    # an odd offset into the page-locked buffer: scalar staging
+    if N % 4 == 0:
+        yo = torch.zeros(M * N + 1, dtype=torch.float32).pin_memory()
+        pkg.check(pkg.lib.cmlb200_gemv_host(W.q, xp.data_ptr(), yo.data_ptr() + 4, M, stream_ptr()), "gemv_host offset")
+        assert np.array_equal(yo.numpy()[1:].reshape(M, N), dev_result)
+    assert pkg.lib.cmlb200_gemv_host(W.q, None, yp.data_ptr(), M, stream_ptr()) == -1
+    assert pkg.lib.cmlb200_gemv_host(W.q, xp.data_ptr(), yp.data_ptr(), 33, stream_ptr()) == -1
