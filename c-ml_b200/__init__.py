@@ -354,6 +354,31 @@ _sig("cml_tp_shard_qblocks", ci, ci, vp, ci, ci, ci, ci, ci, vp)
 _sig("cml_llama_tp_unique_id", ci, vp)
 _sig("cml_llama_tp_init", ci, MP, vp, ci)
 _sig("cml_llama_tp_prompt_allreduce", ci, MP, C.POINTER(sz), C.POINTER(C.c_float), C.POINTER(C.c_float))
+class Tokenizer(C.Structure):
+    _fields_ = [("vocab", C.POINTER(C.c_char_p)), ("vocab_size", C.c_int), ("merges", C.c_void_p), ("num_merges", C.c_int),
+                ("token_to_id", C.c_void_p), ("hash_size", C.c_int), ("bos_token_id", C.c_int), ("eos_token_id", C.c_int),
+                ("pad_token_id", C.c_int), ("unk_token_id", C.c_int)]
+
+
+TKP = C.POINTER(Tokenizer)
+_sig("cml_tokenizer_create", TKP, C.POINTER(C.c_char_p), ci, C.POINTER(C.c_char_p), ci)
+_sig("cml_tokenizer_free", None, TKP)
+_sig("cml_tokenizer_encode", C.POINTER(C.c_int), TKP, C.c_char_p, C.POINTER(C.c_int))
+_sig("cml_tokenizer_decode", vp, TKP, vp, ci)
+_sig("cml_tokenizer_set_special", None, TKP, ci, ci, ci, ci)
+_sig("cml_tokenizer_vocab_size", ci, TKP)
+_sig("gguf_get_num_metadata", ci, vp)
+_sig("gguf_get_metadata_key", C.c_char_p, vp, ci)
+_sig("gguf_get_metadata_type", ci, vp, C.c_char_p)
+_sig("gguf_get_metadata_int", ci, vp, C.c_char_p, C.POINTER(C.c_int64))
+_sig("gguf_get_metadata_float", ci, vp, C.c_char_p, C.POINTER(C.c_double))
+_sig("gguf_get_metadata_string", C.c_char_p, vp, C.c_char_p)
+_sig("gguf_get_metadata_array_length", C.c_int64, vp, C.c_char_p, C.POINTER(ci))
+_sig("gguf_get_metadata_array_string", C.c_char_p, vp, C.c_char_p, C.c_int64)
+_sig("gguf_get_metadata_array_data", vp, vp, C.c_char_p)
+_sig("gguf_create_tokenizer", TKP, vp)
+_sig("cml_llama_config_from_gguf", ci, C.c_char_p, C.POINTER(LlamaConfig))
+_sig("cml_llama_load_gguf_tokenizer", ci, MP, C.c_char_p)
 _sig("cml_init", ci)
 _sig("cml_cleanup", ci)
 _sig("tensor_manual_seed", None, C.c_uint64)

@@ -1,8 +1,11 @@
 /*
  * GGUF v3 reader and the block-type helpers (C-ML: src/core/gguf.c:105-310,
  * src/core/gguf_quant.c:313-391). The file format handling is host work; dequantisation runs on
- * the device. Layout read: magic, version, n_tensors, n_kv, the key/values (skipped by type),
- * the tensor infos (name, ndim, dims, type, offset) and data at align32(end of infos) + offset.
+ * the device. Layout read: magic, version, n_tensors, n_kv, the key/values, the tensor infos
+ * (name, ndim, dims, type, offset) and data at align32(end of infos) + offset. C-ML steps over the
+ * key/values (src/core/gguf.c:75-103); here they are kept, so that a file's tokenizer and
+ * hyper-parameters can be used (gguf_get_metadata_*, gguf_create_tokenizer,
+ * cml_llama_config_from_gguf). A malformed entry fails the open exactly where C-ML's skip would.
  */
 #include <stdio.h>
 #include <stdlib.h>
@@ -10,11 +13,25 @@
 
 #include "cml_internal.h"
 
+/* One key/value. Scalars sit in `bits` as read; a string in `str`; an array of scalars packed in
+ * `data`, an array of strings in `strs`; an array of arrays is stepped over (count kept, no data). */
+typedef struct GGUFMeta {
+    char* key;
+    uint32_t type, elem_type;
+    uint64_t count;
+    uint64_t bits;
+    char* str;
+    void* data;
+    char** strs;
+} GGUFMeta;
+
 struct GGUFContext {
     FILE* file;
     int num_tensors;
     GGUFTensorInfo* tensors;
     uint64_t data_offset;
+    int num_meta;
+    GGUFMeta* meta;
 };
 
 bool gguf_type_is_quantized(GGUFTensorType type) {
@@ -88,6 +105,52 @@ static int skip_value(FILE* f, uint32_t type) {
     return 0;
 }
 
+static const int kMetaSize[] = {1, 1, 2, 2, 4, 4, 4, 1, -1, -2, 8, 8, 8};     /* bytes of a scalar of each GGUF value type */
+
+static void meta_release(GGUFMeta* m) {
+    free(m->key);
+    free(m->str);
+    free(m->data);
+    if (m->strs) {
+        for (uint64_t i = 0; i < m->count; i++) free(m->strs[i]);
+        free(m->strs);
+    }
+    memset(m, 0, sizeof *m);
+}
+
+/* The value of type m->type at the file position; 0 when it was read (or stepped over) whole. */
+static int read_meta_value(FILE* f, GGUFMeta* m) {
+    if (m->type > 12) return -1;
+    const int sz = kMetaSize[m->type];
+    if (sz > 0) return fread(&m->bits, (size_t)sz, 1, f) == 1 ? 0 : -1;
+    if (sz == -1) return (m->str = read_string(f)) ? 0 : -1;
+    if (fread(&m->elem_type, 4, 1, f) != 1 || fread(&m->count, 8, 1, f) != 1 || m->elem_type > 12) return -1;
+    const int esz = kMetaSize[m->elem_type];
+    if (esz > 0) {
+        if (m->count > ((uint64_t)1 << 28)) return -1;
+        m->data = malloc(m->count ? (size_t)m->count * (size_t)esz : 1);
+        return m->data && fread(m->data, (size_t)esz, (size_t)m->count, f) == m->count ? 0 : -1;
+    }
+    if (esz == -1) {
+        if (m->count > ((uint64_t)1 << 28)) return -1;
+        m->strs = (char**)calloc(m->count ? (size_t)m->count : 1, sizeof(char*));
+        if (!m->strs) return -1;
+        for (uint64_t i = 0; i < m->count; i++)
+            if (!(m->strs[i] = read_string(f))) { m->count = i; return -1; }
+        return 0;
+    }
+    for (uint64_t i = 0; i < m->count; i++)
+        if (skip_value(f, 9)) return -1;
+    return 0;
+}
+
+static const GGUFMeta* meta_find(GGUFContext* ctx, const char* key) {
+    if (!ctx || !key) return NULL;
+    for (int i = 0; i < ctx->num_meta; i++)
+        if (strcmp(ctx->meta[i].key, key) == 0) return &ctx->meta[i];
+    return NULL;
+}
+
 static DType gguf_dtype(GGUFTensorType t) {
     switch ((int)t) {
         case GGUF_TENSOR_F16: return DTYPE_FLOAT16;
@@ -113,16 +176,15 @@ GGUFContext* gguf_open_read(const char* filepath) {
     GGUFContext* ctx = (GGUFContext*)calloc(1, sizeof *ctx);
     if (!ctx) { fclose(f); return NULL; }
     ctx->file = f;
+    if (nkv > (1u << 24) || !(ctx->meta = (GGUFMeta*)calloc(nkv ? (size_t)nkv : 1, sizeof(GGUFMeta)))) { gguf_close(ctx); return NULL; }
     for (uint64_t i = 0; i < nkv; i++) {
-        char* key = read_string(f);
-        uint32_t vt;
-        if (!key || fread(&vt, 4, 1, f) != 1 || skip_value(f, vt)) {
-            free(key);
+        GGUFMeta* m = &ctx->meta[i];
+        ctx->num_meta = (int)i + 1;
+        if (!(m->key = read_string(f)) || fread(&m->type, 4, 1, f) != 1 || read_meta_value(f, m)) {
             LOG_ERROR("gguf_open_read: malformed metadata entry %llu", (unsigned long long)i);
             gguf_close(ctx);
             return NULL;
         }
-        free(key);
     }
     ctx->tensors = (GGUFTensorInfo*)calloc(nt ? (size_t)nt : 1, sizeof(GGUFTensorInfo));
     if (!ctx->tensors) { gguf_close(ctx); return NULL; }
@@ -166,8 +228,105 @@ void gguf_close(GGUFContext* ctx) {
         for (int i = 0; i < ctx->num_tensors; i++) free(ctx->tensors[i].name);
         free(ctx->tensors);
     }
+    if (ctx->meta) {
+        for (int i = 0; i < ctx->num_meta; i++) meta_release(&ctx->meta[i]);
+        free(ctx->meta);
+    }
     if (ctx->file) fclose(ctx->file);
     free(ctx);
+}
+
+/* ---- key/value metadata ------------------------------------------------------------------------ */
+int gguf_get_num_metadata(GGUFContext* ctx) { return ctx ? ctx->num_meta : 0; }
+
+const char* gguf_get_metadata_key(GGUFContext* ctx, int index) {
+    return ctx && index >= 0 && index < ctx->num_meta ? ctx->meta[index].key : NULL;
+}
+
+int gguf_get_metadata_type(GGUFContext* ctx, const char* key) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    return m ? (int)m->type : -1;
+}
+
+static int scalar_as_int(uint32_t type, const void* p, int64_t* out) {
+    switch (type) {
+        case 0: case 7: *out = *(const uint8_t*)p; return 0;
+        case 1: *out = *(const int8_t*)p; return 0;
+        case 2: { uint16_t v; memcpy(&v, p, 2); *out = v; return 0; }
+        case 3: { int16_t v; memcpy(&v, p, 2); *out = v; return 0; }
+        case 4: { uint32_t v; memcpy(&v, p, 4); *out = v; return 0; }
+        case 5: { int32_t v; memcpy(&v, p, 4); *out = v; return 0; }
+        case 10: { uint64_t v; memcpy(&v, p, 8); *out = (int64_t)v; return 0; }
+        case 11: memcpy(out, p, 8); return 0;
+        default: return -1;
+    }
+}
+
+int gguf_get_metadata_int(GGUFContext* ctx, const char* key, int64_t* out) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    return m && out ? scalar_as_int(m->type, &m->bits, out) : -1;
+}
+
+int gguf_get_metadata_float(GGUFContext* ctx, const char* key, double* out) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    if (!m || !out) return -1;
+    if (m->type == 6) { float v; memcpy(&v, &m->bits, 4); *out = v; return 0; }
+    if (m->type == 12) { memcpy(out, &m->bits, 8); return 0; }
+    int64_t i;
+    if (scalar_as_int(m->type, &m->bits, &i)) return -1;
+    *out = (double)i;
+    return 0;
+}
+
+const char* gguf_get_metadata_string(GGUFContext* ctx, const char* key) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    return m && m->type == 8 ? m->str : NULL;
+}
+
+int64_t gguf_get_metadata_array_length(GGUFContext* ctx, const char* key, int* elem_type) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    if (!m || m->type != 9) return -1;
+    if (elem_type) *elem_type = (int)m->elem_type;
+    return (int64_t)m->count;
+}
+
+const char* gguf_get_metadata_array_string(GGUFContext* ctx, const char* key, int64_t index) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    return m && m->type == 9 && m->strs && index >= 0 && (uint64_t)index < m->count ? m->strs[index] : NULL;
+}
+
+const void* gguf_get_metadata_array_data(GGUFContext* ctx, const char* key) {
+    const GGUFMeta* m = meta_find(ctx, key);
+    return m && m->type == 9 ? m->data : NULL;
+}
+
+CMLTokenizer* gguf_create_tokenizer(GGUFContext* ctx) {
+    const GGUFMeta* toks = meta_find(ctx, "tokenizer.ggml.tokens");
+    if (!toks || toks->type != 9 || !toks->strs || toks->count == 0 || toks->count > 0x7fffffffu) return NULL;
+    const GGUFMeta* mg = meta_find(ctx, "tokenizer.ggml.merges");
+    const int nm = mg && mg->type == 9 && mg->strs && mg->count <= 0x7fffffffu ? (int)mg->count : 0;
+    char** pairs = nm ? (char**)calloc((size_t)nm, sizeof(char*)) : NULL;
+    for (int i = 0; pairs && i < nm; i++) {
+        /* "left right" -> "leftright": the separator is the first space after the first byte (a
+         * left part may itself be a space) */
+        const char* s = mg->strs[i];
+        const size_t n = strlen(s);
+        const char* sp = n > 1 ? strchr(s + 1, ' ') : NULL;
+        if (!(pairs[i] = (char*)malloc(n + 1))) continue;
+        if (sp) { memcpy(pairs[i], s, (size_t)(sp - s)); strcpy(pairs[i] + (sp - s), sp + 1); }
+        else strcpy(pairs[i], s);
+    }
+    CMLTokenizer* tok = cml_tokenizer_create(toks->strs, (int)toks->count, pairs, pairs ? nm : 0);
+    for (int i = 0; pairs && i < nm; i++) free(pairs[i]);
+    free(pairs);
+    if (!tok) return NULL;
+    int64_t id[4] = {-1, -1, -1, -1};
+    static const char* const keys[4] = {"tokenizer.ggml.bos_token_id", "tokenizer.ggml.eos_token_id", "tokenizer.ggml.padding_token_id",
+                                        "tokenizer.ggml.unknown_token_id"};
+    for (int k = 0; k < 4; k++)
+        if (gguf_get_metadata_int(ctx, keys[k], &id[k])) id[k] = -1;
+    cml_tokenizer_set_special(tok, (int)id[0], (int)id[1], (int)id[2], (int)id[3]);
+    return tok;
 }
 
 int gguf_get_num_tensors(GGUFContext* ctx) { return ctx ? ctx->num_tensors : 0; }

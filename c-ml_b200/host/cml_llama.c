@@ -169,6 +169,10 @@ static void dm_destroy(DevModel* d) {
     free(d);
 }
 
+/* cml_tokenizer.c unless the caller installed its own pair (cml_llama_set_tokenizer_functions) */
+static CMLTokenizerEncodeFn g_tok_encode = NULL;
+static CMLTokenizerDecodeFn g_tok_decode = NULL;
+
 void cml_llama_free(CMLLLaMAModel* model) {
     if (!model) return;
     DevModel* gone = NULL;
@@ -192,6 +196,8 @@ void cml_llama_free(CMLLLaMAModel* model) {
     if (model->lm_head && model->lm_head != model->embed_tokens) tensor_free(model->lm_head);
     tensor_free(model->embed_tokens);
     tensor_free(model->norm);
+    /* the model owns its tokenizer (src/nn/llama.c:258-259), unless the caller's own functions drive it */
+    if (model->tokenizer && !g_tok_encode && !g_tok_decode) cml_tokenizer_free(model->tokenizer);
     free(model);
 }
 
@@ -362,6 +368,56 @@ int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     if (only && only[0] == '1') return 0;
     if (tp_peer_setup(d)) { LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size"); return 0; }
     tp_bulk_setup(d);
+    return 0;
+}
+
+int cml_llama_config_from_gguf(const char* filepath, CMLLLaMAConfig* config) {
+    if (!filepath || !config) { LOG_ERROR("cml_llama_config_from_gguf: NULL argument"); return -1; }
+    GGUFContext* g = gguf_open_read(filepath);
+    if (!g) return -1;
+    const char* arch = gguf_get_metadata_string(g, "general.architecture");
+    if (!arch || strlen(arch) > 64) arch = "llama";
+    char key[160];
+    int64_t layers = 0, hidden = 0, heads = 0, v = 0;
+    double f = 0.0;
+#define ARCH_KEY(suffix) (snprintf(key, sizeof key, "%s.%s", arch, suffix), key)
+    if (gguf_get_metadata_int(g, ARCH_KEY("block_count"), &layers) || gguf_get_metadata_int(g, ARCH_KEY("embedding_length"), &hidden) ||
+        gguf_get_metadata_int(g, ARCH_KEY("attention.head_count"), &heads) || layers <= 0 || hidden <= 0 || heads <= 0 ||
+        layers > 4096 || hidden > (1 << 20) || heads > hidden) {
+        LOG_ERROR("cml_llama_config_from_gguf: %s lacks %s.block_count / embedding_length / attention.head_count", filepath, arch);
+        gguf_close(g);
+        return -1;
+    }
+    CMLLLaMAConfig c = cml_llama_config_7b();
+    c.num_layers = (int)layers;
+    c.hidden_size = (int)hidden;
+    c.num_heads = (int)heads;
+    c.num_kv_heads = (int)heads;
+    if (!gguf_get_metadata_int(g, ARCH_KEY("attention.head_count_kv"), &v) && v > 0 && v <= heads) c.num_kv_heads = (int)v;
+    if (!gguf_get_metadata_int(g, ARCH_KEY("feed_forward_length"), &v) && v > 0 && v < (1 << 24)) c.intermediate_size = (int)v;
+    if (!gguf_get_metadata_int(g, ARCH_KEY("context_length"), &v) && v > 0 && v < (1 << 24)) c.max_seq_len = (int)v;
+    if (!gguf_get_metadata_float(g, ARCH_KEY("rope.freq_base"), &f) && f > 0.0) c.rope_theta = (float)f;
+    if (!gguf_get_metadata_float(g, ARCH_KEY("attention.layer_norm_rms_epsilon"), &f) && f > 0.0) c.rms_norm_eps = (float)f;
+    const GGUFTensorInfo* emb = cml_gguf_find(g, "token_embd.weight");
+    if (!emb) emb = cml_gguf_find(g, "model.embed_tokens.weight");
+    if (!gguf_get_metadata_int(g, ARCH_KEY("vocab_size"), &v) && v > 0 && v < (1 << 24)) c.vocab_size = (int)v;
+    else if ((v = gguf_get_metadata_array_length(g, "tokenizer.ggml.tokens", NULL)) > 0 && v < (1 << 24)) c.vocab_size = (int)v;
+    else if (emb && emb->ndim == 2 && emb->shape[0] > 0 && emb->shape[0] < (1 << 24)) c.vocab_size = (int)emb->shape[0];
+#undef ARCH_KEY
+    gguf_close(g);
+    *config = c;
+    return 0;
+}
+
+int cml_llama_load_gguf_tokenizer(CMLLLaMAModel* model, const char* filepath) {
+    if (!model || !filepath) { LOG_ERROR("cml_llama_load_gguf_tokenizer: NULL argument"); return -1; }
+    GGUFContext* g = gguf_open_read(filepath);
+    if (!g) return -1;
+    CMLTokenizer* tok = gguf_create_tokenizer(g);
+    gguf_close(g);
+    if (!tok) { LOG_ERROR("cml_llama_load_gguf_tokenizer: %s has no tokenizer.ggml.tokens", filepath); return -1; }
+    if (model->tokenizer && !g_tok_encode && !g_tok_decode) cml_tokenizer_free(model->tokenizer);
+    model->tokenizer = tok;
     return 0;
 }
 
@@ -1098,12 +1154,6 @@ int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config) {
     return id;
 }
 
-/* C-ML's tokenizer entry points (include/nn/llm_ops.h:147-149): weak references, so they resolve to
- * the host program's when it links C-ML's src/nn/llm_ops.c and to NULL otherwise. */
-extern int* cml_tokenizer_encode(CMLTokenizer* tok, const char* text, int* num_tokens) __attribute__((weak));
-extern char* cml_tokenizer_decode(CMLTokenizer* tok, const int* tokens, int num_tokens) __attribute__((weak));
-static CMLTokenizerEncodeFn g_tok_encode = NULL;
-static CMLTokenizerDecodeFn g_tok_decode = NULL;
 
 void cml_llama_set_tokenizer_functions(CMLTokenizerEncodeFn encode, CMLTokenizerDecodeFn decode) {
     g_tok_encode = encode;

@@ -75,9 +75,25 @@ def bf16_to_f32(u16):
 
 
 # ---- GGUF v3 writer for synthetic models (little-endian; tensor data 32-byte aligned) ------------
-def write_gguf(path, tensors):
+_GGUF_SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<B", 10: "<Q", 11: "<q", 12: "<d"}
+
+
+def _gguf_value(vtype, value):
+    """One GGUF metadata value: scalars by type id, 8 = string (bytes or str), 9 = (elem_type, items)."""
+    import struct
+    if vtype == 8:
+        raw = value.encode() if isinstance(value, str) else bytes(value)
+        return struct.pack("<Q", len(raw)) + raw
+    if vtype == 9:
+        et, items = value
+        return struct.pack("<IQ", et, len(items)) + b"".join(_gguf_value(et, v) for v in items)
+    return struct.pack(_GGUF_SCALAR[vtype], value)
+
+
+def write_gguf(path, tensors, metadata=None):
     """tensors: list of (name, dims, gguf_type, raw_bytes). dims are written in the given order
-    (for weights: (in_features, out_features), the GGUF convention)."""
+    (for weights: (in_features, out_features), the GGUF convention). metadata: list of
+    (key, value_type, value) written after general.architecture = "llama"."""
     import struct
     infos, blobs, off = [], [], 0
     for name, dims, gtype, raw in tensors:
@@ -87,9 +103,13 @@ def write_gguf(path, tensors):
         blobs.append(raw + b"\0" * pad)
         off += len(raw) + pad
     out = bytearray()
-    out += struct.pack("<IIQQ", 0x46475547, 3, len(tensors), 1)
+    metadata = list(metadata or [])
+    out += struct.pack("<IIQQ", 0x46475547, 3, len(tensors), 1 + len(metadata))
     key = b"general.architecture"
     out += struct.pack("<Q", len(key)) + key + struct.pack("<I", 8) + struct.pack("<Q", 5) + b"llama"
+    for k, vtype, value in metadata:
+        k = k.encode() if isinstance(k, str) else bytes(k)
+        out += struct.pack("<Q", len(k)) + k + struct.pack("<I", vtype) + _gguf_value(vtype, value)
     for name, dims, gtype, o in infos:
         out += struct.pack("<Q", len(name)) + name + struct.pack("<I", len(dims))
         for d in dims:

@@ -116,7 +116,7 @@ bool gguf_type_is_quantized(GGUFTensorType type);
 int gguf_quant_block_size(GGUFTensorType type);
 size_t gguf_quant_type_size(GGUFTensorType type);
 /* Host pointers in, host fp32 out, computed on the device; -1 on NULL, numel == 0, a type
- * without a device kernel (only Q4_0 and Q8_0 have one) or numel % block != 0. */
+ * that is not block-quantized (Q4_0, Q4_1, Q8_0, Q4_K, Q5_K, Q6_K are) or numel % block != 0. */
 int gguf_dequantize(GGUFTensorType type, const void* src, float* dst, size_t numel);
 
 typedef struct GGUFContext GGUFContext;
@@ -291,7 +291,30 @@ Tensor* cml_row_parallel_forward(CMLRowParallelLinear* rp, Tensor* input);     /
 Tensor* cml_tp_all_reduce_sum(Tensor** partials, int num_parts);
 Tensor* cml_tp_shard_weight(Tensor* weight, int dim, int tp_size, int tp_rank);
 
-typedef struct CMLTokenizer CMLTokenizer;
+/* include/nn/llm_ops.h:123-153: byte-level BPE. encode: one token per byte, then every merge rule in
+ * list order joins adjacent tokens that spell its pair (leftmost first); spellings are looked up in
+ * the vocabulary (the last of equal spellings wins), unknown ones map to unk_token_id, or 0 when
+ * that is unset. decode concatenates the spellings; ids outside the vocabulary contribute nothing.
+ * encode returns a malloc'd array (NULL and 0 tokens for an empty text), decode a malloc'd string. */
+typedef struct CMLBPEMerge {
+    char* pair;            /* spelling of the merged token */
+    int new_token_id;      /* its id, -1 when the vocabulary does not hold it */
+} CMLBPEMerge;
+typedef struct CMLTokenizer {
+    char** vocab;
+    int vocab_size;
+    CMLBPEMerge* merges;
+    int num_merges;
+    int* token_to_id;      /* internal: spelling -> id table */
+    int hash_size;
+    int bos_token_id, eos_token_id, pad_token_id, unk_token_id;     /* -1 until cml_tokenizer_set_special */
+} CMLTokenizer;
+CMLTokenizer* cml_tokenizer_create(char** vocab, int vocab_size, char** merge_pairs, int num_merges);
+void cml_tokenizer_free(CMLTokenizer* tok);
+int* cml_tokenizer_encode(CMLTokenizer* tok, const char* text, int* num_tokens);
+char* cml_tokenizer_decode(CMLTokenizer* tok, const int* tokens, int num_tokens);
+void cml_tokenizer_set_special(CMLTokenizer* tok, int bos, int eos, int pad, int unk);
+int cml_tokenizer_vocab_size(const CMLTokenizer* tok);
 
 /* ---- include/nn/llama.h:13-106 -------------------------------------------------------------- */
 typedef struct CMLLLaMAConfig {
@@ -371,10 +394,8 @@ Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tens
 /* src/nn/llama.c:739-851: encode the prompt with model->tokenizer, reset the caches, prefill,
  * then sample / forward one token at a time until max_new_tokens, the EOS id or the sequence
  * limit; the result holds prompt + generated ids, the decoded text, the wall time and generated
- * tokens per second (prefill included, as in C-ML). NULL when the model has no tokenizer (C-ML's
- * GGUF loader never creates one) or no tokenizer functions are known: they are C-ML's
- * cml_tokenizer_encode / cml_tokenizer_decode (include/nn/llm_ops.h:147-149), picked up from the
- * process when it links them, or given with cml_llama_set_tokenizer_functions. */
+ * tokens per second (prefill included, as in C-ML). NULL when the model has no tokenizer: C-ML's
+ * GGUF loader never creates one; cml_llama_load_gguf_tokenizer (below) builds it from the file. */
 CMLGenerationResult* cml_llama_generate(CMLLLaMAModel* model, const char* prompt, const CMLGenerationConfig* config);
 void cml_generation_result_free(CMLGenerationResult* result);
 int cml_llama_sample_token(Tensor* logits, const CMLGenerationConfig* config);
@@ -382,12 +403,41 @@ void cml_llama_reset(CMLLLaMAModel* model);
 void cml_llama_print_config(const CMLLLaMAConfig* config);
 
 /* ---- additions (no C-ML counterpart) ---------------------------------------------------------- */
-/* The tokenizer stays C-ML's (src/nn/llm_ops.c:1140-1400 is not part of this library). A caller
- * whose process does not export cml_tokenizer_encode / cml_tokenizer_decode hands them over here:
- * encode returns a malloc'd id array and its length, decode a malloc'd string. */
+/* cml_llama_generate encodes and decodes with this library's cml_tokenizer_encode / _decode. A caller
+ * with another tokenizer behind model->tokenizer hands its functions over here (NULL, NULL restores
+ * the built-in ones): encode returns a malloc'd id array and its length, decode a malloc'd string. */
 typedef int* (*CMLTokenizerEncodeFn)(CMLTokenizer* tok, const char* text, int* num_tokens);
 typedef char* (*CMLTokenizerDecodeFn)(CMLTokenizer* tok, const int* tokens, int num_tokens);
 void cml_llama_set_tokenizer_functions(CMLTokenizerEncodeFn encode, CMLTokenizerDecodeFn decode);
+/* GGUF key/value metadata. C-ML's reader steps over every value (src/core/gguf.c:75-103,134-140),
+ * so a GGUF file's tokenizer and hyper-parameters are out of its reach; gguf_open_read here keeps
+ * them. Types are the file's own ids (include/core/gguf.h:13-27): 0..7 integers and bool, 6 and 12
+ * floats, 8 string, 9 array. Lookups return -1 / NULL for a missing key or a value of another kind. */
+int gguf_get_num_metadata(GGUFContext* ctx);
+const char* gguf_get_metadata_key(GGUFContext* ctx, int index);
+int gguf_get_metadata_type(GGUFContext* ctx, const char* key);                      /* -1: no such key */
+int gguf_get_metadata_int(GGUFContext* ctx, const char* key, int64_t* out);         /* integer and bool values */
+int gguf_get_metadata_float(GGUFContext* ctx, const char* key, double* out);        /* float and integer values */
+const char* gguf_get_metadata_string(GGUFContext* ctx, const char* key);
+/* Arrays: the element count (-1: not an array) and element type; string elements one by one, scalar
+ * elements as one packed little-endian buffer owned by the context. Arrays of arrays are skipped. */
+int64_t gguf_get_metadata_array_length(GGUFContext* ctx, const char* key, int* elem_type);
+const char* gguf_get_metadata_array_string(GGUFContext* ctx, const char* key, int64_t index);
+const void* gguf_get_metadata_array_data(GGUFContext* ctx, const char* key);
+/* A CMLTokenizer from tokenizer.ggml.tokens, tokenizer.ggml.merges ("left right" pairs become the
+ * merged spelling cml_tokenizer_create expects) and tokenizer.ggml.{bos,eos,padding,unknown}_token_id.
+ * NULL when the file has no token list. */
+CMLTokenizer* gguf_create_tokenizer(GGUFContext* ctx);
+/* Fills a CMLLLaMAConfig from <arch>.block_count / embedding_length / feed_forward_length /
+ * attention.head_count(_kv) / context_length / rope.freq_base / attention.layer_norm_rms_epsilon
+ * (<arch> = general.architecture, "llama" when absent); the vocabulary size comes from
+ * <arch>.vocab_size, else the token list, else the embedding tensor's row count. Fields the file
+ * does not give keep cml_llama_config_7b's values. -1 when the file cannot be read or lacks
+ * block_count, embedding_length or head_count. */
+int cml_llama_config_from_gguf(const char* filepath, CMLLLaMAConfig* config);
+/* Replaces model->tokenizer (freed with cml_tokenizer_free) by gguf_create_tokenizer of the file;
+ * -1 and the model unchanged when the file has no token list. cml_llama_free releases it. */
+int cml_llama_load_gguf_tokenizer(CMLLLaMAModel* model, const char* filepath);
 /* Behaviour switches of a model, to be set after cml_llama_create and before the first forward:
  *   CML_B200_REFERENCE_QUIRKS  reproduce two properties of C-ML's forward pass exactly: RoPE
  *       rotates only head 0 (src/nn/llama.c:483-484 passes 2-D tensors to cml_rope_forward) and

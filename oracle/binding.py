@@ -123,6 +123,8 @@ def load_ref():
         _sig(lib, "ref_paged_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, ci, ci, vp)
         _sig(lib, "ref_speculative_step", ci, vp, vp, ci, ci, vp, ci, ci, vp, vp, vp)
         _sig(lib, "ref_tp_column_then_row", ci, vp, ci, ci, vp, ci, vp, ci, ci, vp)
+        _sig(lib, "ref_tokenizer_encode", ci, C.c_char_p, ci, C.c_char_p, ci, ci, C.c_char_p, vp, ci)
+        _sig(lib, "ref_tokenizer_decode", ci, C.c_char_p, ci, vp, ci, vp, ci)
         lib.ref_init()
     _ref_cache.append(lib)
     return lib

@@ -423,3 +423,45 @@ done:
     tensor_free(t2);
     return rc;
 }
+
+/* cml_tokenizer_create / encode / decode (src/nn/llm_ops.c:1140-1389). Strings travel as blobs of
+ * NUL-terminated spellings back to back. Returns the token count (ids in out, at most cap), or the
+ * decoded length (text in out_text). */
+static char** blob_strings(const char* blob, int n) {
+    char** v = (char**)calloc(n > 0 ? (size_t)n : 1, sizeof(char*));
+    for (int i = 0; v && i < n; i++) { v[i] = (char*)blob; blob += strlen(blob) + 1; }
+    return v;
+}
+int ref_tokenizer_encode(const char* vocab_blob, int n_vocab, const char* merges_blob, int n_merges, int unk,
+                         const char* text, int* out, int cap) {
+    char** vocab = blob_strings(vocab_blob, n_vocab);
+    char** merges = n_merges > 0 ? blob_strings(merges_blob, n_merges) : NULL;
+    CMLTokenizer* tok = cml_tokenizer_create(vocab, n_vocab, merges, n_merges);
+    int n = -1;
+    if (tok) {
+        if (unk >= -1) cml_tokenizer_set_special(tok, -1, -1, -1, unk);
+        int* ids = cml_tokenizer_encode(tok, text, &n);
+        for (int i = 0; ids && i < n && i < cap; i++) out[i] = ids[i];
+        free(ids);
+        cml_tokenizer_free(tok);
+    }
+    free(vocab);
+    free(merges);
+    return n;
+}
+int ref_tokenizer_decode(const char* vocab_blob, int n_vocab, const int* ids, int n, char* out_text, int cap) {
+    char** vocab = blob_strings(vocab_blob, n_vocab);
+    CMLTokenizer* tok = cml_tokenizer_create(vocab, n_vocab, NULL, 0);
+    int len = -1;
+    if (tok) {
+        char* s = cml_tokenizer_decode(tok, ids, n);
+        if (s) {
+            len = (int)strlen(s);
+            if (len < cap) memcpy(out_text, s, (size_t)len + 1);
+            free(s);
+        }
+        cml_tokenizer_free(tok);
+    }
+    free(vocab);
+    return len;
+}

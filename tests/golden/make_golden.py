@@ -208,6 +208,49 @@ def main():
         scases.append(name)
     out["spec_target"] = tgt
 
+    # ---- byte-level BPE tokenizer (src/nn/llm_ops.c:1140-1389) ----------------------------------
+    # vocabulary: single bytes of a small alphabet (one byte >= 0x80), then spellings made by
+    # joining two earlier entries (the merge rules, in that order); a few merged spellings are left
+    # out of the vocabulary (-> unknown id), two spellings appear twice (the later id must win).
+    trng = np.random.default_rng(77)
+    alphabet = [bytes([c]) for c in b"abcde "] + [b"\xc3"]
+    vocab = list(alphabet)
+    merges = []
+    while len(merges) < 40:
+        a, b = vocab[trng.integers(len(vocab))], vocab[trng.integers(len(vocab))]
+        s = a + b
+        if len(s) > 9:
+            continue
+        merges.append(s)
+        if len(merges) % 9 != 0:
+            vocab.append(s)                                  # every ninth merged spelling stays unknown
+    vocab.append(vocab[3])
+    vocab.append(merges[4])                                  # duplicates
+    texts = [b"a", b"ab", b"zzz", b"hello world"]
+    for n in (2, 3, 5, 17, 64, 200, 400):
+        for _ in range(3):
+            texts.append(b"".join(alphabet[i] for i in trng.integers(len(alphabet), size=n)))
+    texts.append(b"a" * 50)
+    texts.append((merges[0] + merges[1]) * 20 + b"z" + merges[2] * 7)
+    vblob = b"".join(v + b"\0" for v in vocab)
+    mblob = b"".join(m + b"\0" for m in merges)
+    ids_all, counts, unks = [], [], []
+    for k, txt in enumerate(texts):
+        unk = [-1, 2, len(vocab) - 1][k % 3]
+        buf = np.zeros(len(txt) + 1, np.int32)
+        n = ref.ref_tokenizer_encode(vblob, len(vocab), mblob, len(merges), unk, txt, p(buf), len(buf))
+        assert 0 < n <= len(txt)
+        ids_all.append(buf[:n].copy()); counts.append(n); unks.append(unk)
+    dec_ids = np.concatenate([ids_all[5], np.array([-3, len(vocab) + 5], np.int32), ids_all[9]])      # two ids outside the vocabulary
+    dbuf = np.zeros(4096, np.uint8)
+    dn = ref.ref_tokenizer_decode(vblob, len(vocab), p(dec_ids), len(dec_ids), p(dbuf), len(dbuf))
+    assert dn >= 0
+    out.update({"tok_vocab_blob": np.frombuffer(vblob, np.uint8), "tok_vocab_n": np.array([len(vocab)], np.int32),
+                "tok_merges_blob": np.frombuffer(mblob, np.uint8), "tok_merges_n": np.array([len(merges)], np.int32),
+                "tok_texts_blob": np.frombuffer(b"".join(x + b"\0" for x in texts), np.uint8),
+                "tok_ids": np.concatenate(ids_all), "tok_counts": np.array(counts, np.int32), "tok_unk": np.array(unks, np.int32),
+                "tok_decode_ids": dec_ids, "tok_decode_text": dbuf[:dn].copy()})
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 

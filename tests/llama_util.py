@@ -7,7 +7,7 @@ import numpy as np
 TINY = dict(vocab=256, hidden=256, inter=512, layers=2, heads=4, kv_heads=2, max_seq=96)
 
 
-def build(entry, rng, cfg, path, qtype=2, wscale=0.05):
+def build(entry, rng, cfg, path, qtype=2, wscale=0.05, metadata=None):
     synth, ob = entry.load_synth(), entry.load_oracle_binding()
     orc = ob.load_orc()
 
@@ -20,7 +20,7 @@ def build(entry, rng, cfg, path, qtype=2, wscale=0.05):
         return blocks
 
     tensors, store = synth.make_llama(rng, cfg, quantize, qtype, wscale)
-    synth.write_gguf(path, tensors)
+    synth.write_gguf(path, tensors, metadata=metadata)
     return store
 
 

@@ -316,9 +316,76 @@ def test_generate_with_a_caller_supplied_tokenizer(pkg, tiny, torch_dev):
         lib.cml_generation_result_free(res)
         m.contents.tokenizer = None
     finally:
+        m.contents.tokenizer = None                                           # the stand-in handle is not the model's to free
         lib.cml_llama_set_tokenizer_functions(ENC(0), DEC(0))
         lib.cml_llama_free(m)
         lib.cml_llama_free(m2)
+
+
+def test_generate_from_a_gguf_file_with_its_own_tokenizer(pkg, tmp_path, torch_dev):
+    """A GGUF file carrying hyper-parameters, a token list and merges: cml_llama_config_from_gguf sizes
+    the model, cml_llama_load_gguf_tokenizer builds model->tokenizer, and cml_llama_generate runs on the
+    library's own byte-level BPE: prompt ids = cml_tokenizer_encode, continuation = step-by-step greedy
+    forward, text = cml_tokenizer_decode of all ids."""
+    lib = pkg.lib
+    cfg = TINY
+    singles = [bytes([c]) for c in range(32, 127)]
+    merged = [b"th", b"he", b"the", b"the ", b" b", b"20", b"200"]
+    vocab = singles + merged + [b"<%d>" % i for i in range(cfg["vocab"] - len(singles) - len(merged))]
+    meta = [("llama.block_count", 4, cfg["layers"]), ("llama.embedding_length", 4, cfg["hidden"]),
+            ("llama.feed_forward_length", 4, cfg["inter"]), ("llama.attention.head_count", 4, cfg["heads"]),
+            ("llama.attention.head_count_kv", 4, cfg["kv_heads"]), ("llama.context_length", 4, cfg["max_seq"]),
+            ("llama.rope.freq_base", 6, 10000.0), ("llama.attention.layer_norm_rms_epsilon", 6, 1e-5),
+            ("tokenizer.ggml.tokens", 9, (8, vocab)),
+            ("tokenizer.ggml.merges", 9, (8, [b"t h", b"h e", b"th e", b"the  ", b"  b", b"2 0", b"20 0"])),
+            ("tokenizer.ggml.unknown_token_id", 4, 31)]
+    path = tmp_path / "with_tokenizer.gguf"
+    build(entry, np.random.default_rng(77), cfg, path, metadata=meta)
+    c = pkg.LlamaConfig()
+    assert lib.cml_llama_config_from_gguf(str(path).encode(), C.byref(c)) == 0
+    assert (c.vocab_size, c.hidden_size, c.intermediate_size, c.num_layers, c.num_heads, c.num_kv_heads, c.max_seq_len) == \
+        (cfg["vocab"], cfg["hidden"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv_heads"], cfg["max_seq"])
+
+    class Result(C.Structure):
+        _fields_ = [("token_ids", C.POINTER(C.c_int)), ("num_tokens", C.c_int), ("text", C.c_char_p),
+                    ("total_time_ms", C.c_float), ("tokens_per_second", C.c_float)]
+
+    models = []
+    try:
+        for _ in range(2):
+            m = lib.cml_llama_create(C.byref(c))
+            assert m and lib.cml_llama_load_gguf(m, str(path).encode()) == 0
+            models.append(m)
+        m, m2 = models
+        assert lib.cml_llama_load_gguf_tokenizer(m, str(path).encode()) == 0
+        assert lib.cml_llama_load_gguf_tokenizer(m, str(path).encode()) == 0          # replacing frees the first
+        tok = C.cast(m.contents.tokenizer, pkg.TKP)
+        prompt = b"the b200 then"
+        n = C.c_int(0)
+        ids_p = lib.cml_tokenizer_encode(tok, prompt, C.byref(n))
+        want_prompt = [ids_p[i] for i in range(n.value)]
+        C.CDLL(None).free(C.cast(ids_p, C.c_void_p))
+        assert want_prompt == [vocab.index(b"the "), vocab.index(b"b"), vocab.index(b"200"), vocab.index(b" "), vocab.index(b"the"), vocab.index(b"n")]
+        gen = lib.cml_generation_default_config()
+        gen.do_sample, gen.max_new_tokens, gen.eos_token_id = False, 5, -1
+        res = lib.cml_llama_generate(m, prompt, C.byref(gen))
+        assert res
+        r = C.cast(res, C.POINTER(Result)).contents
+        ids = [r.token_ids[i] for i in range(r.num_tokens)]
+        assert ids[:len(want_prompt)] == want_prompt and len(ids) == len(want_prompt) + 5
+        want, toks = [], np.array(want_prompt, np.int32)
+        for _ in range(5):
+            t = lib.cml_llama_forward(m2, pkg.np_ptr(toks), len(toks))
+            nxt = lib.cml_llama_sample_token(t, C.byref(gen))
+            lib.tensor_free(t)
+            want.append(nxt)
+            toks = np.array([nxt], np.int32)
+        assert ids[len(want_prompt):] == want
+        assert r.text == b"".join(vocab[i] for i in ids)
+        lib.cml_generation_result_free(res)
+    finally:
+        for m in models:
+            lib.cml_llama_free(m)                                                  # releases the tokenizer with the model
 
 
 @pytest.mark.parametrize("gtype", [3, 12, 13, 14])
