@@ -94,16 +94,19 @@ tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial
 //   3. it waits for flag B of all peers and adds their summed slices onto h.
 // Each slice is summed by one rank, in rank order, so all ranks end with bit-identical h. A rank
 // sends 2 (tp - 1) / tp of the message over NVLink instead of tp - 1 times the message.
-// Element i of a slice belongs to CTA (i / 256) % kBulkCtas on every rank, so CTA c only ever
-// depends on CTA c of its peers; the inboxes alternate with the parity of the sequence number as
-// above. The workspace is a second allocation with its own header:
-//   +64 u32 status   +1024 u32 seq[64]   +4096 u32 flagA[8][64]   +8192 u32 flagB[8][64]
+// Element i of a slice belongs to CTA (i / 256) % gridDim.x on every rank (all ranks launch the same
+// number of CTAs), so CTA c only ever depends on CTA c of its peers; the inboxes alternate with the
+// parity of the sequence number as above. Every loop first loads several independent 16-byte
+// pieces and then stores them: the copies are bound by how many loads are in flight, not by
+// arithmetic. The workspace is a second allocation with its own header:
+//   +64 u32 status   +1024 u32 seq[128]   +4096 u32 flagA[8][128]   +8192 u32 flagB[8][128]
 //   +16384 float4 inbox[A|B][parity][from < tp][region4]
 // With EMU the ranks are blockIdx.y of ONE cooperative launch over buffers of one GPU: the way to
 // exercise the protocol where only one device is at hand (launches that wait on one another must
 // not be separate launches on the same GPU).
-constexpr int kBulkCtas = 64;
+constexpr int kBulkCtas = 128;           // flag words per rank and flag kind; a launch uses at most this many CTAs
 constexpr int kBulkThreads = 256;
+constexpr int kBulkUnroll = 4;
 struct BulkArgs {
     uint8_t* ws[MAX_TP];
     float* h[MAX_TP];               // [0] only, unless emulating
@@ -142,9 +145,10 @@ tp_allreduce_bulk_kernel(BulkArgs a) {
     const uint32_t seq = bulk_seq(mine)[c] + 1;
     const int parity = (int)(seq & 1u);
     const int per = (a.n4 + tp - 1) / tp;                      // float4 per slice
-    const float4* src = reinterpret_cast<const float4*>(a.partial[EMU ? rank : 0]);
-    float4* h4 = reinterpret_cast<float4*>(a.h[EMU ? rank : 0]);
-    constexpr int STEP = kBulkCtas * kBulkThreads;
+    const float4* __restrict__ src = reinterpret_cast<const float4*>(a.partial[EMU ? rank : 0]);
+    float4* __restrict__ h4 = reinterpret_cast<float4*>(a.h[EMU ? rank : 0]);
+    const int step = (int)gridDim.x * kBulkThreads;
+    constexpr int U = kBulkUnroll;
     __shared__ int ok;
     if (t == 0) ok = 1;
 
@@ -152,8 +156,14 @@ tp_allreduce_bulk_kernel(BulkArgs a) {
     for (int d = 1; d < tp; d++) {
         const int q = (rank + d) % tp;
         const int lo = min(a.n4, q * per), len = min(a.n4, lo + per) - lo;
-        float4* dst = bulk_inbox(a.ws[q], 0, parity, rank, tp, a.region4);
-        for (int i = c * kBulkThreads + t; i < len; i += STEP) dst[i] = src[lo + i];
+        float4* __restrict__ dst = bulk_inbox(a.ws[q], 0, parity, rank, tp, a.region4);
+        for (int i = c * kBulkThreads + t; i < len; i += step * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * step < len) v[u] = src[lo + i + u * step];
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * step < len) dst[i + u * step] = v[u];
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -163,13 +173,27 @@ tp_allreduce_bulk_kernel(BulkArgs a) {
     const bool got_a = bulk_wait(mine, 0, tp, rank, c, seq, a.spin_limit, &ok);
     if (got_a) {
         const int lo = min(a.n4, rank * per), len = min(a.n4, lo + per) - lo;
-        for (int i = c * kBulkThreads + t; i < len; i += STEP) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int q = 0; q < tp; q++) add4(acc, q == rank ? src[lo + i] : __ldcg(bulk_inbox(mine, 0, parity, q, tp, a.region4) + i));
-            for (int d = 1; d < tp; d++) bulk_inbox(a.ws[(rank + d) % tp], 1, parity, rank, tp, a.region4)[i] = acc;
-            float4 o = h4[lo + i];
-            add4(o, acc);
-            h4[lo + i] = o;
+        for (int i = c * kBulkThreads + t; i < len; i += step * U) {
+            float4 acc[U], o[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < tp; q++) {
+                const float4* __restrict__ in = q == rank ? src + lo : bulk_inbox(mine, 0, parity, q, tp, a.region4);
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) if (i + u * step < len) v[u] = __ldcg(in + i + u * step);
+#pragma unroll
+                for (int u = 0; u < U; u++) if (i + u * step < len) add4(acc[u], v[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * step < len) o[u] = h4[lo + i + u * step];
+            for (int d = 1; d < tp; d++) {
+                float4* __restrict__ dst = bulk_inbox(a.ws[(rank + d) % tp], 1, parity, rank, tp, a.region4);
+#pragma unroll
+                for (int u = 0; u < U; u++) if (i + u * step < len) dst[i + u * step] = acc[u];
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * step < len) { add4(o[u], acc[u]); h4[lo + i + u * step] = o[u]; }
         }
     }
     __threadfence_system();
@@ -183,11 +207,13 @@ tp_allreduce_bulk_kernel(BulkArgs a) {
         for (int d = 1; d < tp; d++) {
             const int q = (rank + d) % tp;
             const int lo = min(a.n4, q * per), len = min(a.n4, lo + per) - lo;
-            const float4* in = bulk_inbox(mine, 1, parity, q, tp, a.region4);
-            for (int i = c * kBulkThreads + t; i < len; i += STEP) {
-                float4 o = h4[lo + i];
-                add4(o, __ldcg(in + i));
-                h4[lo + i] = o;
+            const float4* __restrict__ in = bulk_inbox(mine, 1, parity, q, tp, a.region4);
+            for (int i = c * kBulkThreads + t; i < len; i += step * U) {
+                float4 v[U], o[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) if (i + u * step < len) { v[u] = __ldcg(in + i + u * step); o[u] = h4[lo + i + u * step]; }
+#pragma unroll
+                for (int u = 0; u < U; u++) if (i + u * step < len) { add4(o[u], v[u]); h4[lo + i + u * step] = o[u]; }
             }
         }
     }
@@ -233,7 +259,7 @@ extern "C" int cmlb200_tp_allreduce_bulk_add(float* d_h, const float* d_partial,
     a.h[0] = d_h;
     a.partial[0] = d_partial;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kBulkCtas);
+    cfg.gridDim = dim3(cmlb_num_sms() < kBulkCtas ? cmlb_num_sms() : kBulkCtas);      // the same on every rank of one box
     cfg.blockDim = dim3(kBulkThreads);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
@@ -261,9 +287,11 @@ extern "C" int cmlb200_tp_allreduce_bulk_emulate(float* const* d_h, const float*
     }
     int per_sm = 0;
     CMLB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_allreduce_bulk_kernel<true>, kBulkThreads, 0));
-    CMLB_REQUIRE(per_sm * cmlb_num_sms() >= kBulkCtas * tp, "cmlb200_tp_allreduce_bulk_emulate: %d CTAs do not fit on the device at once", kBulkCtas * tp);
+    int ctas = per_sm * cmlb_num_sms() / tp;             // per rank, as many as stay resident together
+    if (ctas > kBulkCtas) ctas = kBulkCtas;
+    CMLB_REQUIRE(ctas >= 1, "cmlb200_tp_allreduce_bulk_emulate: %d ranks do not fit on the device at once", tp);
     void* args[] = {&a};
-    CMLB_CUDA(cudaLaunchCooperativeKernel((const void*)tp_allreduce_bulk_kernel<true>, dim3(kBulkCtas, tp), dim3(kBulkThreads), args, 0, as_stream(stream)));
+    CMLB_CUDA(cudaLaunchCooperativeKernel((const void*)tp_allreduce_bulk_kernel<true>, dim3(ctas, tp), dim3(kBulkThreads), args, 0, as_stream(stream)));
     return CMLB200_OK;
 }
 
