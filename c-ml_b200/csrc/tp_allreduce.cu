@@ -41,13 +41,21 @@ tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial
     // slice of this CTA, in float4
     const int per = (n4 + CTAS - 1) / CTAS;
     const int lo = min(n4, c * per), hi = min(n4, lo + per);
-    const float4* src = reinterpret_cast<const float4*>(partial);
+    const float4* __restrict__ src = reinterpret_cast<const float4*>(partial);
+    constexpr int U = 4;                     // independent 16-byte pieces in flight per thread
+    const int bs = blockDim.x;
 
     // 1. push
     for (int q = 0; q < tp; q++) {
         if (q == rank) continue;
-        float4* dst = reinterpret_cast<float4*>(tpws_inbox(peers.ws[q], 0, parity, rank, max_floats));
-        for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+        float4* __restrict__ dst = reinterpret_cast<float4*>(tpws_inbox(peers.ws[q], 0, parity, rank, max_floats));
+        for (int i = lo + (int)threadIdx.x; i < hi; i += bs * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * bs < hi) v[u] = src[i + u * bs];
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * bs < hi) dst[i + u * bs] = v[u];
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -68,16 +76,29 @@ tp_allreduce_add_kernel(float* __restrict__ h, const float* __restrict__ partial
     if (!ok) return;
 
     // 3. sum in rank order onto h
-    float4* out = reinterpret_cast<float4*>(h);
-    for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q = 0; q < tp; q++) {
-            const float4 v = (q == rank) ? src[i] : reinterpret_cast<const float4*>(tpws_inbox(mine, 0, parity, q, max_floats))[i];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    float4* __restrict__ out = reinterpret_cast<float4*>(h);
+    for (int i = lo + (int)threadIdx.x; i < hi; i += bs * U) {
+        float4 acc[U], o[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i + u * bs < hi) o[u] = out[i + u * bs];
         }
-        float4 o = out[i];
-        o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
-        out[i] = o;
+        for (int q = 0; q < tp; q++) {
+            const float4* __restrict__ in = (q == rank) ? src : reinterpret_cast<const float4*>(tpws_inbox(mine, 0, parity, q, max_floats));
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) if (i + u * bs < hi) v[u] = in[i + u * bs];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (i + u * bs < hi) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (i + u * bs < hi) {
+                o[u].x += acc[u].x; o[u].y += acc[u].y; o[u].z += acc[u].z; o[u].w += acc[u].w;
+                out[i + u * bs] = o[u];
+            }
     }
 }
 

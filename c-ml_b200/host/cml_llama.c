@@ -52,6 +52,7 @@ typedef struct DevModel {
     int arb_ok;
     float arb_ms[2];                       /* start-up timing of one sum: peer memory, ncclAllReduce + add */
     size_t arb_probe_floats;
+    float* lineup;                         /* 4 zero floats for tp_line_up */
     int generic_w;                         /* some projection is Q4_1 / Q4_K / Q5_K / Q6_K: fp32 row-block path for every call */
     int hd, heads_l, kvh_l, qw_l, kvw_l, inter_l;
     DevLayer* L;
@@ -164,6 +165,7 @@ static void dm_destroy(DevModel* d) {
         if (r == d->rank) cmlb200_free(d->ar_ws[r]);
         else cmlb200_ipc_close(d->ar_ws[r]);
     }
+    cmlb200_free(d->lineup);
     if (d->comm) cml_nccl_destroy(d->comm);
     if (d->stream) cmlb200_stream_destroy(d->stream);
     free(d);
@@ -366,6 +368,7 @@ int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     if (cml_nccl_init(&d->comm, d->tp, d->rank, id128)) return -1;
     const char* only = getenv("CML_B200_TP_NCCL_ONLY");
     if (only && only[0] == '1') return 0;
+    if (cmlb200_malloc((void**)&d->lineup, 16) || cmlb200_memset(d->lineup, 0, 16, NULL) || cmlb200_device_sync()) { d->lineup = NULL; return 0; }
     if (tp_peer_setup(d)) { LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size"); return 0; }
     tp_bulk_setup(d);
     return 0;
@@ -973,6 +976,16 @@ static int enqueue_forward(DevModel* d, int rows, int mode, int seq, int plan_li
     return enqueue_forward_ex(d, rows, mode, seq, plan_limit, -1, 1);
 }
 
+/* The peer-memory all-reduces wait for a peer for a bounded time (seconds, then a status word and a
+ * failed call). Ranks may reach a call further apart than that: one is still reading its weights,
+ * or was descheduled. A 4-byte ncclAllReduce at the head of every call lines the ranks' streams
+ * up first (NCCL waits without a limit); inside a call the ranks then stay within a kernel's
+ * length of one another. */
+static int tp_line_up(DevModel* d) {
+    if (d->tp <= 1 || !d->comm || !d->lineup || !(d->ar_ok || d->arb_ok)) return 0;
+    return cml_nccl_allreduce_sum_f32(d->comm, d->lineup, 4, d->stream);
+}
+
 /* One forward call. with_logits: the fp32 logits of every row come back as a host tensor (what
  * C-ML's forward returns); without, the head is skipped and a 1 x 1 placeholder is returned. */
 static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows, int mode, int seq, int with_logits, const char* who) {
@@ -994,7 +1007,7 @@ static Tensor* run_forward(CMLLLaMAModel* model, const int* token_ids, int rows,
     int shape[2] = {with_logits ? rows : 1, with_logits ? c->vocab_size : 1};
     Tensor* out = cml_tensor_alloc(DTYPE_FLOAT32, shape, 2, !with_logits);
     if (!out) return NULL;
-    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_tokens, token_ids, (size_t)rows * 4, d->stream), who) ||
+    if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_tokens, token_ids, (size_t)rows * 4, d->stream), who) || tp_line_up(d) ||
         enqueue_forward_ex(d, rows, mode, seq, max_pos - 1, -1, with_logits) ||
         (with_logits && CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->logits, (size_t)rows * c->vocab_size * 4, d->stream), who)) ||
         CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) {
@@ -1064,6 +1077,7 @@ int cml_llama_decode_greedy(CMLLLaMAModel* model, const int* first_tokens, int b
     int plan_limit = splits * ATT_CHUNK - 1;
     if (plan_limit > c->max_seq_len - 1) plan_limit = c->max_seq_len - 1;
     void *e0 = NULL, *e1 = NULL;
+    if (tp_line_up(d)) return -1;
     DEV(cmlb200_event_create(&e0));
     DEV(cmlb200_event_create(&e1));
     DEV(cmlb200_event_record(e0, st));
@@ -1246,7 +1260,7 @@ Tensor* cml_llama_layer_forward(CMLLLaMAModel* model, CMLLLaMALayer* layer, Tens
     int ok = !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->h, hidden->data, bytes, d->stream), who) &&
              !CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &start_pos, sizeof(int), d->stream), who) &&
              !CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who) &&          /* start_pos is a stack variable */
-             !enqueue_forward_ex(d, rows, 0, 0, start_pos + rows - 1, li, 0) &&
+             !tp_line_up(d) && !enqueue_forward_ex(d, rows, 0, 0, start_pos + rows - 1, li, 0) &&
              !CML_DEV_FAIL(cmlb200_memcpy_d2h(out->data, d->h, bytes, d->stream), who);
     /* put the model's own position back whatever happened */
     if (CML_DEV_FAIL(cmlb200_memcpy_h2d(d->d_cur, &saved, sizeof(int), d->stream), who) || CML_DEV_FAIL(cmlb200_stream_sync(d->stream), who)) ok = 0;

@@ -67,6 +67,10 @@ oracle = llama_util.OracleLlama(entry, cfg, store, rope_all_heads=1, mask_absolu
 rng = np.random.default_rng(6)
 prompt = rng.integers(0, cfg["vocab"], 9).astype(np.int32)
 worst = 0.0
+late = case == "tiny" and os.environ.get("CML_B200_TP_NCCL_ONLY") != "1"
+if late and rank == tp - 1:
+    import time
+    time.sleep(6.0)        # longer than the peer kernels' bounded waits: the ranks must line up at the head of the call
 for toks in (prompt, np.array([7], np.int32), np.array([11], np.int32)):     # a 9-token call, then two cached single-token calls
     got = llama_util.dev_forward(pkg, m, toks)
     want = oracle.forward(toks)
@@ -103,6 +107,9 @@ same_on_all_ranks(o_tp, "the greedy tokens")
 # (CML_B200_TP_BULK=1) or by ncclAllReduce (CML_B200_TP_NCCL_ONLY=1)
 pkg.lib.cml_llama_reset(m)
 long = rng.integers(0, cfg["vocab"], 40).astype(np.int32)
+if late and rank == 0:
+    import time
+    time.sleep(6.0)        # the same for the prompt-sized form, with the other rank late
 got = llama_util.dev_forward(pkg, m, long)
 oracle2 = llama_util.OracleLlama(entry, cfg, store, rope_all_heads=1, mask_absolute=1)
 want = oracle2.forward(long)
