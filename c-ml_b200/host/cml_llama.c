@@ -306,23 +306,25 @@ static void tp_bulk_setup(DevModel* d) {
     if (tp_map_workspaces(d, cmlb200_tp_ar_bulk_workspace_bytes(d->arb_max_floats, d->tp), d->arb_ws)) return;
     const size_t n = d->arb_max_floats < ((size_t)4 << 20) ? d->arb_max_floats : ((size_t)4 << 20);
     float *hp = malloc(n * 4), *dh = NULL, *dp = NULL;
+    float ms_bulk = 0.f, ms_nccl = 0.f, worst_bulk = 0.f, worst_nccl = 0.f;
+    const float tri = (float)(d->tp * (d->tp + 1) / 2);
+    unsigned char mine[64] = {0}, all[8 * 64];
+    double t0 = 0.0;
+    int st = 0;
     int good = hp && !cmlb200_malloc((void**)&dh, n * 4) && !cmlb200_malloc((void**)&dp, n * 4);
     if (!tp_all_agree(d, good)) goto done;
     /* (b) exactness: partial = (i mod 251) * (rank + 1) on zeros -> (i mod 251) * tp (tp + 1) / 2 */
-    int st = 0;
     for (size_t i = 0; i < n; i++) hp[i] = (float)((i % 251) * (size_t)(d->rank + 1));
     good = !cmlb200_memcpy_h2d(dp, hp, n * 4, NULL) && !cmlb200_memset(dh, 0, n * 4, NULL) && !cmlb200_device_sync() &&
            !cmlb200_tp_allreduce_bulk_add(dh, dp, n, d->tp, d->rank, d->arb_ws, d->arb_max_floats, NULL) && !cmlb200_device_sync() &&
            !cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) && st == 0 && !cmlb200_memcpy_d2h(hp, dh, n * 4, NULL) && !cmlb200_device_sync();
-    const float tri = (float)(d->tp * (d->tp + 1) / 2);
     for (size_t i = 0; good && i < n; i++) good = hp[i] == (float)(i % 251) * tri;
     if (!tp_all_agree(d, good)) {
         LOG_WARNING("cml_llama_tp_init: the peer-memory all-reduce for prompts failed its start-up check%s; NCCL serves prompts", good ? " on another rank" : "");
         goto done;
     }
     /* (c) the clock: 4 sums of n values each way */
-    float ms_bulk, ms_nccl;
-    double t0 = now_ms();
+    t0 = now_ms();
     for (int k = 0; k < 4; k++) cmlb200_tp_allreduce_bulk_add(dh, dp, n, d->tp, d->rank, d->arb_ws, d->arb_max_floats, NULL);
     cmlb200_device_sync();
     ms_bulk = (float)(now_ms() - t0);
@@ -332,19 +334,21 @@ static void tp_bulk_setup(DevModel* d) {
     for (int k = 0; k < 4; k++) { cml_nccl_allreduce_sum_f32(d->comm, dp, n, NULL); cmlb200_add_f32(dh, dp, n, NULL); }
     cmlb200_device_sync();
     ms_nccl = (float)(now_ms() - t0);
-    unsigned char mine[64] = {0}, all[8 * 64];
+    st = 0;
+    good = !cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) && st == 0;      /* no wait expired while timing */
     memcpy(mine, &ms_bulk, 4);
     memcpy(mine + 4, &ms_nccl, 4);
-    st = 0;
-    if (tp_gather64(d, mine, all) || cmlb200_tp_ar_status(d->arb_ws[d->rank], &st) || st) goto done;
-    float worst_bulk = 0.f, worst_nccl = 0.f;
-    for (int r = 0; r < d->tp; r++) {
+    mine[8] = good ? 1 : 0;
+    if (tp_gather64(d, mine, all)) goto done;
+    for (int r = 0; r < d->tp; r++) {                 /* the same records, hence the same decision, on every rank */
         float b, c;
         memcpy(&b, all + 64 * r, 4);
         memcpy(&c, all + 64 * r + 4, 4);
         if (b > worst_bulk) worst_bulk = b;
         if (c > worst_nccl) worst_nccl = c;
+        if (!all[64 * r + 8]) good = 0;
     }
+    if (!good) goto done;
     d->arb_ok = (env && env[0] == '1') || worst_bulk < worst_nccl;
     d->arb_ms[0] = worst_bulk / 4;
     d->arb_ms[1] = worst_nccl / 4;
