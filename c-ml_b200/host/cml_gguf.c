@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/stat.h>
 
 #include "cml_internal.h"
 
@@ -92,15 +93,27 @@ static char* read_string(FILE* f) {
     return s;
 }
 
+/* Bytes between the read position and the end of the file. Counts read from the file are checked
+ * against it before anything is allocated or looped over: `count` items of at least `each` bytes. */
+static uint64_t bytes_left(FILE* f) {
+    struct stat sb;
+    const long pos = ftell(f);
+    if (pos < 0 || fstat(fileno(f), &sb) != 0 || sb.st_size < pos) return 0;
+    return (uint64_t)(sb.st_size - pos);
+}
+static int fits(FILE* f, uint64_t count, uint64_t each) { return count <= bytes_left(f) / each; }
+
 static int skip_value(FILE* f, uint32_t type) {
     static const int sizes[] = {1, 1, 2, 2, 4, 4, 4, 1, -1, -2, 8, 8, 8};
     if (type > 12) return -1;
     const int sz = sizes[type];
-    if (sz > 0) return fseek(f, sz, SEEK_CUR);
+    if (sz > 0) return fits(f, 1, (uint64_t)sz) ? fseek(f, sz, SEEK_CUR) : -1;
     if (sz == -1) { char* s = read_string(f); if (!s) return -1; free(s); return 0; }
     uint32_t et;
     uint64_t n;
-    if (fread(&et, 4, 1, f) != 1 || fread(&n, 8, 1, f) != 1) return -1;
+    if (fread(&et, 4, 1, f) != 1 || fread(&n, 8, 1, f) != 1 || et > 12) return -1;
+    if (sizes[et] > 0) return fits(f, n, (uint64_t)sizes[et]) ? fseek(f, (long)(n * (uint64_t)sizes[et]), SEEK_CUR) : -1;
+    if (!fits(f, n, sizes[et] == -1 ? 8 : 12)) return -1;           /* a string is at least its length field, an array its header */
     for (uint64_t i = 0; i < n; i++) if (skip_value(f, et)) return -1;
     return 0;
 }
@@ -127,18 +140,19 @@ static int read_meta_value(FILE* f, GGUFMeta* m) {
     if (fread(&m->elem_type, 4, 1, f) != 1 || fread(&m->count, 8, 1, f) != 1 || m->elem_type > 12) return -1;
     const int esz = kMetaSize[m->elem_type];
     if (esz > 0) {
-        if (m->count > ((uint64_t)1 << 28)) return -1;
+        if (!fits(f, m->count, (uint64_t)esz)) return -1;
         m->data = malloc(m->count ? (size_t)m->count * (size_t)esz : 1);
         return m->data && fread(m->data, (size_t)esz, (size_t)m->count, f) == m->count ? 0 : -1;
     }
     if (esz == -1) {
-        if (m->count > ((uint64_t)1 << 28)) return -1;
+        if (!fits(f, m->count, 8)) return -1;
         m->strs = (char**)calloc(m->count ? (size_t)m->count : 1, sizeof(char*));
         if (!m->strs) return -1;
         for (uint64_t i = 0; i < m->count; i++)
             if (!(m->strs[i] = read_string(f))) { m->count = i; return -1; }
         return 0;
     }
+    if (!fits(f, m->count, 12)) return -1;
     for (uint64_t i = 0; i < m->count; i++)
         if (skip_value(f, 9)) return -1;
     return 0;
@@ -176,7 +190,12 @@ GGUFContext* gguf_open_read(const char* filepath) {
     GGUFContext* ctx = (GGUFContext*)calloc(1, sizeof *ctx);
     if (!ctx) { fclose(f); return NULL; }
     ctx->file = f;
-    if (nkv > (1u << 24) || !(ctx->meta = (GGUFMeta*)calloc(nkv ? (size_t)nkv : 1, sizeof(GGUFMeta)))) { gguf_close(ctx); return NULL; }
+    /* an entry is at least a key length, a type and one byte; a tensor info a name length, ndim, type and offset */
+    if (!fits(f, nkv, 13) || !fits(f, nt, 24) || !(ctx->meta = (GGUFMeta*)calloc(nkv ? (size_t)nkv : 1, sizeof(GGUFMeta)))) {
+        LOG_ERROR("gguf_open_read: the header counts (%llu key/values, %llu tensors) exceed the file", (unsigned long long)nkv, (unsigned long long)nt);
+        gguf_close(ctx);
+        return NULL;
+    }
     for (uint64_t i = 0; i < nkv; i++) {
         GGUFMeta* m = &ctx->meta[i];
         ctx->num_meta = (int)i + 1;

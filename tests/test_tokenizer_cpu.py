@@ -217,3 +217,55 @@ def test_gguf_metadata_tokenizer_and_config(pkg, tmp_path):
     cut = tmp_path / "cut.gguf"
     cut.write_bytes(raw[:200])
     assert not lib.gguf_open_read(str(cut).encode())
+
+
+def test_gguf_reader_survives_truncated_and_mutated_files(pkg, tmp_path):
+    """Every truncation of a small GGUF file and 1,500 random byte mutations of it: the reader either
+    refuses the file or returns a context that can be queried, turned into a tokenizer and closed.
+    Counts taken from the file are checked against the bytes left before anything is allocated or
+    looped over (a mutated array length used to make the value skipper seek 2^60 times)."""
+    synth = entry.load_synth()
+    lib = pkg.lib
+    vocab = [b"<unk>", b"a", b"b", b"ab"]
+    meta = [("llama.block_count", 4, 3), ("general.name", 8, "tiny"), ("tokenizer.ggml.tokens", 9, (8, vocab)),
+            ("tokenizer.ggml.token_type", 9, (5, [1, 2, 3, 4])), ("tokenizer.ggml.merges", 9, (8, [b"a b"])),
+            ("nested", 9, (9, [(4, [1, 2]), (8, [b"x"])])), ("f", 12, 2.5)]
+    path = tmp_path / "m.gguf"
+    synth.write_gguf(str(path), [("token_embd.weight", (4, 8), 0, np.zeros((4, 8), np.float32).tobytes())], metadata=meta)
+    raw = path.read_bytes()
+    cut = tmp_path / "c.gguf"
+    lib.cml_set_log_level.argtypes = [C.c_int]
+    lib.cml_set_log_level(5)                                        # the refusals are expected: keep them off the log
+
+    def probe(data):
+        cut.write_bytes(data)
+        g = lib.gguf_open_read(str(cut).encode())
+        if not g:
+            return 0
+        for i in range(lib.gguf_get_num_metadata(g)):
+            key = lib.gguf_get_metadata_key(g, i)
+            assert key is not None
+            lib.gguf_get_metadata_type(g, key)
+            lib.gguf_get_metadata_array_length(g, key, None)
+        tok = lib.gguf_create_tokenizer(g)
+        if tok:
+            n = C.c_int(0)
+            ids = lib.cml_tokenizer_encode(tok, b"abab", C.byref(n))
+            if ids:
+                libc.free(C.cast(ids, C.c_void_p))
+            lib.cml_tokenizer_free(tok)
+        lib.gguf_close(g)
+        lib.cml_llama_config_from_gguf(str(cut).encode(), C.byref(pkg.LlamaConfig()))
+        return 1
+    try:
+        opened = sum(probe(raw[:k]) for k in range(len(raw)))
+        assert 0 < opened < len(raw)                                # cuts inside the tensor data still open, cuts before it do not
+        rng = np.random.default_rng(0)
+        for _ in range(1500):
+            b = bytearray(raw)
+            for _ in range(int(rng.integers(1, 4))):
+                b[int(rng.integers(0, len(b) - 130))] = int(rng.integers(0, 256))
+            probe(bytes(b))
+        assert probe(raw) == 1
+    finally:
+        lib.cml_set_log_level(3)
