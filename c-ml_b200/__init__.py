@@ -379,6 +379,29 @@ _sig("gguf_get_metadata_array_data", vp, vp, C.c_char_p)
 _sig("gguf_create_tokenizer", TKP, vp)
 _sig("cml_llama_config_from_gguf", ci, C.c_char_p, C.POINTER(LlamaConfig))
 _sig("cml_llama_load_gguf_tokenizer", ci, MP, C.c_char_p)
+class LoRALinear(C.Structure):
+    _fields_ = [("in_features", C.c_int), ("out_features", C.c_int), ("rank", C.c_int), ("alpha", C.c_float), ("scaling", C.c_float),
+                ("base_weight", C.POINTER(Tensor)), ("lora_A", C.POINTER(Tensor)), ("lora_B", C.POINTER(Tensor)),
+                ("frozen_base", C.POINTER(Tensor)), ("merged", C.c_bool)]
+
+
+class LoRAAdapter(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("rank", C.c_int), ("alpha", C.c_float), ("scaling", C.c_float), ("num_layers", C.c_int),
+                ("layers", C.POINTER(C.POINTER(LoRALinear))), ("merged", C.c_bool)]
+
+
+LP, AP = C.POINTER(LoRALinear), C.POINTER(LoRAAdapter)
+_sig("cml_lora_linear_create", LP, TP, ci, C.c_float)
+_sig("cml_lora_linear_free", None, LP)
+_sig("cml_lora_linear_forward", TP, LP, TP)
+_sig("cml_lora_linear_merge", ci, LP)
+_sig("cml_lora_linear_unmerge", ci, LP)
+_sig("cml_lora_adapter_create", AP, C.c_char_p, ci, C.c_float)
+_sig("cml_lora_adapter_free", None, AP)
+_sig("cml_lora_adapter_add_layer", ci, AP, LP)
+_sig("cml_lora_adapter_merge_all", ci, AP)
+_sig("cml_lora_adapter_unmerge_all", ci, AP)
+_sig("cmlb200_lora_merge", ci, vp, vp, vp, ci, ci, ci, C.c_float, vp)
 _sig("cml_init", ci)
 _sig("cml_cleanup", ci)
 _sig("tensor_manual_seed", None, C.c_uint64)

@@ -700,6 +700,19 @@ __global__ void lora_up_kernel(const float* __restrict__ t, const float* __restr
     y[(size_t)b * N + o] += scaling * s;
 }
 
+// Merging a LoRA pair into an fp32 weight (src/nn/lora.c:263-273): W[o][i] += scaling * sum_r B[o][r] * A[r][i],
+// one thread per weight, r ascending as in C-ML's loop.
+__global__ void lora_merge_kernel(float* __restrict__ W, const float* __restrict__ A, const float* __restrict__ B, int out_f, int in_f,
+                                  int rank, float scaling) {
+    const size_t n = (size_t)out_f * in_f, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
+        const size_t o = e / in_f, i = e % in_f;
+        float s = 0.f;
+        for (int r = 0; r < rank; r++) s = fmaf(B[o * rank + r], A[(size_t)r * in_f + i], s);
+        W[e] = fmaf(scaling, s, W[e]);
+    }
+}
+
 inline int ew_grid(size_t n) {
     size_t g = (n + 255) / 256;
     const size_t cap = (size_t)cmlb_num_sms() * 8;
@@ -972,6 +985,14 @@ extern "C" int cmlb200_swiglu_f32(const float* d_gate, const float* d_up, float*
     CMLB_LAUNCH_CHECK();
     return CMLB200_OK;
 }
+extern "C" int cmlb200_lora_merge(float* d_W, const float* d_A, const float* d_B, int out_features, int in_features, int rank, float scaling,
+                                  void* stream) {
+    CMLB_REQUIRE(d_W && d_A && d_B && out_features > 0 && in_features > 0 && rank > 0, "cmlb200_lora_merge: bad argument");
+    lora_merge_kernel<<<ew_grid((size_t)out_features * in_features), 256, 0, as_stream(stream)>>>(d_W, d_A, d_B, out_features, in_features, rank, scaling);
+    CMLB_LAUNCH_CHECK();
+    return CMLB200_OK;
+}
+
 extern "C" int cmlb200_lora_accum(const float* d_x, const float* d_A, const float* d_B, int M, int K, int N, int rank,
                                   float scaling, float* d_t, float* d_y, void* stream) {
     CMLB_REQUIRE(d_x && d_A && d_B && d_t && d_y && M > 0 && K > 0 && N > 0 && rank > 0, "cmlb200_lora_accum: bad argument");

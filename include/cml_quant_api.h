@@ -168,6 +168,43 @@ void cml_qlora_linear_invalidate(CMLQLoRALinear* qlora);      /* addition: no C-
 size_t cml_qlora_memory_usage(const CMLQLoRALinear* qlora);
 size_t cml_qlora_full_memory_usage(int in_features, int out_features);
 
+/* ---- include/nn/lora.h:16-64: LoRA over an fp32 base weight ------------------------------------
+ * y = x W^T + (alpha / rank) (x A^T) B^T. base_weight [out, in] is not owned and must outlive the
+ * layer; A [rank, in] starts from C-ML's Box-Muller recipe over rand(), B [out, rank] from zeros.
+ * forward, merge (W += scaling B A in place, a frozen copy kept) run on the device; unmerge restores
+ * the frozen copy bit for bit. An adapter owns the layers added to it. */
+typedef struct CMLLoRALinear {
+    int in_features;
+    int out_features;
+    int rank;
+    float alpha;
+    float scaling;
+    Tensor* base_weight;
+    Tensor* lora_A;
+    Tensor* lora_B;
+    Tensor* frozen_base;
+    bool merged;
+} CMLLoRALinear;
+typedef struct CMLLoRAAdapter {
+    char name[64];
+    int rank;
+    float alpha;
+    float scaling;
+    int num_layers;
+    struct CMLLoRALinear** layers;
+    bool merged;
+} CMLLoRAAdapter;
+CMLLoRALinear* cml_lora_linear_create(Tensor* base_weight, int rank, float alpha);
+void cml_lora_linear_free(CMLLoRALinear* lora);
+Tensor* cml_lora_linear_forward(CMLLoRALinear* lora, Tensor* input);
+int cml_lora_linear_merge(CMLLoRALinear* lora);
+int cml_lora_linear_unmerge(CMLLoRALinear* lora);
+CMLLoRAAdapter* cml_lora_adapter_create(const char* name, int rank, float alpha);
+void cml_lora_adapter_free(CMLLoRAAdapter* adapter);
+int cml_lora_adapter_add_layer(CMLLoRAAdapter* adapter, CMLLoRALinear* layer);
+int cml_lora_adapter_merge_all(CMLLoRAAdapter* adapter);
+int cml_lora_adapter_unmerge_all(CMLLoRAAdapter* adapter);
+
 /* ---- include/nn/llm_ops.h:13-89: KV cache, grouped-query attention, RoPE ------------------------
  * Stand-alone operators on host tensors (arithmetic on the device). A cache made by
  * cml_kv_cache_create holds two dense fp32 host tensors exactly as in C-ML; the caches inside a

@@ -302,6 +302,8 @@ int cmlb200_swiglu_f32(const float* d_gate, const float* d_up, float* d_out, siz
 /* LoRA term of the quantized Linear (src/nn/qlora.c:336-361): y[M,N] += scaling * (x.A^T).B^T
  * with A [rank,K], B [N,rank]; d_t is M*rank floats of scratch. */
 int cmlb200_lora_accum(const float* d_x, const float* d_A, const float* d_B, int M, int K, int N, int rank, float scaling, float* d_t, float* d_y, void* stream);
+/* Merging the pair into an fp32 weight (src/nn/lora.c:263-273): W[out, in] += scaling * B . A. */
+int cmlb200_lora_merge(float* d_W, const float* d_A, const float* d_B, int out_features, int in_features, int rank, float scaling, void* stream);
 
 /* ---- CUDA graph capture of a launch sequence (used for the decode step) ----------------------- */
 int cmlb200_graph_begin(void* stream);

@@ -465,3 +465,39 @@ int ref_tokenizer_decode(const char* vocab_blob, int n_vocab, const int* ids, in
     free(vocab);
     return len;
 }
+
+/* cml_lora_linear_create / forward / merge / unmerge (src/nn/lora.c:10-320). srand(seed) before the
+ * create; a_init receives the A the create drew. With a_in / b_in given the pair is replaced before
+ * the forward passes. y: forward with the pair applied on the fly; w_merged: the base weight after
+ * merge; y_merged: forward on the merged weight. Returns 0 when the unmerge restored W exactly. */
+#include "nn/lora.h"
+int ref_lora(const float* x, int M, int K, int N, const float* W, int rank, float alpha, unsigned seed, const float* a_in,
+             const float* b_in, float* a_init, float* y, float* w_merged, float* y_merged) {
+    int ws[2] = {N, K}, xs[2] = {M, K};
+    Tensor* tw = t_from(W, 2, ws);
+    Tensor* tx = t_from(x, 2, xs);
+    if (!tw || !tx) return -1;
+    srand(seed);
+    CMLLoRALinear* l = cml_lora_linear_create(tw, rank, alpha);
+    if (!l) return -1;
+    memcpy(a_init, tensor_data_ptr(l->lora_A), (size_t)rank * K * sizeof(float));
+    if (a_in) memcpy(tensor_data_ptr(l->lora_A), a_in, (size_t)rank * K * sizeof(float));
+    if (b_in) memcpy(tensor_data_ptr(l->lora_B), b_in, (size_t)N * rank * sizeof(float));
+    int rc = -1;
+    Tensor* o1 = cml_lora_linear_forward(l, tx);
+    if (o1 && cml_lora_linear_merge(l) == 0) {
+        memcpy(y, tensor_data_ptr(o1), (size_t)M * N * sizeof(float));
+        memcpy(w_merged, tensor_data_ptr(tw), (size_t)N * K * sizeof(float));
+        Tensor* o2 = cml_lora_linear_forward(l, tx);
+        if (o2 && cml_lora_linear_unmerge(l) == 0) {
+            memcpy(y_merged, tensor_data_ptr(o2), (size_t)M * N * sizeof(float));
+            rc = memcmp(tensor_data_ptr(tw), W, (size_t)N * K * sizeof(float)) == 0 ? 0 : 1;
+        }
+        if (o2) tensor_free(o2);
+    }
+    if (o1) tensor_free(o1);
+    cml_lora_linear_free(l);
+    tensor_free(tx);
+    tensor_free(tw);
+    return rc;
+}

@@ -251,6 +251,19 @@ def main():
                 "tok_ids": np.concatenate(ids_all), "tok_counts": np.array(counts, np.int32), "tok_unk": np.array(unks, np.int32),
                 "tok_decode_ids": dec_ids, "tok_decode_text": dbuf[:dn].copy()})
 
+    # ---- LoRA over an fp32 weight (src/nn/lora.c) ------------------------------------------------
+    lrng = np.random.default_rng(91)
+    Ml, Kl, Nl, rl, alphal, seedl = 5, 96, 40, 4, 8.0, 4242
+    lW = lrng.standard_normal((Nl, Kl)).astype(np.float32)
+    lx = lrng.standard_normal((Ml, Kl)).astype(np.float32)
+    lA = (lrng.standard_normal((rl, Kl)) * 0.2).astype(np.float32)
+    lB = (lrng.standard_normal((Nl, rl)) * 0.2).astype(np.float32)
+    a_init = np.zeros((rl, Kl), np.float32)
+    ly, lwm, lym = np.zeros((Ml, Nl), np.float32), np.zeros((Nl, Kl), np.float32), np.zeros((Ml, Nl), np.float32)
+    assert ref.ref_lora(p(lx), Ml, Kl, Nl, p(lW), rl, alphal, seedl, p(lA), p(lB), p(a_init), p(ly), p(lwm), p(lym)) == 0
+    out.update({"lora_cfg": np.array([Ml, Kl, Nl, rl, seedl], np.int32), "lora_alpha": np.array([alphal], np.float32), "lora_W": lW,
+                "lora_x": lx, "lora_A": lA, "lora_B": lB, "lora_A_init": a_init, "lora_y": ly, "lora_W_merged": lwm, "lora_y_merged": lym})
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 
