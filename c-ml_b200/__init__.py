@@ -402,6 +402,15 @@ _sig("cml_lora_adapter_add_layer", ci, AP, LP)
 _sig("cml_lora_adapter_merge_all", ci, AP)
 _sig("cml_lora_adapter_unmerge_all", ci, AP)
 _sig("cmlb200_lora_merge", ci, vp, vp, vp, ci, ci, ci, C.c_float, vp)
+class QuantParams(C.Structure):
+    _fields_ = [("scale", C.c_float), ("zero_point", C.c_int32)]
+
+
+_sig("cml_quantize_compute_params", QuantParams, TP, C.c_bool)
+_sig("cml_quantize_int8", TP, TP, C.POINTER(QuantParams), C.POINTER(QuantParams))
+_sig("cml_dequantize_int8", TP, TP, C.POINTER(QuantParams))
+_sig("cml_quantize_uint8", TP, TP, C.POINTER(QuantParams), C.POINTER(QuantParams))
+_sig("cml_dequantize_uint8", TP, TP, C.POINTER(QuantParams))
 _sig("cml_init", ci)
 _sig("cml_cleanup", ci)
 _sig("tensor_manual_seed", None, C.c_uint64)
@@ -414,7 +423,7 @@ def tensor_to_numpy(tp, free=True):
     import numpy as np
     t = tp.contents
     shape = [t.shape[i] for i in range(t.ndim)]
-    np_dtype = {0: np.float32, 8: np.uint8, 5: np.float16, 2: np.int32}[t.dtype]
+    np_dtype = {0: np.float32, 8: np.uint8, 7: np.int8, 5: np.float16, 2: np.int32}[t.dtype]
     n = int(np.prod(shape))
     arr = np.frombuffer((C.c_char * (n * np.dtype(np_dtype).itemsize)).from_address(t.data), dtype=np_dtype).reshape(shape).copy()
     if free:
@@ -423,10 +432,10 @@ def tensor_to_numpy(tp, free=True):
 
 
 def numpy_to_tensor(a):
-    """A host Tensor* owning a copy of `a` (fp32 or uint8); release with lib.tensor_free."""
+    """A host Tensor* owning a copy of `a` (fp32, uint8 or int8); release with lib.tensor_free."""
     import numpy as np
     a = np.ascontiguousarray(a)
-    dt = {np.dtype(np.float32): 0, np.dtype(np.uint8): 8}[a.dtype]
+    dt = {np.dtype(np.float32): 0, np.dtype(np.uint8): 8, np.dtype(np.int8): 7}[a.dtype]
     cfg = TensorConfig(dt, 0, True, True)
     shape = (C.c_int * a.ndim)(*a.shape)
     return lib.tensor_from_data(np_ptr(a), shape, a.ndim, C.byref(cfg))

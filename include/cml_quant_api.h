@@ -127,6 +127,20 @@ const char* gguf_get_tensor_name(GGUFContext* ctx, int index);
 /* As in C-ML: quantized tensors come back dequantized to fp32, others in their own dtype. */
 Tensor* gguf_read_tensor(GGUFContext* ctx, const char* name);
 
+/* ---- include/core/quantization.h:16-25: per-tensor affine quantisation -------------------------
+ * quantized = clamp(round(value / scale) + zero_point), dequantized = (quantized - zero_point) * scale.
+ * params == NULL: symmetric parameters from the tensor's range for int8, the [min, max] mapping onto
+ * 0..255 for uint8. Computed on the device, bit-exact with C-ML's loops; fp32 tensors only. */
+typedef struct QuantParams {
+    float scale;
+    int32_t zero_point;
+} QuantParams;
+QuantParams cml_quantize_compute_params(Tensor* tensor, bool symmetric);
+Tensor* cml_quantize_int8(Tensor* tensor, const QuantParams* params, QuantParams* out_params);
+Tensor* cml_dequantize_int8(Tensor* tensor, const QuantParams* params);
+Tensor* cml_quantize_uint8(Tensor* tensor, const QuantParams* params, QuantParams* out_params);
+Tensor* cml_dequantize_uint8(Tensor* tensor, const QuantParams* params);
+
 /* ---- include/core/quantization.h:28-38, include/nn/qlora.h:18-60 -------------------------- */
 extern const float CML_NF4_TABLE[16];
 Tensor* cml_quantize_nf4(Tensor* tensor, int block_size, float** out_scales, int* out_num_scales);

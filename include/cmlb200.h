@@ -299,6 +299,15 @@ int cmlb200_add_f32(float* d_acc, const float* d_in, size_t n, void* stream);
 int cmlb200_swiglu_bf16(const uint16_t* d_gate, const uint16_t* d_up, uint16_t* d_out, size_t n, void* stream);
 int cmlb200_swiglu_f32(const float* d_gate, const float* d_up, float* d_out, size_t n, void* stream);
 
+/* Per-tensor affine 8-bit quantisation (src/core/quantization.c:8-192), bit-exact with C-ML's loops:
+ * the value range of x (min, max into d_out[0..1]; d_scratch holds cmlb200_range_scratch_floats()
+ * floats), q = clamp(roundf(x / scale) + zero_point) to int8 (or uint8), and back
+ * (q - zero_point) * scale. */
+size_t cmlb200_range_scratch_floats(void);
+int cmlb200_range_f32(const float* d_x, size_t n, float* d_scratch, float* d_out, void* stream);
+int cmlb200_quantize_8bit(const float* d_x, size_t n, float scale, int zero_point, int is_unsigned, void* d_q, void* stream);
+int cmlb200_dequantize_8bit(const void* d_q, size_t n, float scale, int zero_point, int is_unsigned, float* d_out, void* stream);
+
 /* LoRA term of the quantized Linear (src/nn/qlora.c:336-361): y[M,N] += scaling * (x.A^T).B^T
  * with A [rank,K], B [N,rank]; d_t is M*rank floats of scratch. */
 int cmlb200_lora_accum(const float* d_x, const float* d_A, const float* d_B, int M, int K, int N, int rank, float scaling, float* d_t, float* d_y, void* stream);

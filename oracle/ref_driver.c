@@ -501,3 +501,36 @@ int ref_lora(const float* x, int M, int K, int N, const float* W, int rank, floa
     tensor_free(tw);
     return rc;
 }
+
+/* cml_quantize_compute_params / cml_quantize_int8 / uint8 / cml_dequantize_* (src/core/quantization.c:8-192).
+ * params_out = {scale bits, zero_point}. use_params == 0 lets the quantiser derive them. */
+#include "core/quantization.h"
+int ref_quant_params(const float* x, int n, int symmetric, int32_t* params_out) {
+    int s[1] = {n};
+    Tensor* t = t_from(x, 1, s);
+    if (!t) return -1;
+    QuantParams p = cml_quantize_compute_params(t, symmetric != 0);
+    memcpy(&params_out[0], &p.scale, 4);
+    params_out[1] = p.zero_point;
+    tensor_free(t);
+    return 0;
+}
+int ref_quant8(const float* x, int n, int is_unsigned, int use_params, float scale, int zero_point, uint8_t* q_out, int32_t* params_out,
+               float* deq_out) {
+    int s[1] = {n};
+    Tensor* t = t_from(x, 1, s);
+    if (!t) return -1;
+    QuantParams in = {scale, zero_point}, used = {0.f, 0};
+    Tensor* q = is_unsigned ? cml_quantize_uint8(t, use_params ? &in : NULL, &used) : cml_quantize_int8(t, use_params ? &in : NULL, &used);
+    int rc = -1;
+    if (q) {
+        memcpy(q_out, tensor_data_ptr(q), (size_t)n);
+        memcpy(&params_out[0], &used.scale, 4);
+        params_out[1] = used.zero_point;
+        Tensor* d = is_unsigned ? cml_dequantize_uint8(q, &used) : cml_dequantize_int8(q, &used);
+        if (d) { memcpy(deq_out, tensor_data_ptr(d), (size_t)n * sizeof(float)); tensor_free(d); rc = 0; }
+        tensor_free(q);
+    }
+    tensor_free(t);
+    return rc;
+}

@@ -264,6 +264,28 @@ def main():
     out.update({"lora_cfg": np.array([Ml, Kl, Nl, rl, seedl], np.int32), "lora_alpha": np.array([alphal], np.float32), "lora_W": lW,
                 "lora_x": lx, "lora_A": lA, "lora_B": lB, "lora_A_init": a_init, "lora_y": ly, "lora_W_merged": lwm, "lora_y_merged": lym})
 
+    # ---- per-tensor int8 / uint8 quantisation (src/core/quantization.c:8-192) -------------------
+    qrng = np.random.default_rng(17)
+    qx = (qrng.standard_normal(5000) * 3.0).astype(np.float32)
+    qx[:8] = [0.0, -0.0, 0.5 * 0.1, 1.5 * 0.1, -2.5 * 0.1, 40.0, -40.0, 12.7]        # ties of round-half-away and values that clamp
+    out["q8_x"] = qx
+    # values whose quotient leaves the int32 range: C-ML's cast is undefined there; the compiled x86 code
+    # yields INT_MIN ("integer indefinite") and wraps the zero-point addition, which the device code reproduces
+    qo = np.array([1e9, -1e9, 3e10, -3e10, 2.1e8, -2.1e8, 1.0, np.inf, -np.inf], np.float32)
+    out["q8_x_outliers"] = qo
+    for name, uns, sc, zp in (("i8_out", 0, 0.1, 3), ("i8_out_neg", 0, 0.1, -5), ("u8_out", 1, 0.05, 128)):
+        qq, pr, dq = np.zeros(len(qo), np.uint8), np.zeros(2, np.int32), np.zeros(len(qo), np.float32)
+        assert ref.ref_quant8(p(qo), len(qo), uns, 1, sc, zp, p(qq), p(pr), p(dq)) == 0
+        out.update({f"q8_{name}_q": qq, f"q8_{name}_cfg": np.array([uns, zp], np.int32), f"q8_{name}_scale": np.array([sc], np.float32)})
+    for sym in (0, 1):
+        pr = np.zeros(2, np.int32)
+        assert ref.ref_quant_params(p(qx), len(qx), sym, p(pr)) == 0
+        out[f"q8_params_sym{sym}"] = pr
+    for name, uns, use, sc, zp in (("i8_auto", 0, 0, 0.0, 0), ("u8_auto", 1, 0, 0.0, 0), ("i8_given", 0, 1, 0.1, 3), ("u8_given", 1, 1, 0.05, 128)):
+        qq, pr, dq = np.zeros(len(qx), np.uint8), np.zeros(2, np.int32), np.zeros(len(qx), np.float32)
+        assert ref.ref_quant8(p(qx), len(qx), uns, use, sc, zp, p(qq), p(pr), p(dq)) == 0
+        out.update({f"q8_{name}_q": qq, f"q8_{name}_params": pr, f"q8_{name}_deq": dq})
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 

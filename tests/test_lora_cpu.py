@@ -62,3 +62,15 @@ def test_argument_errors_and_adapter_bookkeeping(pkg):
     lib.cml_lora_linear_free(None)
     lib.tensor_free(W)
     lib.tensor_free(W3)
+
+
+def test_quantisation_argument_errors_need_no_device(pkg):
+    """src/core/quantization.c:40-48, 82-90: NULL tensors and parameters are refused before any device work."""
+    lib = pkg.lib
+    assert not lib.cml_quantize_int8(None, None, None) and not lib.cml_quantize_uint8(None, None, None)
+    assert not lib.cml_dequantize_int8(None, None) and not lib.cml_dequantize_uint8(None, None)
+    p0 = lib.cml_quantize_compute_params(None, False)
+    assert (p0.scale, p0.zero_point) == (1.0, 0)
+    u = pkg.numpy_to_tensor(np.zeros(4, np.uint8))
+    assert not lib.cml_dequantize_uint8(u, None)
+    lib.tensor_free(u)
