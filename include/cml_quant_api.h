@@ -107,10 +107,17 @@ typedef enum {
     GGUF_TENSOR_I32 = 18
 } GGUFTensorType;
 
+/* block layouts of the GGUF types (d, dmin, m: fp16 bits) */
 #define QK4_0 32
-typedef struct { uint16_t d; uint8_t qs[QK4_0 / 2]; } BlockQ4_0;
+typedef struct { uint16_t d; uint8_t qs[QK4_0 / 2]; } BlockQ4_0;                                   /* 18 B: d * (nibble - 8) */
+#define QK4_1 32
+typedef struct { uint16_t d; uint16_t m; uint8_t qs[QK4_1 / 2]; } BlockQ4_1;                       /* 20 B: d * nibble + m */
 #define QK8_0 32
-typedef struct { uint16_t d; int8_t qs[QK8_0]; } BlockQ8_0;
+typedef struct { uint16_t d; int8_t qs[QK8_0]; } BlockQ8_0;                                        /* 34 B: d * q */
+#define QK_K 256
+typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qs[QK_K / 2]; } BlockQ4_K;                      /* 144 B */
+typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qh[QK_K / 8]; uint8_t qs[QK_K / 2]; } BlockQ5_K; /* 176 B */
+typedef struct { uint8_t ql[QK_K / 2]; uint8_t qh[QK_K / 4]; int8_t scales[QK_K / 16]; uint16_t d; } BlockQ6_K;         /* 210 B */
 
 bool gguf_type_is_quantized(GGUFTensorType type);
 int gguf_quant_block_size(GGUFTensorType type);

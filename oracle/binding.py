@@ -41,6 +41,16 @@ def build_ref(root=None):
     return so if so.exists() else None
 
 
+def build_reference_tests(root=None):
+    """C-ML's own test programs for the path, compiled unchanged against this repo's headers and linked
+    to its library (which must be built): oracle/_ref/tests/<name>. No-op without the source tree."""
+    root = root or reference_root()
+    if root:
+        subprocess.run(["make", "-s", "-j8", "-C", str(HERE), "reftests", f"REF={root}"], check=True)
+    d = HERE / "_ref" / "tests"
+    return sorted(d.iterdir()) if d.is_dir() else []
+
+
 def p(a):
     return a.ctypes.data_as(vp)
 
