@@ -411,6 +411,11 @@ _sig("cml_quantize_int8", TP, TP, C.POINTER(QuantParams), C.POINTER(QuantParams)
 _sig("cml_dequantize_int8", TP, TP, C.POINTER(QuantParams))
 _sig("cml_quantize_uint8", TP, TP, C.POINTER(QuantParams), C.POINTER(QuantParams))
 _sig("cml_dequantize_uint8", TP, TP, C.POINTER(QuantParams))
+_sig("gguf_open_write", vp, C.c_char_p)
+_sig("gguf_write_tensor", ci, vp, C.c_char_p, TP)
+_sig("gguf_write_blocks", ci, vp, C.c_char_p, ci, C.POINTER(C.c_int64), ci, vp)
+_sig("gguf_write_metadata", ci, vp, C.c_char_p, ci, vp)
+_sig("gguf_write_metadata_array", ci, vp, C.c_char_p, ci, vp, C.c_uint64)
 _sig("cml_init", ci)
 _sig("cml_cleanup", ci)
 _sig("tensor_manual_seed", None, C.c_uint64)
@@ -432,10 +437,10 @@ def tensor_to_numpy(tp, free=True):
 
 
 def numpy_to_tensor(a):
-    """A host Tensor* owning a copy of `a` (fp32, uint8 or int8); release with lib.tensor_free."""
+    """A host Tensor* owning a copy of `a` (fp32, fp16, int32, uint8 or int8); release with lib.tensor_free."""
     import numpy as np
     a = np.ascontiguousarray(a)
-    dt = {np.dtype(np.float32): 0, np.dtype(np.uint8): 8, np.dtype(np.int8): 7}[a.dtype]
+    dt = {np.dtype(np.float32): 0, np.dtype(np.uint8): 8, np.dtype(np.int8): 7, np.dtype(np.int32): 2, np.dtype(np.float16): 5}[a.dtype]
     cfg = TensorConfig(dt, 0, True, True)
     shape = (C.c_int * a.ndim)(*a.shape)
     return lib.tensor_from_data(np_ptr(a), shape, a.ndim, C.byref(cfg))

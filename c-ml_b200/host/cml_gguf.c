@@ -6,6 +6,10 @@
  * key/values (src/core/gguf.c:75-103); here they are kept, so that a file's tokenizer and
  * hyper-parameters can be used (gguf_get_metadata_*, gguf_create_tokenizer,
  * cml_llama_config_from_gguf). A malformed entry fails the open exactly where C-ML's skip would.
+ * The writer (src/core/gguf.c:47-56, 181-232, 312-340) collects tensors and emits the file on
+ * gguf_close with C-ML's layout byte for byte: header with zero key/values, the infos, zero padding to
+ * a multiple of 32, then the tensors' bytes back to back. Beyond C-ML it can also carry key/values
+ * and block-quantized tensors, so a complete model file can be produced from C.
  */
 #include <stdio.h>
 #include <stdlib.h>
@@ -26,6 +30,16 @@ typedef struct GGUFMeta {
     char** strs;
 } GGUFMeta;
 
+/* write mode: a tensor waiting for gguf_close, and serialized key/values */
+typedef struct GGUFPending {
+    char* name;
+    int ndim;
+    uint64_t shape[8];
+    uint32_t type;
+    void* data;
+    size_t bytes;
+} GGUFPending;
+
 struct GGUFContext {
     FILE* file;
     int num_tensors;
@@ -33,6 +47,13 @@ struct GGUFContext {
     uint64_t data_offset;
     int num_meta;
     GGUFMeta* meta;
+    /* write mode */
+    char* write_path;
+    GGUFPending* pending;
+    int num_pending, cap_pending;
+    unsigned char* kv_bytes;
+    size_t kv_size, kv_cap;
+    uint64_t num_kv;
 };
 
 bool gguf_type_is_quantized(GGUFTensorType type) {
@@ -241,8 +262,17 @@ GGUFContext* gguf_open_read(const char* filepath) {
     return ctx;
 }
 
+static void write_flush(GGUFContext* ctx);
+
 void gguf_close(GGUFContext* ctx) {
     if (!ctx) return;
+    if (ctx->write_path) {
+        write_flush(ctx);
+        for (int i = 0; i < ctx->num_pending; i++) { free(ctx->pending[i].name); free(ctx->pending[i].data); }
+        free(ctx->pending);
+        free(ctx->kv_bytes);
+        free(ctx->write_path);
+    }
     if (ctx->tensors) {
         for (int i = 0; i < ctx->num_tensors; i++) free(ctx->tensors[i].name);
         free(ctx->tensors);
@@ -393,4 +423,145 @@ Tensor* gguf_read_tensor(GGUFContext* ctx, const char* name) {
     }
     free(raw);
     return t;
+}
+
+/* ---- writer ------------------------------------------------------------------------------------ */
+#define GGUF_MAX_WRITE_TENSORS 4096          /* src/core/gguf.c:10 */
+
+GGUFContext* gguf_open_write(const char* filepath) {
+    if (!filepath) return NULL;
+    GGUFContext* ctx = (GGUFContext*)calloc(1, sizeof *ctx);
+    if (!ctx) return NULL;
+    ctx->write_path = strdup(filepath);
+    if (!ctx->write_path) { free(ctx); return NULL; }
+    return ctx;
+}
+
+static uint32_t gguf_type_of(DType dtype) {      /* src/core/gguf.c:47-56: anything else is labelled F32 */
+    switch (dtype) {
+        case DTYPE_FLOAT16: return GGUF_TENSOR_F16;
+        case DTYPE_INT8: return GGUF_TENSOR_I8;
+        case DTYPE_INT16: return GGUF_TENSOR_I16;
+        case DTYPE_INT32: return GGUF_TENSOR_I32;
+        default: return GGUF_TENSOR_F32;
+    }
+}
+
+static int write_add(GGUFContext* ctx, const char* name, uint32_t type, const int64_t* shape, int ndim, const void* data, size_t bytes) {
+    if (!ctx || !ctx->write_path || !name || !data || ndim < 0 || ndim > 8 || ctx->num_pending >= GGUF_MAX_WRITE_TENSORS) return -1;
+    if (ctx->num_pending == ctx->cap_pending) {
+        const int cap = ctx->cap_pending ? 2 * ctx->cap_pending : 16;
+        GGUFPending* grown = (GGUFPending*)realloc(ctx->pending, (size_t)cap * sizeof *grown);
+        if (!grown) return -1;
+        ctx->pending = grown;
+        ctx->cap_pending = cap;
+    }
+    GGUFPending* pt = &ctx->pending[ctx->num_pending];
+    memset(pt, 0, sizeof *pt);
+    pt->name = strdup(name);
+    pt->data = malloc(bytes ? bytes : 1);
+    if (!pt->name || !pt->data) { free(pt->name); free(pt->data); return -1; }
+    memcpy(pt->data, data, bytes);
+    pt->bytes = bytes;
+    pt->type = type;
+    pt->ndim = ndim;
+    for (int d = 0; d < ndim; d++) pt->shape[d] = (uint64_t)shape[d];
+    ctx->num_pending++;
+    return 0;
+}
+
+int gguf_write_tensor(GGUFContext* ctx, const char* name, Tensor* tensor) {
+    if (!ctx || !name || !tensor || !ctx->write_path || !tensor->data || tensor->ndim > 8) return -1;
+    int64_t shape[8];
+    for (int d = 0; d < tensor->ndim; d++) shape[d] = tensor->shape[d];
+    return write_add(ctx, name, gguf_type_of(tensor->dtype), shape, tensor->ndim, tensor->data, tensor->numel * cml_dtype_size(tensor->dtype));
+}
+
+int gguf_write_blocks(GGUFContext* ctx, const char* name, GGUFTensorType type, const int64_t* shape, int ndim, const void* blocks) {
+    if (!shape || ndim < 1 || ndim > 8 || !gguf_type_is_quantized(type)) return -1;
+    uint64_t numel = 1;
+    for (int d = 0; d < ndim; d++) {
+        if (shape[d] <= 0) return -1;
+        numel *= (uint64_t)shape[d];
+    }
+    const uint64_t bs = (uint64_t)gguf_quant_block_size(type);
+    if (numel % bs) return -1;
+    return write_add(ctx, name, (uint32_t)type, shape, ndim, blocks, (size_t)(numel / bs) * gguf_quant_type_size(type));
+}
+
+static int kv_append(GGUFContext* ctx, const void* src, size_t n) {
+    if (ctx->kv_size + n > ctx->kv_cap) {
+        size_t cap = ctx->kv_cap ? ctx->kv_cap : 256;
+        while (cap < ctx->kv_size + n) cap *= 2;
+        unsigned char* grown = (unsigned char*)realloc(ctx->kv_bytes, cap);
+        if (!grown) return -1;
+        ctx->kv_bytes = grown;
+        ctx->kv_cap = cap;
+    }
+    memcpy(ctx->kv_bytes + ctx->kv_size, src, n);
+    ctx->kv_size += n;
+    return 0;
+}
+static int kv_append_string(GGUFContext* ctx, const char* s) {
+    const uint64_t len = strlen(s);
+    return len > 65536 || kv_append(ctx, &len, 8) || kv_append(ctx, s, (size_t)len) ? -1 : 0;   /* longer strings would not read back */
+}
+
+int gguf_write_metadata(GGUFContext* ctx, const char* key, int type, const void* value) {
+    if (!ctx || !ctx->write_path || !key || !value || type < 0 || type > 12 || type == 9) return -1;
+    const size_t mark = ctx->kv_size;
+    const uint32_t t = (uint32_t)type;
+    int rc = kv_append_string(ctx, key) || kv_append(ctx, &t, 4);
+    if (!rc) rc = type == 8 ? kv_append_string(ctx, (const char*)value) : kv_append(ctx, value, (size_t)kMetaSize[type]);
+    if (rc) { ctx->kv_size = mark; return -1; }
+    ctx->num_kv++;
+    return 0;
+}
+
+int gguf_write_metadata_array(GGUFContext* ctx, const char* key, int elem_type, const void* values, uint64_t count) {
+    if (!ctx || !ctx->write_path || !key || (!values && count) || elem_type < 0 || elem_type > 12 || elem_type == 9) return -1;
+    const size_t mark = ctx->kv_size;
+    const uint32_t t = 9, et = (uint32_t)elem_type;
+    int rc = kv_append_string(ctx, key) || kv_append(ctx, &t, 4) || kv_append(ctx, &et, 4) || kv_append(ctx, &count, 8);
+    if (!rc && elem_type == 8) {
+        const char* const* strs = (const char* const*)values;
+        for (uint64_t i = 0; !rc && i < count; i++) rc = !strs[i] || kv_append_string(ctx, strs[i]);
+    } else if (!rc) {
+        rc = kv_append(ctx, values, (size_t)count * (size_t)kMetaSize[elem_type]);
+    }
+    if (rc) { ctx->kv_size = mark; return -1; }
+    ctx->num_kv++;
+    return 0;
+}
+
+/* Emits the file (nothing when no tensor was added, as src/core/gguf.c:184). */
+static void write_flush(GGUFContext* ctx) {
+    if (ctx->num_pending == 0) return;
+    FILE* f = fopen(ctx->write_path, "wb");
+    if (!f) { LOG_ERROR("gguf_close: cannot write %s", ctx->write_path); return; }
+    const uint32_t magic = GGUF_MAGIC, version = 3;
+    const uint64_t nt = (uint64_t)ctx->num_pending;
+    fwrite(&magic, 4, 1, f);
+    fwrite(&version, 4, 1, f);
+    fwrite(&nt, 8, 1, f);
+    fwrite(&ctx->num_kv, 8, 1, f);
+    if (ctx->kv_size) fwrite(ctx->kv_bytes, 1, ctx->kv_size, f);
+    uint64_t offset = 0;
+    for (int i = 0; i < ctx->num_pending; i++) {
+        const GGUFPending* pt = &ctx->pending[i];
+        const uint64_t len = strlen(pt->name);
+        const uint32_t nd = (uint32_t)pt->ndim;
+        fwrite(&len, 8, 1, f);
+        fwrite(pt->name, 1, (size_t)len, f);
+        fwrite(&nd, 4, 1, f);
+        for (int d = 0; d < pt->ndim; d++) fwrite(&pt->shape[d], 8, 1, f);
+        fwrite(&pt->type, 4, 1, f);
+        fwrite(&offset, 8, 1, f);
+        offset += pt->bytes;                         /* back to back: C-ML's reader needs no per-tensor alignment */
+    }
+    static const unsigned char zeros[32] = {0};
+    const long pos = ftell(f);
+    fwrite(zeros, 1, (size_t)(((pos + 31) & ~31L) - pos), f);
+    for (int i = 0; i < ctx->num_pending; i++) fwrite(ctx->pending[i].data, 1, ctx->pending[i].bytes, f);
+    if (fclose(f) != 0) LOG_ERROR("gguf_close: short write to %s", ctx->write_path);
 }

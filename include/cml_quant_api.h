@@ -133,6 +133,18 @@ int gguf_get_num_tensors(GGUFContext* ctx);
 const char* gguf_get_tensor_name(GGUFContext* ctx, int index);
 /* As in C-ML: quantized tensors come back dequantized to fp32, others in their own dtype. */
 Tensor* gguf_read_tensor(GGUFContext* ctx, const char* name);
+/* The writer (include/core/gguf.h:46,51): tensors are collected and the file is emitted by gguf_close,
+ * byte for byte as C-ML emits it (version 3, the infos, zero padding to a multiple of 32, the data back
+ * to back; no file when nothing was written; at most 4096 tensors; fp16 / int8 / int16 / int32 keep
+ * their type id, every other dtype is labelled F32 as in src/core/gguf.c:47-56). */
+GGUFContext* gguf_open_write(const char* filepath);
+int gguf_write_tensor(GGUFContext* ctx, const char* name, Tensor* tensor);
+/* Additions (C-ML's writer has neither): a block-quantized tensor from its raw GGUF blocks (shape as it
+ * is to be read back, numel a multiple of the block size), and key/values: a scalar or string by type
+ * id (value points at the scalar, or is the C string), an array of scalars (packed) or of C strings. */
+int gguf_write_blocks(GGUFContext* ctx, const char* name, GGUFTensorType type, const int64_t* shape, int ndim, const void* blocks);
+int gguf_write_metadata(GGUFContext* ctx, const char* key, int type, const void* value);
+int gguf_write_metadata_array(GGUFContext* ctx, const char* key, int elem_type, const void* values, uint64_t count);
 
 /* ---- include/core/quantization.h:16-25: per-tensor affine quantisation -------------------------
  * quantized = clamp(round(value / scale) + zero_point), dequantized = (quantized - zero_point) * scale.

@@ -137,6 +137,7 @@ def load_ref():
         _sig(lib, "ref_tokenizer_decode", ci, C.c_char_p, ci, vp, ci, vp, ci)
         _sig(lib, "ref_lora", ci, vp, ci, ci, ci, vp, ci, cf, C.c_uint, vp, vp, vp, vp, vp, vp)
         _sig(lib, "ref_quant_params", ci, vp, ci, ci, vp)
+        _sig(lib, "ref_gguf_write", ci, C.c_char_p, vp, ci, ci, vp, ci, vp, ci)
         _sig(lib, "ref_quant8", ci, vp, ci, ci, ci, cf, ci, vp, vp, vp)
         lib.ref_init()
     _ref_cache.append(lib)

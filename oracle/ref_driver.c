@@ -534,3 +534,24 @@ int ref_quant8(const float* x, int n, int is_unsigned, int use_params, float sca
     tensor_free(t);
     return rc;
 }
+
+/* gguf_open_write / gguf_write_tensor / gguf_close (src/core/gguf.c:47-56, 181-232, 312-340): an fp32
+ * [rows, cols] tensor "w.f32", an int32 vector "v.i32" and an fp16 vector "h.f16" into `path`. */
+#include "core/gguf.h"
+int ref_gguf_write(const char* path, const float* a, int rows, int cols, const int32_t* b, int nb, const uint16_t* c, int nc) {
+    GGUFContext* ctx = gguf_open_write(path);
+    if (!ctx) return -1;
+    int sa[2] = {rows, cols}, sb[1] = {nb}, sc[1] = {nc};
+    TensorConfig cb = {.dtype = DTYPE_INT32, .device = DEVICE_CPU, .has_dtype = true, .has_device = true};
+    TensorConfig cc = {.dtype = DTYPE_FLOAT16, .device = DEVICE_CPU, .has_dtype = true, .has_device = true};
+    Tensor* ta = t_from(a, 2, sa);
+    Tensor* tb = tensor_from_data(b, sb, 1, &cb);
+    Tensor* tc = tensor_from_data(c, sc, 1, &cc);
+    int rc = -1;
+    if (ta && tb && tc) rc = gguf_write_tensor(ctx, "w.f32", ta) | gguf_write_tensor(ctx, "v.i32", tb) | gguf_write_tensor(ctx, "h.f16", tc);
+    gguf_close(ctx);
+    if (ta) tensor_free(ta);
+    if (tb) tensor_free(tb);
+    if (tc) tensor_free(tc);
+    return rc;
+}

@@ -286,6 +286,17 @@ def main():
         assert ref.ref_quant8(p(qx), len(qx), uns, use, sc, zp, p(qq), p(pr), p(dq)) == 0
         out.update({f"q8_{name}_q": qq, f"q8_{name}_params": pr, f"q8_{name}_deq": dq})
 
+    # ---- GGUF writer (src/core/gguf.c:181-232, 312-340): the bytes of a three-tensor file ----------
+    import tempfile
+    wr = np.random.default_rng(33)
+    wa = wr.standard_normal((3, 5)).astype(np.float32)
+    wb = wr.integers(-1000, 1000, 7).astype(np.int32)
+    wc = wr.standard_normal(9).astype(np.float16).view(np.uint16)
+    with tempfile.TemporaryDirectory() as td:
+        fp = str(Path(td) / "ref.gguf")
+        assert ref.ref_gguf_write(fp.encode(), p(wa), 3, 5, p(wb), len(wb), p(wc), len(wc)) == 0
+        out.update({"ggufw_a": wa, "ggufw_b": wb, "ggufw_c": wc, "ggufw_file": np.frombuffer(Path(fp).read_bytes(), np.uint8)})
+
     np.savez_compressed(ROOT / "tests" / "golden" / "golden.npz", **out)
     print("wrote golden.npz with", len(out), "arrays,", sum(v.nbytes for v in out.values()), "bytes")
 

@@ -269,3 +269,66 @@ def test_gguf_reader_survives_truncated_and_mutated_files(pkg, tmp_path):
         assert probe(raw) == 1
     finally:
         lib.cml_set_log_level(3)
+
+
+def test_gguf_writer_emits_c_ml_bytes_and_reads_back(pkg, golden, tmp_path):
+    """gguf_open_write / gguf_write_tensor / gguf_close produce, for the same three tensors, the file
+    C-ML's writer produces (src/core/gguf.c:181-232, 312-340; bytes from the compiled reference); the
+    additions (key/values, block-quantized tensors) read back through gguf_open_read."""
+    lib = pkg.lib
+    path = tmp_path / "mine.gguf"
+    g = lib.gguf_open_write(str(path).encode())
+    assert g
+    tensors = [pkg.numpy_to_tensor(np.ascontiguousarray(golden["ggufw_a"])), pkg.numpy_to_tensor(np.ascontiguousarray(golden["ggufw_b"])),
+               pkg.numpy_to_tensor(np.ascontiguousarray(golden["ggufw_c"]).view(np.float16))]
+    for name, t in zip((b"w.f32", b"v.i32", b"h.f16"), tensors):
+        assert lib.gguf_write_tensor(g, name, t) == 0
+    assert lib.gguf_write_tensor(g, None, tensors[0]) == -1 and lib.gguf_write_tensor(g, b"x", None) == -1
+    assert lib.gguf_get_num_tensors(g) == 0                                   # a write context lists nothing
+    lib.gguf_close(g)
+    assert path.read_bytes() == bytes(golden["ggufw_file"])
+    # nothing written -> no file (src/core/gguf.c:184)
+    empty = tmp_path / "empty.gguf"
+    lib.gguf_close(lib.gguf_open_write(str(empty).encode()))
+    assert not empty.exists()
+    # a model-like file from C: key/values, a string array, a Q4_0 tensor, an fp32 tensor
+    synth = entry.load_synth()
+    rng = np.random.default_rng(3)
+    blocks = synth.q4_0_blocks(rng, 8, 64)
+    full = tmp_path / "full.gguf"
+    g = lib.gguf_open_write(str(full).encode())
+    u32, f32 = C.c_uint32(7), C.c_float(1e-5)
+    assert lib.gguf_write_metadata(g, b"llama.block_count", 4, C.byref(u32)) == 0
+    assert lib.gguf_write_metadata(g, b"llama.attention.layer_norm_rms_epsilon", 6, C.byref(f32)) == 0
+    assert lib.gguf_write_metadata(g, b"general.name", 8, b"from-c") == 0
+    toks = (C.c_char_p * 3)(b"a", b"b", b"ab")
+    assert lib.gguf_write_metadata_array(g, b"tokenizer.ggml.tokens", 8, toks, 3) == 0
+    types = (C.c_int32 * 3)(1, 1, 2)
+    assert lib.gguf_write_metadata_array(g, b"tokenizer.ggml.token_type", 5, types, 3) == 0
+    assert lib.gguf_write_metadata(g, b"bad", 9, C.byref(u32)) == -1 and lib.gguf_write_metadata(g, None, 4, C.byref(u32)) == -1
+    shape = (C.c_int64 * 2)(8, 64)
+    assert lib.gguf_write_blocks(g, b"blk.0.attn_q.weight", 2, shape, 2, blocks.ctypes.data) == 0
+    assert lib.gguf_write_blocks(g, b"odd", 2, (C.c_int64 * 1)(33), 1, blocks.ctypes.data) == -1      # not a whole number of blocks
+    assert lib.gguf_write_blocks(g, b"f32", 0, shape, 2, blocks.ctypes.data) == -1                    # not a block type
+    assert lib.gguf_write_tensor(g, b"norm.weight", tensors[0]) == 0
+    lib.gguf_close(g)
+    r = lib.gguf_open_read(str(full).encode())
+    assert r and lib.gguf_get_num_tensors(r) == 2 and lib.gguf_get_num_metadata(r) == 5
+    assert lib.gguf_get_tensor_name(r, 0) == b"blk.0.attn_q.weight" and lib.gguf_get_tensor_name(r, 1) == b"norm.weight"
+    v, f = C.c_int64(0), C.c_double(0)
+    assert lib.gguf_get_metadata_int(r, b"llama.block_count", C.byref(v)) == 0 and v.value == 7
+    assert lib.gguf_get_metadata_float(r, b"llama.attention.layer_norm_rms_epsilon", C.byref(f)) == 0 and f.value == float(np.float32(1e-5))
+    assert lib.gguf_get_metadata_string(r, b"general.name") == b"from-c"
+    assert lib.gguf_get_metadata_array_string(r, b"tokenizer.ggml.tokens", 2) == b"ab"
+    tok = lib.gguf_create_tokenizer(r)
+    assert tok and encode(pkg, tok, b"abb")[0] == [0, 1, 1]                   # no merges in the file: bytes only
+    lib.cml_tokenizer_free(tok)
+    back = lib.gguf_read_tensor(r, b"norm.weight")                            # not quantized: no device involved
+    assert back and np.array_equal(pkg.tensor_to_numpy(back), golden["ggufw_a"])
+    lib.gguf_close(r)
+    # the block payload sits, unpadded, right behind the aligned start of the data section
+    raw = full.read_bytes()
+    at = raw.find(blocks.tobytes())
+    assert at > 0 and at % 32 == 0 and raw[at + blocks.nbytes:at + blocks.nbytes + 60] == golden["ggufw_a"].tobytes()
+    for t in tensors:
+        lib.tensor_free(t)
