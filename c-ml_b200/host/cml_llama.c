@@ -372,7 +372,10 @@ int cml_llama_tp_init(CMLLLaMAModel* model, const void* id128, int device) {
     if (cml_nccl_init(&d->comm, d->tp, d->rank, id128)) return -1;
     const char* only = getenv("CML_B200_TP_NCCL_ONLY");
     if (only && only[0] == '1') return 0;
-    if (cmlb200_malloc((void**)&d->lineup, 16) || cmlb200_memset(d->lineup, 0, 16, NULL) || cmlb200_device_sync()) { d->lineup = NULL; return 0; }
+    if (cmlb200_malloc((void**)&d->lineup, 16) || cmlb200_memset(d->lineup, 0, 16, NULL) || cmlb200_device_sync()) {
+        LOG_ERROR("cml_llama_tp_init: %s", cmlb200_last_error());       /* the other ranks are about to enter collectives: fail loudly */
+        return -1;
+    }
     if (tp_peer_setup(d)) { LOG_WARNING("cml_llama_tp_init: no peer-memory all-reduce, using NCCL for every size"); return 0; }
     tp_bulk_setup(d);
     return 0;
