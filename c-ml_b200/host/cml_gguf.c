@@ -239,6 +239,7 @@ GGUFContext* gguf_open_read(const char* filepath) {
             uint64_t dim;
             if (fread(&dim, 8, 1, f) != 1) goto bad;
             ti->shape[d] = (int64_t)dim;
+            if (dim > 0 && numel > ((size_t)1 << 48) / (size_t)(dim > ((uint64_t)1 << 48) ? ((uint64_t)1 << 48) : dim)) goto bad;   /* more elements than any file holds */
             numel *= (size_t)dim;
         }
         if (fread(&ty, 4, 1, f) != 1 || fread(&ti->offset, 8, 1, f) != 1) goto bad;
@@ -394,6 +395,12 @@ const GGUFTensorInfo* cml_gguf_find(GGUFContext* ctx, const char* name) {
 
 void* cml_gguf_read_raw(GGUFContext* ctx, const GGUFTensorInfo* info) {
     if (!ctx || !info) return NULL;
+    struct stat sb;
+    if (fstat(fileno(ctx->file), &sb) != 0 || (uint64_t)sb.st_size < ctx->data_offset || info->offset > (uint64_t)sb.st_size - ctx->data_offset ||
+        info->data_size > (uint64_t)sb.st_size - ctx->data_offset - info->offset) {
+        LOG_ERROR("gguf: tensor '%s' reaches past the end of the file", info->name);
+        return NULL;
+    }
     void* raw = malloc(info->data_size ? info->data_size : 1);
     if (!raw) { LOG_ERROR("gguf: allocation of %zu bytes failed", info->data_size); return NULL; }
     if (fseek(ctx->file, (long)(ctx->data_offset + info->offset), SEEK_SET) != 0 ||
