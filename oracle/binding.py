@@ -90,6 +90,11 @@ def load_orc():
     _sig(lib, "orc_rope", None, vp, ci, ci, ci, ci, cf, ci)
     _sig(lib, "orc_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp)
     _sig(lib, "orc_paged_gqa", ci, vp, vp, vp, ci, ci, ci, ci, ci, cf, ci, vp)
+    _sig(lib, "orc_lora_forward", None, vp, ci, ci, ci, vp, vp, vp, ci, cf, ci, vp, vp)
+    _sig(lib, "orc_lora_merge", None, vp, vp, vp, ci, ci, ci, cf)
+    _sig(lib, "orc_quant_params", None, vp, C.c_size_t, ci, vp)
+    _sig(lib, "orc_quantize8", None, vp, C.c_size_t, cf, C.c_int32, ci, vp)
+    _sig(lib, "orc_dequantize8", None, vp, C.c_size_t, cf, C.c_int32, ci, vp)
     _sig(lib, "orc_llama_forward", ci, C.POINTER(OrcLlamaStruct), vp, ci, vp)
     _sig(lib, "orc_argmax_first", ci, vp, ci)
     _sig(lib, "orc_tp_shard", ci, vp, ci, ci, ci, ci, ci, vp)

@@ -2,8 +2,8 @@
  * cml_oracle.c -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
  *
  * A plain-C CPU restatement of the C-ML algorithms on the quantized-LLM path
- * (block dequantisation, NF4, the quantized Linear forward, and the LLaMA
- * forward pass). It exists only so that the CUDA path can be checked against
+ * (block dequantisation, NF4, the quantized Linear forward, the LLaMA forward
+ * pass, paged attention, the LoRA layer and the per-tensor 8-bit quantisers). It exists only so that the CUDA path can be checked against
  * it; nothing shipped may call it. Every function cites the C-ML file:line it
  * restates (paths relative to the C-ML source tree).
  *
@@ -580,4 +580,80 @@ void orc_tp_allreduce_sum(const float* const* parts, int nparts, size_t numel, f
     for (size_t i = 0; i < numel; i++) out[i] = 0.f;
     for (int p = 0; p < nparts; p++)
         for (size_t i = 0; i < numel; i++) out[i] += parts[p][i];
+}
+
+/* ---- LoRA over an fp32 weight (src/nn/lora.c:105-273) ----------------------
+ * y[b][o] = sum_i x[b][i] W[o][i]  (+ scaling * sum_r (sum_i x[b][i] A[r][i]) B[o][r] unless merged),
+ * every sum in fp32, ascending index, as C-ML's loops. t: M * rank floats of scratch. */
+void orc_lora_forward(const float* x, int M, int K, int N, const float* W, const float* A, const float* B, int rank,
+                      float scaling, int merged, float* t, float* y) {
+    for (int b = 0; b < M; b++)
+        for (int o = 0; o < N; o++) {
+            float s = 0.0f;
+            for (int i = 0; i < K; i++) s += x[(size_t)b * K + i] * W[(size_t)o * K + i];
+            y[(size_t)b * N + o] = s;
+        }
+    if (merged) return;
+    for (int b = 0; b < M; b++)
+        for (int r = 0; r < rank; r++) {
+            float s = 0.0f;
+            for (int i = 0; i < K; i++) s += x[(size_t)b * K + i] * A[(size_t)r * K + i];
+            t[(size_t)b * rank + r] = s;
+        }
+    for (int b = 0; b < M; b++)
+        for (int o = 0; o < N; o++) {
+            float s = 0.0f;
+            for (int r = 0; r < rank; r++) s += t[(size_t)b * rank + r] * B[(size_t)o * rank + r];
+            y[(size_t)b * N + o] += scaling * s;
+        }
+}
+/* src/nn/lora.c:263-273: W[o][i] += scaling * sum_r B[o][r] A[r][i] */
+void orc_lora_merge(float* W, const float* A, const float* B, int N, int K, int rank, float scaling) {
+    for (int o = 0; o < N; o++)
+        for (int i = 0; i < K; i++) {
+            float s = 0.0f;
+            for (int r = 0; r < rank; r++) s += B[(size_t)o * rank + r] * A[(size_t)r * K + i];
+            W[(size_t)o * K + i] += scaling * s;
+        }
+}
+
+/* ---- per-tensor affine 8-bit quantisation (src/core/quantization.c:8-192) ----
+ * params_out = {scale bits, zero_point}. mode 0: symmetric int8 parameters, 1: asymmetric int8
+ * (zero point shifted by -128), 2: the uint8 mapping of [min, max] onto 0..255. */
+void orc_quant_params(const float* x, size_t n, int mode, int32_t* params_out) {
+    float lo = 3.402823466e+38f, hi = -3.402823466e+38f, scale;
+    int32_t zp = 0;
+    for (size_t i = 0; i < n; i++) {
+        if (x[i] < lo) lo = x[i];
+        if (x[i] > hi) hi = x[i];
+    }
+    if (mode == 0) {
+        scale = fmaxf(fabsf(lo), fabsf(hi)) / 127.0f;
+    } else {
+        scale = (hi - lo) / 255.0f;
+        if (scale < 1e-10f) scale = 1e-10f;
+        zp = (int32_t)roundf(-lo / scale) - (mode == 1 ? 128 : 0);
+    }
+    if (scale < 1e-10f) scale = 1e-10f;
+    memcpy(&params_out[0], &scale, 4);
+    params_out[1] = zp;
+}
+/* q = clamp(round(v / scale) + zero_point). Where the quotient leaves the int32 range C-ML's cast is
+ * undefined; the compiled x86 reference yields INT_MIN there and wraps the addition, restated here
+ * without undefined behaviour. */
+void orc_quantize8(const float* x, size_t n, float scale, int32_t zero_point, int is_unsigned, uint8_t* q) {
+    const int32_t lo = is_unsigned ? 0 : -128, hi = is_unsigned ? 255 : 127;
+    for (size_t i = 0; i < n; i++) {
+        const float r = roundf(x[i] / scale);
+        const int32_t c = (r >= -2147483648.0f && r < 2147483648.0f) ? (int32_t)r : INT32_MIN;
+        int32_t v = (int32_t)((uint32_t)c + (uint32_t)zero_point);
+        v = v < lo ? lo : (v > hi ? hi : v);
+        q[i] = (uint8_t)v;
+    }
+}
+void orc_dequantize8(const uint8_t* q, size_t n, float scale, int32_t zero_point, int is_unsigned, float* out) {
+    for (size_t i = 0; i < n; i++) {
+        const float v = is_unsigned ? (float)q[i] : (float)(int8_t)q[i];
+        out[i] = (v - (float)zero_point) * scale;
+    }
 }

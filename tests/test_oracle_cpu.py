@@ -306,3 +306,42 @@ def test_paged_attention_matches_golden_and_reference(ob, orc, golden):
     assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), 1, 37, 4, 2, 16, 0.0, 0, ob.p(b)) == 0
     assert np.array_equal(a, b)
     assert orc.orc_paged_gqa(ob.p(q), ob.p(k), ob.p(v), 1, 37, 3, 2, 16, 0.0, 1, ob.p(a)) == -1
+
+
+def test_lora_restatement_matches_reference_vectors(ob, orc, golden):
+    """orc_lora_forward / orc_lora_merge against the compiled reference's outputs (src/nn/lora.c)."""
+    M, K, N, r, _ = (int(v) for v in golden["lora_cfg"])
+    scaling = float(golden["lora_alpha"][0]) / r
+    x, W, A, B = (np.ascontiguousarray(golden[k]) for k in ("lora_x", "lora_W", "lora_A", "lora_B"))
+    t, y = np.zeros((M, r), np.float32), np.zeros((M, N), np.float32)
+    orc.orc_lora_forward(ob.p(x), M, K, N, ob.p(W), ob.p(A), ob.p(B), r, scaling, 0, ob.p(t), ob.p(y))
+    assert np.abs(y - golden["lora_y"]).max() <= 1e-5 * np.abs(golden["lora_y"]).max()
+    Wm = W.copy()
+    orc.orc_lora_merge(ob.p(Wm), ob.p(A), ob.p(B), N, K, r, scaling)
+    assert np.abs(Wm - golden["lora_W_merged"]).max() <= 1e-6 * np.abs(Wm).max()
+    orc.orc_lora_forward(ob.p(x), M, K, N, ob.p(Wm), ob.p(A), ob.p(B), r, scaling, 1, ob.p(t), ob.p(y))
+    assert np.abs(y - golden["lora_y_merged"]).max() <= 1e-5 * np.abs(golden["lora_y_merged"]).max()
+
+
+def test_quant8_restatement_matches_reference_vectors(ob, orc, golden):
+    """orc_quant_params / orc_quantize8 / orc_dequantize8 bit for bit against the compiled reference
+    (src/core/quantization.c:8-192), the out-of-range quotients included."""
+    x = np.ascontiguousarray(golden["q8_x"])
+    pr = np.zeros(2, np.int32)
+    for mode, key in ((0, "q8_params_sym1"), (1, "q8_params_sym0"), (0, "q8_i8_auto_params"), (2, "q8_u8_auto_params")):
+        orc.orc_quant_params(ob.p(x), x.size, mode, ob.p(pr))
+        assert np.array_equal(pr, golden[key]), key
+    for name, uns in (("i8_auto", 0), ("u8_auto", 1), ("i8_given", 0), ("u8_given", 1)):
+        prm = golden[f"q8_{name}_params"]
+        scale, zp = float(prm[:1].view(np.float32)[0]), int(prm[1])
+        q, d = np.zeros(x.size, np.uint8), np.zeros(x.size, np.float32)
+        orc.orc_quantize8(ob.p(x), x.size, scale, zp, uns, ob.p(q))
+        assert np.array_equal(q, golden[f"q8_{name}_q"]), name
+        orc.orc_dequantize8(ob.p(q), x.size, scale, zp, uns, ob.p(d))
+        assert np.array_equal(d.view(np.uint32), golden[f"q8_{name}_deq"].view(np.uint32)), name
+    xo = np.ascontiguousarray(golden["q8_x_outliers"])
+    for name in ("i8_out", "i8_out_neg", "u8_out"):
+        uns, zp = (int(v) for v in golden[f"q8_{name}_cfg"])
+        q = np.zeros(xo.size, np.uint8)
+        orc.orc_quantize8(ob.p(xo), xo.size, float(golden[f"q8_{name}_scale"][0]), zp, uns, ob.p(q))
+        assert np.array_equal(q, golden[f"q8_{name}_q"]), name
