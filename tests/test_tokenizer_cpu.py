@@ -332,3 +332,35 @@ def test_gguf_writer_emits_c_ml_bytes_and_reads_back(pkg, golden, tmp_path):
     assert at > 0 and at % 32 == 0 and raw[at + blocks.nbytes:at + blocks.nbytes + 60] == golden["ggufw_a"].tobytes()
     for t in tensors:
         lib.tensor_free(t)
+
+
+def test_gguf_tensor_reads_are_bounded_by_the_file(pkg, tmp_path):
+    """A tensor is read when its bytes lie inside the file (padded tail, unpadded tail) and refused when
+    they reach past its end, before anything is allocated for it."""
+    synth = entry.load_synth()
+    lib = pkg.lib
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((7, 9)).astype(np.float32)
+    b = rng.standard_normal(5).astype(np.float32)
+    path = tmp_path / "s.gguf"
+    synth.write_gguf(str(path), [("a", (7, 9), 0, a.tobytes()), ("q", (4, 64), 2, synth.q4_0_blocks(rng, 4, 64).tobytes()),
+                                 ("b", (5,), 0, b.tobytes())])
+    raw = path.read_bytes()
+    end = raw.rfind(b.tobytes()) + b.nbytes
+    lib.cml_set_log_level.argtypes = [C.c_int]
+    lib.cml_set_log_level(5)
+    try:
+        for data, last_ok in ((raw, True), (raw[:end], True), (raw[:end - 1], False)):
+            path.write_bytes(data)
+            g = lib.gguf_open_read(str(path).encode())
+            assert g
+            t = lib.gguf_read_tensor(g, b"a")
+            assert t and np.array_equal(pkg.tensor_to_numpy(t), a)
+            t = lib.gguf_read_tensor(g, b"b")
+            assert bool(t) == last_ok
+            if t:
+                assert np.array_equal(pkg.tensor_to_numpy(t), b)
+            assert not lib.gguf_read_tensor(g, b"missing")
+            lib.gguf_close(g)
+    finally:
+        lib.cml_set_log_level(3)
